@@ -1,0 +1,11 @@
+#!/bin/bash
+# Builds the C-ABI shared library for sm_100a next to the Python package.
+set -e
+HERE="$(cd "$(dirname "$0")" && pwd)"
+OUT="$HERE/../deltanet_b200/libdeltanet_b200.so"
+NVCC="${NVCC:-/usr/local/cuda/bin/nvcc}"
+"$NVCC" -std=c++17 -O3 -lineinfo -gencode arch=compute_100a,code=sm_100a \
+  --expt-extended-lambda -Xcompiler -fPIC -shared ${DN_PTXAS_V:+-Xptxas -v} \
+  "$HERE"/dn_api.cu "$HERE"/dn_prepass_fwd.cu "$HERE"/dn_state.cu "$HERE"/dn_prepass_bwd.cu \
+  "$HERE"/dn_decode.cu "$HERE"/dn_misc.cu -o "$OUT"
+echo "built $OUT"

@@ -1,0 +1,300 @@
+// extern "C" surface declared in include/deltanet_b200.h: argument checks, buffer carving,
+// and the order in which the kernels are enqueued.  Nothing here allocates or synchronises.
+#include "dn_kernels.cuh"
+
+using namespace dn;
+
+static inline size_t align_up(size_t x, size_t a = 256) { return (x + a - 1) / a * a; }
+
+extern "C" {
+
+int dn_version(void) { return 1; }
+
+const char* dn_status_string(int st) {
+  switch (st) {
+    case DN_OK: return "ok";
+    case DN_ERR_BAD_SHAPE: return "unsupported shape (K,V in {64,128}; chunk in {64,128}; gate heads in {1,Hk,Hv})";
+    case DN_ERR_BAD_DTYPE: return "unsupported dtype or precision";
+    case DN_ERR_NULL_POINTER: return "a required buffer is NULL";
+    case DN_ERR_SCRATCH_TOO_SMALL: return "scratch buffer too small (see dn_scratch_bytes)";
+    case DN_ERR_CUDA_LAUNCH: return "a CUDA kernel launch failed";
+    case DN_ERR_UNSUPPORTED: return "unsupported combination of options";
+    default: return "unknown status";
+  }
+}
+
+int dn_exec_view(const dn_shape* s, dn_exec* out) {
+  Geo g;
+  int rc = make_geo(s, &g);
+  if (rc) return rc;
+  if (!out) return DN_ERR_NULL_POINTER;
+  out->H = g.H; out->Vw = g.Vw; out->G = g.G; out->NC = g.NC; out->pre_dtype = g.pre_dt;
+  return DN_OK;
+}
+
+// Residual block layout: W | U | M | qe | ke | lam_end | T | states, each 256-byte aligned.
+static void residual_sizes(const Geo& g, size_t sz[8]) {
+  const size_t n = (size_t)g.B * g.H * g.NC, ps = dt_size(g.pre_dt);
+  const bool keep = !(g.flags & DN_INFERENCE);
+  sz[0] = n * g.C * g.K * ps;
+  sz[1] = n * g.C * g.Vw * ps;
+  sz[2] = n * g.C * g.C * ps;
+  sz[3] = sz[0];
+  sz[4] = sz[0];
+  sz[5] = n * g.K * sizeof(float);
+  sz[6] = keep ? n * g.C * g.C * sizeof(float) : 0;
+  sz[7] = keep ? n * g.K * g.Vw * sizeof(float) : 0;
+}
+
+size_t dn_residual_bytes(const dn_shape* s) {
+  Geo g;
+  if (make_geo(s, &g)) return 0;
+  size_t sz[8], tot = 0;
+  residual_sizes(g, sz);
+  for (int i = 0; i < 8; ++i) tot += align_up(sz[i]);
+  return tot;
+}
+
+int dn_residual_carve(const dn_shape* s, void* block, dn_residuals* out) {
+  Geo g;
+  int rc = make_geo(s, &g);
+  if (rc) return rc;
+  if (!block || !out) return DN_ERR_NULL_POINTER;
+  size_t sz[8];
+  residual_sizes(g, sz);
+  char* p = reinterpret_cast<char*>(block);
+  void* ptr[8];
+  for (int i = 0; i < 8; ++i) { ptr[i] = sz[i] ? p : nullptr; p += align_up(sz[i]); }
+  out->W = ptr[0]; out->U = ptr[1]; out->M = ptr[2]; out->qe = ptr[3]; out->ke = ptr[4];
+  out->lam_end = reinterpret_cast<float*>(ptr[5]);
+  out->T = reinterpret_cast<float*>(ptr[6]);
+  out->states = reinterpret_cast<float*>(ptr[7]);
+  return DN_OK;
+}
+
+// ---- scratch accounting -------------------------------------------------------------------
+static size_t fwd_kernel_scratch(const Geo& g) {
+  size_t items = (size_t)g.B * g.H * g.NC;
+  size_t ctas = items < 148 ? items : 148;
+  return align_up(ctas * prepass_fwd_scratch_per_cta(g) * sizeof(float));
+}
+static size_t bwd_kernel_scratch(const Geo& g) {
+  size_t items = (size_t)g.B * g.H * g.NC;
+  size_t ctas = items < 296 ? items : 296;
+  return align_up(ctas * prepass_bwd_scratch_per_cta(g) * sizeof(float));
+}
+static size_t staging_bytes(const Geo& g) {
+  // f32 staging of gradients that must be summed over heads afterwards
+  size_t rows = (size_t)g.B * g.L, tot = 0;
+  if (g.qk_div > 1) tot += 2 * align_up(rows * g.H * g.K * sizeof(float));
+  if (g.gH != g.H) tot += align_up(rows * g.H * g.gC * sizeof(float));
+  if (g.bH != g.H) tot += align_up(rows * g.H * g.bC * sizeof(float));
+  if (g.wH != g.Hv) tot += align_up(rows * g.Hv * g.wC * sizeof(float));
+  return tot;
+}
+static size_t full_residual_bytes(const dn_shape* s) {
+  dn_shape t = *s;
+  t.flags &= ~DN_INFERENCE;
+  return dn_residual_bytes(&t);
+}
+
+size_t dn_scratch_bytes(const dn_shape* s, int for_backward, int recompute) {
+  Geo g;
+  if (make_geo(s, &g)) return 0;
+  const size_t n = (size_t)g.B * g.H * g.NC;
+  if (!for_backward) {
+    // forward without residuals keeps the prepass outputs in scratch
+    return fwd_kernel_scratch(g) + align_up(dn_residual_bytes(s));
+  }
+  size_t tot = bwd_kernel_scratch(g) > fwd_kernel_scratch(g) ? bwd_kernel_scratch(g) : fwd_kernel_scratch(g);
+  tot += align_up(n * g.C * g.Vw * sizeof(float));   // dV
+  tot += align_up(n * g.K * g.Vw * sizeof(float));   // dH
+  tot += staging_bytes(g);
+  if (recompute) tot += align_up(full_residual_bytes(s));
+  return tot;
+}
+
+int dn_canonical_segments(const int32_t* raw, const int32_t* first_is_new, int32_t* out,
+                          int32_t B, int32_t L, void* stream) {
+  if (!raw || !out) return DN_ERR_NULL_POINTER;
+  if (B < 1 || L < 1) return DN_ERR_BAD_SHAPE;
+  return launch_canonical_segments(raw, first_is_new, out, B, L, (cudaStream_t)stream);
+}
+
+// ---- phases -------------------------------------------------------------------------------
+int dn_prepass_fwd(const dn_shape* s, const void* q, const void* k, const void* v,
+                   const void* g_, const void* b, const void* w, const int32_t* seg,
+                   const dn_residuals* res, void* scratch, size_t scratch_bytes, void* stream) {
+  Geo g;
+  int rc = make_geo(s, &g);
+  if (rc) return rc;
+  if (!q || !k || !v || !g_ || !b || !w || !res || !scratch) return DN_ERR_NULL_POINTER;
+  if (!res->W || !res->U || !res->M || !res->qe || !res->ke || !res->lam_end) return DN_ERR_NULL_POINTER;
+  return launch_prepass_fwd(g, q, k, v, g_, b, w, seg, *res, reinterpret_cast<float*>(scratch),
+                            scratch_bytes / sizeof(float), (cudaStream_t)stream);
+}
+
+int dn_state_fwd(const dn_shape* s, const dn_residuals* res, const int32_t* seg,
+                 const float* init_state, void* out, float* final_state, void* stream) {
+  Geo g;
+  int rc = make_geo(s, &g);
+  if (rc) return rc;
+  if (!res || !out) return DN_ERR_NULL_POINTER;
+  if ((g.flags & DN_HAS_INIT) && !init_state) return DN_ERR_NULL_POINTER;
+  StateArgs a{};
+  a.g = g; a.res = *res; a.seg = seg; a.init_state = (g.flags & DN_HAS_INIT) ? init_state : nullptr;
+  a.out = out; a.final_state = final_state; a.states = res->states;
+  return launch_state_fwd(a, (cudaStream_t)stream);
+}
+
+int dn_recompute_states(const dn_shape* s, const dn_residuals* res, const int32_t* seg,
+                        const float* init_state, void* stream) {
+  Geo g;
+  int rc = make_geo(s, &g);
+  if (rc) return rc;
+  if (!res || !res->states) return DN_ERR_NULL_POINTER;
+  if ((g.flags & DN_HAS_INIT) && !init_state) return DN_ERR_NULL_POINTER;
+  StateArgs a{};
+  a.g = g; a.res = *res; a.seg = seg; a.init_state = (g.flags & DN_HAS_INIT) ? init_state : nullptr;
+  a.states = res->states;
+  return launch_state_fwd(a, (cudaStream_t)stream);
+}
+
+int dn_state_bwd(const dn_shape* s, const dn_residuals* res, const int32_t* seg,
+                 const void* d_out, const float* d_final_state,
+                 float* dV, float* dH, float* d_init, void* stream) {
+  Geo g;
+  int rc = make_geo(s, &g);
+  if (rc) return rc;
+  if (!res || !d_out || !dV || !dH) return DN_ERR_NULL_POINTER;
+  StateArgs a{};
+  a.g = g; a.res = *res; a.seg = seg; a.d_out = d_out; a.d_final = d_final_state;
+  a.dV = dV; a.dH = dH; a.d_init = (g.flags & DN_HAS_INIT) ? d_init : nullptr;
+  return launch_state_bwd(a, (cudaStream_t)stream);
+}
+
+// Carves gradient staging out of `p`, runs the chunk-parallel backward, then the head sums.
+static int run_prepass_bwd(const Geo& g, const void* q, const void* k, const void* v, const void* g_,
+                           const void* b, const void* w, const int32_t* seg, const dn_residuals& res,
+                           const void* d_out, const float* dV, const float* dH,
+                           void* dq, void* dk, void* dv, void* dg, void* db, void* dw,
+                           char* p, size_t bytes, cudaStream_t st) {
+  const size_t rows = (size_t)g.B * g.L;
+  char* end = p + bytes;
+  PrepassBwdArgs a{};
+  a.g = g; a.q = q; a.k = k; a.v = v; a.gg = g_; a.b = b; a.w = w; a.seg = seg; a.res = res;
+  a.d_out = d_out; a.dV = dV; a.dH = dH;
+  a.dq = dq; a.dk = dk; a.dv = dv; a.dg = dg; a.db = db; a.dw = dw;
+  a.dq_dt = g.qkv_dt; a.dg_dt = a.db_dt = a.dw_dt = g.gate_dt;
+  float *sq = nullptr, *sk = nullptr, *sg = nullptr, *sb = nullptr, *sw = nullptr;
+  auto take = [&](size_t nfl) { float* r = reinterpret_cast<float*>(p); p += align_up(nfl * sizeof(float)); return r; };
+  if (g.qk_div > 1) { sq = take(rows * g.H * g.K); sk = take(rows * g.H * g.K); a.dq = sq; a.dk = sk; a.dq_dt = DN_F32; }
+  if (g.gH != g.H) { sg = take(rows * g.H * g.gC); a.dg = sg; a.dg_dt = DN_F32; }
+  if (g.bH != g.H) { sb = take(rows * g.H * g.bC); a.db = sb; a.db_dt = DN_F32; }
+  if (g.wH != g.Hv) { sw = take(rows * g.Hv * g.wC); a.dw = sw; a.dw_dt = DN_F32; }
+  if (p > end) return DN_ERR_SCRATCH_TOO_SMALL;
+  int rc = launch_prepass_bwd(a, (size_t)(end - p) / sizeof(float), st);
+  if (rc) return rc;
+  if (sq) {
+    if ((rc = launch_group_sum(sq, dq, g.qkv_dt, rows, g.Hk, g.qk_div, g.K, st))) return rc;
+    if ((rc = launch_group_sum(sk, dk, g.qkv_dt, rows, g.Hk, g.qk_div, g.K, st))) return rc;
+  }
+  if (sg && (rc = launch_group_sum(sg, dg, g.gate_dt, rows, g.gH, g.H / g.gH, g.gC, st))) return rc;
+  if (sb && (rc = launch_group_sum(sb, db, g.gate_dt, rows, g.bH, g.H / g.bH, g.bC, st))) return rc;
+  if (sw && (rc = launch_group_sum(sw, dw, g.gate_dt, rows, g.wH, g.Hv / g.wH, g.wC, st))) return rc;
+  return DN_OK;
+}
+
+int dn_prepass_bwd(const dn_shape* s, const void* q, const void* k, const void* v,
+                   const void* g_, const void* b, const void* w, const int32_t* seg,
+                   const dn_residuals* res, const void* d_out, const float* dV, const float* dH,
+                   void* dq, void* dk, void* dv, void* dg, void* db, void* dw,
+                   void* scratch, size_t scratch_bytes, void* stream) {
+  Geo g;
+  int rc = make_geo(s, &g);
+  if (rc) return rc;
+  if (!q || !k || !v || !g_ || !b || !w || !res || !d_out || !dV || !dH || !scratch) return DN_ERR_NULL_POINTER;
+  if (!dq || !dk || !dv || !dg || !db || !dw) return DN_ERR_NULL_POINTER;
+  if (!res->W || !res->U || !res->T || !res->states || !res->lam_end) return DN_ERR_NULL_POINTER;
+  return run_prepass_bwd(g, q, k, v, g_, b, w, seg, *res, d_out, dV, dH, dq, dk, dv, dg, db, dw,
+                         reinterpret_cast<char*>(scratch), scratch_bytes, (cudaStream_t)stream);
+}
+
+// ---- the operator boundary ------------------------------------------------------------------
+int dn_chunk_fwd(const dn_shape* s, const void* q, const void* k, const void* v,
+                 const void* g_, const void* b, const void* w, const int32_t* seg,
+                 const float* init_state, void* out, float* final_state,
+                 const dn_residuals* res, void* scratch, size_t scratch_bytes, void* stream) {
+  Geo g;
+  int rc = make_geo(s, &g);
+  if (rc) return rc;
+  if (!q || !k || !v || !g_ || !b || !w || !out || !scratch) return DN_ERR_NULL_POINTER;
+  if ((g.flags & DN_HAS_INIT) && !init_state) return DN_ERR_NULL_POINTER;
+  char* p = reinterpret_cast<char*>(scratch);
+  char* end = p + scratch_bytes;
+  dn_residuals local;
+  if (!res) {
+    dn_shape t = *s;
+    t.flags |= DN_INFERENCE;                      // nothing is kept: no T, no chunk states
+    size_t need = align_up(dn_residual_bytes(&t));
+    if (p + need > end) return DN_ERR_SCRATCH_TOO_SMALL;
+    if ((rc = dn_residual_carve(&t, p, &local))) return rc;
+    p += need;
+    res = &local;
+  }
+  if ((rc = dn_prepass_fwd(s, q, k, v, g_, b, w, seg, res, p, (size_t)(end - p), stream))) return rc;
+  return dn_state_fwd(s, res, seg, init_state, out, final_state, stream);
+}
+
+int dn_chunk_bwd(const dn_shape* s, const void* q, const void* k, const void* v,
+                 const void* g_, const void* b, const void* w, const int32_t* seg,
+                 const float* init_state, const dn_residuals* res,
+                 const void* d_out, const float* d_final_state,
+                 void* dq, void* dk, void* dv, void* dg, void* db, void* dw, float* d_init,
+                 void* scratch, size_t scratch_bytes, void* stream) {
+  Geo g;
+  int rc = make_geo(s, &g);
+  if (rc) return rc;
+  if (!q || !k || !v || !g_ || !b || !w || !d_out || !scratch) return DN_ERR_NULL_POINTER;
+  if (!dq || !dk || !dv || !dg || !db || !dw) return DN_ERR_NULL_POINTER;
+  if (g.flags & DN_INFERENCE) return DN_ERR_UNSUPPORTED;
+  cudaStream_t st = (cudaStream_t)stream;
+  char* p = reinterpret_cast<char*>(scratch);
+  char* end = p + scratch_bytes;
+  const size_t n = (size_t)g.B * g.H * g.NC;
+  auto take = [&](size_t bytes) { char* r = p; p += align_up(bytes); return r; };
+  float* dV = reinterpret_cast<float*>(take(n * g.C * g.Vw * sizeof(float)));
+  float* dH = reinterpret_cast<float*>(take(n * g.K * g.Vw * sizeof(float)));
+  if (p > end) return DN_ERR_SCRATCH_TOO_SMALL;
+  dn_residuals local;
+  if (!res) {
+    // recompute_states: rebuild the prepass outputs (with T) and the chunk-entry states
+    size_t need = align_up(full_residual_bytes(s));
+    if (p + need > end) return DN_ERR_SCRATCH_TOO_SMALL;
+    if ((rc = dn_residual_carve(s, p, &local))) return rc;
+    p += need;
+    if ((rc = dn_prepass_fwd(s, q, k, v, g_, b, w, seg, &local, p, (size_t)(end - p), stream))) return rc;
+    if ((rc = dn_recompute_states(s, &local, seg, init_state, stream))) return rc;
+    res = &local;
+  }
+  if (!res->T || !res->states) return DN_ERR_NULL_POINTER;
+  if ((rc = dn_state_bwd(s, res, seg, d_out, d_final_state, dV, dH, d_init, stream))) return rc;
+  return run_prepass_bwd(g, q, k, v, g_, b, w, seg, *res, d_out, dV, dH, dq, dk, dv, dg, db, dw,
+                         p, (size_t)(end - p), st);
+}
+
+int dn_decode_step(const dn_decode_shape* s, const void* q, const void* k, const void* v,
+                   const void* g_, const void* b, const void* w, const void* state_in,
+                   const uint8_t* reset, void* out, void* state_out, void* stream) {
+  if (!s || !q || !k || !v || !g_ || !b || !w || !state_in || !out || !state_out) return DN_ERR_NULL_POINTER;
+  if (s->B < 1 || s->Hk < 1 || s->Hv % s->Hk) return DN_ERR_BAD_SHAPE;
+  if ((s->K != 64 && s->K != 128) || (s->V != 64 && s->V != 128)) return DN_ERR_BAD_SHAPE;
+  auto okh = [&](int h) { return h == 1 || h == s->Hk || h == s->Hv; };
+  if (!okh(s->g_heads) || !okh(s->b_heads) || !okh(s->w_heads)) return DN_ERR_BAD_SHAPE;
+  if ((s->g_cols != 1 && s->g_cols != s->K) || (s->b_cols != 1 && s->b_cols != s->K) ||
+      (s->w_cols != 1 && s->w_cols != s->V)) return DN_ERR_BAD_SHAPE;
+  if (state_in == state_out && s->state_in_dtype != s->state_out_dtype) return DN_ERR_UNSUPPORTED;
+  return launch_decode(*s, q, k, v, g_, b, w, state_in, reset, out, state_out, (cudaStream_t)stream);
+}
+
+}  // extern "C"

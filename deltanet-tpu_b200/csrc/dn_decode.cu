@@ -1,0 +1,252 @@
+// Single-token decode step: streams the (B,Hv,K,V) state through registers exactly once.
+//
+// Math (src/deltanet_tpu/gdn2.py:2471-2478 of the reference), per sequence and value head:
+//     Sd = diag(exp g) S ;  e = Sd^T (b*k) ;  v_new = w*v - e ;  S' = Sd + k v_new^T ;  o = S'^T q
+// o uses the un-rounded S'; S' is then cast to the output state dtype (gdn2.py:2478-2489).
+//
+// The update is independent per value column, so one CTA owns a K x 64 column slab of one
+// (sequence, value head): every thread loads its share with 16-byte vector loads issued
+// back to back, the two reductions over K go through shared memory, and the slab is written
+// back with 16-byte stores.  Bytes moved = state read once + state written once.
+#include "dn_kernels.cuh"
+
+namespace dn {
+
+constexpr int DV = 64;                 // value columns per CTA
+constexpr int DEC_THREADS = 256;
+
+template <typename T> struct Vec16;    // 16-byte vector of state elements
+template <> struct Vec16<float> { static constexpr int N = 4; };
+template <> struct Vec16<__nv_bfloat16> { static constexpr int N = 8; };
+
+template <typename T>
+__device__ __forceinline__ void load16(const T* p, float (&x)[Vec16<T>::N]);
+template <>
+__device__ __forceinline__ void load16<float>(const float* p, float (&x)[4]) {
+  float4 v = __ldcs(reinterpret_cast<const float4*>(p));
+  x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
+}
+template <>
+__device__ __forceinline__ void load16<__nv_bfloat16>(const __nv_bfloat16* p, float (&x)[8]) {
+  uint4 v = __ldcs(reinterpret_cast<const uint4*>(p));
+  const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    x[2 * i] = __uint_as_float(u[i] << 16);
+    x[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u);
+  }
+}
+template <int N>
+__device__ __forceinline__ void store_row(float* p, const float (&x)[N]) {
+#pragma unroll
+  for (int i = 0; i < N; i += 4) __stcs(reinterpret_cast<float4*>(p + i), make_float4(x[i], x[i + 1], x[i + 2], x[i + 3]));
+}
+template <int N>
+__device__ __forceinline__ void store_row(__nv_bfloat16* p, const float (&x)[N]) {
+  static_assert(N % 8 == 0 || N == 4, "row width");
+  if (N == 4) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(x[0], x[1]), b = __floats2bfloat162_rn(x[2], x[3]);
+    uint2 v = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
+    __stcs(reinterpret_cast<uint2*>(p), v);
+  } else {
+#pragma unroll
+    for (int i = 0; i < N; i += 8) {
+      uint32_t u[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(x[i + 2 * j], x[i + 2 * j + 1]);
+        u[j] = *reinterpret_cast<uint32_t*>(&h);
+      }
+      __stcs(reinterpret_cast<uint4*>(p + i), make_uint4(u[0], u[1], u[2], u[3]));
+    }
+  }
+}
+
+struct DecodeArgs {
+  dn_decode_shape s;
+  const void *q, *k, *v, *g, *b, *w;
+  const void* state_in;
+  const uint8_t* reset;
+  void* out;
+  void* state_out;
+};
+
+__device__ __forceinline__ int dec_gate_head(int hv, int nheads, int Hk, int Hv) {
+  if (nheads == 1) return 0;
+  if (nheads == Hv) return hv;
+  return hv / (Hv / Hk);
+}
+
+template <typename SI, typename SO, int KD>
+__global__ void __launch_bounds__(DEC_THREADS) decode_kernel(DecodeArgs a) {
+  constexpr int CPT = Vec16<SI>::N;        // columns per thread
+  constexpr int VC = DV / CPT;             // vector columns per row slab
+  constexpr int RG = DEC_THREADS / VC;     // row groups
+  constexpr int R = KD / RG;               // rows per thread
+  const dn_decode_shape& s = a.s;
+  const int V = s.V;
+  const int nslab = V / DV;
+  const int slab = blockIdx.x % nslab, hv = (blockIdx.x / nslab) % s.Hv, b = blockIdx.x / (nslab * s.Hv);
+  const int tid = threadIdx.x, vc = tid % VC, rg = tid / VC;
+  const int col0 = slab * DV + vc * CPT;
+
+  __shared__ float qs[KD], ks[KD], dec[KD], beta[KD];
+  __shared__ float red[RG][DV + 4];
+  __shared__ float vnew[DV], wvs[DV], nrm[2];
+
+  // ---- state loads first: they are the long-latency part
+  const size_t sbase = ((size_t)b * s.Hv + hv) * KD * V;
+  const SI* Sin = reinterpret_cast<const SI*>(a.state_in) + sbase;
+  const bool zero = a.reset && a.reset[b];
+  float S[R][CPT];
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    if (zero) {
+#pragma unroll
+      for (int c = 0; c < CPT; ++c) S[r][c] = 0.f;
+    } else {
+      load16<SI>(Sin + (size_t)(rg + r * RG) * V + col0, S[r]);
+    }
+  }
+
+  // ---- token vectors
+  const int G = s.Hv / s.Hk, hk = hv / G;
+  const bool guard = s.flags & DN_STABILITY_GUARD;
+  if (tid < 64) {
+    // two warps: warp 0 normalises q, warp 1 normalises k
+    const int wq = tid >> 5, lane = tid & 31;
+    const void* src = wq == 0 ? a.q : a.k;
+    float x[KD / 32], ss = 0.f;
+#pragma unroll
+    for (int u = 0; u < KD / 32; ++u) {
+      x[u] = ldf(src, ((size_t)b * s.Hk + hk) * KD + lane + 32 * u, s.qkv_dtype);
+      ss += x[u] * x[u];
+    }
+    ss = warp_sum(ss);
+    float r = 1.f;
+    if (s.flags & DN_QK_L2NORM) r = 1.f / sqrtf(ss + 1e-6f);
+#pragma unroll
+    for (int u = 0; u < KD / 32; ++u) {
+      if (wq == 0) qs[lane + 32 * u] = x[u] * r * s.scale;
+      else ks[lane + 32 * u] = x[u] * r;
+    }
+  } else if (tid < 64 + DV) {
+    const int j = tid - 64, cv = slab * DV + j;
+    const float vv = ldf(a.v, ((size_t)b * s.Hv + hv) * V + cv, s.qkv_dtype);
+    const int hw = dec_gate_head(hv, s.w_heads, s.Hk, s.Hv);
+    const float ww = ldf(a.w, ((size_t)b * s.w_heads + hw) * s.w_cols + (s.w_cols == 1 ? 0 : cv), s.gate_dtype);
+    wvs[j] = ww * vv;
+  }
+  __syncthreads();
+  if (tid < KD) {
+    const int hg = dec_gate_head(hv, s.g_heads, s.Hk, s.Hv), hb = dec_gate_head(hv, s.b_heads, s.Hk, s.Hv);
+    float gg = ldf(a.g, ((size_t)b * s.g_heads + hg) * s.g_cols + (s.g_cols == 1 ? 0 : tid), s.gate_dtype);
+    float bb = ldf(a.b, ((size_t)b * s.b_heads + hb) * s.b_cols + (s.b_cols == 1 ? 0 : tid), s.gate_dtype);
+    gg = fminf(gg, 0.f);
+    if (guard) { bb = fmaxf(bb, 0.f); gg = fminf(gg, -1e-6f); }
+    dec[tid] = expf(gg);
+    beta[tid] = bb * ks[tid];
+  }
+  __syncthreads();
+
+  // ---- decay, erase projection e = Sd^T beta
+  float part[CPT];
+#pragma unroll
+  for (int c = 0; c < CPT; ++c) part[c] = 0.f;
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const int kk = rg + r * RG;
+    const float d = dec[kk], be = beta[kk];
+#pragma unroll
+    for (int c = 0; c < CPT; ++c) {
+      S[r][c] *= d;
+      part[c] = fmaf(be, S[r][c], part[c]);
+    }
+  }
+#pragma unroll
+  for (int c = 0; c < CPT; ++c) red[rg][vc * CPT + c] = part[c];
+  __syncthreads();
+  if (tid < DV) {
+    float e = 0.f;
+#pragma unroll
+    for (int r = 0; r < RG; ++r) e += red[r][tid];
+    vnew[tid] = wvs[tid] - e;
+  }
+  __syncthreads();
+  // ---- rank-one write, output projection o = S'^T q
+  float vn[CPT];
+#pragma unroll
+  for (int c = 0; c < CPT; ++c) { vn[c] = vnew[vc * CPT + c]; part[c] = 0.f; }
+  float sq = 0.f;
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const int kk = rg + r * RG;
+    const float kx = ks[kk], qx = qs[kk];
+#pragma unroll
+    for (int c = 0; c < CPT; ++c) {
+      S[r][c] = fmaf(kx, vn[c], S[r][c]);
+      part[c] = fmaf(qx, S[r][c], part[c]);
+      sq = fmaf(S[r][c], S[r][c], sq);
+    }
+  }
+  __syncthreads();                     // red is reused
+#pragma unroll
+  for (int c = 0; c < CPT; ++c) red[rg][vc * CPT + c] = part[c];
+  __syncthreads();
+  if (tid < DV) {
+    float o = 0.f;
+#pragma unroll
+    for (int r = 0; r < RG; ++r) o += red[r][tid];
+    stf(a.out, ((size_t)b * s.Hv + hv) * V + slab * DV + tid, o, s.qkv_dtype);
+  }
+  (void)sq; (void)nrm;
+  // ---- state out
+  SO* Sout = reinterpret_cast<SO*>(a.state_out) + sbase;
+#pragma unroll
+  for (int r = 0; r < R; ++r) store_row<CPT>(Sout + (size_t)(rg + r * RG) * V + col0, S[r]);
+}
+
+// Frobenius cap of the returned state (gdn2.py:2484-2487): one CTA per (sequence, value head).
+template <typename SO>
+__global__ void __launch_bounds__(256) decode_cap_kernel(SO* state, int KV, float tau) {
+  SO* p = state + (size_t)blockIdx.x * KV;
+  __shared__ float wsum[8];
+  float s = 0.f;
+  for (int e = threadIdx.x; e < KV; e += 256) { float x = (float)p[e]; s += x * x; }
+  s = warp_sum(s);
+  if ((threadIdx.x & 31) == 0) wsum[threadIdx.x >> 5] = s;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) tot += wsum[i];
+  const float f = fminf(1.f, tau / sqrtf(tot + 1e-6f));
+  if (f < 1.f)
+    for (int e = threadIdx.x; e < KV; e += 256) p[e] = (SO)((float)p[e] * f);
+}
+
+template <typename SI, typename SO>
+static int launch_decode_t(const DecodeArgs& a, cudaStream_t st) {
+  const dn_decode_shape& s = a.s;
+  const int grid = s.B * s.Hv * (s.V / DV);
+  if (s.K == 128) decode_kernel<SI, SO, 128><<<grid, DEC_THREADS, 0, st>>>(a);
+  else decode_kernel<SI, SO, 64><<<grid, DEC_THREADS, 0, st>>>(a);
+  if (cudaGetLastError() != cudaSuccess) return DN_ERR_CUDA_LAUNCH;
+  if (s.flags & DN_STABILITY_GUARD) {
+    decode_cap_kernel<SO><<<s.B * s.Hv, 256, 0, st>>>(reinterpret_cast<SO*>(a.state_out), s.K * s.V, s.stability_tau);
+    if (cudaGetLastError() != cudaSuccess) return DN_ERR_CUDA_LAUNCH;
+  }
+  return DN_OK;
+}
+
+int launch_decode(const dn_decode_shape& s, const void* q, const void* k, const void* v,
+                  const void* g, const void* b, const void* w, const void* state_in,
+                  const uint8_t* reset, void* out, void* state_out, cudaStream_t st) {
+  DecodeArgs a{s, q, k, v, g, b, w, state_in, reset, out, state_out};
+  const bool ib = s.state_in_dtype == DN_BF16, ob = s.state_out_dtype == DN_BF16;
+  if (ib && ob) return launch_decode_t<__nv_bfloat16, __nv_bfloat16>(a, st);
+  if (ib && !ob) return launch_decode_t<__nv_bfloat16, float>(a, st);
+  if (!ib && ob) return launch_decode_t<float, __nv_bfloat16>(a, st);
+  return launch_decode_t<float, float>(a, st);
+}
+
+}  // namespace dn

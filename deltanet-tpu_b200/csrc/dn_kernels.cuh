@@ -1,0 +1,67 @@
+// Argument blocks and host launchers of the kernels behind the C ABI.
+#pragma once
+#include "dn_common.cuh"
+
+namespace dn {
+
+struct PrepassFwdArgs {
+  Geo g;
+  const void *q, *k, *v, *gg, *b, *w;
+  const int32_t* seg;
+  dn_residuals res;
+  float* scratch;
+  size_t scratch_per_cta;
+  int items;
+  int smem_tile_off;
+};
+
+struct StateArgs {
+  Geo g;
+  dn_residuals res;
+  const int32_t* seg;
+  const float* init_state;   // (B,Hv,K,V) or null
+  void* out;                 // (B,L,Hv,V) qkv dtype, or null (states only)
+  float* final_state;        // (B,Hv,K,V) or null
+  float* states;             // (B,H,NC,K,Vw) chunk-entry states or null
+  // backward chain
+  const void* d_out;
+  const float* d_final;
+  float* dV;                 // (B,H,NC,C,Vw)
+  float* dH;                 // (B,H,NC,K,Vw)
+  float* d_init;             // (B,Hv,K,V) or null
+};
+
+struct PrepassBwdArgs {
+  Geo g;
+  const void *q, *k, *v, *gg, *b, *w;
+  const int32_t* seg;
+  dn_residuals res;
+  const void* d_out;
+  const float *dV, *dH;
+  // gradient sinks at exec-head granularity: either the user's buffer (typed) or f32 staging
+  void *dq, *dk, *dv, *dg, *db, *dw;
+  int dq_dt, dg_dt, db_dt, dw_dt;   // dtype actually written (f32 when staged)
+  float* scratch;
+  size_t scratch_per_cta;
+  int items;
+};
+
+size_t prepass_fwd_scratch_per_cta(const Geo& g);
+size_t prepass_bwd_scratch_per_cta(const Geo& g);
+
+int launch_prepass_fwd(const Geo& g, const void* q, const void* k, const void* v, const void* gg,
+                       const void* b, const void* w, const int32_t* seg, const dn_residuals& res,
+                       float* scratch, size_t scratch_floats, cudaStream_t st);
+int launch_state_fwd(const StateArgs& a, cudaStream_t st);
+int launch_state_bwd(const StateArgs& a, cudaStream_t st);
+int launch_prepass_bwd(PrepassBwdArgs& a, size_t scratch_floats, cudaStream_t st);
+int launch_canonical_segments(const int32_t* raw, const int32_t* first_is_new, int32_t* out,
+                              int B, int L, cudaStream_t st);
+// sums `groups` consecutive heads: in (rows, heads_out*groups, cols) f32 -> out (rows, heads_out, cols)
+int launch_group_sum(const float* in, void* out, int out_dt, size_t rows, int heads_out, int groups,
+                     int cols, cudaStream_t st);
+int launch_decode(const dn_decode_shape& s, const void* q, const void* k, const void* v,
+                  const void* g, const void* b, const void* w, const void* state_in,
+                  const uint8_t* reset, void* out, void* state_out, cudaStream_t st);
+
+}  // namespace dn

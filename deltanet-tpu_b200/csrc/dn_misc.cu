@@ -1,0 +1,61 @@
+// Small integer / reduction kernels around the main path.
+#include "dn_kernels.cuh"
+
+namespace dn {
+
+// One CTA per batch row: out[t] = first_is_new + number of id changes in raw[1..t]
+// (the reference's canonicalisation, src/deltanet_tpu/gdn2.py:2081-2094).
+__global__ void __launch_bounds__(256) canonical_segments_kernel(const int32_t* raw, const int32_t* first_is_new,
+                                                                  int32_t* out, int L) {
+  __shared__ int part[256];
+  const int b = blockIdx.x, tid = threadIdx.x;
+  const int32_t* r = raw + (size_t)b * L;
+  int32_t* o = out + (size_t)b * L;
+  const int per = (L + 255) / 256, lo = tid * per, hi = min(L, lo + per);
+  int cnt = 0;
+  for (int t = max(lo, 1); t < hi; ++t) cnt += r[t] != r[t - 1];
+  part[tid] = cnt;
+  __syncthreads();
+  if (tid == 0) {
+    int run = first_is_new ? first_is_new[b] : 0;
+    for (int i = 0; i < 256; ++i) { int c = part[i]; part[i] = run; run += c; }
+  }
+  __syncthreads();
+  int run = part[tid];
+  for (int t = lo; t < hi; ++t) {
+    if (t > 0) run += r[t] != r[t - 1];
+    o[t] = run;
+  }
+}
+
+int launch_canonical_segments(const int32_t* raw, const int32_t* first_is_new, int32_t* out,
+                              int B, int L, cudaStream_t st) {
+  canonical_segments_kernel<<<B, 256, 0, st>>>(raw, first_is_new, out, L);
+  return cudaGetLastError() == cudaSuccess ? DN_OK : DN_ERR_CUDA_LAUNCH;
+}
+
+// out[row][ho][c] = sum over gi of in[row][ho*groups + gi][c], added in a fixed order.
+__global__ void __launch_bounds__(256) group_sum_kernel(const float* in, void* out, int out_dt, size_t total,
+                                                        int heads_out, int groups, int cols) {
+  for (size_t e = (size_t)blockIdx.x * 256 + threadIdx.x; e < total; e += (size_t)gridDim.x * 256) {
+    const int c = (int)(e % cols);
+    const size_t rh = e / cols;
+    const int ho = (int)(rh % heads_out);
+    const size_t row = rh / heads_out;
+    const float* p = in + ((row * heads_out + ho) * groups) * cols + c;
+    float s = 0.f;
+    for (int gi = 0; gi < groups; ++gi) s += p[(size_t)gi * cols];
+    stf(out, e, s, out_dt);
+  }
+}
+
+int launch_group_sum(const float* in, void* out, int out_dt, size_t rows, int heads_out, int groups,
+                     int cols, cudaStream_t st) {
+  const size_t total = rows * heads_out * cols;
+  size_t blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  group_sum_kernel<<<(unsigned)blocks, 256, 0, st>>>(in, out, out_dt, total, heads_out, groups, cols);
+  return cudaGetLastError() == cudaSuccess ? DN_OK : DN_ERR_CUDA_LAUNCH;
+}
+
+}  // namespace dn

@@ -1,0 +1,198 @@
+/*
+ * deltanet_b200.h -- C ABI of the B200 (sm_100a) delta-rule recurrence library.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream (passed as
+ * void* so that this header needs no CUDA include), only ENQUEUES work on that stream,
+ * allocates nothing, keeps no pointer after it returns, and reports problems through an
+ * int status (0 = ok; see dn_status_string).  The caller owns every buffer.
+ *
+ * The functions replace, one for one, the device work behind the reference package's
+ * differentiable operator (paths are those inside the reference project):
+ *
+ *   reference interface                                              replaced by
+ *   -----------------------------------------------------------------------------------------
+ *   custom-VJP op fwd     src/deltanet_tpu/gdn2.py:1479-1494,1176-1389   dn_chunk_fwd
+ *   custom-VJP op bwd     src/deltanet_tpu/gdn2.py:1496-1766             dn_chunk_bwd
+ *   pallas_prepass_fwd    src/deltanet_tpu/gdn2.py:1262-1276 (body 115-240)   dn_prepass_fwd
+ *   pallas_split_fwd      src/deltanet_tpu/gdn2.py:1331-1376 (body 585-652)   dn_state_fwd
+ *   pallas_recompute_states src/deltanet_tpu/gdn2.py:1614-1630 (body 655-695) dn_recompute_states
+ *   pallas_split_bwd      src/deltanet_tpu/gdn2.py:1674-1690 (body 698-769)   dn_state_bwd
+ *   pallas_prepass_bwd    src/deltanet_tpu/gdn2.py:1737-1752 (body 243-582)   dn_prepass_bwd
+ *   segment canonicalisation src/deltanet_tpu/gdn2.py:2081-2094               dn_canonical_segments
+ *   gdn2_decode_step core src/deltanet_tpu/gdn2.py:2393-2489                  dn_decode_step
+ *
+ * Tensor layouts are the reference's own, un-broadcast and un-padded:
+ *   q,k   (B, L, Hk, K)      v, out, d_out   (B, L, Hv, V)      state  (B, Hv, K, V)
+ *   g,b   (B, L, gh[, gc])   gh in {1,Hk,Hv}, gc in {1,K}        w  (B, L, wh[, wc]), wc in {1,V}
+ *   segment ids (B, L) int32, canonical (they step by one at every document change).
+ * L need not be a multiple of the chunk: rows past L behave as the reference's padding.
+ *
+ * "Exec heads": as in the reference (gdn2.py:1992-2007) the recurrence runs on H = Hk heads of
+ * value width Vw = (Hv/Hk)*V when neither g nor b is given per value head, and on H = Hv heads
+ * of width Vw = V otherwise.  Residual and scratch buffers use the exec-head layout (B,H,NC,...).
+ */
+#ifndef DELTANET_B200_H_
+#define DELTANET_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* element types */
+enum { DN_F32 = 0, DN_BF16 = 1 };
+/* matmul precision, the reference's precision="fp32" | "bf16" (gdn2.py:28-35) */
+enum { DN_PREC_FP32 = 0, DN_PREC_BF16 = 1 };
+
+/* flags */
+enum {
+  DN_QK_L2NORM      = 1u << 0, /* normalise q,k in the kernel prologue (gdn2.py:2113-2122 / 133-138) */
+  DN_FUSE_PROLOGUE  = 1u << 1, /* g,b,w are pre-activations (gdn2.py:133-142, adjoints 558-575)   */
+  DN_HAS_INIT       = 1u << 2, /* an initial state is given (gdn2.py:613-617)                      */
+  DN_STABILITY_GUARD= 1u << 3, /* with DN_FUSE_PROLOGUE: clamp the activated decay to <= -1e-6      */
+  DN_STATE_FP32_MM  = 1u << 4, /* state_fp32_matmul (gdn2.py:625)                                   */
+  DN_INFERENCE      = 1u << 5, /* forward only: no T / chunk-state residuals (gdn2.py:1257,1322)    */
+  DN_TRUNC_DT_BF16  = 1u << 6  /* truncate_bwd_dT_bf16 (gdn2.py:327-330)                            */
+};
+
+/* status codes */
+enum {
+  DN_OK = 0,
+  DN_ERR_BAD_SHAPE = 1,      /* a dimension outside what the kernels support          */
+  DN_ERR_BAD_DTYPE = 2,
+  DN_ERR_NULL_POINTER = 3,   /* a required buffer is NULL                              */
+  DN_ERR_SCRATCH_TOO_SMALL = 4,
+  DN_ERR_CUDA_LAUNCH = 5,    /* cudaGetLastError() after a launch was not cudaSuccess  */
+  DN_ERR_UNSUPPORTED = 6
+};
+
+typedef struct dn_shape {
+  int32_t B, L, Hk, Hv, K, V;
+  int32_t chunk;               /* 64 or 128                                    */
+  int32_t g_heads, g_cols;     /* layout of g (see above)                      */
+  int32_t b_heads, b_cols;
+  int32_t w_heads, w_cols;
+  int32_t qkv_dtype;           /* dtype of q,k,v,out,d_out,dq,dk,dv            */
+  int32_t gate_dtype;          /* dtype of g,b,w,dg,db,dw                      */
+  int32_t precision;           /* DN_PREC_*                                    */
+  uint32_t flags;
+  float scale;                 /* query scale (already resolved, gdn2.py:1978) */
+} dn_shape;
+
+/* Exec-head view of a shape (what the residual layouts are expressed in). */
+typedef struct dn_exec {
+  int32_t H, Vw, G, NC;        /* exec heads, value width, value heads per exec head, chunks */
+  int32_t pre_dtype;           /* dtype of W,U,M,qe,ke: bf16 in bf16 precision else f32 (gdn2.py:1247) */
+} dn_exec;
+int dn_exec_view(const dn_shape* s, dn_exec* out);
+
+/*
+ * Residuals written by the forward and read by the backward: the reference's residual tuple
+ * (gdn2.py:1384-1388).  All in exec-head layout; NC = ceil(L/chunk), C = chunk.
+ */
+typedef struct dn_residuals {
+  void*  W;        /* (B,H,NC,C,K)   pre_dtype */
+  void*  U;        /* (B,H,NC,C,Vw)  pre_dtype */
+  void*  M;        /* (B,H,NC,C,C)   pre_dtype */
+  void*  qe;       /* (B,H,NC,C,K)   pre_dtype */
+  void*  ke;       /* (B,H,NC,C,K)   pre_dtype */
+  float* lam_end;  /* (B,H,NC,K)     */
+  float* T;        /* (B,H,NC,C,C)   or NULL (inference) */
+  float* states;   /* (B,H,NC,K,Vw)  chunk-entry states, or NULL (inference) */
+} dn_residuals;
+
+/* Bytes of one packed residual block, and a helper that carves the block into the struct. */
+size_t dn_residual_bytes(const dn_shape* s);
+int dn_residual_carve(const dn_shape* s, void* block, dn_residuals* out);
+
+/* Scratch bytes needed by dn_chunk_fwd / dn_chunk_bwd (upper bound over their phases). */
+size_t dn_scratch_bytes(const dn_shape* s, int for_backward, int recompute);
+
+/* (B,L) raw ids -> canonical ids; first_is_new (B) may be NULL (gdn2.py:2081-2094). */
+int dn_canonical_segments(const int32_t* raw, const int32_t* first_is_new, int32_t* out,
+                          int32_t B, int32_t L, void* stream);
+
+/*
+ * Forward of the chunked recurrence.  seg may be NULL (one document).  init_state
+ * (B,Hv,K,V) f32 is read when DN_HAS_INIT.  final_state (B,Hv,K,V) f32 may be NULL.
+ * res == NULL means "keep nothing" (inference, or recompute_states): the prepass
+ * outputs then live in scratch only.
+ */
+int dn_chunk_fwd(const dn_shape* s,
+                 const void* q, const void* k, const void* v,
+                 const void* g, const void* b, const void* w,
+                 const int32_t* seg, const float* init_state,
+                 void* out, float* final_state,
+                 const dn_residuals* res, void* scratch, size_t scratch_bytes, void* stream);
+
+/*
+ * Backward.  res == NULL means recompute_states=True: the prepass and the chunk states are
+ * rebuilt in scratch first (gdn2.py:1545-1630).  d_final_state and d_init may be NULL.
+ * dq,dk have q's shape; dv has v's; dg,db,dw have the shapes g,b,w were given in.
+ */
+int dn_chunk_bwd(const dn_shape* s,
+                 const void* q, const void* k, const void* v,
+                 const void* g, const void* b, const void* w,
+                 const int32_t* seg, const float* init_state,
+                 const dn_residuals* res,
+                 const void* d_out, const float* d_final_state,
+                 void* dq, void* dk, void* dv, void* dg, void* db, void* dw, float* d_init,
+                 void* scratch, size_t scratch_bytes, void* stream);
+
+/* ---- the single phases (same buffers as above) ------------------------------------------ */
+int dn_prepass_fwd(const dn_shape* s, const void* q, const void* k, const void* v,
+                   const void* g, const void* b, const void* w, const int32_t* seg,
+                   const dn_residuals* res, void* scratch, size_t scratch_bytes, void* stream);
+
+int dn_state_fwd(const dn_shape* s, const dn_residuals* res, const int32_t* seg,
+                 const float* init_state, void* out, float* final_state, void* stream);
+
+int dn_recompute_states(const dn_shape* s, const dn_residuals* res, const int32_t* seg,
+                        const float* init_state, void* stream);
+
+/*
+ * Reverse chain.  Writes, in exec-head layout, dV (B,H,NC,C,Vw) f32 -- the cotangent of
+ * U, the reference's dU -- and dH (B,H,NC,K,Vw) f32, the state cotangent each chunk
+ * receives from its successor.  The remaining per-chunk cotangents of the reference's
+ * state-backward kernel (dW, dM, dqe, dke, d lambda_end) are contractions over the value
+ * width that do not depend on the chain; dn_prepass_bwd forms them chunk-parallel.
+ */
+int dn_state_bwd(const dn_shape* s, const dn_residuals* res, const int32_t* seg,
+                 const void* d_out, const float* d_final_state,
+                 float* dV, float* dH, float* d_init, void* stream);
+
+int dn_prepass_bwd(const dn_shape* s, const void* q, const void* k, const void* v,
+                   const void* g, const void* b, const void* w, const int32_t* seg,
+                   const dn_residuals* res, const void* d_out, const float* dV, const float* dH,
+                   void* dq, void* dk, void* dv, void* dg, void* db, void* dw,
+                   void* scratch, size_t scratch_bytes, void* stream);
+
+/* ---- decode ------------------------------------------------------------------------------ */
+typedef struct dn_decode_shape {
+  int32_t B, Hk, Hv, K, V;
+  int32_t g_heads, g_cols, b_heads, b_cols, w_heads, w_cols;
+  int32_t qkv_dtype, gate_dtype;
+  int32_t state_in_dtype, state_out_dtype;
+  uint32_t flags;              /* DN_QK_L2NORM, DN_STABILITY_GUARD */
+  float scale, stability_tau;
+} dn_decode_shape;
+
+/*
+ * One token for B sequences.  state_in and state_out may be the same buffer when their
+ * dtypes match (in-place update).  reset (B) uint8 may be NULL.  out is (B,Hv,V) in qkv_dtype.
+ */
+int dn_decode_step(const dn_decode_shape* s,
+                   const void* q, const void* k, const void* v,
+                   const void* g, const void* b, const void* w,
+                   const void* state_in, const uint8_t* reset,
+                   void* out, void* state_out, void* stream);
+
+const char* dn_status_string(int status);
+int dn_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DELTANET_B200_H_ */
