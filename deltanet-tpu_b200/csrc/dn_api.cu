@@ -193,6 +193,7 @@ static int run_prepass_bwd(const Geo& g, const void* q, const void* k, const voi
   if (g.bH != g.H) { sb = take(rows * g.H * g.bC); a.db = sb; a.db_dt = DN_F32; }
   if (g.wH != g.Hv) { sw = take(rows * g.Hv * g.wC); a.dw = sw; a.dw_dt = DN_F32; }
   if (p > end) return DN_ERR_SCRATCH_TOO_SMALL;
+  a.scratch = reinterpret_cast<float*>(p);
   int rc = launch_prepass_bwd(a, (size_t)(end - p) / sizeof(float), st);
   if (rc) return rc;
   if (sq) {

@@ -184,27 +184,31 @@ __global__ void __launch_bounds__(DN_THREADS, 1) prepass_bwd_kernel(PrepassBwdAr
         [&](int i, int j, float acc) { DA[i * C + j] = (i > j && seg_s[i] == seg_s[j]) ? -acc : 0.f; }, tile);
 
     // ---- adjoints of A and M, pair by pair.  Row side: dbeta', dq'.  Column side: dk'.
+    // The diagonal pair (i == i) has exponent 0: it feeds dq and dk but not dLambda, and is
+    // kept out of the dLambda products so that they do not leave a rounding residue.
     for (int e = tid; e < C * K; e += DN_THREADS) {
       const int i = e / K, c = e - i * K;
       const float li = LAM[e] * DN_LOG2E;
       float sb = 0.f, sq = 0.f;
-      for (int j = dstart_s[i]; j <= i; ++j) {
+      for (int j = dstart_s[i]; j < i; ++j) {
         const float ek = KH[j * K + c] * exp2f(fminf(li - LAM[j * K + c] * DN_LOG2E, 0.f));
         sb = fmaf(DA[i * C + j], ek, sb);
         sq = fmaf(DM[i * C + j], ek, sq);
       }
+      DLAM[e] = GB[e] * sb + QH[e] * sq;
       DBP[e] = sb;
-      DQP[e] = sq;
+      DQP[e] = fmaf(DM[i * C + i], KH[e], sq);
     }
     for (int e = tid; e < C * K; e += DN_THREADS) {
       const int j = e / K, c = e - j * K;
       const float lj = LAM[e] * DN_LOG2E;
       float sk = 0.f;
-      for (int i = j; i < C && seg_s[i] == seg_s[j]; ++i) {
+      for (int i = j + 1; i < C && seg_s[i] == seg_s[j]; ++i) {
         const float ex = exp2f(fminf(LAM[i * K + c] * DN_LOG2E - lj, 0.f));
         sk = fmaf(fmaf(DA[i * C + j], GB[i * K + c], DM[i * C + j] * QH[i * K + c]), ex, sk);
       }
-      DKP[e] = sk;
+      DLAM[e] -= KH[e] * sk;
+      DKP[e] = fmaf(DM[j * C + j], QH[e], sk);
     }
     __syncthreads();
 
@@ -221,23 +225,30 @@ __global__ void __launch_bounds__(DN_THREADS, 1) prepass_bwd_kernel(PrepassBwdAr
       const float dbeta = dbp + (first ? dx * el : 0.f);
       const float dq = dqp + (first ? dqe * el : 0.f);
       const float dk = dkp + (last ? dke * eke : 0.f) + dbeta * BA[e];
-      DLAM[e] = be * dbp + qh * dqp - kh * dkp + dx * X + dqe * qe - dke * ke;
-      DKE[e] = dke * ke;          // summed down the rows into dLambda_end below
+      DLAM[e] += dx * X + dqe * qe;
+      DKE[e] = dke * ke;          // enters dg as a prefix sum over earlier rows (below)
       DQP[e] = dq;
       DKP[e] = dk;
       DBP[e] = dbeta * kh;        // d b_act
     }
     __syncthreads();
-    // ---- dg: reverse cumulative sum of dLambda inside each document, then the g adjoint
+    // ---- dg_t = sum_{i >= t, same doc} dLambda_i  +  the Lambda_end path.  A row i of the last
+    // document reaches the chunk end through every later g, so the ke term adds the prefix sum
+    // of dke*ke over EARLIER rows (the equivalent "-dke*ke at row i, +sum at the last row" form
+    // cancels only up to rounding); the carried-state term dLambda_end reaches every row.
     if (tid < K) {
       const int c = tid;
-      float colsum = dlend_s[c];
-      for (int i = 0; i < C; ++i) colsum += DKE[i * K + c];
       float run = 0.f;
       for (int i = C - 1; i >= 0; --i) {
         if (i < C - 1 && seg_s[i] != seg_s[i + 1]) run = 0.f;
-        run += DLAM[i * K + c] + (i == C - 1 ? colsum : 0.f);
+        run += DLAM[i * K + c];
         DLAM[i * K + c] = run;
+      }
+      float acc = dlend_s[c];              // zero unless the chunk is one document
+      for (int i = 0; i < C; ++i) {
+        if (seg_s[i] != segL) continue;
+        DLAM[i * K + c] += acc;
+        acc += DKE[i * K + c];
       }
     }
     __syncthreads();

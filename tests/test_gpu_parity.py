@@ -64,8 +64,13 @@ def run_both(dn, q, k, v, g, b, w, *, do=None, dfs=None, tol, grads=True, oracle
         leaves_g = gpu_in + ([gpu_init] if init is not None else [])
         gr = torch.autograd.grad((o_ref.float() * do).sum() + (s_ref.float() * dfs).sum(), leaves_c)
         gg = torch.autograd.grad((o.float() * do.cuda()).sum() + (s * dfs.cuda()).sum(), leaves_g)
+        scale_ref = max(float(r.float().norm()) for r in gr)
         for nm, a, r in zip(NAMES + ("dinit",), gg, gr):
-            errs[nm] = O.rel_l2(a.float().cpu(), r.float())
+            if float(r.float().norm()) < 1e-6 * scale_ref:
+                # a gradient that is (numerically) zero in the oracle: compare on the scale of the others
+                errs[nm] = float((a.float().cpu() - r.float()).norm()) / scale_ref
+            else:
+                errs[nm] = O.rel_l2(a.float().cpu(), r.float())
     bad = {k_: e for k_, e in errs.items() if not e < tol}
     assert not bad, f"rel-L2 above {tol}: {bad} (all: {errs})"
     return errs
@@ -209,7 +214,7 @@ def test_many_small_documents_and_cu_seqlens(dn):
     o_ref = O.chunk_gdn2(q, k, v, g, b, w, cu_seqlens=cu, chunk_size=64, precision="fp32")
     o = dn.chunk_gdn2(*(x.cuda() for x in (q, k, v, g, b, w)), cu_seqlens=cu, chunk_size=64, precision="fp32")
     assert O.rel_l2(o.cpu(), o_ref) < FP32_TOL
-    ids = torch.repeat_interleave(torch.tensor([3, 7, 3, 3, 9, 3, 7], dtype=torch.int32),
+    ids = torch.repeat_interleave(torch.tensor([3, 7, 3, 5, 9, 3, 7], dtype=torch.int32),
                                   torch.tensor(np.diff(cu)))     # reused ids still split documents
     o2 = dn.chunk_gdn2(*(x.cuda() for x in (q, k, v, g, b, w)), segment_ids=ids.cuda(), chunk_size=64,
                        precision="fp32")
@@ -254,7 +259,7 @@ def test_repeat_runs_are_bit_identical(dn):
 
     def run():
         xs = [x.clone().requires_grad_() for x in ins]
-        o = dn.chunk_gdn2(*xs, chunk_size=64, precision="bf16")
+        o = dn.chunk_gdn2(*xs, chunk_size=64, precision="bf16", qk_l2norm=True)
         return [o.detach()] + list(torch.autograd.grad(o.sum(), xs))
 
     for x, y in zip(run(), run()):
