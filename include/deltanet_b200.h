@@ -189,6 +189,16 @@ int dn_decode_step(const dn_decode_shape* s,
                    const void* state_in, const uint8_t* reset,
                    void* out, void* state_out, void* stream);
 
+/*
+ * Diagnostic (no reference counterpart): D[128 x N] = A B^T in bf16 with fp32 accumulation through
+ * the library's tcgen05 building blocks, one CTA.  a_mn / b_mn = 0: the operand is given as
+ * (rows, Kc) with the contraction index contiguous; = 1: as (Kc, rows) with the row index
+ * contiguous.  N in {32,64,128,256}, Kc a multiple of 16 up to 256.  *err is set to 1 if a bounded
+ * wait inside the kernel gave up.
+ */
+int dn_selftest_umma(int32_t a_mn, int32_t b_mn, int32_t N, int32_t Kc, const void* A, const void* B,
+                     float* D, int32_t* err, void* stream);
+
 const char* dn_status_string(int status);
 int dn_version(void);
 
