@@ -10,6 +10,8 @@ extern "C" {
 
 int dn_version(void) { return 1; }
 
+int dn_device_error(void) { return read_device_error(); }
+
 const char* dn_status_string(int st) {
   switch (st) {
     case DN_OK: return "ok";

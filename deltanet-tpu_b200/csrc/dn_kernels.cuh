@@ -53,6 +53,13 @@ int launch_prepass_fwd(const Geo& g, const void* q, const void* k, const void* v
                        const void* b, const void* w, const int32_t* seg, const dn_residuals& res,
                        float* scratch, size_t scratch_floats, cudaStream_t st);
 int launch_state_fwd(const StateArgs& a, cudaStream_t st);
+// tensor-core (tcgen05) variants of the chain kernels, used when state_tc_eligible()
+bool state_tc_eligible(const Geo& g);
+int launch_state_fwd_tc(const StateArgs& a, cudaStream_t st);
+int launch_state_bwd_tc(const StateArgs& a, cudaStream_t st);
+int read_device_error();
+// true when the environment asks for the fp32 SIMT kernels everywhere (DN_FORCE_SIMT=1)
+bool force_simt();
 int launch_state_bwd(const StateArgs& a, cudaStream_t st);
 int launch_prepass_bwd(PrepassBwdArgs& a, size_t scratch_floats, cudaStream_t st);
 int launch_canonical_segments(const int32_t* raw, const int32_t* first_is_new, int32_t* out,

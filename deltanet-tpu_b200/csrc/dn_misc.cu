@@ -1,7 +1,14 @@
 // Small integer / reduction kernels around the main path.
 #include "dn_kernels.cuh"
 
+#include <cstdlib>
+
 namespace dn {
+
+bool force_simt() {
+  static const bool v = [] { const char* e = std::getenv("DN_FORCE_SIMT"); return e && e[0] == '1'; }();
+  return v;
+}
 
 // One CTA per batch row: out[t] = first_is_new + number of id changes in raw[1..t]
 // (the reference's canonicalisation, src/deltanet_tpu/gdn2.py:2081-2094).

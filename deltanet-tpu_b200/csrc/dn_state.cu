@@ -169,6 +169,7 @@ static size_t state_smem(const Geo& g, bool bwd) {
 
 int launch_state_fwd(const StateArgs& a, cudaStream_t st) {
   const Geo& g = a.g;
+  if (state_tc_eligible(g) && !force_simt()) return launch_state_fwd_tc(a, st);
   dim3 grid(g.Vw / VS, g.H, g.B);
   size_t smem = state_smem(g, false);
   static bool done = false;
@@ -184,6 +185,7 @@ int launch_state_fwd(const StateArgs& a, cudaStream_t st) {
 
 int launch_state_bwd(const StateArgs& a, cudaStream_t st) {
   const Geo& g = a.g;
+  if (state_tc_eligible(g) && !force_simt()) return launch_state_bwd_tc(a, st);
   dim3 grid(g.Vw / VS, g.H, g.B);
   size_t smem = state_smem(g, true);
   static bool done = false;

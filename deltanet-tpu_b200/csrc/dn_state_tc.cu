@@ -1,0 +1,392 @@
+// Inter-chunk recurrence on the tcgen05 tensor cores (bf16 precision, chunk = K = 128).
+//
+// Same math and same CTA decomposition as the fp32 formulation in dn_state.cu: one CTA carries
+// a (128 x VS) column slice of the state of one (batch, exec head) through all chunks.  Here
+//   * the fp32 master copy of the slice lives in registers, one state row per thread
+//     (128 threads), and a bf16 copy in shared memory is the MMA operand -- the reference rounds
+//     the state to bf16 for these products as well (src/deltanet_tpu/gdn2.py:627-632);
+//   * the four 128x128 bf16 tiles of a chunk (W, qe, M, ke) are brought in with 16-byte
+//     cp.async copies one chunk ahead, each buffer refilled as soon as the MMA reading it
+//     has completed;
+//   * every product is a 128 x VS x 128 tcgen05.mma with the accumulator in tensor memory,
+//     read back one row per thread.  A 128x128 tile image in shared memory serves both as the
+//     operand (K-major descriptor) and as its transpose (MN-major descriptor), so ke^T, M^T,
+//     qe^T and W^T need no data movement.
+// Every wait on the MMA barrier is bounded; on a timeout the CTA stops issuing tensor work,
+// raises the library's device error word and runs to its end.
+#include "dn_kernels.cuh"
+#include "dn_umma.cuh"
+
+namespace dn {
+
+__device__ int g_device_error = 0;
+
+int read_device_error() {
+  int v = 0;
+  cudaMemcpyFromSymbol(&v, g_device_error, sizeof(int));
+  return v;
+}
+
+namespace {
+
+constexpr int TILE_U4 = 128 * 16;   // a 128x128 bf16 tile in 16-byte units
+
+__device__ __forceinline__ size_t native_state_index_tc(const Geo& g, int b, int h, int k, int jj) {
+  const int hv = h * g.G + jj / g.V, cv = jj % g.V;
+  return (((size_t)b * g.Hv + hv) * g.K + k) * g.V + cv;
+}
+
+// Thread `row` copies its 256-byte row of a (128,128) bf16 tile into the panel image.
+__device__ __forceinline__ void copy_tile_async(uint4* dst, const __nv_bfloat16* src, int row) {
+  const uint4* s = reinterpret_cast<const uint4*>(src + (size_t)row * 128);
+#pragma unroll
+  for (int p = 0; p < 16; ++p) umma::cp_async16(dst + p * 128 + row, s + p);
+}
+
+template <int VS>
+__device__ __forceinline__ void stage_rows(uint4* dst, int row, const float (&x)[VS], float sign = 1.f) {
+#pragma unroll
+  for (int p = 0; p < VS / 8; ++p) {
+    float t[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) t[i] = sign * x[p * 8 + i];
+    dst[p * 128 + row] = umma::pack8(t);
+  }
+}
+
+template <int VS>
+__device__ __forceinline__ void read_acc(const umma::Ctx& cx, uint32_t col, int warp, float (&x)[VS]) {
+#pragma unroll
+  for (int c = 0; c < VS; c += 16) {
+    float v[16];
+    if (!cx.dead) umma::tmem_ld16(cx.tmem + ((uint32_t)(warp * 32) << 16) + col + c, v);
+    else {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) v[i] = 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < 16; ++i) x[c + i] = v[i];
+  }
+}
+
+__host__ __device__ constexpr uint32_t tmem_cols(int vs) { return 3 * vs <= 128 ? 128u : (3 * vs <= 256 ? 256u : 512u); }
+
+template <int VS, bool WITH_OUT>
+__global__ void __launch_bounds__(128, 1) state_fwd_tc_kernel(StateArgs a) {
+  extern __shared__ __align__(128) uint8_t sm[];
+  __shared__ uint64_t bar;
+  __shared__ uint32_t tmem_base;
+  const Geo& g = a.g;
+  constexpr int C = 128, K = 128;
+  const int Vw = g.Vw, v0 = blockIdx.x * VS, h = blockIdx.y, b = blockIdx.z;
+  const int row = threadIdx.x, warp = row >> 5;
+  uint4* sW = reinterpret_cast<uint4*>(sm);
+  uint4* sQE = sW + TILE_U4;
+  uint4* sM = sQE + TILE_U4;
+  uint4* sKE = sM + TILE_U4;
+  uint4* sS = sKE + TILE_U4;
+  uint4* sVn = sS + (VS / 8) * 128;
+  if (row == 0) { umma::mbar_init(&bar, 1); umma::fence_mbar_init(); }
+  if (warp == 0) umma::tmem_alloc(&tmem_base, tmem_cols(VS));
+  umma::tc_fence_before();
+  __syncthreads();
+  umma::tc_fence_after();
+  umma::Ctx cx{tmem_base, &bar, 0u, &g_device_error, false};
+  constexpr uint32_t colP = 0, colO = VS, colS = 2 * VS;
+
+  const __nv_bfloat16* Wg = reinterpret_cast<const __nv_bfloat16*>(a.res.W);
+  const __nv_bfloat16* QEg = reinterpret_cast<const __nv_bfloat16*>(a.res.qe);
+  const __nv_bfloat16* KEg = reinterpret_cast<const __nv_bfloat16*>(a.res.ke);
+  const __nv_bfloat16* Mg = reinterpret_cast<const __nv_bfloat16*>(a.res.M);
+  const __nv_bfloat16* Ug = reinterpret_cast<const __nv_bfloat16*>(a.res.U);
+  const size_t item0 = ((size_t)b * g.H + h) * g.NC;
+
+  copy_tile_async(sW, Wg + item0 * C * K, row);
+  umma::cp_async_commit();
+  copy_tile_async(sQE, QEg + item0 * C * K, row);
+  copy_tile_async(sM, Mg + item0 * C * C, row);
+  copy_tile_async(sKE, KEg + item0 * C * K, row);
+  umma::cp_async_commit();
+
+  float S[VS];
+#pragma unroll
+  for (int j = 0; j < VS; ++j) S[j] = 0.f;
+
+  for (int c = 0; c < g.NC; ++c) {
+    bool is_new, all_same;
+    chunk_flags(a.seg, g, b, c, is_new, all_same);
+    const size_t item = item0 + c;
+    if (c == 0 && !is_new && a.init_state) {
+#pragma unroll
+      for (int j = 0; j < VS; ++j) S[j] = a.init_state[native_state_index_tc(g, b, h, row, v0 + j)];
+    } else if (is_new) {
+#pragma unroll
+      for (int j = 0; j < VS; ++j) S[j] = 0.f;
+    }
+    if (a.states) {
+      float4* dst = reinterpret_cast<float4*>(a.states + item * K * Vw + (size_t)row * Vw + v0);
+#pragma unroll
+      for (int j = 0; j < VS / 4; ++j) dst[j] = make_float4(S[4 * j], S[4 * j + 1], S[4 * j + 2], S[4 * j + 3]);
+    }
+    stage_rows<VS>(sS, row, S);
+    uint4 ureg[VS / 8];
+    {
+      const uint4* up = reinterpret_cast<const uint4*>(Ug + item * C * Vw + (size_t)row * Vw + v0);
+#pragma unroll
+      for (int p = 0; p < VS / 8; ++p) ureg[p] = up[p];
+    }
+    const float dec = all_same ? expf(fminf(a.res.lam_end[item * K + row], 0.f)) : 0.f;
+
+    umma::cp_async_wait<1>();                           // this chunk's W has landed
+    umma::pre_issue_sync();
+    umma::issue<VS, false, true>(cx, sW, sS, K, colP, false);          // P = W S
+    umma::commit_wait(cx);
+    if (c + 1 < g.NC) copy_tile_async(sW, Wg + (item + 1) * C * K, row);
+    umma::cp_async_commit();
+
+    float vn[VS];
+    read_acc<VS>(cx, colP, warp, vn);
+#pragma unroll
+    for (int p = 0; p < VS / 8; ++p) {
+      float u[8];
+      umma::unpack8(ureg[p], u);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) vn[p * 8 + i] = u[i] - vn[p * 8 + i];      // V_new = U - W S
+    }
+    stage_rows<VS>(sVn, row, vn);
+
+    umma::cp_async_wait<1>();                           // this chunk's qe, M, ke have landed
+    umma::pre_issue_sync();
+    if (WITH_OUT) {
+      umma::issue<VS, false, true>(cx, sQE, sS, K, colO, false);       // O  = qe S
+      umma::issue<VS, false, true>(cx, sM, sVn, C, colO, true);        //    + M V_new
+    }
+    umma::issue<VS, true, true>(cx, sKE, sVn, C, colS, false);         // ke^T V_new
+    umma::commit_wait(cx);
+    if (c + 1 < g.NC) {
+      copy_tile_async(sQE, QEg + (item + 1) * C * K, row);
+      copy_tile_async(sM, Mg + (item + 1) * C * C, row);
+      copy_tile_async(sKE, KEg + (item + 1) * C * K, row);
+    }
+    umma::cp_async_commit();
+
+    if (WITH_OUT) {
+      float o[VS];
+      read_acc<VS>(cx, colO, warp, o);
+      const int t = c * C + row;
+      if (t < g.L) {
+        const size_t off = ((size_t)b * g.L + t) * g.Hv * g.V + (size_t)h * Vw + v0;
+        if (g.qkv_dt == DN_BF16) {
+          uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.out) + off);
+#pragma unroll
+          for (int p = 0; p < VS / 8; ++p) {
+            float t8[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) t8[i] = o[p * 8 + i];
+            dst[p] = umma::pack8(t8);
+          }
+        } else {
+          float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(a.out) + off);
+#pragma unroll
+          for (int j = 0; j < VS / 4; ++j) dst[j] = make_float4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+        }
+      }
+    }
+    float sn[VS];
+    read_acc<VS>(cx, colS, warp, sn);
+#pragma unroll
+    for (int j = 0; j < VS; ++j) S[j] = fmaf(dec, S[j], sn[j]);       // S <- decay * S + ke^T V_new
+    umma::tc_fence_before();
+  }
+  if (a.final_state) {
+#pragma unroll
+    for (int j = 0; j < VS; ++j) a.final_state[native_state_index_tc(g, b, h, row, v0 + j)] = S[j];
+  }
+  umma::cp_async_wait<0>();
+  __syncthreads();
+  if (warp == 0) umma::tmem_dealloc(tmem_base, tmem_cols(VS));
+}
+
+template <int VS>
+__global__ void __launch_bounds__(128, 1) state_bwd_tc_kernel(StateArgs a) {
+  extern __shared__ __align__(128) uint8_t sm[];
+  __shared__ uint64_t bar;
+  __shared__ uint32_t tmem_base;
+  const Geo& g = a.g;
+  constexpr int C = 128, K = 128;
+  const int Vw = g.Vw, v0 = blockIdx.x * VS, h = blockIdx.y, b = blockIdx.z;
+  const int row = threadIdx.x, warp = row >> 5;
+  uint4* sM = reinterpret_cast<uint4*>(sm);
+  uint4* sKE = sM + TILE_U4;
+  uint4* sQE = sKE + TILE_U4;
+  uint4* sW = sQE + TILE_U4;
+  uint4* sdO = sW + TILE_U4;
+  uint4* sdH = sdO + (VS / 8) * 128;
+  uint4* sdV = sdH + (VS / 8) * 128;
+  if (row == 0) { umma::mbar_init(&bar, 1); umma::fence_mbar_init(); }
+  if (warp == 0) umma::tmem_alloc(&tmem_base, tmem_cols(VS));
+  umma::tc_fence_before();
+  __syncthreads();
+  umma::tc_fence_after();
+  umma::Ctx cx{tmem_base, &bar, 0u, &g_device_error, false};
+  constexpr uint32_t colV = 0, colH = VS;
+
+  const __nv_bfloat16* Wg = reinterpret_cast<const __nv_bfloat16*>(a.res.W);
+  const __nv_bfloat16* QEg = reinterpret_cast<const __nv_bfloat16*>(a.res.qe);
+  const __nv_bfloat16* KEg = reinterpret_cast<const __nv_bfloat16*>(a.res.ke);
+  const __nv_bfloat16* Mg = reinterpret_cast<const __nv_bfloat16*>(a.res.M);
+  const size_t item0 = ((size_t)b * g.H + h) * g.NC;
+  const size_t last = item0 + g.NC - 1;
+
+  copy_tile_async(sM, Mg + last * C * C, row);
+  copy_tile_async(sKE, KEg + last * C * K, row);
+  umma::cp_async_commit();
+  copy_tile_async(sQE, QEg + last * C * K, row);
+  copy_tile_async(sW, Wg + last * C * K, row);
+  umma::cp_async_commit();
+
+  float dH[VS];
+#pragma unroll
+  for (int j = 0; j < VS; ++j)
+    dH[j] = a.d_final ? a.d_final[native_state_index_tc(g, b, h, row, v0 + j)] : 0.f;
+
+  for (int c = g.NC - 1; c >= 0; --c) {
+    bool is_new, all_same;
+    chunk_flags(a.seg, g, b, c, is_new, all_same);
+    const size_t item = item0 + c;
+    // this thread's row of dO (token c*C+row), rounded to bf16 as the reference does (gdn2.py:731)
+    float dO[VS];
+    {
+      const int t = c * C + row;
+      if (t < g.L) {
+        const size_t off = ((size_t)b * g.L + t) * g.Hv * g.V + (size_t)h * Vw + v0;
+        if (g.qkv_dt == DN_BF16) {
+          const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(a.d_out) + off);
+#pragma unroll
+          for (int p = 0; p < VS / 8; ++p) {
+            float t8[8];
+            umma::unpack8(src[p], t8);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) dO[p * 8 + i] = t8[i];
+          }
+        } else {
+          const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.d_out) + off);
+#pragma unroll
+          for (int j = 0; j < VS / 4; ++j) {
+            const float4 f = src[j];
+            dO[4 * j] = f.x; dO[4 * j + 1] = f.y; dO[4 * j + 2] = f.z; dO[4 * j + 3] = f.w;
+          }
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < VS; ++j) dO[j] = 0.f;
+      }
+    }
+    stage_rows<VS>(sdO, row, dO);
+    stage_rows<VS>(sdH, row, dH);
+    {
+      float4* dst = reinterpret_cast<float4*>(a.dH + item * K * Vw + (size_t)row * Vw + v0);
+#pragma unroll
+      for (int j = 0; j < VS / 4; ++j) dst[j] = make_float4(dH[4 * j], dH[4 * j + 1], dH[4 * j + 2], dH[4 * j + 3]);
+    }
+    const float dec = all_same ? expf(fminf(a.res.lam_end[item * K + row], 0.f)) : 0.f;
+
+    umma::cp_async_wait<1>();                           // M, ke of this chunk
+    umma::pre_issue_sync();
+    umma::issue<VS, true, true>(cx, sM, sdO, C, colV, false);          // dV  = M^T dO
+    umma::issue<VS, false, true>(cx, sKE, sdH, K, colV, true);         //     + ke dH
+    umma::commit_wait(cx);
+    if (c > 0) {
+      copy_tile_async(sM, Mg + (item - 1) * C * C, row);
+      copy_tile_async(sKE, KEg + (item - 1) * C * K, row);
+    }
+    umma::cp_async_commit();
+
+    float dv[VS];
+    read_acc<VS>(cx, colV, warp, dv);
+    {
+      float4* dst = reinterpret_cast<float4*>(a.dV + item * C * Vw + (size_t)row * Vw + v0);
+#pragma unroll
+      for (int j = 0; j < VS / 4; ++j) dst[j] = make_float4(dv[4 * j], dv[4 * j + 1], dv[4 * j + 2], dv[4 * j + 3]);
+    }
+    stage_rows<VS>(sdV, row, dv, -1.f);                 // staged negated: the product below is -W^T dV
+
+    umma::cp_async_wait<1>();                           // qe, W of this chunk
+    umma::pre_issue_sync();
+    umma::issue<VS, true, true>(cx, sQE, sdO, C, colH, false);         // qe^T dO
+    umma::issue<VS, true, true>(cx, sW, sdV, C, colH, true);           // - W^T dV
+    umma::commit_wait(cx);
+    if (c > 0) {
+      copy_tile_async(sQE, QEg + (item - 1) * C * K, row);
+      copy_tile_async(sW, Wg + (item - 1) * C * K, row);
+    }
+    umma::cp_async_commit();
+
+    float dn_[VS];
+    read_acc<VS>(cx, colH, warp, dn_);
+#pragma unroll
+    for (int j = 0; j < VS; ++j) dH[j] = is_new ? 0.f : fmaf(dec, dH[j], dn_[j]);
+    umma::tc_fence_before();
+  }
+  if (a.d_init) {
+#pragma unroll
+    for (int j = 0; j < VS; ++j) a.d_init[native_state_index_tc(g, b, h, row, v0 + j)] = dH[j];
+  }
+  umma::cp_async_wait<0>();
+  __syncthreads();
+  if (warp == 0) umma::tmem_dealloc(tmem_base, tmem_cols(VS));
+}
+
+int pick_vs(const Geo& g) {
+  const int chains = g.B * g.H;
+  if (g.Vw % 64 == 0 && chains * (g.Vw / 64) >= 148) return 64;
+  return 32;
+}
+
+template <int VS>
+size_t tc_smem(bool bwd) { return (size_t)4 * TILE_U4 * 16 + (size_t)(bwd ? 3 : 2) * (VS / 8) * 128 * 16; }
+
+template <int VS>
+int launch_fwd_vs(const StateArgs& a, cudaStream_t st) {
+  dim3 grid(a.g.Vw / VS, a.g.H, a.g.B);
+  const size_t smem = tc_smem<VS>(false);
+  if (a.out) {
+    cudaFuncSetAttribute(state_fwd_tc_kernel<VS, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    state_fwd_tc_kernel<VS, true><<<grid, 128, smem, st>>>(a);
+  } else {
+    cudaFuncSetAttribute(state_fwd_tc_kernel<VS, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    state_fwd_tc_kernel<VS, false><<<grid, 128, smem, st>>>(a);
+  }
+  return cudaGetLastError() == cudaSuccess ? DN_OK : DN_ERR_CUDA_LAUNCH;
+}
+
+template <int VS>
+int launch_bwd_vs(const StateArgs& a, cudaStream_t st) {
+  dim3 grid(a.g.Vw / VS, a.g.H, a.g.B);
+  const size_t smem = tc_smem<VS>(true);
+  cudaFuncSetAttribute(state_bwd_tc_kernel<VS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  state_bwd_tc_kernel<VS><<<grid, 128, smem, st>>>(a);
+  return cudaGetLastError() == cudaSuccess ? DN_OK : DN_ERR_CUDA_LAUNCH;
+}
+
+}  // namespace
+
+bool state_tc_eligible(const Geo& g) {
+  return g.prec == DN_PREC_BF16 && !(g.flags & DN_STATE_FP32_MM) && g.C == 128 && g.K == 128 && g.Vw % 32 == 0;
+}
+
+int launch_state_fwd_tc(const StateArgs& a, cudaStream_t st) {
+  switch (pick_vs(a.g)) {
+    case 64: return launch_fwd_vs<64>(a, st);
+    default: return launch_fwd_vs<32>(a, st);
+  }
+}
+
+int launch_state_bwd_tc(const StateArgs& a, cudaStream_t st) {
+  switch (pick_vs(a.g)) {
+    case 64: return launch_bwd_vs<64>(a, st);
+    default: return launch_bwd_vs<32>(a, st);
+  }
+}
+
+}  // namespace dn

@@ -97,6 +97,14 @@ __device__ __forceinline__ void mma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+// ---- asynchronous 16-byte global -> shared copies (generic proxy; follow with fence_async_smem) -------
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int PENDING>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(PENDING) : "memory"); }
+
 // ---- packing helpers ---------------------------------------------------------------------
 __device__ __forceinline__ uint32_t pack2(float a, float b) {
   __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
@@ -135,32 +143,47 @@ __device__ __forceinline__ void stage_operand(uint4* dst, int panels, int inner,
   }
 }
 
-// Issue the MMAs of D[128 x N] (+)= A[128 x Kc] B[N x Kc]^T on staged operands (one thread),
-// commit, and make every thread wait for completion.  tmem_col: first column of D.
-template <int N, bool A_MN, bool B_MN>
-__device__ __forceinline__ void issue_and_wait(Ctx& cx, const void* sA, const void* sB, int Kc, uint32_t tmem_col,
-                                               bool accumulate) {
+// Make operand writes of all threads visible to the tensor core and order TMEM accesses: call
+// once by every thread after staging and before `issue`.
+__device__ __forceinline__ void pre_issue_sync() {
   fence_async_smem();                  // operand writes (generic proxy) -> visible to the MMA (async proxy)
   tc_fence_before();
   __syncthreads();
-  if (threadIdx.x == 0 && !cx.dead) {
-    tc_fence_after();
-    const uint32_t a0 = smem_u32(sA), b0 = smem_u32(sB);
-    constexpr uint32_t idesc = instr_desc(N, A_MN ? 1 : 0, B_MN ? 1 : 0);
-    const uint32_t a_lbo = A_MN ? 128u : 128u * 16u, a_sbo = A_MN ? (uint32_t)Kc * 16u : 128u;
-    const uint32_t b_lbo = B_MN ? 128u : (uint32_t)N * 16u, b_sbo = B_MN ? (uint32_t)Kc * 16u : 128u;
-    const uint32_t a_step = A_MN ? 256u : 2u * 128u * 16u, b_step = B_MN ? 256u : 2u * (uint32_t)N * 16u;
-    for (int ks = 0; ks < Kc / 16; ++ks)
-      mma_bf16(cx.tmem + tmem_col, smem_desc(a0 + ks * a_step, a_lbo, a_sbo), smem_desc(b0 + ks * b_step, b_lbo, b_sbo),
-               idesc, (accumulate || ks > 0) ? 1u : 0u);
-    mma_commit(cx.bar);
-  }
+  tc_fence_after();
+}
+
+// Issue (one thread) the MMAs of D[128 x N] (+)= A[128 x Kc] B[N x Kc]^T on staged operands.
+template <int N, bool A_MN, bool B_MN>
+__device__ __forceinline__ void issue(const Ctx& cx, const void* sA, const void* sB, int Kc, uint32_t tmem_col,
+                                      bool accumulate) {
+  if (threadIdx.x != 0 || cx.dead) return;
+  const uint32_t a0 = smem_u32(sA), b0 = smem_u32(sB);
+  constexpr uint32_t idesc = instr_desc(N, A_MN ? 1 : 0, B_MN ? 1 : 0);
+  const uint32_t a_lbo = A_MN ? 128u : 128u * 16u, a_sbo = A_MN ? (uint32_t)Kc * 16u : 128u;
+  const uint32_t b_lbo = B_MN ? 128u : (uint32_t)N * 16u, b_sbo = B_MN ? (uint32_t)Kc * 16u : 128u;
+  const uint32_t a_step = A_MN ? 256u : 2u * 128u * 16u, b_step = B_MN ? 256u : 2u * (uint32_t)N * 16u;
+  for (int ks = 0; ks < Kc / 16; ++ks)
+    mma_bf16(cx.tmem + tmem_col, smem_desc(a0 + ks * a_step, a_lbo, a_sbo), smem_desc(b0 + ks * b_step, b_lbo, b_sbo),
+             idesc, (accumulate || ks > 0) ? 1u : 0u);
+}
+
+// Commit everything issued so far (one thread) and make every thread wait for it, boundedly.
+__device__ __forceinline__ void commit_wait(Ctx& cx) {
+  if (threadIdx.x == 0 && !cx.dead) mma_commit(cx.bar);
   if (!cx.dead && !mbar_wait(cx.bar, cx.phase)) {
     cx.dead = true;
     if (cx.err) atomicExch(cx.err, 1);
   }
   cx.phase ^= 1u;
   tc_fence_after();
+}
+
+template <int N, bool A_MN, bool B_MN>
+__device__ __forceinline__ void issue_and_wait(Ctx& cx, const void* sA, const void* sB, int Kc, uint32_t tmem_col,
+                                               bool accumulate) {
+  pre_issue_sync();
+  issue<N, A_MN, B_MN>(cx, sA, sB, Kc, tmem_col, accumulate);
+  commit_wait(cx);
 }
 
 // Hand D[128 x N] (fp32, tensor memory) to epi(row, col0, v[16]) in 16-column pieces.

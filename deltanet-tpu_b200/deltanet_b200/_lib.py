@@ -47,6 +47,7 @@ class DecodeShape(C.Structure):
 _P = C.c_void_p
 _SIGNATURES = {
     "dn_version": (C.c_int, []),
+    "dn_device_error": (C.c_int, []),
     "dn_status_string": (C.c_char_p, [C.c_int]),
     "dn_exec_view": (C.c_int, [C.POINTER(Shape), C.POINTER(Exec)]),
     "dn_residual_bytes": (C.c_size_t, [C.POINTER(Shape)]),

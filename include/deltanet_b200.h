@@ -199,6 +199,13 @@ int dn_decode_step(const dn_decode_shape* s,
 int dn_selftest_umma(int32_t a_mn, int32_t b_mn, int32_t N, int32_t Kc, const void* A, const void* B,
                      float* D, int32_t* err, void* stream);
 
+/*
+ * Diagnostic (no reference counterpart): reads the library's device error word.  It is 0 unless a
+ * bounded wait inside a tensor-core kernel gave up (the kernel then finished without the
+ * affected products).  Synchronises with the device; meant for tests and debugging.
+ */
+int dn_device_error(void);
+
 const char* dn_status_string(int status);
 int dn_version(void);
 

@@ -359,3 +359,10 @@ def test_variants_against_oracle(dn, variant):
     else:
         o, r = dn.chunk_delta_rule(*c(q, k, v, beta), **kw), O.chunk_gdn2(q, k, v, torch.zeros_like(k), beta, beta, **kw)
     assert O.rel_l2(o.cpu(), r) < FP32_TOL
+
+
+def test_no_tensor_core_wait_timed_out(dn):
+    """Every wait on a tensor-core barrier is bounded; none of the runs above may have hit its bound."""
+    from deltanet_b200 import _lib
+    torch.cuda.synchronize()
+    assert _lib.lib().dn_device_error() == 0
