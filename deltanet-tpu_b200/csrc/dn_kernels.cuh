@@ -44,6 +44,7 @@ struct PrepassBwdArgs {
   float* scratch;
   size_t scratch_per_cta;
   int items;
+  int* err;                        // device error word (bounded waits report here)
 };
 
 size_t prepass_fwd_scratch_per_cta(const Geo& g);
@@ -58,6 +59,7 @@ bool state_tc_eligible(const Geo& g);
 int launch_state_fwd_tc(const StateArgs& a, cudaStream_t st);
 int launch_state_bwd_tc(const StateArgs& a, cudaStream_t st);
 int read_device_error();
+int* device_error_ptr();
 // true when the environment asks for the fp32 SIMT kernels everywhere (DN_FORCE_SIMT=1)
 bool force_simt();
 int launch_state_bwd(const StateArgs& a, cudaStream_t st);

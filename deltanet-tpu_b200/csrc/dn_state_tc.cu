@@ -27,6 +27,12 @@ int read_device_error() {
   return v;
 }
 
+int* device_error_ptr() {
+  int* p = nullptr;
+  cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_device_error);
+  return p;
+}
+
 namespace {
 
 constexpr int TILE_U4 = 128 * 16;   // a 128x128 bf16 tile in 16-byte units
