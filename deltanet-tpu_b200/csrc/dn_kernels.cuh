@@ -53,6 +53,10 @@ size_t prepass_bwd_scratch_per_cta(const Geo& g);
 int launch_prepass_fwd(const Geo& g, const void* q, const void* k, const void* v, const void* gg,
                        const void* b, const void* w, const int32_t* seg, const dn_residuals& res,
                        float* scratch, size_t scratch_floats, cudaStream_t st);
+bool prepass_fwd_tc_eligible(const Geo& g);
+int launch_prepass_fwd_tc(const Geo& g, const void* q, const void* k, const void* v, const void* gg,
+                          const void* b, const void* w, const int32_t* seg, const dn_residuals& res,
+                          float* scratch, size_t scratch_floats, cudaStream_t st);
 int launch_state_fwd(const StateArgs& a, cudaStream_t st);
 // tensor-core (tcgen05) variants of the chain kernels, used when state_tc_eligible()
 bool state_tc_eligible(const Geo& g);
@@ -64,6 +68,8 @@ int* device_error_ptr();
 bool force_simt();
 int launch_state_bwd(const StateArgs& a, cudaStream_t st);
 int launch_prepass_bwd(PrepassBwdArgs& a, size_t scratch_floats, cudaStream_t st);
+int launch_prepass_bwd_tc(PrepassBwdArgs& a, size_t scratch_floats, cudaStream_t st);
+size_t prepass_bwd_tc_scratch_per_cta(const Geo& g);
 int launch_canonical_segments(const int32_t* raw, const int32_t* first_is_new, int32_t* out,
                               int B, int L, cudaStream_t st);
 // sums `groups` consecutive heads: in (rows, heads_out*groups, cols) f32 -> out (rows, heads_out, cols)

@@ -167,7 +167,7 @@ __global__ void __launch_bounds__(DN_THREADS, 1) prepass_bwd_kernel(PrepassBwdAr
       io.rows_valid = g.L - t0 < C ? g.L - t0 : C;
       io.DQE = DQE; io.DKE = DKE; io.DX = DX; io.DY = DY; io.DM = DM; io.DA = DA;
       io.seg_s = seg_s; io.trunc = trunc;
-      bwd_gemms_tc<TCW ? TCW : 128>(cx, reinterpret_cast<uint8_t*>(smem), io);
+      bwd_gemms_tc<TCW ? TCW : 128, DN_THREADS>(cx, reinterpret_cast<uint8_t*>(smem), io);
     } else {
     // ---- V_new = U - W S
       cta_gemm<true, true>(C, Vw, K,
@@ -386,6 +386,7 @@ int launch_prepass_bwd(PrepassBwdArgs& a, size_t scratch_floats, cudaStream_t st
   a.scratch_per_cta = prepass_bwd_scratch_per_cta(g);
   const bool tc = prepass_bwd_tc_eligible(g) && !force_simt();
   a.err = device_error_ptr();
+  if (tc) return launch_prepass_bwd_tc(a, scratch_floats, st);
   const int max_ctas = tc ? 148 : 296;
   int grid = a.items < max_ctas ? a.items : max_ctas;
   if (scratch_floats < (size_t)grid * a.scratch_per_cta) return DN_ERR_SCRATCH_TOO_SMALL;

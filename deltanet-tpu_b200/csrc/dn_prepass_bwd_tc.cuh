@@ -31,22 +31,22 @@ struct BwdTcIo {
   bool trunc;
 };
 
-template <int R>
+template <int R, int NT>
 __device__ __forceinline__ void stage_f32(uint4* dst, const float* src, int pitch, int panels) {
-  for (int e = threadIdx.x; e < panels * R; e += DN_THREADS) {
+  for (int e = threadIdx.x; e < panels * R; e += NT) {
     const int p = e / R, x = e - p * R;
     dst[e] = umma::ld8_f32(src + (size_t)x * pitch + 8 * p);
   }
 }
-template <int R>
+template <int R, int NT>
 __device__ __forceinline__ void stage_bf16(uint4* dst, const __nv_bfloat16* src, int pitch, int panels) {
-  for (int e = threadIdx.x; e < panels * R; e += DN_THREADS) {
+  for (int e = threadIdx.x; e < panels * R; e += NT) {
     const int p = e / R, x = e - p * R;
     dst[e] = umma::ld8_bf16(src + (size_t)x * pitch + 8 * p);
   }
 }
 
-template <int VW>
+template <int VW, int NT>
 __device__ __forceinline__ void bwd_gemms_tc(umma::Ctx& cx, uint8_t* img, const BwdTcIo& io) {
   constexpr int SLOT = 128 * VW * 2;
   uint4* X = reinterpret_cast<uint4*>(img);
@@ -59,12 +59,12 @@ __device__ __forceinline__ void bwd_gemms_tc(umma::Ctx& cx, uint8_t* img, const 
   const int* seg_s = io.seg_s;
 
   // ---- 1. V_new = U - W S
-  stage_bf16<128>(P, io.W, 128, 16);
-  stage_f32<128>(X, io.S, VW, PV);
+  stage_bf16<128, NT>(P, io.W, 128, 16);
+  stage_f32<128, NT>(X, io.S, VW, PV);
   umma::pre_issue_sync();
   umma::issue<VW, false, true>(cx, P, X, 128, 0, false);
   umma::commit_wait(cx);
-  umma::drain<DN_THREADS, VW>(cx, 0, [&](int row, int col, const float (&v)[16]) {
+  umma::drain<NT, VW>(cx, 0, [&](int row, int col, const float (&v)[16]) {
     float u0[8], u1[8];
     const uint4* up = reinterpret_cast<const uint4*>(io.U + (size_t)row * VW + col);
     umma::unpack8(up[0], u0);
@@ -76,7 +76,7 @@ __device__ __forceinline__ void bwd_gemms_tc(umma::Ctx& cx, uint8_t* img, const 
   });
 
   // ---- 2. dqe = dO S^T, dM = dO V_new^T
-  for (int e = threadIdx.x; e < PV * 128; e += DN_THREADS) {
+  for (int e = threadIdx.x; e < PV * 128; e += NT) {
     const int p = e / 128, x = e - p * 128;
     uint4 val = make_uint4(0, 0, 0, 0);
     if (x < io.rows_valid) {
@@ -90,12 +90,12 @@ __device__ __forceinline__ void bwd_gemms_tc(umma::Ctx& cx, uint8_t* img, const 
   umma::issue<128, false, false>(cx, Z, X, VW, 256, false);
   umma::issue<128, false, false>(cx, Z, Y, VW, 384, false);
   umma::commit_wait(cx);
-  umma::drain<DN_THREADS, 128>(cx, 256, [&](int row, int col, const float (&v)[16]) {
+  umma::drain<NT, 128>(cx, 256, [&](int row, int col, const float (&v)[16]) {
     float4* d = reinterpret_cast<float4*>(io.DQE + row * 128 + col);
 #pragma unroll
     for (int i = 0; i < 4; ++i) d[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
   });
-  umma::drain<DN_THREADS, 128>(cx, 384, [&](int row, int col, const float (&v)[16]) {
+  umma::drain<NT, 128>(cx, 384, [&](int row, int col, const float (&v)[16]) {
     float m[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) m[i] = (row >= col + i && seg_s[row] == seg_s[col + i]) ? v[i] : 0.f;
@@ -105,11 +105,11 @@ __device__ __forceinline__ void bwd_gemms_tc(umma::Ctx& cx, uint8_t* img, const 
   });
 
   // ---- 3. dW = -dV S^T (kept only as the operand image of step 5)
-  stage_f32<128>(Z, io.dV, VW, PV);
+  stage_f32<128, NT>(Z, io.dV, VW, PV);
   umma::pre_issue_sync();
   umma::issue<128, false, false>(cx, Z, X, VW, 0, false);
   umma::commit_wait(cx);
-  umma::drain<DN_THREADS, 128>(cx, 0, [&](int row, int col, const float (&v)[16]) {
+  umma::drain<NT, 128>(cx, 0, [&](int row, int col, const float (&v)[16]) {
     float a[8], b[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) { a[i] = -v[i]; b[i] = -v[8 + i]; }
@@ -118,23 +118,23 @@ __device__ __forceinline__ void bwd_gemms_tc(umma::Ctx& cx, uint8_t* img, const 
   });
 
   // ---- 4. dke = V_new dH^T
-  stage_f32<128>(X, io.dH, VW, PV);
+  stage_f32<128, NT>(X, io.dH, VW, PV);
   umma::pre_issue_sync();
   umma::issue<128, false, false>(cx, Y, X, VW, 128, false);
   umma::commit_wait(cx);
-  umma::drain<DN_THREADS, 128>(cx, 128, [&](int row, int col, const float (&v)[16]) {
+  umma::drain<NT, 128>(cx, 128, [&](int row, int col, const float (&v)[16]) {
     float4* d = reinterpret_cast<float4*>(io.DKE + row * 128 + col);
 #pragma unroll
     for (int i = 0; i < 4; ++i) d[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
   });
 
   // ---- 5. dX = T^T dW, dY = T^T dV
-  stage_f32<128>(Y, io.T, 128, 16);
+  stage_f32<128, NT>(Y, io.T, 128, 16);
   umma::pre_issue_sync();
   umma::issue<128, true, true>(cx, Y, P, 128, 0, false);
   umma::issue<VW, true, true>(cx, Y, Z, 128, 256, false);
   umma::commit_wait(cx);
-  umma::drain<DN_THREADS, 128>(cx, 0, [&](int row, int col, const float (&v)[16]) {
+  umma::drain<NT, 128>(cx, 0, [&](int row, int col, const float (&v)[16]) {
     float a[8], b[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) { a[i] = io.trunc ? bf16r(v[i]) : v[i]; b[i] = io.trunc ? bf16r(v[8 + i]) : v[8 + i]; }
@@ -144,7 +144,7 @@ __device__ __forceinline__ void bwd_gemms_tc(umma::Ctx& cx, uint8_t* img, const 
     Y2[(col / 8) * 128 + row] = umma::pack8(a);
     Y2[(col / 8 + 1) * 128 + row] = umma::pack8(b);
   });
-  umma::drain<DN_THREADS, VW>(cx, 256, [&](int row, int col, const float (&v)[16]) {
+  umma::drain<NT, VW>(cx, 256, [&](int row, int col, const float (&v)[16]) {
     float a[8], b[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) { a[i] = io.trunc ? bf16r(v[i]) : v[i]; b[i] = io.trunc ? bf16r(v[8 + i]) : v[8 + i]; }
@@ -156,13 +156,13 @@ __device__ __forceinline__ void bwd_gemms_tc(umma::Ctx& cx, uint8_t* img, const 
   });
 
   // ---- 6. dA = -(dX W^T + dY U^T), strictly lower and same document
-  stage_bf16<128>(P, io.W, 128, 16);
-  stage_bf16<128>(Z, io.U, VW, PV);
+  stage_bf16<128, NT>(P, io.W, 128, 16);
+  stage_bf16<128, NT>(Z, io.U, VW, PV);
   umma::pre_issue_sync();
   umma::issue<128, false, false>(cx, Y2, P, 128, 0, false);
   umma::issue<128, false, false>(cx, X, Z, VW, 0, true);
   umma::commit_wait(cx);
-  umma::drain<DN_THREADS, 128>(cx, 0, [&](int row, int col, const float (&v)[16]) {
+  umma::drain<NT, 128>(cx, 0, [&](int row, int col, const float (&v)[16]) {
     float m[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) m[i] = (row > col + i && seg_s[row] == seg_s[col + i]) ? -v[i] : 0.f;
