@@ -316,6 +316,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--only", default="all", choices=["all", "chunk", "decode"],
+                    help="profiling aid: run only the chunked fwd+bwd device loop, or only the decode loop")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
@@ -335,6 +337,13 @@ def main():
     peaks = measured_peaks()
     tokens = CFG["B"] * CFG["L"]
 
+    if args.only == "decode":
+        dj = DecodeJob(DEC, dev, seed=3000 + rank, heads=DEC["Hv"] // world)
+        ms_dec = time_steps(dj.step, args.steps, args.warmup, dist) / args.steps
+        if rank == 0:
+            print(json.dumps(dict(only="decode", us_per_step=ms_dec * 1e3,
+                                  state_gbs=world * dj.state_bytes / (ms_dec * 1e-3) / 1e9)), flush=True)
+        return
     # ---- device-resident throughput through the C ABI
     job = DeviceJob(CFG, dev, seed=1000 + rank)
     with ClockSampler(local) as clk:
@@ -343,6 +352,10 @@ def main():
     ms_step = ms / args.steps
     value = world * tokens / (ms_step * 1e-3)
 
+    if args.only == "chunk":
+        if rank == 0:
+            print(json.dumps(dict(only="chunk", ms_per_step=ms_step, tokens_per_s=value)), flush=True)
+        return
     # ---- per-kernel timing (each kernel alone, CUDA events on its stream) and the roofline of the slowest
     fl = alg_flops(CFG)
     items = CFG["B"] * job.ex.H * job.ex.NC
