@@ -7,5 +7,5 @@ NVCC="${NVCC:-/usr/local/cuda/bin/nvcc}"
 "$NVCC" -std=c++17 -O3 -lineinfo -gencode arch=compute_100a,code=sm_100a \
   --expt-extended-lambda -Xcompiler -fPIC -shared ${DN_PTXAS_V:+-Xptxas -v} \
   "$HERE"/dn_api.cu "$HERE"/dn_prepass_fwd.cu "$HERE"/dn_state.cu "$HERE"/dn_prepass_bwd.cu \
-  "$HERE"/dn_decode.cu "$HERE"/dn_misc.cu "$HERE"/dn_umma_selftest.cu "$HERE"/dn_state_tc.cu "$HERE"/dn_prepass_fwd_tc.cu "$HERE"/dn_prepass_bwd_tc.cu -o "$OUT"
+  "$HERE"/dn_decode.cu "$HERE"/dn_misc.cu "$HERE"/dn_umma_selftest.cu "$HERE"/dn_state_tc.cu "$HERE"/dn_prepass_fwd_tc.cu "$HERE"/dn_prepass_bwd_tc.cu "$HERE"/dn_noalloc.cu -o "$OUT"
 echo "built $OUT"

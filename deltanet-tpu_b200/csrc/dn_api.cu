@@ -21,6 +21,7 @@ const char* dn_status_string(int st) {
     case DN_ERR_SCRATCH_TOO_SMALL: return "scratch buffer too small (see dn_scratch_bytes)";
     case DN_ERR_CUDA_LAUNCH: return "a CUDA kernel launch failed";
     case DN_ERR_UNSUPPORTED: return "unsupported combination of options";
+    case DN_ERR_STATIC_SCRATCH_EXCEEDED: return "this shape needs more scratch than the built-in static array (see dn_static_scratch_bytes)";
     default: return "unknown status";
   }
 }

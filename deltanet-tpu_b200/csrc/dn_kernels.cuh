@@ -54,6 +54,7 @@ int launch_prepass_fwd(const Geo& g, const void* q, const void* k, const void* v
                        const void* b, const void* w, const int32_t* seg, const dn_residuals& res,
                        float* scratch, size_t scratch_floats, cudaStream_t st);
 bool prepass_fwd_tc_eligible(const Geo& g);
+size_t prepass_fwd_tc_scratch_per_cta();
 int launch_prepass_fwd_tc(const Geo& g, const void* q, const void* k, const void* v, const void* gg,
                           const void* b, const void* w, const int32_t* seg, const dn_residuals& res,
                           float* scratch, size_t scratch_floats, cudaStream_t st);

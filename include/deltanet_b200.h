@@ -65,7 +65,8 @@ enum {
   DN_ERR_NULL_POINTER = 3,   /* a required buffer is NULL                              */
   DN_ERR_SCRATCH_TOO_SMALL = 4,
   DN_ERR_CUDA_LAUNCH = 5,    /* cudaGetLastError() after a launch was not cudaSuccess  */
-  DN_ERR_UNSUPPORTED = 6
+  DN_ERR_UNSUPPORTED = 6,
+  DN_ERR_STATIC_SCRATCH_EXCEEDED = 7  /* dn_prepass_fwd_static: the shape needs more scratch than the built-in array */
 };
 
 typedef struct dn_shape {
@@ -168,6 +169,31 @@ int dn_prepass_bwd(const dn_shape* s, const void* q, const void* k, const void* 
                    const dn_residuals* res, const void* d_out, const float* dV, const float* dH,
                    void* dq, void* dk, void* dv, void* dg, void* db, void* dw,
                    void* scratch, size_t scratch_bytes, void* stream);
+
+/*
+ * Allocation-free forward prepass.  No counterpart in the reference.
+ *
+ * Same results as dn_prepass_fwd, for callers that cannot give the library a scratch buffer
+ * because they cannot allocate device memory where they call it: a runtime whose call handlers
+ * may not allocate and that was not asked for scratch when the call was built, a serving loop
+ * with a frozen memory plan, a sandboxed plugin without access to the CUDA allocator.  The
+ * scratch is a fixed array of dn_static_scratch_bytes() (32 MiB) inside the library image; every
+ * GPU that loads the library holds it until the process exits.  The function calls no cudaMalloc,
+ * cudaFree or other allocating routine.
+ *
+ *  - Shapes whose prepass needs more scratch than the array return DN_ERR_STATIC_SCRATCH_EXCEEDED
+ *    (the tensor-core path, bf16 precision with chunk = K = 128, needs 9.3 MiB and always fits;
+ *    the fp32 path fits for chunk = K = V = 64).
+ *  - The first call on each device looks up the array's device address (with that device
+ *    current).  Make that first call outside any stream capture.
+ *  - All calls share the one array and it keeps the previous call's contents.  Nothing in it has
+ *    to start at zero (every word is written before it is read within a call), but two calls that
+ *    overlap on the GPU -- different streams, or different host threads -- race on it: serialise them.
+ */
+size_t dn_static_scratch_bytes(void);
+int dn_prepass_fwd_static(const dn_shape* s, const void* q, const void* k, const void* v,
+                          const void* g, const void* b, const void* w, const int32_t* seg,
+                          const dn_residuals* res, void* stream);
 
 /* ---- decode ------------------------------------------------------------------------------ */
 typedef struct dn_decode_shape {
