@@ -77,22 +77,22 @@ __device__ __forceinline__ int dec_gate_head(int hv, int nheads, int Hk, int Hv)
   return hv / (Hv / Hk);
 }
 
-template <typename SI, typename SO, int KD>
-__global__ void __launch_bounds__(DEC_THREADS) decode_kernel(DecodeArgs a) {
+template <typename SI, typename SO, int KD, int DVT = DV, int NTH = DEC_THREADS>
+__global__ void __launch_bounds__(NTH) decode_kernel(DecodeArgs a) {
   constexpr int CPT = Vec16<SI>::N;        // columns per thread
-  constexpr int VC = DV / CPT;             // vector columns per row slab
-  constexpr int RG = DEC_THREADS / VC;     // row groups
+  constexpr int VC = DVT / CPT;             // vector columns per row slab
+  constexpr int RG = NTH / VC;     // row groups
   constexpr int R = KD / RG;               // rows per thread
   const dn_decode_shape& s = a.s;
   const int V = s.V;
-  const int nslab = V / DV;
+  const int nslab = V / DVT;
   const int slab = blockIdx.x % nslab, hv = (blockIdx.x / nslab) % s.Hv, b = blockIdx.x / (nslab * s.Hv);
   const int tid = threadIdx.x, vc = tid % VC, rg = tid / VC;
-  const int col0 = slab * DV + vc * CPT;
+  const int col0 = slab * DVT + vc * CPT;
 
   __shared__ float qs[KD], ks[KD], dec[KD], beta[KD];
-  __shared__ float red[RG][DV + 4];
-  __shared__ float vnew[DV], wvs[DV], nrm[2];
+  __shared__ float red[RG][DVT + 4];
+  __shared__ float vnew[DVT], wvs[DVT], nrm[2];
 
   // ---- state loads first: they are the long-latency part
   const size_t sbase = ((size_t)b * s.Hv + hv) * KD * V;
@@ -130,8 +130,8 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_kernel(DecodeArgs a) {
       if (wq == 0) qs[lane + 32 * u] = x[u] * r * s.scale;
       else ks[lane + 32 * u] = x[u] * r;
     }
-  } else if (tid < 64 + DV) {
-    const int j = tid - 64, cv = slab * DV + j;
+  } else if (tid < 64 + DVT) {
+    const int j = tid - 64, cv = slab * DVT + j;
     const float vv = ldf(a.v, ((size_t)b * s.Hv + hv) * V + cv, s.qkv_dtype);
     const int hw = dec_gate_head(hv, s.w_heads, s.Hk, s.Hv);
     const float ww = ldf(a.w, ((size_t)b * s.w_heads + hw) * s.w_cols + (s.w_cols == 1 ? 0 : cv), s.gate_dtype);
@@ -166,7 +166,7 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_kernel(DecodeArgs a) {
 #pragma unroll
   for (int c = 0; c < CPT; ++c) red[rg][vc * CPT + c] = part[c];
   __syncthreads();
-  if (tid < DV) {
+  if (tid < DVT) {
     float e = 0.f;
 #pragma unroll
     for (int r = 0; r < RG; ++r) e += red[r][tid];
@@ -193,11 +193,11 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_kernel(DecodeArgs a) {
 #pragma unroll
   for (int c = 0; c < CPT; ++c) red[rg][vc * CPT + c] = part[c];
   __syncthreads();
-  if (tid < DV) {
+  if (tid < DVT) {
     float o = 0.f;
 #pragma unroll
     for (int r = 0; r < RG; ++r) o += red[r][tid];
-    stf(a.out, ((size_t)b * s.Hv + hv) * V + slab * DV + tid, o, s.qkv_dtype);
+    stf(a.out, ((size_t)b * s.Hv + hv) * V + slab * DVT + tid, o, s.qkv_dtype);
   }
   (void)sq; (void)nrm;
   // ---- state out
