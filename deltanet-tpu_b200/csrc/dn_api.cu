@@ -142,7 +142,7 @@ int dn_state_fwd(const dn_shape* s, const dn_residuals* res, const int32_t* seg,
   Geo g;
   int rc = make_geo(s, &g);
   if (rc) return rc;
-  if (!res || !out) return DN_ERR_NULL_POINTER;
+  if (!res || (!out && !final_state && !res->states)) return DN_ERR_NULL_POINTER;
   if ((g.flags & DN_HAS_INIT) && !init_state) return DN_ERR_NULL_POINTER;
   StateArgs a{};
   a.g = g; a.res = *res; a.seg = seg; a.init_state = (g.flags & DN_HAS_INIT) ? init_state : nullptr;
@@ -285,6 +285,32 @@ int dn_chunk_bwd(const dn_shape* s, const void* q, const void* k, const void* v,
   if ((rc = dn_state_bwd(s, res, seg, d_out, d_final_state, dV, dH, d_init, stream))) return rc;
   return run_prepass_bwd(g, q, k, v, g_, b, w, seg, *res, d_out, dV, dH, dq, dk, dv, dg, db, dw,
                          p, (size_t)(end - p), st);
+}
+
+// ---- sequence-parallel helpers ------------------------------------------------------------------
+// Transition matrix of a shard: the map S_in -> S_out of the state pass is affine, S_out = P S_in + Q
+// with P (K x K) per (batch, exec head).  P is the state pass run on K "value" columns with U = 0
+// and S_in = I, because the recurrence acts on every value column independently.
+int dn_sp_transition(const dn_shape* s, const dn_residuals* res, const int32_t* seg,
+                     const float* identity, float* P, void* stream) {
+  Geo g;
+  int rc = make_geo(s, &g);
+  if (rc) return rc;
+  if (!res || !identity || !P) return DN_ERR_NULL_POINTER;
+  Geo t = g;                       // same chunks and heads, value width K, one "value head" per exec head
+  t.Hv = g.H; t.G = 1; t.V = g.K; t.Vw = g.K; t.qk_div = 1;
+  t.flags |= DN_HAS_INIT;
+  StateArgs a{};
+  a.g = t; a.res = *res; a.res.U = nullptr; a.res.states = nullptr; a.seg = seg;
+  a.init_state = identity; a.final_state = P;
+  return launch_state_fwd(a, (cudaStream_t)stream);
+}
+
+int dn_sp_apply(const float* P, const float* S_in, const float* Q, float* S_out, int32_t B, int32_t H,
+                int32_t G, int32_t K, int32_t V, int32_t transpose, void* stream) {
+  if (!P || !S_in || !S_out) return DN_ERR_NULL_POINTER;
+  if (B < 1 || H < 1 || G < 1 || K < 1 || V < 1) return DN_ERR_BAD_SHAPE;
+  return launch_sp_apply(P, S_in, Q, S_out, B, H, G, K, V, transpose, (cudaStream_t)stream);
 }
 
 int dn_decode_step(const dn_decode_shape* s, const void* q, const void* k, const void* v,

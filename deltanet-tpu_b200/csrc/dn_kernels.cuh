@@ -76,6 +76,9 @@ int launch_canonical_segments(const int32_t* raw, const int32_t* first_is_new, i
 // sums `groups` consecutive heads: in (rows, heads_out*groups, cols) f32 -> out (rows, heads_out, cols)
 int launch_group_sum(const float* in, void* out, int out_dt, size_t rows, int heads_out, int groups,
                      int cols, cudaStream_t st);
+// S_out[b, h*G+g] = op(P[b,h]) S_in[b, h*G+g] (+ Q); op = transpose when asked.  P (B,H,K,K), states (B,H*G,K,V).
+int launch_sp_apply(const float* P, const float* S_in, const float* Q, float* S_out, int B, int H, int G,
+                    int K, int V, int transpose, cudaStream_t st);
 int launch_decode(const dn_decode_shape& s, const void* q, const void* k, const void* v,
                   const void* g, const void* b, const void* w, const void* state_in,
                   const uint8_t* reset, void* out, void* state_out, cudaStream_t st);

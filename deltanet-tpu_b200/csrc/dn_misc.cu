@@ -65,4 +65,28 @@ int launch_group_sum(const float* in, void* out, int out_dt, size_t rows, int he
   return cudaGetLastError() == cudaSuccess ? DN_OK : DN_ERR_CUDA_LAUNCH;
 }
 
+// One CTA per (batch, value head): S_out = op(P) S_in + Q with the CTA-wide fp32 GEMM.
+__global__ void __launch_bounds__(DN_THREADS) sp_apply_kernel(const float* P, const float* S_in, const float* Q,
+                                                              float* S_out, int H, int G, int K, int V, int transpose) {
+  __shared__ __align__(16) float tile[GEMM_SMEM_FLOATS];
+  const int hv = blockIdx.x % (H * G), b = blockIdx.x / (H * G), h = hv / G;
+  const float* p = P + ((size_t)b * H + h) * K * K;
+  const size_t so = ((size_t)b * H * G + hv) * K * V;
+  const float* si = S_in + so;
+  const float* q = Q ? Q + so : nullptr;
+  float* o = S_out + so;
+  if (transpose)
+    cta_gemm<false, true>(K, V, K, [&](int i, int kk) { return p[kk * K + i]; }, [&](int kk, int j) { return si[kk * V + j]; },
+                          [&](int i, int j, float acc) { o[i * V + j] = acc + (q ? q[i * V + j] : 0.f); }, tile);
+  else
+    cta_gemm<true, true>(K, V, K, [&](int i, int kk) { return p[i * K + kk]; }, [&](int kk, int j) { return si[kk * V + j]; },
+                         [&](int i, int j, float acc) { o[i * V + j] = acc + (q ? q[i * V + j] : 0.f); }, tile);
+}
+
+int launch_sp_apply(const float* P, const float* S_in, const float* Q, float* S_out, int B, int H, int G,
+                    int K, int V, int transpose, cudaStream_t st) {
+  sp_apply_kernel<<<B * H * G, DN_THREADS, 0, st>>>(P, S_in, Q, S_out, H, G, K, V, transpose);
+  return cudaGetLastError() == cudaSuccess ? DN_OK : DN_ERR_CUDA_LAUNCH;
+}
+
 }  // namespace dn

@@ -59,7 +59,10 @@ __global__ void __launch_bounds__(DN_THREADS) state_fwd_kernel(StateArgs a) {
     cta_gemm<true, true>(C, VS, K,
         [&](int i, int kk) { return ldf(a.res.W, bW + (size_t)i * K + kk, pre); },
         [&](int kk, int j) { float s = S[kk * VS + j]; return sbf ? bf16r(s) : s; },
-        [&](int i, int j, float acc) { Vn[i * VS + j] = ldf(a.res.U, bU + (size_t)i * Vw + v0 + j, pre) - acc; },
+        [&](int i, int j, float acc) {
+          const float u = a.res.U ? ldf(a.res.U, bU + (size_t)i * Vw + v0 + j, pre) : 0.f;   // U == NULL: transition pass
+          Vn[i * VS + j] = u - acc;
+        },
         tile);
     if (WITH_OUT) {
       // O = [qe | M] [S ; V_new]

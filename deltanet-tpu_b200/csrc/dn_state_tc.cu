@@ -136,10 +136,13 @@ __global__ void __launch_bounds__(128, 1) state_fwd_tc_kernel(StateArgs a) {
     }
     stage_rows<VS>(sS, row, S);
     uint4 ureg[VS / 8];
-    {
+    if (Ug) {
       const uint4* up = reinterpret_cast<const uint4*>(Ug + item * C * Vw + (size_t)row * Vw + v0);
 #pragma unroll
       for (int p = 0; p < VS / 8; ++p) ureg[p] = up[p];
+    } else {                                            // U == NULL: transition pass (U = 0)
+#pragma unroll
+      for (int p = 0; p < VS / 8; ++p) ureg[p] = make_uint4(0, 0, 0, 0);
     }
     const float dec = all_same ? expf(fminf(a.res.lam_end[item * K + row], 0.f)) : 0.f;
 

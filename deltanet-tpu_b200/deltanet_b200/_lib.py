@@ -62,6 +62,8 @@ _SIGNATURES = {
     "dn_state_bwd": (C.c_int, [C.POINTER(Shape), C.POINTER(Residuals)] + [_P] * 7),
     "dn_prepass_bwd": (C.c_int, [C.POINTER(Shape)] + [_P] * 7 + [C.POINTER(Residuals)] + [_P] * 9 + [_P, C.c_size_t, _P]),
     "dn_decode_step": (C.c_int, [C.POINTER(DecodeShape)] + [_P] * 11),
+    "dn_sp_transition": (C.c_int, [C.POINTER(Shape), C.POINTER(Residuals)] + [_P] * 4),
+    "dn_sp_apply": (C.c_int, [_P] * 4 + [C.c_int32] * 6 + [_P]),
     "dn_static_scratch_bytes": (C.c_size_t, []),
     "dn_prepass_fwd_static": (C.c_int, [C.POINTER(Shape)] + [_P] * 7 + [C.POINTER(Residuals), _P]),
     "dn_selftest_umma": (C.c_int, [C.c_int32] * 4 + [_P] * 5),

@@ -1,0 +1,303 @@
+"""Sequence-parallel chunk_gdn2: one contiguous shard of a long packed sequence per rank.
+
+The reference has no sequence-parallel implementation; it provides the hooks
+(``initial_state`` / ``output_final_state`` / ``initial_state_segment_id``,
+``src/deltanet_tpu/gdn2.py:2081-2085``).  Chaining those serially would make every rank wait for
+the whole state pass of its predecessor.  Instead the chain only carries small states:
+
+  forward   1. every rank: prepass + state pass from a zero state  -> Q (its final state) and
+               the transition matrix P (the state pass is affine: S_out = P S_in + Q);
+            2. chain: rank r receives S_in from r-1, sends P S_in + Q to r+1 (zeroed where the
+               next shard starts a new document);
+            3. every rank: state pass again from its true S_in (outputs, chunk states).
+  backward  the mirror image with the state cotangent: a reverse pass with zero incoming
+            cotangent gives d_init0, the chain carries d_S_in = P^T d_final + d_init0 from rank
+            r to r-1, and a second reverse pass with the true d_final feeds the chunk-parallel
+            backward.
+
+The per-shard arithmetic is behind an ``ops`` object: ``CudaOps`` (the C-ABI kernels) on GPUs;
+tests substitute CPU ops to exercise the chain logic with the gloo backend.  Point-to-point
+transfers use ``torch.distributed`` (NCCL over NVLink on a B200 box); the received state always
+lands in a local buffer before any kernel reads it.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from . import _lib as L
+from . import gdn2 as _g
+
+
+# --------------------------------------------------------------------------------- chain helpers
+class Chain:
+    """Neighbour transfers along the sequence: rank r-1 <- r -> r+1."""
+
+    def __init__(self, group=None):
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.size = dist.get_world_size(group)
+
+    def _peer(self, r):
+        return dist.get_global_rank(self.group, r) if self.group is not None else r
+
+    def forward(self, first_value, step):
+        """first_value on rank 0, else what rank-1 sent; returns (received, produced); sends produced on."""
+        x = first_value
+        if self.rank > 0:
+            x = torch.empty_like(first_value)
+            dist.recv(x, src=self._peer(self.rank - 1), group=self.group)
+        y = step(x)
+        if self.rank < self.size - 1:
+            dist.send(y.contiguous(), dst=self._peer(self.rank + 1), group=self.group)
+        return x, y
+
+    def backward(self, last_value, step):
+        x = last_value
+        if self.rank < self.size - 1:
+            x = torch.empty_like(last_value)
+            dist.recv(x, src=self._peer(self.rank + 1), group=self.group)
+        y = step(x)
+        if self.rank > 0:
+            dist.send(y.contiguous(), dst=self._peer(self.rank - 1), group=self.group)
+        return x, y
+
+    def gather_edges(self, edges):
+        """all ranks' (B,2) [first raw id, last raw id] -> list indexed by rank (control metadata)."""
+        out = [torch.empty_like(edges) for _ in range(self.size)]
+        dist.all_gather(out, edges, group=self.group)
+        return out
+
+
+class LocalChain:
+    """The same neighbour transfers between threads of ONE process (tests on a single device).
+
+    Build the set with ``LocalChain.make(n)`` and run each rank's call in its own host thread; only
+    host threads wait on each other, kernels never do.
+    """
+
+    def __init__(self, rank, size, shared):
+        self.rank, self.size, self._s = rank, size, shared
+
+    @staticmethod
+    def make(n):
+        import queue
+        import threading
+        shared = dict(fwd=[queue.Queue() for _ in range(n)], bwd=[queue.Queue() for _ in range(n)],
+                      edges=[None] * n, barrier=threading.Barrier(n))
+        return [LocalChain(r, n, shared) for r in range(n)]
+
+    def forward(self, first_value, step):
+        x = first_value if self.rank == 0 else self._s["fwd"][self.rank].get(timeout=120)
+        y = step(x)
+        if self.rank < self.size - 1:
+            self._s["fwd"][self.rank + 1].put(y.clone())
+        return x, y
+
+    def backward(self, last_value, step):
+        x = last_value if self.rank == self.size - 1 else self._s["bwd"][self.rank].get(timeout=120)
+        y = step(x)
+        if self.rank > 0:
+            self._s["bwd"][self.rank - 1].put(y.clone())
+        return x, y
+
+    def gather_edges(self, edges):
+        self._s["edges"][self.rank] = edges
+        self._s["barrier"].wait(timeout=120)
+        return list(self._s["edges"])
+
+
+def continues_from_previous(edges_prev, edges_mine):
+    """(B,) bool: this shard's first token belongs to the same document as the previous shard's last."""
+    return edges_prev[:, 1] == edges_mine[:, 0]
+
+
+# --------------------------------------------------------------------------------- CUDA shard ops
+class CudaOps:
+    """Per-shard work through the C-ABI phase entry points (no torch arithmetic on the path)."""
+
+    def __init__(self, *, chunk_size=128, precision="bf16", scale=None, qk_l2norm=False, fuse_prologue=False):
+        self.chunk, self.precision, self.scale = chunk_size, precision, scale
+        self.l2, self.fuse = qk_l2norm, fuse_prologue
+
+    # -- forward
+    def prepare(self, q, k, v, g, b, w, seg_raw):
+        lib = L.lib()
+        B, Lq, Hk, K = q.shape
+        Hv, V = v.shape[2], v.shape[3]
+        qkv_dt, gate_dt = _g._common_dtype((q, k, v)), _g._common_dtype((g, b, w))
+        q, k, v = (t.to(qkv_dt).contiguous() for t in (q, k, v))
+        g, b, w = (t.to(gate_dt).contiguous() for t in (g, b, w))
+        gh, gc = _g._gate_layout(g, K)
+        bh, bc = _g._gate_layout(b, K)
+        wh, wc = _g._gate_layout(w, V)
+        flags = (L.DN_QK_L2NORM if self.l2 else 0) | (L.DN_FUSE_PROLOGUE if self.fuse else 0) | L.DN_HAS_INIT
+        scale = self.scale if self.scale is not None else K ** -0.5
+        shape = L.Shape(B=B, L=Lq, Hk=Hk, Hv=Hv, K=K, V=V, chunk=self.chunk, g_heads=gh, g_cols=gc, b_heads=bh,
+                        b_cols=bc, w_heads=wh, w_cols=wc, qkv_dtype=_g._DT[qkv_dt], gate_dtype=_g._DT[gate_dt],
+                        precision=_g._precision_code(self.precision), flags=flags, scale=float(scale))
+        ex = L.Exec()
+        L.check(lib.dn_exec_view(shape, ex), "dn_exec_view")
+        seg = torch.empty(B, Lq, dtype=torch.int32, device=q.device)
+        raw = seg_raw.to(device=q.device, dtype=torch.int32).contiguous()
+        L.check(lib.dn_canonical_segments(raw.data_ptr(), None, seg.data_ptr(), B, Lq, _g._stream()), "segments")
+        block = torch.empty(lib.dn_residual_bytes(shape), dtype=torch.uint8, device=q.device)
+        res = L.Residuals()
+        L.check(lib.dn_residual_carve(shape, block.data_ptr(), res), "carve")
+        n = max(lib.dn_scratch_bytes(shape, 0, 0), lib.dn_scratch_bytes(shape, 1, 0))
+        scratch = torch.empty(n, dtype=torch.uint8, device=q.device)
+        L.check(lib.dn_prepass_fwd(shape, q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), b.data_ptr(),
+                                   w.data_ptr(), seg.data_ptr(), res, scratch.data_ptr(), n, _g._stream()),
+                "dn_prepass_fwd")
+        return dict(shape=shape, ex=ex, res=res, block=block, scratch=scratch, seg=seg, ins=(q, k, v, g, b, w),
+                    dims=(B, Lq, Hk, Hv, K, V))
+
+    def summary(self, c):
+        lib = L.lib()
+        B, Lq, Hk, Hv, K, V = c["dims"]
+        dev = c["seg"].device
+        H = c["ex"].H
+        zero = torch.zeros(B, Hv, K, V, device=dev)
+        Q = torch.empty(B, Hv, K, V, device=dev)
+        states_ptr, c["res"].states = c["res"].states, None          # no chunk states from this pass
+        L.check(lib.dn_state_fwd(c["shape"], c["res"], c["seg"].data_ptr(), zero.data_ptr(), None, Q.data_ptr(),
+                                 _g._stream()), "dn_state_fwd (Q)")
+        eye = torch.eye(K, device=dev).expand(B, H, K, K).contiguous()
+        P = torch.empty(B, H, K, K, device=dev)
+        L.check(lib.dn_sp_transition(c["shape"], c["res"], c["seg"].data_ptr(), eye.data_ptr(), P.data_ptr(),
+                                     _g._stream()), "dn_sp_transition")
+        c["res"].states = states_ptr
+        return P, Q
+
+    def apply(self, c, P, S_in, Q, transpose=False):
+        B, Lq, Hk, Hv, K, V = c["dims"]
+        H = c["ex"].H
+        out = torch.empty_like(S_in)
+        L.check(L.lib().dn_sp_apply(P.data_ptr(), S_in.contiguous().data_ptr(), None if Q is None else Q.data_ptr(),
+                                    out.data_ptr(), B, H, Hv // H, K, V, 1 if transpose else 0, _g._stream()),
+                "dn_sp_apply")
+        return out
+
+    def finish(self, c, S_in):
+        lib = L.lib()
+        B, Lq, Hk, Hv, K, V = c["dims"]
+        q = c["ins"][0]
+        out = torch.empty(B, Lq, Hv, V, dtype=c["ins"][2].dtype, device=q.device)
+        final = torch.empty(B, Hv, K, V, device=q.device)
+        c["S_in"] = S_in.contiguous()
+        L.check(lib.dn_state_fwd(c["shape"], c["res"], c["seg"].data_ptr(), c["S_in"].data_ptr(), out.data_ptr(),
+                                 final.data_ptr(), _g._stream()), "dn_state_fwd")
+        return out, final
+
+    # -- backward
+    def _chain_bwd(self, c, d_out, d_final):
+        lib = L.lib()
+        B, Lq, Hk, Hv, K, V = c["dims"]
+        ex, dev = c["ex"], d_out.device
+        items = B * ex.H * ex.NC
+        dV = torch.empty(items * self.chunk * ex.Vw, device=dev)
+        dH = torch.empty(items * K * ex.Vw, device=dev)
+        d_init = torch.empty(B, Hv, K, V, device=dev)
+        L.check(lib.dn_state_bwd(c["shape"], c["res"], c["seg"].data_ptr(), d_out.data_ptr(),
+                                 None if d_final is None else d_final.contiguous().data_ptr(), dV.data_ptr(),
+                                 dH.data_ptr(), d_init.data_ptr(), _g._stream()), "dn_state_bwd")
+        return dV, dH, d_init
+
+    def bwd_summary(self, c, d_out):
+        c["d_out"] = d_out.to(c["ins"][2].dtype).contiguous()
+        return self._chain_bwd(c, c["d_out"], None)[2]
+
+    def bwd_finish(self, c, d_final):
+        lib = L.lib()
+        q, k, v, g, b, w = c["ins"]
+        dV, dH, d_init = self._chain_bwd(c, c["d_out"], d_final)
+        grads = [torch.empty_like(t) for t in (q, k, v, g, b, w)]
+        sc = c["scratch"]
+        L.check(lib.dn_prepass_bwd(c["shape"], q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), b.data_ptr(),
+                                   w.data_ptr(), c["seg"].data_ptr(), c["res"], c["d_out"].data_ptr(), dV.data_ptr(),
+                                   dH.data_ptr(), *[t.data_ptr() for t in grads], sc.data_ptr(), sc.numel(),
+                                   _g._stream()), "dn_prepass_bwd")
+        return grads
+
+
+# --------------------------------------------------------------------------------- the sharded op
+def shard_edges(seg_raw):
+    return torch.stack([seg_raw[:, 0], seg_raw[:, -1]], dim=1).to(torch.int32).contiguous()
+
+
+def sp_forward(ops, chain, tensors, seg_raw, initial_state):
+    """Runs the three forward steps on this rank.  Returns (out, final_state, saved context)."""
+    q, k, v, g, b, w = tensors
+    B, Hv, K, V = q.shape[0], v.shape[2], q.shape[3], v.shape[3]
+    c = ops.prepare(q, k, v, g, b, w, seg_raw)
+    P, Q = ops.summary(c)
+    edges = chain.gather_edges(shard_edges(seg_raw).to(q.device))
+    r = chain.rank
+    cont_in = continues_from_previous(edges[r - 1], edges[r]) if r > 0 else torch.ones(B, dtype=torch.bool, device=q.device)
+    cont_out = continues_from_previous(edges[r], edges[r + 1]) if r < chain.size - 1 else None
+    first = initial_state if initial_state is not None else torch.zeros(B, Hv, K, V, device=q.device)
+
+    def step(S_in):
+        S_out = ops.apply(c, P, S_in, Q)
+        if cont_out is not None:                      # what the next shard may keep of it
+            S_out = S_out * cont_out.view(B, 1, 1, 1).to(S_out.dtype)
+        return S_out
+
+    S_in, _ = chain.forward(first.float().contiguous(), step)
+    out, final = ops.finish(c, S_in)
+    c.update(P=P, cont_in=cont_in, cont_out=cont_out)
+    return out, final, c
+
+
+def sp_backward(ops, chain, c, d_out, d_final_state):
+    """Mirror of sp_forward for the cotangents; returns (grads of q,k,v,g,b,w, d_initial_state)."""
+    B = d_out.shape[0]
+    d_init0 = ops.bwd_summary(c, d_out)
+    last = d_final_state if d_final_state is not None else torch.zeros_like(d_init0)
+
+    def step(d_final):
+        d_in = ops.apply(c, c["P"], d_final, d_init0, transpose=True)      # P^T d_final + d_init0
+        if chain.rank > 0:                                                  # previous shard's state was dropped
+            d_in = d_in * c["cont_in"].view(B, 1, 1, 1).to(d_in.dtype)      # where this shard starts a document
+        return d_in
+
+    d_final, d_in = chain.backward(last.float().contiguous(), step)
+    grads = ops.bwd_finish(c, d_final)
+    return grads, d_in
+
+
+class _SPFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, ops, chain, seg_raw, q, k, v, g, b, w, initial_state):
+        out, final, c = sp_forward(ops, chain, (q, k, v, g, b, w), seg_raw, initial_state)
+        ctx.ops, ctx.chain, ctx.c = ops, chain, c
+        ctx.has_init = initial_state is not None
+        ctx.set_materialize_grads(False)
+        return out, final
+
+    @staticmethod
+    def backward(ctx, d_out, d_final):
+        c = ctx.c
+        if d_out is None:
+            B, Lq, Hk, Hv, K, V = c["dims"]
+            d_out = torch.zeros(B, Lq, Hv, V, device=c["seg"].device)
+        (dq, dk, dv, dg, db, dw), d_in = sp_backward(ctx.ops, ctx.chain, c, d_out, d_final)
+        return None, None, None, dq, dk, dv, dg, db, dw, (d_in if ctx.has_init else None)
+
+
+def chunk_gdn2_sp(q, k, v, g, b, w, *, segment_ids: torch.Tensor, initial_state: Optional[torch.Tensor] = None,
+                  group=None, chunk_size: int = 128, precision: str = "bf16", scale: Optional[float] = None,
+                  qk_l2norm: bool = False, fuse_prologue: bool = False, ops=None, chain=None):
+    """chunk_gdn2 on this rank's contiguous shard of a packed sequence split over the ranks of ``group``.
+
+    ``segment_ids`` (B, L_shard) are the GLOBAL document ids of the shard's tokens (any change of id is
+    a boundary, also across shards).  ``initial_state`` is used on the first rank only.  Returns
+    ``(out, final_state)``; ``final_state`` is the state after this shard (the sequence's final state on
+    the last rank).  Differentiable: backward runs the reverse chain, so every rank must take part.
+    """
+    ops = ops or CudaOps(chunk_size=chunk_size, precision=precision, scale=scale, qk_l2norm=qk_l2norm,
+                         fuse_prologue=fuse_prologue)
+    chain = chain or Chain(group)
+    return _SPFunction.apply(ops, chain, segment_ids, q, k, v, g, b, w, initial_state)

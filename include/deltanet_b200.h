@@ -170,6 +170,23 @@ int dn_prepass_bwd(const dn_shape* s, const void* q, const void* k, const void* 
                    void* dq, void* dk, void* dv, void* dg, void* db, void* dw,
                    void* scratch, size_t scratch_bytes, void* stream);
 
+/* ---- sequence sharding --------------------------------------------------------------------
+ * The reference has no sequence-parallel implementation, only the hooks for one (initial_state,
+ * output_final_state and initial_state_segment_id, src/deltanet_tpu/gdn2.py:2081-2085; README
+ * "when a packed sequence is split across calls or chips").  These two entry points are what a
+ * sharded caller adds on top of the phases above.  The state pass of a shard is affine in the
+ * incoming state, S_out = P S_in + Q per (batch, exec head), with Q the final state from S_in = 0.
+ *
+ * dn_sp_transition: P (B,H,K,K) f32 of a shard whose prepass residuals are `res` (W, ke, lam_end are
+ *   read).  identity is a (B,H,K,K) f32 buffer holding the identity per head.
+ * dn_sp_apply: S_out[b,hv] = P[b,hv/G] S_in[b,hv] + Q[b,hv] (Q may be NULL), or with P transposed
+ *   (the adjoint, for the state cotangent).  States are (B, H*G, K, V) f32.
+ */
+int dn_sp_transition(const dn_shape* s, const dn_residuals* res, const int32_t* seg,
+                     const float* identity, float* P, void* stream);
+int dn_sp_apply(const float* P, const float* S_in, const float* Q, float* S_out, int32_t B, int32_t H,
+                int32_t G, int32_t K, int32_t V, int32_t transpose, void* stream);
+
 /*
  * Allocation-free forward prepass.  No counterpart in the reference.
  *

@@ -1,0 +1,117 @@
+"""Sequence-parallel chain logic on CPU: world_size-2 (and 3) gloo processes, with the per-shard
+arithmetic supplied by the CPU oracle, against the oracle on the unsplit sequence.  This exercises
+what is new in the sharded path -- the affine state chain, the document-continuation rule across
+shards and the reverse chain of the state cotangent -- without a GPU."""
+import os
+import socket
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from conftest import PKG_DIR, ROOT
+
+
+class OracleOps:
+    """CPU stand-in for the per-shard kernels, built on the oracle (one exec head per value head)."""
+
+    def __init__(self, chunk_size=64):
+        self.chunk = chunk_size
+
+    def _run(self, c, init, v=None, w=None):
+        from oracle import delta_oracle as O
+        q, k, vv, g, b, ww = c["leaves"]
+        return O.chunk_gdn2(q, k, vv if v is None else v, g, b, ww if w is None else w, segment_ids=c["seg"],
+                            initial_state=init, output_final_state=True, chunk_size=self.chunk, precision="fp32",
+                            qk_l2norm=True)
+
+    def prepare(self, q, k, v, g, b, w, seg_raw):
+        leaves = [t.detach().clone().requires_grad_() for t in (q, k, v, g, b, w)]
+        B, Lq, Hk, K = q.shape
+        return dict(leaves=leaves, seg=seg_raw, dims=(B, Lq, Hk, v.shape[2], K, v.shape[3]))
+
+    def summary(self, c):
+        B, Lq, Hk, Hv, K, V = c["dims"]
+        with torch.no_grad():
+            _, Q = self._run(c, torch.zeros(B, Hv, K, V))
+            zero_v = torch.zeros(B, Lq, Hv, K)
+            _, P = self._run(c, torch.eye(K).expand(B, Hv, K, K).contiguous(), v=zero_v, w=torch.ones(B, Lq, Hv, K))
+        return P, Q
+
+    def apply(self, c, P, S_in, Q, transpose=False):
+        out = torch.einsum("bhji,bhjv->bhiv" if transpose else "bhij,bhjv->bhiv", P, S_in)
+        return out if Q is None else out + Q
+
+    def finish(self, c, S_in):
+        c["S_in"] = S_in.detach().clone().requires_grad_()
+        with torch.enable_grad():                      # called from inside an autograd.Function forward
+            c["out"], c["final"] = self._run(c, c["S_in"])
+        return c["out"].detach(), c["final"].detach()
+
+    def bwd_summary(self, c, d_out):
+        c["d_out"] = d_out
+        return torch.autograd.grad(c["out"], c["S_in"], d_out, retain_graph=True)[0]
+
+    def bwd_finish(self, c, d_final):
+        return list(torch.autograd.grad([c["out"], c["final"]], c["leaves"], [c["d_out"], d_final]))
+
+
+def _inputs():
+    from oracle import delta_oracle as O
+    B, L, Hk, Hv, K, V = 2, 384, 1, 2, 64, 64
+    q, k, v, g, b, w = O.make_inputs(77, B, L, Hk, Hv, K, V, qkv_scale=0.5)
+    seg = torch.stack([torch.repeat_interleave(torch.tensor([0, 1, 2], dtype=torch.int32), torch.tensor([100, 156, 128])),
+                       torch.repeat_interleave(torch.tensor([5, 6], dtype=torch.int32), torch.tensor([256, 128]))])
+    init = torch.randn(B, Hv, K, V, generator=torch.Generator().manual_seed(3)) * 0.1
+    gen = torch.Generator().manual_seed(4)
+    do = torch.randn(B, L, Hv, V, generator=gen)
+    dfs = torch.randn(B, Hv, K, V, generator=gen) * 0.1
+    return (q, k, v, g, b, w), seg, init, do, dfs
+
+
+def _worker(rank, world, port, ret):
+    for p in (ROOT, PKG_DIR):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from deltanet_b200 import sp
+    ins, seg, init, do, dfs = _inputs()
+    L = ins[0].shape[1]
+    lo, hi = rank * L // world, (rank + 1) * L // world
+    shard = [t[:, lo:hi].contiguous().requires_grad_() for t in ins]
+    init_leaf = init.clone().requires_grad_()
+    out, final = sp.chunk_gdn2_sp(*shard, segment_ids=seg[:, lo:hi].contiguous(),
+                                  initial_state=init_leaf if rank == 0 else None, ops=OracleOps(), chain=sp.Chain())
+    loss = (out * do[:, lo:hi]).sum()
+    if rank == world - 1:
+        loss = loss + (final * dfs).sum()
+    grads = torch.autograd.grad(loss, shard + ([init_leaf] if rank == 0 else []))
+    ret[rank] = dict(out=out.detach(), final=final.detach(), grads=[x.detach() for x in grads])
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_sp_chain_matches_unsplit_oracle(world):
+    from oracle import delta_oracle as O
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ret = mp.Manager().dict()
+    mp.spawn(_worker, args=(world, port, ret), nprocs=world, join=True)
+    ins, seg, init, do, dfs = _inputs()
+    leaves = [t.clone().requires_grad_() for t in ins]
+    init_leaf = init.clone().requires_grad_()
+    o_ref, f_ref = O.chunk_gdn2(*leaves, segment_ids=seg, initial_state=init_leaf, output_final_state=True,
+                                chunk_size=64, precision="fp32", qk_l2norm=True)
+    g_ref = torch.autograd.grad((o_ref * do).sum() + (f_ref * dfs).sum(), leaves + [init_leaf])
+    out = torch.cat([ret[r]["out"] for r in range(world)], 1)
+    assert O.rel_l2(out, o_ref) < 1e-5
+    assert O.rel_l2(ret[world - 1]["final"], f_ref) < 1e-5
+    for i in range(6):
+        got = torch.cat([ret[r]["grads"][i] for r in range(world)], 1)
+        assert O.rel_l2(got, g_ref[i]) < 1e-4, i
+    assert O.rel_l2(ret[0]["grads"][6], g_ref[6]) < 1e-4
