@@ -172,63 +172,58 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
       __syncthreads();
     }
 
-    // ---- D. diagonal 16x16 blocks, exact: one thread per (block, channel); two sweeps (row side,
-    //         then column side) to keep the register footprint down
+    // ---- D. diagonal 16x16 blocks, exact: one thread per (block, channel).  Row side first
+    //         (dbeta'_i, dq'_i: one output row at a time, inner loop over the earlier rows j), then
+    //         the column side (dk'_j, inner loop over the later rows i).
     for (int task = tid; task < 8 * K; task += NT) {
       const int r0 = (task >> 7) * 16, c = task & 127;
-      float lam[16], kh[16], u0[16], u1[16];
+      float lam[16], kh[16], be[16], qh[16];
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
         const int x = r0 + i;
         lam[i] = LAM[x * LP + c] * DN_LOG2E;
-        float kv = 0.f;
+        float kv = 0.f, qv = 0.f, bv = 0.f;
         if (x < r.rows_valid) {
           kv = ldf(r.k, r.qk_row0 + (size_t)x * r.qk_pitch + c, r.qkv_dt);
-          if (l2) { kv *= rk_s[x]; if (r.round_in) kv = bf16r(kv); }
-        }
-        kh[i] = kv;
-        u0[i] = u1[i] = 0.f;
-      }
-#pragma unroll
-      for (int i = 1; i < 16; ++i) {
-#pragma unroll
-        for (int j = 0; j < i; ++j) {
-          const float ek = exp2f(fminf(lam[i] - lam[j], 0.f)) * kh[j];
-          u0[i] = fmaf(DA[(r0 + i) * C + r0 + j], ek, u0[i]);       // dbeta'
-          u1[i] = fmaf(DM[(r0 + i) * C + r0 + j], ek, u1[i]);       // dq'
-        }
-      }
-#pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        DBP[(r0 + i) * K + c] += u0[i];
-        DQP[(r0 + i) * K + c] += u1[i];
-      }
-      // column side: dk'_j += (dA_ij beta_i + dM_ij q_i) exp(Lam_i - Lam_j); kh -> beta, u0 -> q_hat
-#pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const int x = r0 + i;
-        float qv = 0.f, bv = 0.f;
-        if (x < r.rows_valid) {
           qv = ldf(r.q, r.qk_row0 + (size_t)x * r.qk_pitch + c, r.qkv_dt);
           bv = ldf(r.b, r.b_row0 + (size_t)x * r.b_pitch + (r.bC == 1 ? 0 : c), r.gate_dt);
+          if (l2) { kv *= rk_s[x]; if (r.round_in) kv = bf16r(kv); }
           qv = (qv * rq_s[x]) * r.scale;
           if (r.round_in) qv = bf16r(qv);
           if (fuse) bv = 1.f / (1.f + expf(-bv));
         }
-        kh[i] *= bv;
-        u0[i] = qv;
-        u1[i] = 0.f;
+        kh[i] = kv; qh[i] = qv; be[i] = bv * kv;
       }
-#pragma unroll
+#pragma unroll 1
       for (int i = 1; i < 16; ++i) {
+        const float li = LAM[(r0 + i) * LP + c] * DN_LOG2E;
+        const float* da = DA + (r0 + i) * C + r0;
+        const float* dm = DM + (r0 + i) * C + r0;
+        float sb = 0.f, sq = 0.f;
 #pragma unroll
-        for (int j = 0; j < i; ++j) {
-          const float e = exp2f(fminf(lam[i] - lam[j], 0.f));
-          u1[j] = fmaf(fmaf(DA[(r0 + i) * C + r0 + j], kh[i], DM[(r0 + i) * C + r0 + j] * u0[i]), e, u1[j]);
+        for (int j = 0; j < 15; ++j) {
+          if (j < i) {
+            const float ek = exp2f(fminf(li - lam[j], 0.f)) * kh[j];
+            sb = fmaf(da[j], ek, sb);
+            sq = fmaf(dm[j], ek, sq);
+          }
         }
+        DBP[(r0 + i) * K + c] += sb;
+        DQP[(r0 + i) * K + c] += sq;
       }
+#pragma unroll 1
+      for (int j = 0; j < 15; ++j) {
+        const float lj = LAM[(r0 + j) * LP + c] * DN_LOG2E;
+        float sk = 0.f;
 #pragma unroll
-      for (int i = 0; i < 16; ++i) DKP[(r0 + i) * K + c] += u1[i];
+        for (int i = 1; i < 16; ++i) {
+          if (i > j) {
+            const float e = exp2f(fminf(lam[i] - lj, 0.f));
+            sk = fmaf(fmaf(DA[(r0 + i) * C + r0 + j], be[i], DM[(r0 + i) * C + r0 + j] * qh[i]), e, sk);
+          }
+        }
+        DKP[(r0 + j) * K + c] += sk;
+      }
     }
     __syncthreads();
 
