@@ -70,6 +70,11 @@ __device__ __forceinline__ float ldf(const void* p, size_t i, int dt) {
   return dt == DN_BF16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i])
                        : reinterpret_cast<const float*>(p)[i];
 }
+// the same load through the read-only path: only for data no thread of the running kernel writes
+__device__ __forceinline__ float ldf_ro(const void* p, size_t i, int dt) {
+  return dt == DN_BF16 ? __bfloat162float(__ldg(reinterpret_cast<const __nv_bfloat16*>(p) + i))
+                       : __ldg(reinterpret_cast<const float*>(p) + i);
+}
 __device__ __forceinline__ void stf(void* p, size_t i, float v, int dt) {
   if (dt == DN_BF16) reinterpret_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v);
   else reinterpret_cast<float*>(p)[i] = v;

@@ -16,24 +16,18 @@
 //  * all clamps exp(min(x,0)) are inactive by construction (the cumulative decay is
 //    monotone inside a document), so their subgradients are 1.
 #include "dn_kernels.cuh"
-#include "dn_prepass_bwd_tc.cuh"
 
 namespace dn {
 
 
-// TCW == 0: fp32 SIMT products.  TCW == 128 / 256: the products run on the tensor cores
-// (bf16 precision, chunk = K = 128, value width TCW).
-template <int TCW>
+// fp32 SIMT products (the tensor-core variant lives in dn_prepass_bwd_tc.cu).
 __global__ void __launch_bounds__(DN_THREADS, 1) prepass_bwd_kernel(PrepassBwdArgs a) {
   extern __shared__ __align__(128) float smem[];
-  __shared__ uint64_t mma_bar;
-  __shared__ uint32_t tmem_base;
   const Geo& g = a.g;
   const int C = g.C, K = g.K, Vw = g.Vw;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  constexpr int IMG_FLOATS = TCW ? bwd_tc_image_bytes(TCW) / 4 : 0;
-  float* tile = smem + IMG_FLOATS;         // SIMT GEMM staging (unused with tensor cores)
-  float* rq_s = tile + (TCW ? 0 : GEMM_SMEM_FLOATS);   // C
+  float* tile = smem;                      // SIMT GEMM staging
+  float* rq_s = tile + GEMM_SMEM_FLOATS;   // C
   float* rk_s = rq_s + C;                  // C
   float* dlend_s = rk_s + C;               // K
   int* seg_s = reinterpret_cast<int*>(dlend_s + K);   // C
@@ -53,16 +47,6 @@ __global__ void __launch_bounds__(DN_THREADS, 1) prepass_bwd_kernel(PrepassBwdAr
   const bool round_in = !fuse && g.qkv_dt == DN_BF16;
   const bool sbf = g.state_bf16(), ibf = g.bf16_mode(), trunc = ibf && (g.flags & DN_TRUNC_DT_BF16);
   const int pre = g.pre_dt;
-
-  umma::Ctx cx{0u, &mma_bar, 0u, a.err, false};
-  if (TCW) {
-    if (tid == 0) { umma::mbar_init(&mma_bar, 1); umma::fence_mbar_init(); }
-    if (warp == 0) umma::tmem_alloc(&tmem_base, 512);
-    umma::tc_fence_before();
-    __syncthreads();
-    umma::tc_fence_after();
-    cx.tmem = tmem_base;
-  }
 
   for (int item = blockIdx.x; item < a.items; item += gridDim.x) {
     const int c_idx = item % g.NC, h = (item / g.NC) % g.H, b = item / (g.NC * g.H);
@@ -156,64 +140,50 @@ __global__ void __launch_bounds__(DN_THREADS, 1) prepass_bwd_kernel(PrepassBwdAr
     }
     __syncthreads();
 
-    if (TCW) {
-      BwdTcIo io;
-      io.W = reinterpret_cast<const __nv_bfloat16*>(a.res.W) + bW;
-      io.U = reinterpret_cast<const __nv_bfloat16*>(a.res.U) + bU;
-      io.S = S; io.dH = dH; io.dV = dV; io.T = T;
-      io.d_out = a.d_out; io.qkv_dt = g.qkv_dt;
-      io.dO_off = ((size_t)b * g.L + t0) * g.Hv * g.V + (size_t)h * Vw;
-      io.dO_pitch = (size_t)g.Hv * g.V;
-      io.rows_valid = g.L - t0 < C ? g.L - t0 : C;
-      io.DQE = DQE; io.DKE = DKE; io.DX = DX; io.DY = DY; io.DM = DM; io.DA = DA;
-      io.seg_s = seg_s; io.trunc = trunc;
-      bwd_gemms_tc<TCW ? TCW : 128, DN_THREADS>(cx, reinterpret_cast<uint8_t*>(smem), io);
-    } else {
     // ---- V_new = U - W S
-      cta_gemm<true, true>(C, Vw, K,
-          [&](int i, int kk) { return ldf(a.res.W, bW + (size_t)i * K + kk, pre); },
-          [&](int kk, int j) { float s = S[(size_t)kk * Vw + j]; return sbf ? bf16r(s) : s; },
-          [&](int i, int j, float acc) { VN[i * Vw + j] = ldf(a.res.U, bU + (size_t)i * Vw + j, pre) - acc; },
-          tile);
-      auto dO_at = [&](int i, int j) -> float {
-        const int t = t0 + i;
-        return t < g.L ? ldf(a.d_out, ((size_t)b * g.L + t) * g.Hv * g.V + (size_t)h * Vw + j, g.qkv_dt) : 0.f;
-      };
-      // ---- dW = -dV S^T, dqe = dO S^T, dke = V_new dH^T, dM = dO V_new^T
-      cta_gemm<true, false>(C, K, Vw,
-          [&](int i, int kk) { float x = dV[(size_t)i * Vw + kk]; return sbf ? bf16r(x) : x; },
-          [&](int kk, int j) { float s = S[(size_t)j * Vw + kk]; return sbf ? bf16r(s) : s; },
-          [&](int i, int j, float acc) { DW[i * K + j] = -acc; }, tile);
-      cta_gemm<true, false>(C, K, Vw,
-          [&](int i, int kk) { float x = dO_at(i, kk); return sbf ? bf16r(x) : x; },
-          [&](int kk, int j) { float s = S[(size_t)j * Vw + kk]; return sbf ? bf16r(s) : s; },
-          [&](int i, int j, float acc) { DQE[i * K + j] = acc; }, tile);
-      cta_gemm<true, false>(C, K, Vw,
-          [&](int i, int kk) { float x = VN[i * Vw + kk]; return sbf ? bf16r(x) : x; },
-          [&](int kk, int j) { float x = dH[(size_t)j * Vw + kk]; return sbf ? bf16r(x) : x; },
-          [&](int i, int j, float acc) { DKE[i * K + j] = acc; }, tile);
-      cta_gemm<true, false>(C, C, Vw,
-          [&](int i, int kk) { float x = dO_at(i, kk); return ibf ? bf16r(x) : x; },
-          [&](int kk, int j) { float x = VN[j * Vw + kk]; return ibf ? bf16r(x) : x; },
-          [&](int i, int j, float acc) { DM[i * C + j] = (i >= j && seg_s[i] == seg_s[j]) ? acc : 0.f; }, tile);
-      // ---- dX = T^T dW, dY = T^T dV
-      cta_gemm<false, true>(C, K, C,
-          [&](int i, int kk) { float t = T[(size_t)kk * C + i]; return ibf ? bf16r(t) : t; },
-          [&](int kk, int j) { float x = DW[kk * K + j]; return ibf ? bf16r(x) : x; },
-          [&](int i, int j, float acc) { DX[i * K + j] = trunc ? bf16r(acc) : acc; }, tile);
-      cta_gemm<false, true>(C, Vw, C,
-          [&](int i, int kk) { float t = T[(size_t)kk * C + i]; return ibf ? bf16r(t) : t; },
-          [&](int kk, int j) { float x = dV[(size_t)kk * Vw + j]; return ibf ? bf16r(x) : x; },
-          [&](int i, int j, float acc) { DY[i * Vw + j] = trunc ? bf16r(acc) : acc; }, tile);
-      // ---- dA = -(dX W^T + dY U^T), strictly lower and same document
-      cta_gemm<true, false>(C, C, K + Vw,
-          [&](int i, int kk) { return kk < K ? DX[i * K + kk] : DY[i * Vw + (kk - K)]; },
-          [&](int kk, int j) {
-            return kk < K ? ldf(a.res.W, bW + (size_t)j * K + kk, pre)
-                          : ldf(a.res.U, bU + (size_t)j * Vw + (kk - K), pre);
-          },
-          [&](int i, int j, float acc) { DA[i * C + j] = (i > j && seg_s[i] == seg_s[j]) ? -acc : 0.f; }, tile);
-    }
+    cta_gemm<true, true>(C, Vw, K,
+        [&](int i, int kk) { return ldf(a.res.W, bW + (size_t)i * K + kk, pre); },
+        [&](int kk, int j) { float s = S[(size_t)kk * Vw + j]; return sbf ? bf16r(s) : s; },
+        [&](int i, int j, float acc) { VN[i * Vw + j] = ldf(a.res.U, bU + (size_t)i * Vw + j, pre) - acc; },
+        tile);
+    auto dO_at = [&](int i, int j) -> float {
+      const int t = t0 + i;
+      return t < g.L ? ldf(a.d_out, ((size_t)b * g.L + t) * g.Hv * g.V + (size_t)h * Vw + j, g.qkv_dt) : 0.f;
+    };
+    // ---- dW = -dV S^T, dqe = dO S^T, dke = V_new dH^T, dM = dO V_new^T
+    cta_gemm<true, false>(C, K, Vw,
+        [&](int i, int kk) { float x = dV[(size_t)i * Vw + kk]; return sbf ? bf16r(x) : x; },
+        [&](int kk, int j) { float s = S[(size_t)j * Vw + kk]; return sbf ? bf16r(s) : s; },
+        [&](int i, int j, float acc) { DW[i * K + j] = -acc; }, tile);
+    cta_gemm<true, false>(C, K, Vw,
+        [&](int i, int kk) { float x = dO_at(i, kk); return sbf ? bf16r(x) : x; },
+        [&](int kk, int j) { float s = S[(size_t)j * Vw + kk]; return sbf ? bf16r(s) : s; },
+        [&](int i, int j, float acc) { DQE[i * K + j] = acc; }, tile);
+    cta_gemm<true, false>(C, K, Vw,
+        [&](int i, int kk) { float x = VN[i * Vw + kk]; return sbf ? bf16r(x) : x; },
+        [&](int kk, int j) { float x = dH[(size_t)j * Vw + kk]; return sbf ? bf16r(x) : x; },
+        [&](int i, int j, float acc) { DKE[i * K + j] = acc; }, tile);
+    cta_gemm<true, false>(C, C, Vw,
+        [&](int i, int kk) { float x = dO_at(i, kk); return ibf ? bf16r(x) : x; },
+        [&](int kk, int j) { float x = VN[j * Vw + kk]; return ibf ? bf16r(x) : x; },
+        [&](int i, int j, float acc) { DM[i * C + j] = (i >= j && seg_s[i] == seg_s[j]) ? acc : 0.f; }, tile);
+    // ---- dX = T^T dW, dY = T^T dV
+    cta_gemm<false, true>(C, K, C,
+        [&](int i, int kk) { float t = T[(size_t)kk * C + i]; return ibf ? bf16r(t) : t; },
+        [&](int kk, int j) { float x = DW[kk * K + j]; return ibf ? bf16r(x) : x; },
+        [&](int i, int j, float acc) { DX[i * K + j] = trunc ? bf16r(acc) : acc; }, tile);
+    cta_gemm<false, true>(C, Vw, C,
+        [&](int i, int kk) { float t = T[(size_t)kk * C + i]; return ibf ? bf16r(t) : t; },
+        [&](int kk, int j) { float x = dV[(size_t)kk * Vw + j]; return ibf ? bf16r(x) : x; },
+        [&](int i, int j, float acc) { DY[i * Vw + j] = trunc ? bf16r(acc) : acc; }, tile);
+    // ---- dA = -(dX W^T + dY U^T), strictly lower and same document
+    cta_gemm<true, false>(C, C, K + Vw,
+        [&](int i, int kk) { return kk < K ? DX[i * K + kk] : DY[i * Vw + (kk - K)]; },
+        [&](int kk, int j) {
+          return kk < K ? ldf(a.res.W, bW + (size_t)j * K + kk, pre)
+                        : ldf(a.res.U, bU + (size_t)j * Vw + (kk - K), pre);
+        },
+        [&](int i, int j, float acc) { DA[i * C + j] = (i > j && seg_s[i] == seg_s[j]) ? -acc : 0.f; }, tile);
 
     // ---- adjoints of A and M, pair by pair.  Row side: dbeta', dq'.  Column side: dk'.
     // The diagonal pair (i == i) has exponent 0: it feeds dq and dk but not dLambda, and is
@@ -289,7 +259,6 @@ __global__ void __launch_bounds__(DN_THREADS, 1) prepass_bwd_kernel(PrepassBwdAr
       const int t = t0 + i;
       if (t >= g.L) continue;
       const size_t rowg = ((size_t)(b * (size_t)g.L + t) * g.gH + hg) * g.gC;
-      const size_t rowb = ((size_t)(b * (size_t)g.L + t) * g.bH + hb) * g.bC;
       const size_t outg = ((size_t)(b * (size_t)g.L + t) * g.H + h) * g.gC;   // exec-head granularity
       const size_t outb = ((size_t)(b * (size_t)g.L + t) * g.H + h) * g.bC;
       float sg = 0.f, sb2 = 0.f;
@@ -364,11 +333,6 @@ __global__ void __launch_bounds__(DN_THREADS, 1) prepass_bwd_kernel(PrepassBwdAr
     }
     __syncthreads();
   }
-  if (TCW) {
-    umma::tc_fence_before();
-    __syncthreads();
-    if (warp == 0) umma::tmem_dealloc(tmem_base, 512);
-  }
 }
 
 size_t prepass_bwd_scratch_per_cta(const Geo& g) {
@@ -387,23 +351,11 @@ int launch_prepass_bwd(PrepassBwdArgs& a, size_t scratch_floats, cudaStream_t st
   const bool tc = prepass_bwd_tc_eligible(g) && !force_simt();
   a.err = device_error_ptr();
   if (tc) return launch_prepass_bwd_tc(a, scratch_floats, st);
-  const int max_ctas = tc ? 148 : 296;
+  const int max_ctas = 296;
   int grid = a.items < max_ctas ? a.items : max_ctas;
   if (scratch_floats < (size_t)grid * a.scratch_per_cta) return DN_ERR_SCRATCH_TOO_SMALL;
-  const size_t small = ((size_t)4 * g.C + g.K) * sizeof(float);
-  if (tc) {
-    const size_t smem = bwd_tc_image_bytes(g.Vw) + small;
-    if (g.Vw == 256) {
-      cudaFuncSetAttribute(prepass_bwd_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      prepass_bwd_kernel<256><<<grid, DN_THREADS, smem, st>>>(a);
-    } else {
-      cudaFuncSetAttribute(prepass_bwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      prepass_bwd_kernel<128><<<grid, DN_THREADS, smem, st>>>(a);
-    }
-  } else {
-    const size_t smem = GEMM_SMEM_FLOATS * sizeof(float) + small;
-    prepass_bwd_kernel<0><<<grid, DN_THREADS, smem, st>>>(a);
-  }
+  const size_t smem = (GEMM_SMEM_FLOATS + (size_t)4 * g.C + g.K) * sizeof(float);
+  prepass_bwd_kernel<<<grid, DN_THREADS, smem, st>>>(a);
   return cudaGetLastError() == cudaSuccess ? DN_OK : DN_ERR_CUDA_LAUNCH;
 }
 

@@ -4,15 +4,26 @@
 //
 // Per (batch, exec head, chunk), 512 threads, one CTA per SM:
 //   G. nine matrix products (bwd_gemms_tc): V_new, dqe, dM, dW, dke, dX, dY, dA.
-//   L. the cumulative log-decay of the chunk in shared memory.
-//   H. adjoints of A and M through the same three-level factorisation as the forward: per level
-//        dbeta' += rowfac * (dA_s kc),  dq' += rowfac * (dM_s kc),
-//        dk'    += colfac * (dA_s^T rb + dM_s^T rq)
-//      where dA_s / dM_s keep only the entries the level owns, kc / rb / rq are the level's scaled
-//      operand images and rowfac / colfac the same exp(Lam - Lam_ref) factors (all <= 1).
-//   D. the 16x16 diagonal blocks, exact, one thread per (block, channel).
-//   C. combination into dLambda, d q_hat, d k_hat, d b; R. dg by a within-document reverse
-//      cumulative sum; W. row pass (gate adjoints, l2norm adjoint, writes); V. dv and dw.
+//   L. row normalisers and the cumulative log-decay of the chunk in shared memory.
+//   D. the 16x16 diagonal blocks of dA and dM, exact, one thread per (block, channel); this pass
+//      initialises dbeta', dq', dk'.
+//   H. adjoints of A and M through the same three-level factorisation as the forward.  In one level
+//      every row is either a ROW of the level's entries (lower block of its pair) or a COLUMN (upper
+//      block), so with dA_s / dM_s the entries the level owns, KR the image holding beta-images on
+//      lower rows and k-images on upper rows, and QK holding q-images / k-images,
+//        T1 = (dA_s + dA_s^T) KR,   T2 = (dM_s + dM_s^T) QK        (four MMAs, one drain)
+//        lower rows:  dbeta' += rowfac * T1,  dq' += rowfac * T2
+//        upper rows:  dk'    += colfac * (T1 + T2)
+//      with the same exp(Lam - Lam_ref) factors (all <= 1) as the forward.  Levels alternate between
+//      two halves of tensor memory, so a level's drain overlaps the next level's image build.
+//   E. combination into dLambda, d q_hat, d k_hat, d b (written), the l2norm adjoint and dq, dk.
+//   R. dg by a within-document reverse cumulative sum plus the Lambda_end path; written with the
+//      gate adjoint.   V. dv and dw.
+//
+// Thread mappings: phases that touch the operator's row-major tensors let a warp cover 8 rows x 4
+// pieces of 8 channels (row = 8 * warp + (lane & 7) is fixed per thread); phases that drain tensor
+// memory own one row per thread and use the panel layout of the scratch (see the header).
+#include <cstdio>
 #include "dn_chunkprep.cuh"
 #include "dn_kernels.cuh"
 #include "dn_prepass_bwd_tc.cuh"
@@ -23,29 +34,85 @@ namespace {
 using namespace prep;
 constexpr int NT = 512;
 
-template <int VW>
+__device__ __forceinline__ void ld2x4(const float4* p, float (&o)[8]) {      // scratch written by this CTA
+  const float4 a = __ldcg(p), b = __ldcg(p + 128);
+  o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
+}
+__device__ __forceinline__ void st2x4(float4* p, const float (&v)[8]) {
+  __stcg(p, make_float4(v[0], v[1], v[2], v[3]));
+  __stcg(p + 128, make_float4(v[4], v[5], v[6], v[7]));
+}
+__device__ __forceinline__ void out8(void* base, size_t off, int dt, const float (&v)[8]) {
+  if (dt == DN_BF16) *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(base) + off) = umma::pack8(v);
+  else {
+    float4* d = reinterpret_cast<float4*>(reinterpret_cast<float*>(base) + off);
+    d[0] = make_float4(v[0], v[1], v[2], v[3]);
+    d[1] = make_float4(v[4], v[5], v[6], v[7]);
+  }
+}
+
+// One row i of a diagonal block: columns [0, JF) always, columns [JF, JF + JP) while j < i.
+template <int JF, int JP>
+__device__ __forceinline__ void diag_row(int i, float li, const float (&lam)[16], const float (&kh)[16], float (&sk)[16],
+                                         const float4* da4, const float4* dm4, float be, float qv, float& sb, float& sq) {
+  constexpr int NJ = JF + JP, NV = (NJ + 3) / 4;
+  float da[4 * NV], dm[4 * NV];
+#pragma unroll
+  for (int u = 0; u < NV; ++u) {
+    const float4 va = da4[u], vm = dm4[u];
+    da[4 * u] = va.x; da[4 * u + 1] = va.y; da[4 * u + 2] = va.z; da[4 * u + 3] = va.w;
+    dm[4 * u] = vm.x; dm[4 * u + 1] = vm.y; dm[4 * u + 2] = vm.z; dm[4 * u + 3] = vm.w;
+  }
+  sb = 0.f; sq = 0.f;
+#pragma unroll
+  for (int j = 0; j < NJ; ++j) {
+    if (j < JF || j < i) {
+      const float e = umma::ex2_fast(fminf(li - lam[j], 0.f));
+      const float ek = e * kh[j];
+      sb = fmaf(da[j], ek, sb);
+      sq = fmaf(dm[j], ek, sq);
+      sk[j] = fmaf(fmaf(da[j], be, dm[j] * qv), e, sk[j]);
+    }
+  }
+}
+
+template <int VW, int MODE>
 __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a) {
+  using CF = InCfg<MODE>;
   extern __shared__ __align__(128) uint8_t smraw[];
   __shared__ uint64_t mma_bar;
   __shared__ uint32_t tmem_base;
   __shared__ int seg_s[C];
+  __shared__ int reset_s[8];                 // per 32-row quarter: a document starts inside it
   __shared__ float rq_s[C], rk_s[C], dlend_s[K];
   const Geo& g = a.g;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int myrow = warp * 8 + (lane & 7), lgrp = lane >> 3;      // the 8 rows x 4 pieces mapping
   constexpr int OFF_IMG = C * LP * 4;
   float* LAM = reinterpret_cast<float*>(smraw);
   uint4* I_DA = reinterpret_cast<uint4*>(smraw + OFF_IMG);
   uint4* I_DM = I_DA + IMG;
-  uint4* I_KR = I_DM + IMG;                 // kc, then rb
-  uint4* I_RQ = I_KR + IMG;
+  uint4* I_KR = I_DM + IMG;
+  uint4* I_QK = I_KR + IMG;
   float* DLs = reinterpret_cast<float*>(smraw + OFF_IMG);          // dLambda (pitch LP), over the images
   float* DKs = DLs + C * LP;                                        // dke*ke   (pitch LP)
+  float* TOT = reinterpret_cast<float*>(smraw + 3 * C * LP * 4);   // 2 x 4 x 128 partial sums of phase R
+  float* TOTL = reinterpret_cast<float*>(smraw + OFF_IMG);         // 4 x 128 partial sums of phase L
 
   const size_t CK = (size_t)C * K, CV = (size_t)C * VW, CC = (size_t)C * C;
   float* sc = a.scratch + (size_t)blockIdx.x * a.scratch_per_cta;
   float* DQE = sc;          float* DKE = DQE + CK;   float* DX = DKE + CK;
   float* DBP = DX + CK;     float* DQP = DBP + CK;   float* DKP = DQP + CK;
   float* DY = DKP + CK;     float* DM = DY + CV;     float* DA = DM + CC;
+  float4* DA4 = reinterpret_cast<float4*>(DA);
+  float4* DM4 = reinterpret_cast<float4*>(DM);
+  float4* DBP4 = reinterpret_cast<float4*>(DBP);
+  float4* DQP4 = reinterpret_cast<float4*>(DQP);
+  float4* DKP4 = reinterpret_cast<float4*>(DKP);
+  const float4* DX4 = reinterpret_cast<const float4*>(DX);
+  const float4* DQE4 = reinterpret_cast<const float4*>(DQE);
+  const float4* DKE4 = reinterpret_cast<const float4*>(DKE);
+  const float4* DY4 = reinterpret_cast<const float4*>(DY);
 
   if (tid == 0) { umma::mbar_init(&mma_bar, 1); umma::fence_mbar_init(); }
   if (warp == 0) umma::tmem_alloc(&tmem_base, 512);
@@ -62,334 +129,475 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
     const int c_idx = item % g.NC, h = (item / g.NC) % g.H, b = item / (g.NC * g.H);
     const int t0 = c_idx * C;
     const size_t ibase = (size_t)item;
+    DN_MARK(0);
     for (int i = tid; i < C; i += NT) seg_s[i] = seg_at(a.seg, b, t0 + i, g.L);
     bool is_new, all_same;
     chunk_flags(a.seg, g, b, c_idx, is_new, all_same);
-    const float* S = a.res.states + ibase * K * VW;
-    const float* dH = a.dH + ibase * K * VW;
-    // dLambda_end from the carried state: [one doc] sum_v dH*S*exp(Lambda_end)   (gdn2.py:759-762)
-    for (int kk = warp; kk < K; kk += NT / 32) {
-      float s = 0.f;
-      for (int j = lane; j < VW; j += 32) s += dH[(size_t)kk * VW + j] * S[(size_t)kk * VW + j];
-      s = warp_sum(s);
-      if (lane == 0) dlend_s[kk] = all_same ? s * expf(fminf(a.res.lam_end[ibase * K + kk], 0.f)) : 0.f;
-    }
     __syncthreads();
     const int seg0 = seg_s[0], segL = seg_s[C - 1];
 
-    // ---- G. the matrix products
+    // ---- G. the matrix products (and dLambda_end from the carried state)
     {
       BwdTcIo io;
       io.W = reinterpret_cast<const __nv_bfloat16*>(a.res.W) + ibase * CK;
       io.U = reinterpret_cast<const __nv_bfloat16*>(a.res.U) + ibase * CV;
-      io.S = S; io.dH = dH; io.dV = a.dV + ibase * CV; io.T = a.res.T + ibase * CC;
-      io.d_out = a.d_out; io.qkv_dt = g.qkv_dt;
+      io.S = a.res.states + ibase * K * VW;
+      io.dH = a.dH + ibase * K * VW;
+      io.dV = a.dV + ibase * CV; io.T = a.res.T + ibase * CC;
+      io.lam_end = a.res.lam_end + ibase * K;
+      io.d_out = a.d_out; io.qkv_dt = CF::fixed ? CF::qkv_dt : g.qkv_dt;
       io.dO_off = ((size_t)b * g.L + t0) * g.Hv * g.V + (size_t)h * VW;
       io.dO_pitch = (size_t)g.Hv * g.V;
       io.rows_valid = g.L - t0 < C ? g.L - t0 : C;
       io.DQE = DQE; io.DKE = DKE; io.DX = DX; io.DY = DY; io.DM = DM; io.DA = DA;
+      io.dlend_s = dlend_s; io.all_same = all_same;
       io.seg_s = seg_s; io.trunc = trunc;
       bwd_gemms_tc<VW, NT>(cx, smraw, io);
     }
 
-    // ---- L. rows, normalisers, cumulative decay; zero the accumulators of phase H
-    const Rows r = make_rows(g, a.q, a.k, a.gg, a.b, b, h, t0, rq_s, rk_s);
-    row_norms<NT>(r, rq_s, rk_s);
-    for (int e = tid; e < 3 * C * K / 4; e += NT) reinterpret_cast<float4*>(DBP)[e] = make_float4(0.f, 0.f, 0.f, 0.f);
-    __syncthreads();
-    build_lambda<NT>(r, seg_s, LAM);
-
-    // ---- H. three levels
-    for (int lv = 0; lv < 3; ++lv) {
-      const int s = 16 << lv;
-      for (int e = tid; e < IMG; e += NT) {            // dA_s, dM_s: the entries this level owns
-        const int p = e >> 7, x = e & 127;
-        const int bi = x >> 4, bj = p >> 1;
-        uint4 va = make_uint4(0, 0, 0, 0), vm = va;
-        if (bj < bi && owner_level(bi, bj) == lv) {
-          va = umma::ld8_f32(DA + x * C + 8 * p);
-          vm = umma::ld8_f32(DM + x * C + 8 * p);
+    DN_MARK(7);
+    // ---- L. rows, normalisers, cumulative decay
+    const Rows r = make_rows<CF>(g, a.q, a.k, a.gg, a.b, b, h, t0, rq_s, rk_s);
+    const int qdt = r.qkv_dt, gdt = r.gate_dt;           // compile-time constants in the fixed modes
+    const int wC = CF::fixed ? g.V : g.wC;
+    {
+      float sq = 0.f, sk = 0.f;
+      if (l2) {                       // rows past the end read as zero
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+          float qv[8], kv[8];
+          raw_q8(r, myrow, it * 4 + lgrp, qv);
+          raw_k8(r, myrow, it * 4 + lgrp, kv);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) { sq = fmaf(qv[i], qv[i], sq); sk = fmaf(kv[i], kv[i], sk); }
         }
-        I_DA[e] = va;
-        I_DM[e] = vm;
       }
-      build_level<NT>(r, LAM, s, nullptr, I_RQ, I_KR);               // kc and rq
-      umma::pre_issue_sync();
-      umma::issue<128, false, true>(cx, I_DA, I_KR, C, 0, false);    // dA_s kc
-      umma::issue<128, false, true>(cx, I_DM, I_KR, C, 128, false);  // dM_s kc
-      umma::commit_wait(cx);
-      build_level<NT>(r, LAM, s, I_KR, nullptr, nullptr);            // rb over kc
-      umma::pre_issue_sync();
-      umma::issue<128, true, true>(cx, I_DA, I_KR, C, 256, false);   // dA_s^T rb
-      umma::issue<128, true, true>(cx, I_DM, I_RQ, C, 256, true);    //  + dM_s^T rq
-      umma::commit_wait(cx);
-      {
-        const int quarter = warp & 3, group = warp >> 2;
-        const int x = quarter * 32 + lane, ref = level_ref(x, s);
-        const bool lower = x >= ref;
-        const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
-        for (int c = 0; c < 32; c += 16) {
-          const int col = group * 32 + c;
-          float vb[16], vq[16], vk[16];
-          if (!cx.dead) {
-            umma::tmem_ld16(cx.tmem + lane_base + col, vb);
-            umma::tmem_ld16(cx.tmem + lane_base + 128 + col, vq);
-            umma::tmem_ld16(cx.tmem + lane_base + 256 + col, vk);
-          } else {
+      sq += __shfl_xor_sync(0xffffffffu, sq, 8);  sk += __shfl_xor_sync(0xffffffffu, sk, 8);
+      sq += __shfl_xor_sync(0xffffffffu, sq, 16); sk += __shfl_xor_sync(0xffffffffu, sk, 16);
+      if (lgrp == 0) {
+        rq_s[myrow] = l2 ? rsqrtf(sq + 1e-6f) : 1.f;
+        rk_s[myrow] = l2 ? rsqrtf(sk + 1e-6f) : 1.f;
+      }
+    }
+    {
+      // cumulative log-decay: thread (channel c, quarter qd) scans 32 rows in registers, the quarters
+      // are chained through shared memory
+      const int c = tid & 127, qd = tid >> 7, x0 = qd * 32;
+      const size_t gcol = r.gC == 1 ? 0 : c;
+      float v[32];
 #pragma unroll
-            for (int i = 0; i < 16; ++i) vb[i] = vq[i] = vk[i] = 0.f;
-          }
-          float f0[8], f1[8];
-          if (lower) {
-            decay8(LAM + x * LP + col, LAM + ref * LP + col, f0);
-            decay8(LAM + x * LP + col + 8, LAM + ref * LP + col + 8, f1);
-            float4* db = reinterpret_cast<float4*>(DBP + x * K + col);
-            float4* dq = reinterpret_cast<float4*>(DQP + x * K + col);
+      for (int i = 0; i < 32; ++i) {
+        const int x = x0 + i;
+        const bool live = x < r.rows_valid;
+        float gv = ldf_ro(r.gg, r.g_row0 + (size_t)(live ? x : 0) * r.g_pitch + gcol, gdt);
+        if (fuse) { gv = -expf(fminf(gv, 5.f)); if (guard) gv = fminf(gv, -1e-6f); }
+        else gv = gv <= 0.f ? gv : 0.f;
+        v[i] = live ? gv : 0.f;
+      }
+      float run = 0.f;
+      int nr = 32;                                   // first row of the quarter that starts a document
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const float* f = i < 2 ? f0 + 4 * i : f1 + 4 * (i - 2);
-              float4 ob = db[i], oq = dq[i];
-              ob.x += vb[4 * i] * f[0]; ob.y += vb[4 * i + 1] * f[1]; ob.z += vb[4 * i + 2] * f[2]; ob.w += vb[4 * i + 3] * f[3];
-              oq.x += vq[4 * i] * f[0]; oq.y += vq[4 * i + 1] * f[1]; oq.z += vq[4 * i + 2] * f[2]; oq.w += vq[4 * i + 3] * f[3];
-              db[i] = ob;
-              dq[i] = oq;
-            }
-          } else {
-            decay8(LAM + ref * LP + col, LAM + x * LP + col, f0);
-            decay8(LAM + ref * LP + col + 8, LAM + x * LP + col + 8, f1);
-            float4* dk = reinterpret_cast<float4*>(DKP + x * K + col);
+      for (int i = 0; i < 32; ++i) {
+        const int x = x0 + i;
+        if (x > 0 && seg_s[x] != seg_s[x - 1]) { run = 0.f; if (nr == 32) nr = i; }
+        run += v[i];
+        v[i] = run;
+      }
+      TOTL[qd * 128 + c] = run;
+      if (c == 0) reset_s[qd] = nr < 32;
+      __syncthreads();
+      float carry = 0.f;
+      for (int q2 = qd - 1; q2 >= 0; --q2) {
+        carry += TOTL[q2 * 128 + c];
+        if (reset_s[q2]) break;
+      }
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const float* f = i < 2 ? f0 + 4 * i : f1 + 4 * (i - 2);
-              float4 ok = dk[i];
-              ok.x += vk[4 * i] * f[0]; ok.y += vk[4 * i + 1] * f[1]; ok.z += vk[4 * i + 2] * f[2]; ok.w += vk[4 * i + 3] * f[3];
-              dk[i] = ok;
-            }
-          }
-        }
-        umma::tc_fence_before();
+      for (int i = 0; i < 32; ++i) LAM[(x0 + i) * LP + c] = v[i] + (i < nr ? carry : 0.f);
+    }
+    __syncthreads();
+
+    DN_MARK(8);
+    // ---- D. diagonal 16x16 blocks, exact.  The blocks of dA and dM are staged in shared memory
+    //         (all lanes of a warp read the same entry); one thread per (block, channel) walks the
+    //         rows i of the block with the next row's q, k, b already in flight, and for every
+    //         earlier row j adds to dbeta'_i, dq'_i (scalars) and dk'_j (one register per j).
+    //         This pass initialises DBP / DQP / DKP; the levels of phase H add to them.
+    {
+      float4* DG4 = reinterpret_cast<float4*>(smraw + OFF_IMG);      // [2][8 blocks][16 rows][4]
+      for (int e = tid; e < 512; e += NT) {
+        const int blk = e >> 6, q4 = (e >> 4) & 3, row = e & 15;
+        DG4[(blk * 16 + row) * 4 + q4] = __ldcg(DA4 + p4v(blk * 16 + row, blk * 16 + 4 * q4));
+        DG4[512 + (blk * 16 + row) * 4 + q4] = __ldcg(DM4 + p4v(blk * 16 + row, blk * 16 + 4 * q4));
       }
       __syncthreads();
-    }
-
-    // ---- D. diagonal 16x16 blocks, exact: one thread per (block, channel).  Row side first
-    //         (dbeta'_i, dq'_i: one output row at a time, inner loop over the earlier rows j), then
-    //         the column side (dk'_j, inner loop over the later rows i).
-    for (int task = tid; task < 8 * K; task += NT) {
-      const int r0 = (task >> 7) * 16, c = task & 127;
-      float lam[16], kh[16], be[16], qh[16];
+      for (int task = tid; task < 8 * K; task += NT) {
+        const int blk = task >> 7, r0 = blk * 16, c = task & 127;
+        const size_t bcol = r.bC == 1 ? 0 : c;
+        float lam[16], kh[16], sk[16];
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const int x = r0 + i;
-        lam[i] = LAM[x * LP + c] * DN_LOG2E;
-        float kv = 0.f, qv = 0.f, bv = 0.f;
-        if (x < r.rows_valid) {
-          kv = ldf(r.k, r.qk_row0 + (size_t)x * r.qk_pitch + c, r.qkv_dt);
-          qv = ldf(r.q, r.qk_row0 + (size_t)x * r.qk_pitch + c, r.qkv_dt);
-          bv = ldf(r.b, r.b_row0 + (size_t)x * r.b_pitch + (r.bC == 1 ? 0 : c), r.gate_dt);
+        for (int i = 0; i < 16; ++i) {
+          const int x = r0 + i;
+          lam[i] = LAM[x * LP + c] * DN_LOG2E;
+          const bool live = x < r.rows_valid;
+          float kv = ldf_ro(r.k, r.qk_row0 + (size_t)(live ? x : 0) * r.qk_pitch + c, qdt);
+          if (!live) kv = 0.f;
           if (l2) { kv *= rk_s[x]; if (r.round_in) kv = bf16r(kv); }
+          kh[i] = kv;
+          sk[i] = 0.f;
+        }
+        DBP[p4f(r0, c)] = 0.f;
+        DQP[p4f(r0, c)] = 0.f;
+        auto row_inputs = [&](int i, float kv, float& be, float& qv) {
+          const int x = r0 + i;
+          const bool live = x < r.rows_valid;
+          qv = ldf_ro(r.q, r.qk_row0 + (size_t)(live ? x : 0) * r.qk_pitch + c, qdt);
+          float bv = ldf_ro(r.b, r.b_row0 + (size_t)(live ? x : 0) * r.b_pitch + bcol, gdt);
           qv = (qv * rq_s[x]) * r.scale;
           if (r.round_in) qv = bf16r(qv);
           if (fuse) bv = 1.f / (1.f + expf(-bv));
-        }
-        kh[i] = kv; qh[i] = qv; be[i] = bv * kv;
-      }
-#pragma unroll 1
-      for (int i = 1; i < 16; ++i) {
-        const float li = LAM[(r0 + i) * LP + c] * DN_LOG2E;
-        const float* da = DA + (r0 + i) * C + r0;
-        const float* dm = DM + (r0 + i) * C + r0;
-        float sb = 0.f, sq = 0.f;
+          if (!live) { bv = 0.f; qv = 0.f; }
+          be = bv * kv;
+        };
 #pragma unroll
-        for (int j = 0; j < 15; ++j) {
-          if (j < i) {
-            const float ek = exp2f(fminf(li - lam[j], 0.f)) * kh[j];
-            sb = fmaf(da[j], ek, sb);
-            sq = fmaf(dm[j], ek, sq);
-          }
+        for (int i = 1; i < 8; ++i) {                 // upper-left triangle: static row index
+          float be, qv, sb, sq;
+          row_inputs(i, kh[i], be, qv);
+          diag_row<0, 7>(i, lam[i], lam, kh, sk, DG4 + (r0 + i) * 4, DG4 + 512 + (r0 + i) * 4, be, qv, sb, sq);
+          DBP[p4f(r0 + i, c)] = sb;
+          DQP[p4f(r0 + i, c)] = sq;
         }
-        DBP[(r0 + i) * K + c] += sb;
-        DQP[(r0 + i) * K + c] += sq;
-      }
-#pragma unroll 1
-      for (int j = 0; j < 15; ++j) {
-        const float lj = LAM[(r0 + j) * LP + c] * DN_LOG2E;
-        float sk = 0.f;
 #pragma unroll
-        for (int i = 1; i < 16; ++i) {
-          if (i > j) {
-            const float e = exp2f(fminf(lam[i] - lj, 0.f));
-            sk = fmaf(fmaf(DA[(r0 + i) * C + r0 + j], be[i], DM[(r0 + i) * C + r0 + j] * qh[i]), e, sk);
-          }
+        for (int i = 8; i < 16; ++i) {                // square below it, then the lower-right triangle
+          float be, qv, sb, sq;
+          row_inputs(i, kh[i], be, qv);
+          diag_row<8, 7>(i, lam[i], lam, kh, sk, DG4 + (r0 + i) * 4, DG4 + 512 + (r0 + i) * 4, be, qv, sb, sq);
+          DBP[p4f(r0 + i, c)] = sb;
+          DQP[p4f(r0 + i, c)] = sq;
         }
-        DKP[(r0 + j) * K + c] += sk;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) DKP[p4f(r0 + j, c)] = sk[j];
       }
     }
     __syncthreads();
 
-    // ---- C. combine (pieces of 8 channels): dLambda and dke*ke to shared memory; d q_hat, d k_hat,
-    //         d b_act in place over DQP, DKP, DBP
-    for (int e = tid; e < IMG; e += NT) {
-      const int x = e >> 4, p = e & 15;
-      float qh[8], kh[8], ba[8];
-      qhat8(r, x, p, qh);
-      khat8(r, x, p, kh);
-      bact8(r, x, p, ba);
-      const bool first = seg_s[x] == seg0, last = seg_s[x] == segL;
-      const float dmii = DM[x * C + x];
-      float4* pDB = reinterpret_cast<float4*>(DBP + x * K + 8 * p);
-      float4* pDQ = reinterpret_cast<float4*>(DQP + x * K + 8 * p);
-      float4* pDK = reinterpret_cast<float4*>(DKP + x * K + 8 * p);
-      const float4* pDX = reinterpret_cast<const float4*>(DX + x * K + 8 * p);
-      const float4* pQE = reinterpret_cast<const float4*>(DQE + x * K + 8 * p);
-      const float4* pKE = reinterpret_cast<const float4*>(DKE + x * K + 8 * p);
+    DN_MARK(9);
+    // ---- H. three levels
+    auto build = [&](int lv) {
+      const int s = 16 << lv;
+      static_assert(IMG == 4 * NT, "four pieces per thread");
 #pragma unroll
-      for (int hh = 0; hh < 2; ++hh) {
-        float4 vdb = pDB[hh], vdq = pDQ[hh], vdk = pDK[hh];
-        const float4 vdx = pDX[hh], vqe = pQE[hh], vke = pKE[hh];
-        const float4 vl = *reinterpret_cast<const float4*>(LAM + x * LP + 8 * p + 4 * hh);
-        const float4 vle = *reinterpret_cast<const float4*>(LAM + (C - 1) * LP + 8 * p + 4 * hh);
-        float dbp[4] = {vdb.x, vdb.y, vdb.z, vdb.w}, dqp[4] = {vdq.x, vdq.y, vdq.z, vdq.w}, dkp[4] = {vdk.x, vdk.y, vdk.z, vdk.w};
-        const float dx[4] = {vdx.x, vdx.y, vdx.z, vdx.w}, dqe[4] = {vqe.x, vqe.y, vqe.z, vqe.w}, dke[4] = {vke.x, vke.y, vke.z, vke.w};
-        const float lam[4] = {vl.x, vl.y, vl.z, vl.w}, lend[4] = {vle.x, vle.y, vle.z, vle.w};
-        float odl[4], odk[4];
+      for (int half = 0; half < 2; ++half) {           // dA_s, dM_s: the entries this level owns
+        float4 a0[2], a1[2], m0[2], m1[2];
+        bool own[2];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {                  // loads are unconditional: entries of other levels are discarded
+          const int e = (2 * half + u) * NT + tid, p = e >> 7, x = e & 127;
+          const int bi = x >> 4, bj = p >> 1;
+          own[u] = bj < bi && owner_level(bi, bj) == lv;
+          a0[u] = __ldcg(DA4 + p4v(x, 8 * p)); a1[u] = __ldcg(DA4 + p4v(x, 8 * p + 4));
+          m0[u] = __ldcg(DM4 + p4v(x, 8 * p)); m1[u] = __ldcg(DM4 + p4v(x, 8 * p + 4));
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int e = (2 * half + u) * NT + tid;
+          uint4 va = make_uint4(umma::pack2(a0[u].x, a0[u].y), umma::pack2(a0[u].z, a0[u].w), umma::pack2(a1[u].x, a1[u].y), umma::pack2(a1[u].z, a1[u].w));
+          uint4 vm = make_uint4(umma::pack2(m0[u].x, m0[u].y), umma::pack2(m0[u].z, m0[u].w), umma::pack2(m1[u].x, m1[u].y), umma::pack2(m1[u].z, m1[u].w));
+          if (!own[u]) va = vm = make_uint4(0, 0, 0, 0);
+          I_DA[e] = va;
+          I_DM[e] = vm;
+        }
+      }
+#pragma unroll 2
+      for (int it = 0; it < 4; ++it) build_level_piece(r, LAM, s, myrow, it * 4 + lgrp, I_KR, I_QK);
+    };
+    auto drain_level = [&](int lv) {
+      const int s = 16 << lv;
+      const int quarter = warp & 3, group = warp >> 2;
+      const int x = quarter * 32 + lane, ref = level_ref(x, s);
+      const bool lower = x >= ref;
+      const uint32_t tbase = cx.tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)((lv & 1) * 256);
+      // one code path for both roles: a lower row adds rowfac * T1 to dbeta' and rowfac * T2 to dq',
+      // an upper row adds colfac * (T1 + T2) to dk'
+      float4* const pb = lower ? DBP4 : DKP4;
+      const float* const la = LAM + (lower ? x : ref) * LP;
+      const float* const lb = LAM + (lower ? ref : x) * LP;
+#pragma unroll 1
+      for (int cc = 0; cc < 32; cc += 16) {
+        const int col = group * 32 + cc;
+        float4 ob[4], oq[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { ob[i] = __ldcg(pb + p4v(x, col + 4 * i)); oq[i] = __ldcg(DQP4 + p4v(x, col + 4 * i)); }
+        float t1[16], t2[16];
+        if (!cx.dead) {
+          umma::tmem_ld16(tbase + col, t1);
+          umma::tmem_ld16(tbase + 128 + col, t2);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) t1[i] = t2[i] = 0.f;
+        }
+        float f[16];
+        decay8(la + col, lb + col, *reinterpret_cast<float(*)[8]>(f));
+        decay8(la + col + 8, lb + col + 8, *reinterpret_cast<float(*)[8]>(f + 8));
+#pragma unroll
+        for (int i = 0; i < 16; ++i) t1[i] = lower ? t1[i] : t1[i] + t2[i];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const int ci = 4 * hh + i;
-          const float el = expf(fminf(lam[i], 0.f)), eke = expf(fminf(lend[i] - lam[i], 0.f));
-          const float be = ba[ci] * kh[ci];
-          const float X = first ? be * el : 0.f, qe = first ? qh[ci] * el : 0.f, ke = last ? kh[ci] * eke : 0.f;
-          const float dbeta = dbp[i] + (first ? dx[i] * el : 0.f);
-          const float dq = dqp[i] + dmii * kh[ci] + (first ? dqe[i] * el : 0.f);
-          const float dk = dkp[i] + dmii * qh[ci] + (last ? dke[i] * eke : 0.f) + dbeta * ba[ci];
-          odl[i] = be * dbp[i] + qh[ci] * dqp[i] - kh[ci] * dkp[i] + dx[i] * X + dqe[i] * qe;
-          odk[i] = dke[i] * ke;
-          dbp[i] = dbeta * kh[ci];     // d b_act
-          dqp[i] = dq;
-          dkp[i] = dk;
+          ob[i].x = fmaf(t1[4 * i], f[4 * i], ob[i].x); ob[i].y = fmaf(t1[4 * i + 1], f[4 * i + 1], ob[i].y);
+          ob[i].z = fmaf(t1[4 * i + 2], f[4 * i + 2], ob[i].z); ob[i].w = fmaf(t1[4 * i + 3], f[4 * i + 3], ob[i].w);
+          oq[i].x = fmaf(t2[4 * i], f[4 * i], oq[i].x); oq[i].y = fmaf(t2[4 * i + 1], f[4 * i + 1], oq[i].y);
+          oq[i].z = fmaf(t2[4 * i + 2], f[4 * i + 2], oq[i].z); oq[i].w = fmaf(t2[4 * i + 3], f[4 * i + 3], oq[i].w);
+          __stcg(pb + p4v(x, col + 4 * i), ob[i]);
+          if (lower) __stcg(DQP4 + p4v(x, col + 4 * i), oq[i]);
         }
-        pDB[hh] = make_float4(dbp[0], dbp[1], dbp[2], dbp[3]);
-        pDQ[hh] = make_float4(dqp[0], dqp[1], dqp[2], dqp[3]);
-        pDK[hh] = make_float4(dkp[0], dkp[1], dkp[2], dkp[3]);
-        *reinterpret_cast<float4*>(DLs + x * LP + 8 * p + 4 * hh) = make_float4(odl[0], odl[1], odl[2], odl[3]);
-        *reinterpret_cast<float4*>(DKs + x * LP + 8 * p + 4 * hh) = make_float4(odk[0], odk[1], odk[2], odk[3]);
       }
+      umma::tc_fence_before();
+    };
+    build(0);
+    for (int lv = 0; lv < 3; ++lv) {
+      const uint32_t tcol = (uint32_t)((lv & 1) * 256);
+      umma::pre_issue_sync();
+      umma::issue<128, false, true>(cx, I_DA, I_KR, C, tcol, false);        // dA_s   KR
+      umma::issue<128, true, true>(cx, I_DA, I_KR, C, tcol, true);          // dA_s^T KR
+      umma::issue<128, false, true>(cx, I_DM, I_QK, C, tcol + 128, false);  // dM_s   QK
+      umma::issue<128, true, true>(cx, I_DM, I_QK, C, tcol + 128, true);    // dM_s^T QK
+      umma::commit_wait(cx);
+      DN_MARK(10 + lv);
+      if (lv < 2) build(lv + 1);
+      drain_level(lv);
     }
     __syncthreads();
+
+    DN_MARK(13);
+    // ---- E. combination (8 rows x 4 pieces per warp step; a thread keeps row `myrow`):
+    //         dLambda and dke*ke to shared memory, d b written, d q_hat / d k_hat back in place;
+    //         then the l2norm adjoint needs each row's <q_n, dq_n> and <k_n, dk_n>: partial sums per
+    //         thread, the four threads of a row sit 8 lanes apart.
+    {
+      const int x = myrow, t = t0 + x;
+      const bool live = x < r.rows_valid;
+      const bool first = seg_s[x] == seg0, last = seg_s[x] == segL;
+      const float dmii = __ldcg(DM + p4f(x, x));
+      const float rq = rq_s[x], rk = rk_s[x];
+      const size_t tok = (size_t)b * g.L + t;
+      const size_t outb = (tok * g.H + h) * r.bC;
+      const size_t rowqk = (tok * g.Hk + h / g.qk_div) * K;
+      const size_t outqk = (tok * g.H + h) * K;
+      float dq_dot = 0.f, dk_dot = 0.f, sb2 = 0.f;
+#pragma unroll 1
+      for (int it = 0; it < 4; ++it) {
+        const int p = it * 4 + lgrp;
+        float qr[8], kr[8], ba[8], dbp[8], dqp[8], dkp[8], dx[8], dqe[8], dke[8];
+        raw_q8(r, x, p, qr);
+        raw_k8(r, x, p, kr);
+        bact8(r, x, p, ba);
+        ld2x4(DBP4 + p4v(x, 8 * p), dbp);
+        ld2x4(DQP4 + p4v(x, 8 * p), dqp);
+        ld2x4(DKP4 + p4v(x, 8 * p), dkp);
+        ld2x4(DX4 + p4v(x, 8 * p), dx);
+        ld2x4(DQE4 + p4v(x, 8 * p), dqe);
+        ld2x4(DKE4 + p4v(x, 8 * p), dke);
+        float lam[8], lend[8], odl[8], odk[8], odb[8];
+        *reinterpret_cast<float4*>(lam) = *reinterpret_cast<const float4*>(LAM + x * LP + 8 * p);
+        *reinterpret_cast<float4*>(lam + 4) = *reinterpret_cast<const float4*>(LAM + x * LP + 8 * p + 4);
+        *reinterpret_cast<float4*>(lend) = *reinterpret_cast<const float4*>(LAM + (C - 1) * LP + 8 * p);
+        *reinterpret_cast<float4*>(lend + 4) = *reinterpret_cast<const float4*>(LAM + (C - 1) * LP + 8 * p + 4);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          float qh = (qr[i] * rq) * r.scale, kh = kr[i];
+          if (r.round_in) qh = bf16r(qh);
+          if (l2) { kh *= rk; if (r.round_in) kh = bf16r(kh); }
+          const float el = expf(fminf(lam[i], 0.f)), eke = expf(fminf(lend[i] - lam[i], 0.f));
+          const float be = ba[i] * kh;
+          const float X = first ? be * el : 0.f, qe = first ? qh * el : 0.f, ke = last ? kh * eke : 0.f;
+          const float dbeta = dbp[i] + (first ? dx[i] * el : 0.f);
+          const float dq = dqp[i] + dmii * kh + (first ? dqe[i] * el : 0.f);
+          const float dk = dkp[i] + dmii * qh + (last ? dke[i] * eke : 0.f) + dbeta * ba[i];
+          odl[i] = be * dbp[i] + qh * dqp[i] - kh * dkp[i] + dx[i] * X + dqe[i] * qe;
+          odk[i] = dke[i] * ke;
+          float dbv = dbeta * kh;                               // d b_act
+          if (fuse) dbv *= ba[i] * (1.f - ba[i]);               // through the sigmoid
+          odb[i] = dbv;
+          sb2 += dbv;
+          dqp[i] = dq * g.scale;                                // d q_n (before the l2norm adjoint)
+          dkp[i] = dk;
+          dq_dot = fmaf(qr[i] * rq, dqp[i], dq_dot);
+          dk_dot = fmaf(kr[i] * rk, dkp[i], dk_dot);
+        }
+        st2x4(DQP4 + p4v(x, 8 * p), dqp);
+        st2x4(DKP4 + p4v(x, 8 * p), dkp);
+        *reinterpret_cast<float4*>(DLs + x * LP + 8 * p) = make_float4(odl[0], odl[1], odl[2], odl[3]);
+        *reinterpret_cast<float4*>(DLs + x * LP + 8 * p + 4) = make_float4(odl[4], odl[5], odl[6], odl[7]);
+        *reinterpret_cast<float4*>(DKs + x * LP + 8 * p) = make_float4(odk[0], odk[1], odk[2], odk[3]);
+        *reinterpret_cast<float4*>(DKs + x * LP + 8 * p + 4) = make_float4(odk[4], odk[5], odk[6], odk[7]);
+        if (live && r.bC != 1) out8(a.db, outb + 8 * p, a.db_dt, odb);
+      }
+      dq_dot += __shfl_xor_sync(0xffffffffu, dq_dot, 8);  dk_dot += __shfl_xor_sync(0xffffffffu, dk_dot, 8);
+      dq_dot += __shfl_xor_sync(0xffffffffu, dq_dot, 16); dk_dot += __shfl_xor_sync(0xffffffffu, dk_dot, 16);
+      if (r.bC == 1) {
+        sb2 += __shfl_xor_sync(0xffffffffu, sb2, 8);
+        sb2 += __shfl_xor_sync(0xffffffffu, sb2, 16);
+        if (live && lgrp == 0) stf(a.db, outb, sb2, a.db_dt);
+      }
+      if (live) {
+#pragma unroll 2
+        for (int it = 0; it < 4; ++it) {
+          const int p = it * 4 + lgrp;
+          float qr[8], kr[8], dqn[8], dkn[8];
+          raw_q8(r, x, p, qr);
+          raw_k8(r, x, p, kr);
+          ld2x4(DQP4 + p4v(x, 8 * p), dqn);
+          ld2x4(DKP4 + p4v(x, 8 * p), dkn);
+          if (l2) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              dqn[i] = rq * (dqn[i] - (qr[i] * rq) * dq_dot);
+              dkn[i] = rk * (dkn[i] - (kr[i] * rk) * dk_dot);
+            }
+          }
+          out8(a.dq, outqk + 8 * p, a.dq_dt, dqn);
+          out8(a.dk, outqk + 8 * p, a.dq_dt, dkn);
+        }
+      }
+      (void)rowqk;
+    }
+    __syncthreads();
+
+    DN_MARK(14);
     // ---- R. dg_t = sum_{i >= t, same doc} dLambda_i + the Lambda_end path (prefix sum of dke*ke over
-    //         earlier rows of the last document, plus the carried-state term)
-    if (tid < K) {
-      const int c = tid;
-      float run = 0.f;
-      for (int i = C - 1; i >= 0; --i) {
-        if (i < C - 1 && seg_s[i] != seg_s[i + 1]) run = 0.f;
-        run += DLs[i * LP + c];
-        DLs[i * LP + c] = run;
+    //         earlier rows of the last document, plus the carried-state term).  Thread (channel c,
+    //         quarter qd) scans 32 rows in registers; the quarters are chained through shared memory.
+    {
+      const int c = tid & 127, qd = tid >> 7, x0 = qd * 32;
+      float v[32];
+      float run = 0.f, ksum = 0.f;
+      int nb = -1;                                  // lowest row (largest index) after which a document ends
+#pragma unroll
+      for (int i = 31; i >= 0; --i) {
+        const int x = x0 + i;
+        if (i < 31 && seg_s[x] != seg_s[x + 1]) { run = 0.f; if (nb < 0) nb = i; }
+        run += DLs[x * LP + c];
+        v[i] = run;
+        if (seg_s[x] == segL) ksum += DKs[x * LP + c];
+      }
+      TOT[qd * 128 + c] = run;                      // sum from the quarter's first row to its first document end
+      TOT[512 + qd * 128 + c] = ksum;
+      if (c == 0) reset_s[4 + qd] = nb >= 0;
+      __syncthreads();
+      // what flows in from the rows below this quarter
+      float carry = 0.f;
+      for (int q2 = 3; q2 > qd; --q2) {
+        const bool joins = seg_s[q2 * 32] == seg_s[q2 * 32 - 1];      // quarter q2 continues the document above it
+        const float inner = reset_s[4 + q2] ? 0.f : carry;              // what passed through all of q2
+        carry = joins ? TOT[q2 * 128 + c] + inner : 0.f;
       }
       float acc = dlend_s[c];
-      for (int i = 0; i < C; ++i) {
-        if (seg_s[i] != segL) continue;
-        DLs[i * LP + c] += acc;
-        acc += DKs[i * LP + c];
+      for (int q2 = 0; q2 < qd; ++q2) acc += TOT[512 + q2 * 128 + c];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const int x = x0 + i;
+        float o = v[i] + (i > nb ? carry : 0.f);
+        if (seg_s[x] == segL) { o += acc; acc += DKs[x * LP + c]; }
+        DLs[x * LP + c] = o;
       }
     }
     __syncthreads();
-    // ---- W. row pass: gate adjoints, l2norm adjoint, writes (one warp per row, 4 channels per lane)
-    const int hq = h / g.qk_div;
-    const int hg = g.gate_head(h, g.gH), hb = g.gate_head(h, g.bH);
-    for (int i = warp; i < C; i += NT / 32) {
-      const int t = t0 + i;
-      if (t >= g.L) continue;
-      const size_t rowg = ((size_t)(b * (size_t)g.L + t) * g.gH + hg) * g.gC;
-      const size_t outg = ((size_t)(b * (size_t)g.L + t) * g.H + h) * g.gC;
-      const size_t outb = ((size_t)(b * (size_t)g.L + t) * g.H + h) * g.bC;
-      const size_t rowqk = ((size_t)(b * (size_t)g.L + t) * g.Hk + hq) * K;
-      const size_t outqk = ((size_t)(b * (size_t)g.L + t) * g.H + h) * K;
-      const float rq = rq_s[i], rk = rk_s[i];
-      float sg = 0.f, sb2 = 0.f, qn[4], kn[4], dqn[4], dkn[4], dq_dot = 0.f, dk_dot = 0.f;
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int c = lane + 32 * u;
-        const float gr = ldf(a.gg, rowg + (g.gC == 1 ? 0 : c), g.gate_dt);
-        float dgv = DLs[i * LP + c], dbv = DBP[i * K + c];
-        if (fuse) {
-          const float gexp = -expf(fminf(gr, 5.f));
-          const bool pass = gr <= 5.f && (!guard || gexp < -1e-6f);
-          dgv = pass ? dgv * gexp : 0.f;
-          float bb = ldf(r.b, r.b_row0 + (size_t)i * r.b_pitch + (r.bC == 1 ? 0 : c), r.gate_dt);
-          bb = 1.f / (1.f + expf(-bb));
-          dbv = dbv * (bb * (1.f - bb));
+
+    DN_MARK(15);
+    // ---- dg: one warp per row, 4 channels per lane
+    {
+      const int hg = g.gate_head(h, g.gH);
+#pragma unroll 4
+      for (int i = warp; i < C; i += NT / 32) {
+        const bool live = t0 + i < g.L;
+        const int t = live ? t0 + i : t0;              // a row past the end reads row 0 and writes nothing
+        const size_t tok = (size_t)b * g.L + t;
+        const size_t rowg = (tok * g.gH + hg) * r.gC, outg = (tok * g.H + h) * r.gC;
+        const float4 dl = *reinterpret_cast<const float4*>(DLs + i * LP + 4 * lane);
+        float dgv[4] = {dl.x, dl.y, dl.z, dl.w}, gr[4];
+        if (r.gC == 1) { gr[0] = gr[1] = gr[2] = gr[3] = ldf_ro(a.gg, rowg, gdt); }
+        else if (gdt == DN_BF16) {
+          const uint2 u = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(a.gg) + rowg + 4 * lane));
+          gr[0] = __uint_as_float(u.x << 16); gr[1] = __uint_as_float(u.x & 0xffff0000u);
+          gr[2] = __uint_as_float(u.y << 16); gr[3] = __uint_as_float(u.y & 0xffff0000u);
         } else {
-          dgv = gr <= 0.f ? dgv : 0.f;
+          const float4 u = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.gg) + rowg + 4 * lane));
+          gr[0] = u.x; gr[1] = u.y; gr[2] = u.z; gr[3] = u.w;
         }
-        if (g.gC == 1) sg += dgv; else stf(a.dg, outg + c, dgv, a.dg_dt);
-        if (g.bC == 1) sb2 += dbv; else stf(a.db, outb + c, dbv, a.db_dt);
-        qn[u] = ldf(a.q, rowqk + c, g.qkv_dt) * rq;
-        kn[u] = ldf(a.k, rowqk + c, g.qkv_dt) * rk;
-        dqn[u] = DQP[i * K + c] * g.scale;
-        dkn[u] = DKP[i * K + c];
-        dq_dot += qn[u] * dqn[u];
-        dk_dot += kn[u] * dkn[u];
-      }
-      if (g.gC == 1) { sg = warp_sum(sg); if (lane == 0) stf(a.dg, outg, sg, a.dg_dt); }
-      if (g.bC == 1) { sb2 = warp_sum(sb2); if (lane == 0) stf(a.db, outb, sb2, a.db_dt); }
-      if (l2) { dq_dot = warp_sum(dq_dot); dk_dot = warp_sum(dk_dot); }
+        float sg = 0.f;
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int c = lane + 32 * u;
-        stf(a.dq, outqk + c, l2 ? rq * (dqn[u] - qn[u] * dq_dot) : dqn[u], a.dq_dt);
-        stf(a.dk, outqk + c, l2 ? rk * (dkn[u] - kn[u] * dk_dot) : dkn[u], a.dq_dt);
+        for (int u = 0; u < 4; ++u) {
+          if (fuse) {
+            const float gexp = -expf(fminf(gr[u], 5.f));
+            const bool pass = gr[u] <= 5.f && (!guard || gexp < -1e-6f);
+            dgv[u] = pass ? dgv[u] * gexp : 0.f;
+          } else {
+            dgv[u] = gr[u] <= 0.f ? dgv[u] : 0.f;
+          }
+          sg += dgv[u];
+        }
+        if (r.gC == 1) { sg = warp_sum(sg); if (lane == 0 && live) stf(a.dg, outg, sg, a.dg_dt); }
+        else if (!live) { }
+        else if (a.dg_dt == DN_BF16)
+          *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(a.dg) + outg + 4 * lane) = make_uint2(umma::pack2(dgv[0], dgv[1]), umma::pack2(dgv[2], dgv[3]));
+        else
+          *reinterpret_cast<float4*>(reinterpret_cast<float*>(a.dg) + outg + 4 * lane) = make_float4(dgv[0], dgv[1], dgv[2], dgv[3]);
       }
     }
+
+    DN_MARK(16);
     // ---- V. dv = dY * w_act, dw = dY * v (+ sigmoid adjoint; summed over a value head's columns
-    //         when w is one scalar per head)
-    constexpr int PV = VW / 8;
-    const int pieces_per_head = g.V / 8;
-    for (int e = tid; e < C * PV; e += NT) {
-      const int x = e / PV, p = e - x * PV, t = t0 + x;
+    //         when w is one scalar per head): 8 rows x 4 pieces per warp step
+    {
+      constexpr int PV = VW / 8;
+      const int x = myrow, t = t0 + x;
+      const bool live = t < g.L;
+      const size_t tok = (size_t)b * g.L + t;
+      const int steps_per_head = g.V / 32;            // warp steps that cover one value head
       float sw = 0.f;
-      const int col0 = h * VW + 8 * p, hv = col0 / g.V, cv = col0 - hv * g.V;
-      if (t < g.L) {
-        const size_t vrow = (size_t)(b * (size_t)g.L + t) * g.Hv * g.V + col0;
-        const size_t wrow = ((size_t)(b * (size_t)g.L + t) * g.wH + g.w_head(hv)) * g.wC;
-        float vv[8], ww[8], dv8[8], dw8[8];
-        load8(a.v, vrow, g.qkv_dt, vv);
-        if (g.wC == 1) {
-          const float w1 = ldf(a.w, wrow, g.gate_dt);
+      const size_t tokr = live ? tok : (size_t)b * g.L + t0;      // row read when this one does not exist
+#pragma unroll 4
+      for (int it = 0; it < PV / 4; ++it) {
+        const int p = it * 4 + lgrp;
+        const int col0 = h * VW + 8 * p, hv = col0 / g.V, cv = col0 - hv * g.V;
+        float vv[8], ww[8], dy[8], dv8[8], dw8[8];
+        load8(a.v, tokr * g.Hv * g.V + col0, qdt, vv);
+        if (wC == 1) {
+          const float w1 = ldf_ro(a.w, tokr * g.wH + g.w_head(hv), gdt);
 #pragma unroll
           for (int i = 0; i < 8; ++i) ww[i] = w1;
         } else {
-          load8(a.w, wrow + cv, g.gate_dt, ww);
+          load8(a.w, (tokr * g.wH + g.w_head(hv)) * wC + cv, gdt, ww);
         }
-        const float4 y0 = *reinterpret_cast<const float4*>(DY + (size_t)x * VW + 8 * p), y1 = *reinterpret_cast<const float4*>(DY + (size_t)x * VW + 8 * p + 4);
-        const float dy[8] = {y0.x, y0.y, y0.z, y0.w, y1.x, y1.y, y1.z, y1.w};
+        ld2x4(DY4 + p4v(x, 8 * p), dy);
+        if (live) {
+          const size_t vrow = tok * g.Hv * g.V + col0;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          float wa = ww[i], dwv = dy[i] * vv[i];
-          if (fuse) { wa = 1.f / (1.f + expf(-ww[i])); dwv *= wa * (1.f - wa); }
-          dv8[i] = dy[i] * wa;
-          dw8[i] = dwv;
-          sw += dwv;
+          for (int i = 0; i < 8; ++i) {
+            float wa = ww[i], dwv = dy[i] * vv[i];
+            if (fuse) { wa = 1.f / (1.f + expf(-ww[i])); dwv *= wa * (1.f - wa); }
+            dv8[i] = dy[i] * wa;
+            dw8[i] = dwv;
+            sw += dwv;
+          }
+          out8(a.dv, vrow, qdt, dv8);
+          if (wC != 1) out8(a.dw, (tok * g.Hv + hv) * wC + cv, a.dw_dt, dw8);
         }
-        if (g.qkv_dt == DN_BF16) *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.dv) + vrow) = umma::pack8(dv8);
-        else {
-          float4* d = reinterpret_cast<float4*>(reinterpret_cast<float*>(a.dv) + vrow);
-          d[0] = make_float4(dv8[0], dv8[1], dv8[2], dv8[3]);
-          d[1] = make_float4(dv8[4], dv8[5], dv8[6], dv8[7]);
+        if (wC == 1 && (it + 1) % steps_per_head == 0) {
+          sw += __shfl_xor_sync(0xffffffffu, sw, 8);
+          sw += __shfl_xor_sync(0xffffffffu, sw, 16);
+          if (live && lgrp == 0) stf(a.dw, tok * g.Hv + hv, sw, a.dw_dt);
+          sw = 0.f;
         }
-        if (g.wC != 1) {
-          const size_t outw = ((size_t)(b * (size_t)g.L + t) * g.Hv + hv) * g.wC + cv;
-#pragma unroll
-          for (int i = 0; i < 8; ++i) stf(a.dw, outw + i, dw8[i], a.dw_dt);
-        }
-      }
-      if (g.wC == 1) {
-        for (int o = pieces_per_head >> 1; o > 0; o >>= 1) sw += __shfl_xor_sync(0xffffffffu, sw, o);
-        if (t < g.L && (p % pieces_per_head) == 0)
-          stf(a.dw, (size_t)(b * (size_t)g.L + t) * g.Hv + hv, sw, a.dw_dt);
       }
     }
     __syncthreads();
+#ifdef DN_PHASE_TIMING
+    DN_MARK(17);
+    if (blockIdx.x == 0 && tid == 0 && item == 0) {
+      for (int i = 1; i < 18; ++i) printf("mark %d -> %d: %lld\n", i - 1, i, g_phase_marks[i] - g_phase_marks[i - 1]);
+      printf("item total %lld\n", g_phase_marks[17] - g_phase_marks[0]);
+    }
+#endif
   }
   umma::tc_fence_before();
   __syncthreads();
@@ -412,13 +620,16 @@ int launch_prepass_bwd_tc(PrepassBwdArgs& a, size_t scratch_floats, cudaStream_t
   const size_t lam_phase = (size_t)C * LP * 4 + 4 * 32768;
   size_t smem = bwd_tc_image_bytes(g.Vw);
   if (smem < lam_phase) smem = lam_phase;
-  if (smem < (size_t)3 * C * LP * 4) smem = (size_t)3 * C * LP * 4;
+  if (smem < (size_t)3 * C * LP * 4 + 4096) smem = (size_t)3 * C * LP * 4 + 4096;
+  auto go = [&](auto kernel) {
+    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    kernel<<<grid, NT, smem, st>>>(a);
+  };
+  const int mode = input_mode(g);
   if (g.Vw == 256) {
-    cudaFuncSetAttribute(prepass_bwd_tc_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    prepass_bwd_tc_kernel<256><<<grid, NT, smem, st>>>(a);
+    if (mode == 0) go(prepass_bwd_tc_kernel<256, 0>); else if (mode == 1) go(prepass_bwd_tc_kernel<256, 1>); else go(prepass_bwd_tc_kernel<256, 2>);
   } else {
-    cudaFuncSetAttribute(prepass_bwd_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    prepass_bwd_tc_kernel<128><<<grid, NT, smem, st>>>(a);
+    if (mode == 0) go(prepass_bwd_tc_kernel<128, 0>); else if (mode == 1) go(prepass_bwd_tc_kernel<128, 1>); else go(prepass_bwd_tc_kernel<128, 2>);
   }
   return cudaGetLastError() == cudaSuccess ? DN_OK : DN_ERR_CUDA_LAUNCH;
 }

@@ -6,48 +6,93 @@
 // and are drained one row per thread.  An image written once serves as a matrix and as its
 // transpose (the descriptor says which), which is why S, V_new, dV, W and U are staged only once
 // per use group:
-//   1. V_new = U - W S                      A = W (P)        B = S (X)          -> image Y
-//   2. dqe   = dO S^T ; dM = dO V_new^T      A = dO (Z)       B = S (X), V_new (Y)
-//   3. dW    = -dV S^T                       A = dV (Z)       B = S (X)          -> image P
-//   4. dke   = V_new dH^T                    A = V_new (Y)    B = dH (X)
-//   5. dX    = T^T dW ; dY = T^T dV          A = T^T (Y)      B = dW (P), dV (Z) -> images Y', X
+//   1. V_new = W (-S) + I U                  A = W (P), I (Y)   B = -S (X), U (Z) -> image Y
+//   2. dqe   = dO S^T ; dM = dO V_new^T      A = dO (Z)         B = -S (X), V_new (Y)
+//   3. dW    = -dV S^T                       A = dV (Z)         B = -S (X)        -> image P
+//   4. dke   = V_new dH^T                    A = V_new (Y)      B = dH (X)
+//   5. dX    = T^T dW ; dY = T^T dV          A = T^T (Y)        B = dW (P), dV (Z) -> images Y', X
 //   6. dA    = -(dX W^T + dY U^T)            A = dX (Y'), dY (X)   B = W (P), U (Z)
+//
+// Global memory is touched in two patterns only.  Inputs are read by warps that cover 8 rows x 4
+// pieces of 8 elements per step (stage_coords), through the read-only path so that several loads
+// stay in flight.  fp32 results go to the per-CTA scratch in a PANEL layout, [column / 4][row][4]:
+// a thread that owns one row of tensor memory then writes 16 bytes next to its neighbours' and a
+// warp store covers 512 contiguous bytes.
 #pragma once
 #include "dn_common.cuh"
 #include "dn_umma.cuh"
 
 namespace dn {
 
+// Optional phase clock (compile with -DDN_PHASE_TIMING): CTA 0 records clock64 at marked points of
+// its first item and prints the differences.  Compiled out otherwise.
+#ifdef DN_PHASE_TIMING
+__device__ long long g_phase_marks[48];
+#define DN_MARK(i) do { if (blockIdx.x == 0 && threadIdx.x == 0) g_phase_marks[i] = clock64(); } while (0)
+#else
+#define DN_MARK(i) do { } while (0)
+#endif
+
+// float4 index of (row, col) in a panel-layout array (col a multiple of 4)
+__device__ __forceinline__ int p4v(int row, int col) { return ((col >> 2) << 7) + row; }
+// float index of (row, col) in a panel-layout array
+__device__ __forceinline__ int p4f(int row, int col) { return ((((col >> 2) << 7) + row) << 2) + (col & 3); }
+
 struct BwdTcIo {
   const __nv_bfloat16 *W, *U;          // this item's (128,128) and (128,VW) tiles
   const float *S, *dH, *dV, *T;        // this item's fp32 arrays: (128,VW), (128,VW), (128,VW), (128,128)
+  const float* lam_end;                // this item's (128) log-decay to the chunk end
   const void* d_out;                   // whole tensor
   int qkv_dt;
   size_t dO_off;                       // element offset of (row 0, column 0) of this item's dO block
   size_t dO_pitch;                     // elements between token rows
   int rows_valid;                      // rows of the chunk that exist (others read as 0)
-  float *DQE, *DKE, *DX, *DY, *DM, *DA;  // fp32 results in scratch
+  float *DQE, *DKE, *DX, *DY, *DM, *DA;  // fp32 results in scratch, panel layout
+  float* dlend_s;                      // out (shared, 128): [one doc] exp(lam_end) * sum_v dH * S
+  bool all_same;
   const int* seg_s;
   bool trunc;
 };
 
-template <int R, int NT>
-__device__ __forceinline__ void stage_f32(uint4* dst, const float* src, int pitch, int panels) {
-  for (int e = threadIdx.x; e < panels * R; e += NT) {
-    const int p = e / R, x = e - p * R;
-    dst[e] = umma::ld8_f32(src + (size_t)x * pitch + 8 * p);
+// Operand staging.  A warp covers 8 rows x 4 panels per step: its 32 global loads fall in 8 row
+// segments of 128 B (fp32) or 64 B (bf16), and each quarter-warp writes 8 consecutive rows of one
+// panel (128 contiguous bytes of shared memory).  With 512 threads and 128 rows a thread keeps the
+// same row over all its steps: row = 8 * warp + (lane & 7).
+template <int R>
+__device__ __forceinline__ void stage_coords(int e, int& p, int& x) {
+  const int lane = e & 31, w = e >> 5;
+  x = (w % (R / 8)) * 8 + (lane & 7);
+  p = (w / (R / 8)) * 4 + (lane >> 3);
+}
+template <int R, int PANELS, int NT, bool NEGATE = false>
+__device__ __forceinline__ void stage_f32(uint4* dst, const float* src, int pitch) {
+  static_assert((PANELS * R) % NT == 0, "whole passes");
+#pragma unroll 8
+  for (int it = 0; it < PANELS * R / NT; ++it) {
+    int p, x;
+    stage_coords<R>(it * NT + threadIdx.x, p, x);
+    uint4 v = umma::ld8_f32_ro(src + (size_t)x * pitch + 8 * p);
+    if (NEGATE) { v.x ^= 0x80008000u; v.y ^= 0x80008000u; v.z ^= 0x80008000u; v.w ^= 0x80008000u; }
+    dst[p * R + x] = v;
   }
 }
-template <int R, int NT>
-__device__ __forceinline__ void stage_bf16(uint4* dst, const __nv_bfloat16* src, int pitch, int panels) {
-  for (int e = threadIdx.x; e < panels * R; e += NT) {
-    const int p = e / R, x = e - p * R;
-    dst[e] = umma::ld8_bf16(src + (size_t)x * pitch + 8 * p);
+// bf16 sources need no conversion: asynchronous 16-byte copies, no registers.  The caller waits
+// (umma::cp_async_wait<0>) before the operands are handed to the tensor core.
+template <int R, int PANELS, int NT>
+__device__ __forceinline__ void stage_bf16_async(uint4* dst, const __nv_bfloat16* src, int pitch) {
+  static_assert((PANELS * R) % NT == 0, "whole passes");
+#pragma unroll
+  for (int it = 0; it < PANELS * R / NT; ++it) {
+    int p, x;
+    stage_coords<R>(it * NT + threadIdx.x, p, x);
+    umma::cp_async16(dst + p * R + x, src + (size_t)x * pitch + 8 * p);
   }
+  umma::cp_async_commit();
 }
 
 template <int VW, int NT>
 __device__ __forceinline__ void bwd_gemms_tc(umma::Ctx& cx, uint8_t* img, const BwdTcIo& io) {
+  static_assert(NT == 512, "a thread keeps one row while staging");
   constexpr int SLOT = 128 * VW * 2;
   uint4* X = reinterpret_cast<uint4*>(img);
   uint4* Y = reinterpret_cast<uint4*>(img + SLOT);
@@ -57,107 +102,148 @@ __device__ __forceinline__ void bwd_gemms_tc(umma::Ctx& cx, uint8_t* img, const 
   if (VW == 128) Y2 = reinterpret_cast<uint4*>(img + 3 * SLOT + 32768);   // ... an extra slot after P
   constexpr int PV = VW / 8;                      // panels along the value width
   const int* seg_s = io.seg_s;
+  float4* DQE4 = reinterpret_cast<float4*>(io.DQE);
+  float4* DKE4 = reinterpret_cast<float4*>(io.DKE);
+  float4* DX4 = reinterpret_cast<float4*>(io.DX);
+  float4* DY4 = reinterpret_cast<float4*>(io.DY);
+  float4* DM4 = reinterpret_cast<float4*>(io.DM);
+  float4* DA4 = reinterpret_cast<float4*>(io.DA);
 
-  // ---- 1. V_new = U - W S
-  stage_bf16<128, NT>(P, io.W, 128, 16);
-  stage_f32<128, NT>(X, io.S, VW, PV);
+  DN_MARK(1);
+  // ---- 1. V_new = U - W S, as W (-S) + I U so that U arrives through the tensor core as well.
+  //         The image X holds -S from here to step 3.
+  stage_bf16_async<128, 16, NT>(P, io.W, 128);
+  stage_bf16_async<128, PV, NT>(Z, io.U, VW);
+  stage_f32<128, PV, NT, true>(X, io.S, VW);
+  for (int e = threadIdx.x; e < 128 * 16; e += NT) {          // identity, K-major
+    const int p = e >> 7, x = e & 127;
+    uint32_t w[4] = {0u, 0u, 0u, 0u};
+    if ((x >> 3) == p) w[(x & 7) >> 1] = 0x3F80u << (16 * (x & 1));
+    Y[e] = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+  umma::cp_async_wait<0>();
   umma::pre_issue_sync();
   umma::issue<VW, false, true>(cx, P, X, 128, 0, false);
+  umma::issue<VW, false, true>(cx, Y, Z, 128, 0, true);
   umma::commit_wait(cx);
   umma::drain<NT, VW>(cx, 0, [&](int row, int col, const float (&v)[16]) {
-    float u0[8], u1[8];
-    const uint4* up = reinterpret_cast<const uint4*>(io.U + (size_t)row * VW + col);
-    umma::unpack8(up[0], u0);
-    umma::unpack8(up[1], u1);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) { u0[i] -= v[i]; u1[i] -= v[8 + i]; }
-    Y[(col / 8) * 128 + row] = umma::pack8(u0);
-    Y[(col / 8 + 1) * 128 + row] = umma::pack8(u1);
+    Y[(col / 8) * 128 + row] = umma::pack8p(v);
+    Y[(col / 8 + 1) * 128 + row] = umma::pack8p(v + 8);
   });
 
-  // ---- 2. dqe = dO S^T, dM = dO V_new^T
-  for (int e = threadIdx.x; e < PV * 128; e += NT) {
-    const int p = e / 128, x = e - p * 128;
-    uint4 val = make_uint4(0, 0, 0, 0);
-    if (x < io.rows_valid) {
-      const size_t off = io.dO_off + (size_t)x * io.dO_pitch + 8 * p;
-      val = io.qkv_dt == DN_BF16 ? umma::ld8_bf16(reinterpret_cast<const __nv_bfloat16*>(io.d_out) + off)
-                                 : umma::ld8_f32(reinterpret_cast<const float*>(io.d_out) + off);
+  DN_MARK(2);
+  // ---- 2. dqe = dO S^T (= -(dO X^T)), dM = dO V_new^T
+  if (io.qkv_dt == DN_BF16) {
+#pragma unroll
+    for (int it = 0; it < PV * 128 / NT; ++it) {
+      int p, x;
+      stage_coords<128>(it * NT + threadIdx.x, p, x);
+      if (x < io.rows_valid)
+        umma::cp_async16(Z + p * 128 + x, reinterpret_cast<const __nv_bfloat16*>(io.d_out) + io.dO_off + (size_t)x * io.dO_pitch + 8 * p);
+      else
+        Z[p * 128 + x] = make_uint4(0, 0, 0, 0);
     }
-    Z[e] = val;
+    umma::cp_async_commit();
+    umma::cp_async_wait<0>();
+  } else {
+#pragma unroll 8
+    for (int it = 0; it < PV * 128 / NT; ++it) {
+      int p, x;
+      stage_coords<128>(it * NT + threadIdx.x, p, x);
+      const bool live = x < io.rows_valid;
+      uint4 val = umma::ld8_f32_ro(reinterpret_cast<const float*>(io.d_out) + io.dO_off + (size_t)(live ? x : 0) * io.dO_pitch + 8 * p);
+      if (!live) val = make_uint4(0, 0, 0, 0);
+      Z[p * 128 + x] = val;
+    }
   }
   umma::pre_issue_sync();
   umma::issue<128, false, false>(cx, Z, X, VW, 256, false);
   umma::issue<128, false, false>(cx, Z, Y, VW, 384, false);
   umma::commit_wait(cx);
   umma::drain<NT, 128>(cx, 256, [&](int row, int col, const float (&v)[16]) {
-    float4* d = reinterpret_cast<float4*>(io.DQE + row * 128 + col);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) d[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+    for (int i = 0; i < 4; ++i) DQE4[p4v(row, col + 4 * i)] = make_float4(-v[4 * i], -v[4 * i + 1], -v[4 * i + 2], -v[4 * i + 3]);
   });
   umma::drain<NT, 128>(cx, 384, [&](int row, int col, const float (&v)[16]) {
     float m[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) m[i] = (row >= col + i && seg_s[row] == seg_s[col + i]) ? v[i] : 0.f;
-    float4* d = reinterpret_cast<float4*>(io.DM + row * 128 + col);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) d[i] = make_float4(m[4 * i], m[4 * i + 1], m[4 * i + 2], m[4 * i + 3]);
+    for (int i = 0; i < 4; ++i) DM4[p4v(row, col + 4 * i)] = make_float4(m[4 * i], m[4 * i + 1], m[4 * i + 2], m[4 * i + 3]);
   });
 
-  // ---- 3. dW = -dV S^T (kept only as the operand image of step 5)
-  stage_f32<128, NT>(Z, io.dV, VW, PV);
+  DN_MARK(3);
+  // ---- 3. dW = -dV S^T = dV X^T (kept only as the operand image of step 5)
+  stage_f32<128, PV, NT>(Z, io.dV, VW);
   umma::pre_issue_sync();
   umma::issue<128, false, false>(cx, Z, X, VW, 0, false);
   umma::commit_wait(cx);
   umma::drain<NT, 128>(cx, 0, [&](int row, int col, const float (&v)[16]) {
-    float a[8], b[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) { a[i] = -v[i]; b[i] = -v[8 + i]; }
-    P[(col / 8) * 128 + row] = umma::pack8(a);
-    P[(col / 8 + 1) * 128 + row] = umma::pack8(b);
+    P[(col / 8) * 128 + row] = umma::pack8p(v);
+    P[(col / 8 + 1) * 128 + row] = umma::pack8p(v + 8);
   });
 
-  // ---- 4. dke = V_new dH^T
-  stage_f32<128, NT>(X, io.dH, VW, PV);
+  DN_MARK(4);
+  // ---- 4. dke = V_new dH^T.  While dH is staged, the same threads read S once more in fp32 and
+  //         reduce dLambda_end = [one doc] exp(Lambda_end) sum_v dH * S  (gdn2.py:759-762): a thread
+  //         keeps one row, the four threads of a row sit 8 lanes apart.
+  {
+    float part = 0.f;
+    int row = 0;
+#pragma unroll 4
+    for (int it = 0; it < PV * 128 / NT; ++it) {
+      int p, x;
+      stage_coords<128>(it * NT + threadIdx.x, p, x);
+      row = x;
+      const float4* ph = reinterpret_cast<const float4*>(io.dH + (size_t)x * VW + 8 * p);
+      const float4* ps = reinterpret_cast<const float4*>(io.S + (size_t)x * VW + 8 * p);
+      const float4 h0 = __ldg(ph), h1 = __ldg(ph + 1), s0 = __ldg(ps), s1 = __ldg(ps + 1);
+      part += h0.x * s0.x + h0.y * s0.y + h0.z * s0.z + h0.w * s0.w + h1.x * s1.x + h1.y * s1.y + h1.z * s1.z + h1.w * s1.w;
+      X[p * 128 + x] = make_uint4(umma::pack2(h0.x, h0.y), umma::pack2(h0.z, h0.w), umma::pack2(h1.x, h1.y), umma::pack2(h1.z, h1.w));
+    }
+    part += __shfl_xor_sync(0xffffffffu, part, 8);
+    part += __shfl_xor_sync(0xffffffffu, part, 16);
+    if ((threadIdx.x & 31) < 8) io.dlend_s[row] = io.all_same ? part * expf(fminf(__ldg(io.lam_end + row), 0.f)) : 0.f;
+  }
   umma::pre_issue_sync();
   umma::issue<128, false, false>(cx, Y, X, VW, 128, false);
   umma::commit_wait(cx);
   umma::drain<NT, 128>(cx, 128, [&](int row, int col, const float (&v)[16]) {
-    float4* d = reinterpret_cast<float4*>(io.DKE + row * 128 + col);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) d[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+    for (int i = 0; i < 4; ++i) DKE4[p4v(row, col + 4 * i)] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
   });
 
+  DN_MARK(5);
   // ---- 5. dX = T^T dW, dY = T^T dV
-  stage_f32<128, NT>(Y, io.T, 128, 16);
+  stage_f32<128, 16, NT>(Y, io.T, 128);
   umma::pre_issue_sync();
   umma::issue<128, true, true>(cx, Y, P, 128, 0, false);
   umma::issue<VW, true, true>(cx, Y, Z, 128, 256, false);
   umma::commit_wait(cx);
   umma::drain<NT, 128>(cx, 0, [&](int row, int col, const float (&v)[16]) {
-    float a[8], b[8];
+    float r[16];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) { a[i] = io.trunc ? bf16r(v[i]) : v[i]; b[i] = io.trunc ? bf16r(v[8 + i]) : v[8 + i]; }
-    float4* d = reinterpret_cast<float4*>(io.DX + row * 128 + col);
-    d[0] = make_float4(a[0], a[1], a[2], a[3]); d[1] = make_float4(a[4], a[5], a[6], a[7]);
-    d[2] = make_float4(b[0], b[1], b[2], b[3]); d[3] = make_float4(b[4], b[5], b[6], b[7]);
-    Y2[(col / 8) * 128 + row] = umma::pack8(a);
-    Y2[(col / 8 + 1) * 128 + row] = umma::pack8(b);
+    for (int i = 0; i < 16; ++i) r[i] = io.trunc ? bf16r(v[i]) : v[i];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) DX4[p4v(row, col + 4 * i)] = make_float4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
+    Y2[(col / 8) * 128 + row] = umma::pack8p(r);
+    Y2[(col / 8 + 1) * 128 + row] = umma::pack8p(r + 8);
   });
   umma::drain<NT, VW>(cx, 256, [&](int row, int col, const float (&v)[16]) {
-    float a[8], b[8];
+    float r[16];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) { a[i] = io.trunc ? bf16r(v[i]) : v[i]; b[i] = io.trunc ? bf16r(v[8 + i]) : v[8 + i]; }
-    float4* d = reinterpret_cast<float4*>(io.DY + (size_t)row * VW + col);
-    d[0] = make_float4(a[0], a[1], a[2], a[3]); d[1] = make_float4(a[4], a[5], a[6], a[7]);
-    d[2] = make_float4(b[0], b[1], b[2], b[3]); d[3] = make_float4(b[4], b[5], b[6], b[7]);
-    X[(col / 8) * 128 + row] = umma::pack8(a);
-    X[(col / 8 + 1) * 128 + row] = umma::pack8(b);
+    for (int i = 0; i < 16; ++i) r[i] = io.trunc ? bf16r(v[i]) : v[i];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) DY4[p4v(row, col + 4 * i)] = make_float4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
+    X[(col / 8) * 128 + row] = umma::pack8p(r);
+    X[(col / 8 + 1) * 128 + row] = umma::pack8p(r + 8);
   });
 
+  DN_MARK(6);
   // ---- 6. dA = -(dX W^T + dY U^T), strictly lower and same document
-  stage_bf16<128, NT>(P, io.W, 128, 16);
-  stage_bf16<128, NT>(Z, io.U, VW, PV);
+  stage_bf16_async<128, 16, NT>(P, io.W, 128);
+  stage_bf16_async<128, PV, NT>(Z, io.U, VW);
+  umma::cp_async_wait<0>();
   umma::pre_issue_sync();
   umma::issue<128, false, false>(cx, Y2, P, 128, 0, false);
   umma::issue<128, false, false>(cx, X, Z, VW, 0, true);
@@ -166,9 +252,8 @@ __device__ __forceinline__ void bwd_gemms_tc(umma::Ctx& cx, uint8_t* img, const 
     float m[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) m[i] = (row > col + i && seg_s[row] == seg_s[col + i]) ? -v[i] : 0.f;
-    float4* d = reinterpret_cast<float4*>(io.DA + row * 128 + col);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) d[i] = make_float4(m[4 * i], m[4 * i + 1], m[4 * i + 2], m[4 * i + 3]);
+    for (int i = 0; i < 4; ++i) DA4[p4v(row, col + 4 * i)] = make_float4(m[4 * i], m[4 * i + 1], m[4 * i + 2], m[4 * i + 3]);
   });
   __syncthreads();
 }

@@ -113,11 +113,28 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
 __device__ __forceinline__ uint4 pack8(const float (&x)[8]) {
   return make_uint4(pack2(x[0], x[1]), pack2(x[2], x[3]), pack2(x[4], x[5]), pack2(x[6], x[7]));
 }
+__device__ __forceinline__ uint4 pack8p(const float* x) {
+  return make_uint4(pack2(x[0], x[1]), pack2(x[2], x[3]), pack2(x[4], x[5]), pack2(x[6], x[7]));
+}
+// 2^x for x <= 0 on the special-function unit, results below the normal range flushed to 0
+__device__ __forceinline__ float ex2_fast(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ uint4 ld8_f32(const float* p) {       // 8 consecutive floats -> 8 bf16
   const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
   return make_uint4(pack2(a.x, a.y), pack2(a.z, a.w), pack2(b.x, b.y), pack2(b.z, b.w));
 }
 __device__ __forceinline__ uint4 ld8_bf16(const __nv_bfloat16* p) { return *reinterpret_cast<const uint4*>(p); }
+// The same two loads through the read-only path: only for data written by EARLIER launches.  The
+// compiler may move these above shared-memory stores, which is what lets a staging loop keep
+// several loads in flight.
+__device__ __forceinline__ uint4 ld8_f32_ro(const float* p) {
+  const float4 a = __ldg(reinterpret_cast<const float4*>(p)), b = __ldg(reinterpret_cast<const float4*>(p + 4));
+  return make_uint4(pack2(a.x, a.y), pack2(a.z, a.w), pack2(b.x, b.y), pack2(b.z, b.w));
+}
+__device__ __forceinline__ uint4 ld8_bf16_ro(const __nv_bfloat16* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
 __device__ __forceinline__ void unpack8(uint4 u, float (&x)[8]) {
   const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
