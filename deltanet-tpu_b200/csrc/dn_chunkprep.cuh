@@ -127,56 +127,65 @@ __device__ __forceinline__ void beta8(const Rows& r, int x, int p, float (&o)[8]
   for (int i = 0; i < 8; ++i) o[i] *= kk[i];
 }
 
-// Row normalisers: one warp per row.
-template <int NT>
-__device__ __forceinline__ void row_norms(const Rows& r, float* rq, float* rk) {
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int x = warp; x < C; x += NT / 32) {
-    float sq = 0.f, sk = 0.f;
-    if (r.l2 && x < r.rows_valid) {
+// Row normalisers, 512 threads, a warp covering 8 rows x 4 pieces: thread (myrow = 8*warp + (lane&7),
+// lgrp = lane>>3) sums its 4 pieces of q and k, the four threads of a row sit 8 lanes apart.
+__device__ __forceinline__ void row_norms_8x4(const Rows& r, int myrow, int lgrp, float* rq, float* rk) {
+  float sq = 0.f, sk = 0.f;
+  if (r.l2) {                       // rows past the end read as zero
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const float a = ldf_ro(r.q, r.qk_row0 + (size_t)x * r.qk_pitch + lane + 32 * u, r.qkv_dt);
-        const float b = ldf_ro(r.k, r.qk_row0 + (size_t)x * r.qk_pitch + lane + 32 * u, r.qkv_dt);
-        sq += a * a;
-        sk += b * b;
-      }
+    for (int it = 0; it < 4; ++it) {
+      float qv[8], kv[8];
+      raw_q8(r, myrow, it * 4 + lgrp, qv);
+      raw_k8(r, myrow, it * 4 + lgrp, kv);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { sq = fmaf(qv[i], qv[i], sq); sk = fmaf(kv[i], kv[i], sk); }
     }
-    sq = warp_sum(sq);
-    sk = warp_sum(sk);
-    if (lane == 0) {
-      rq[x] = r.l2 ? rsqrtf(sq + 1e-6f) : 1.f;
-      rk[x] = r.l2 ? rsqrtf(sk + 1e-6f) : 1.f;
-    }
+  }
+  sq += __shfl_xor_sync(0xffffffffu, sq, 8);  sk += __shfl_xor_sync(0xffffffffu, sk, 8);
+  sq += __shfl_xor_sync(0xffffffffu, sq, 16); sk += __shfl_xor_sync(0xffffffffu, sk, 16);
+  if (lgrp == 0) {
+    rq[myrow] = r.l2 ? rsqrtf(sq + 1e-6f) : 1.f;
+    rk[myrow] = r.l2 ? rsqrtf(sk + 1e-6f) : 1.f;
   }
 }
 
 // Cumulative log-decay of the chunk into shared memory (C rows of pitch LP, fp32), restarting at
-// document changes.  Needs a __syncthreads() before and leaves one after.
-template <int NT>
-__device__ __forceinline__ void build_lambda(const Rows& r, const int* seg_s, float* LAM) {
-  for (int e = threadIdx.x; e < IMG; e += NT) {
-    const int x = e >> 4, p = e & 15;
-    float gv[8];
-    gact8(r, x, p, gv);
-    float4* d = reinterpret_cast<float4*>(LAM + x * LP + 8 * p);
-    d[0] = make_float4(gv[0], gv[1], gv[2], gv[3]);
-    d[1] = make_float4(gv[4], gv[5], gv[6], gv[7]);
+// document changes.  512 threads: thread (channel c, quarter qd) loads and scans 32 rows in
+// registers; the quarters are chained through `tot` (4 x 128 floats of shared memory) and `reset`
+// (4 ints: a document starts inside the quarter).  seg_s must be visible before; a __syncthreads()
+// is needed after.
+__device__ __forceinline__ void lambda_scan_512(const Rows& r, const int* seg_s, float* LAM, float* tot, int* reset) {
+  const int c = threadIdx.x & 127, qd = threadIdx.x >> 7, x0 = qd * 32;
+  const size_t gcol = r.gC == 1 ? 0 : c;
+  float v[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    const int x = x0 + i;
+    const bool live = x < r.rows_valid;
+    float gv = ldf_ro(r.gg, r.g_row0 + (size_t)(live ? x : 0) * r.g_pitch + gcol, r.gate_dt);
+    if (r.fuse) { gv = -expf(fminf(gv, 5.f)); if (r.guard) gv = fminf(gv, -1e-6f); }
+    else gv = gv <= 0.f ? gv : 0.f;
+    v[i] = live ? gv : 0.f;
   }
-  __syncthreads();
-  if (threadIdx.x < K) {
-    float run = 0.f;
-    int prev = seg_s[0];
-#pragma unroll 4
-    for (int i = 0; i < C; ++i) {
-      const int s = seg_s[i];
-      if (s != prev) run = 0.f;
-      prev = s;
-      run += LAM[i * LP + threadIdx.x];
-      LAM[i * LP + threadIdx.x] = run;
-    }
+  float run = 0.f;
+  int nr = 32;                                   // first row of the quarter that starts a document
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    const int x = x0 + i;
+    if (x > 0 && seg_s[x] != seg_s[x - 1]) { run = 0.f; if (nr == 32) nr = i; }
+    run += v[i];
+    v[i] = run;
   }
+  tot[qd * 128 + c] = run;
+  if (c == 0) reset[qd] = nr < 32;
   __syncthreads();
+  float carry = 0.f;
+  for (int q2 = qd - 1; q2 >= 0; --q2) {
+    carry += tot[q2 * 128 + c];
+    if (reset[q2]) break;
+  }
+#pragma unroll
+  for (int i = 0; i < 32; ++i) LAM[(x0 + i) * LP + c] = v[i] + (i < nr ? carry : 0.f);
 }
 
 __device__ __forceinline__ int level_ref(int x, int s) { return (x / (2 * s)) * 2 * s + s; }
@@ -191,49 +200,10 @@ __device__ __forceinline__ void decay8(const float* la, const float* lb, float (
 }
 
 // Operand images of level s (pairs of adjacent s-row blocks; reference row = first row of the
-// lower block): rows of the lower blocks carry beta and q_hat scaled by exp(Lam_x - Lam_ref),
-// rows of the upper blocks carry k_hat scaled by exp(Lam_ref - Lam_x); the other rows are 0.
-// Piece e = (p = channel group, x = row) sits at image[p*128 + x].
-template <int NT>
-__device__ __forceinline__ void build_level(const Rows& r, const float* LAM, int s, uint4* RB, uint4* RQ, uint4* KC) {
-  const uint4 zero = make_uint4(0, 0, 0, 0);
-  for (int e = threadIdx.x; e < IMG; e += NT) {
-    const int p = e >> 7, x = e & 127;
-    const int ref = level_ref(x, s);
-    float f[8], a[8];
-    if (x >= ref) {
-      decay8(LAM + x * LP + 8 * p, LAM + ref * LP + 8 * p, f);
-      if (RB) {
-        beta8(r, x, p, a);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) a[i] *= f[i];
-        RB[e] = umma::pack8(a);
-      }
-      if (RQ) {
-        qhat8(r, x, p, a);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) a[i] *= f[i];
-        RQ[e] = umma::pack8(a);
-      }
-      if (KC) KC[e] = zero;
-    } else {
-      if (KC) {
-        decay8(LAM + ref * LP + 8 * p, LAM + x * LP + 8 * p, f);
-        khat8(r, x, p, a);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) a[i] *= f[i];
-        KC[e] = umma::pack8(a);
-      }
-      if (RB) RB[e] = zero;
-      if (RQ) RQ[e] = zero;
-    }
-  }
-}
-
-// The same images for the backward, where every row has one role per level: rows of the upper
-// blocks (x < ref) carry k_hat * exp(Lam_ref - Lam_x) in BOTH images; rows of the lower blocks carry
-// beta * exp(Lam_x - Lam_ref) in KR and q_hat * exp(Lam_x - Lam_ref) in QK.  One piece (row x,
-// channel group p) per call.
+// lower block).  Every row has one role per level: rows of the upper blocks (x < ref) carry
+// k_hat * exp(Lam_ref - Lam_x) in BOTH images; rows of the lower blocks carry
+// beta * exp(Lam_x - Lam_ref) in KR and q_hat * exp(Lam_x - Lam_ref) in QK.  All scale factors are
+// <= 1.  One piece (row x, channel group p) per call, stored at image[p*128 + x].
 __device__ __forceinline__ void build_level_piece(const Rows& r, const float* LAM, int s, int x, int p, uint4* KR, uint4* QK) {
   const int ref = level_ref(x, s);
   const bool lower = x >= ref;

@@ -12,6 +12,9 @@
 
 namespace dn {
 
+// true when the environment asks for the fp32 SIMT kernels everywhere (DN_FORCE_SIMT=1)
+bool force_simt();
+
 // --------------------------------------------------------------------------- geometry
 // Everything a kernel needs to know about where a (batch, exec head, chunk) lives.
 struct Geo {
@@ -22,6 +25,12 @@ struct Geo {
   int qkv_dt, gate_dt, pre_dt, prec;
   uint32_t flags;
   float scale;
+  // Layout of the bf16 residual tiles W, U, M, qe, ke.  false: row-major (rows x cols).  true: the
+  // operand image of the tensor-core kernels, [col / 8][row][8] -- a tile is then copied into shared
+  // memory as it lies, and a thread that owns one row writes 16 bytes next to its neighbours'.
+  // Chosen once per shape (prepass on the tensor cores <=> image layout); every kernel reading or
+  // writing these tiles goes through rix().
+  bool img;
   __host__ __device__ bool bf16_mode() const { return prec == DN_PREC_BF16; }
   __host__ __device__ bool state_bf16() const { return prec == DN_PREC_BF16 && !(flags & DN_STATE_FP32_MM); }
   // head of a gate tensor that exec head h (and, for w, value head hv) reads
@@ -60,7 +69,14 @@ inline int make_geo(const dn_shape* s, Geo* g) {
   g->qkv_dt = s->qkv_dtype; g->gate_dt = s->gate_dtype; g->prec = s->precision;
   g->pre_dt = s->precision == DN_PREC_BF16 ? DN_BF16 : DN_F32;
   g->flags = s->flags; g->scale = s->scale;
+  g->img = s->precision == DN_PREC_BF16 && g->C == 128 && g->K == 128 && (g->Vw == 128 || g->Vw == 256) &&
+           !force_simt();
   return DN_OK;
+}
+
+// element index of (row, col) in a residual tile of 128 rows (image layout) or `ncols` columns (row-major)
+__host__ __device__ __forceinline__ size_t rix(bool img, int row, int col, int ncols) {
+  return img ? ((size_t)((col >> 3) * 128 + row) << 3) + (col & 7) : (size_t)row * ncols + col;
 }
 
 // --------------------------------------------------------------------------- dtype helpers

@@ -65,8 +65,6 @@ int launch_state_fwd_tc(const StateArgs& a, cudaStream_t st);
 int launch_state_bwd_tc(const StateArgs& a, cudaStream_t st);
 int read_device_error();
 int* device_error_ptr();
-// true when the environment asks for the fp32 SIMT kernels everywhere (DN_FORCE_SIMT=1)
-bool force_simt();
 int launch_state_bwd(const StateArgs& a, cudaStream_t st);
 int launch_prepass_bwd(PrepassBwdArgs& a, size_t scratch_floats, cudaStream_t st);
 int launch_prepass_bwd_tc(PrepassBwdArgs& a, size_t scratch_floats, cudaStream_t st);

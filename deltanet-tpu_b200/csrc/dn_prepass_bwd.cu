@@ -142,9 +142,9 @@ __global__ void __launch_bounds__(DN_THREADS, 1) prepass_bwd_kernel(PrepassBwdAr
 
     // ---- V_new = U - W S
     cta_gemm<true, true>(C, Vw, K,
-        [&](int i, int kk) { return ldf(a.res.W, bW + (size_t)i * K + kk, pre); },
+        [&](int i, int kk) { return ldf(a.res.W, bW + rix(g.img, i, kk, K), pre); },
         [&](int kk, int j) { float s = S[(size_t)kk * Vw + j]; return sbf ? bf16r(s) : s; },
-        [&](int i, int j, float acc) { VN[i * Vw + j] = ldf(a.res.U, bU + (size_t)i * Vw + j, pre) - acc; },
+        [&](int i, int j, float acc) { VN[i * Vw + j] = ldf(a.res.U, bU + rix(g.img, i, j, Vw), pre) - acc; },
         tile);
     auto dO_at = [&](int i, int j) -> float {
       const int t = t0 + i;
@@ -180,8 +180,8 @@ __global__ void __launch_bounds__(DN_THREADS, 1) prepass_bwd_kernel(PrepassBwdAr
     cta_gemm<true, false>(C, C, K + Vw,
         [&](int i, int kk) { return kk < K ? DX[i * K + kk] : DY[i * Vw + (kk - K)]; },
         [&](int kk, int j) {
-          return kk < K ? ldf(a.res.W, bW + (size_t)j * K + kk, pre)
-                        : ldf(a.res.U, bU + (size_t)j * Vw + (kk - K), pre);
+          return kk < K ? ldf(a.res.W, bW + rix(g.img, j, kk, K), pre)
+                        : ldf(a.res.U, bU + rix(g.img, j, kk - K, Vw), pre);
         },
         [&](int i, int j, float acc) { DA[i * C + j] = (i > j && seg_s[i] == seg_s[j]) ? -acc : 0.f; }, tile);
 
@@ -339,16 +339,13 @@ size_t prepass_bwd_scratch_per_cta(const Geo& g) {
   return (size_t)13 * g.C * g.K + (size_t)2 * g.C * g.Vw + (size_t)2 * g.C * g.C;
 }
 
-bool prepass_bwd_tc_eligible(const Geo& g) {
-  return g.prec == DN_PREC_BF16 && !(g.flags & DN_STATE_FP32_MM) && g.C == 128 && g.K == 128 &&
-         (g.Vw == 128 || g.Vw == 256);
-}
+bool prepass_bwd_tc_eligible(const Geo& g) { return g.img && !(g.flags & DN_STATE_FP32_MM); }
 
 int launch_prepass_bwd(PrepassBwdArgs& a, size_t scratch_floats, cudaStream_t st) {
   const Geo& g = a.g;
   a.items = g.B * g.H * g.NC;
   a.scratch_per_cta = prepass_bwd_scratch_per_cta(g);
-  const bool tc = prepass_bwd_tc_eligible(g) && !force_simt();
+  const bool tc = prepass_bwd_tc_eligible(g);
   a.err = device_error_ptr();
   if (tc) return launch_prepass_bwd_tc(a, scratch_floats, st);
   const int max_ctas = 296;

@@ -160,60 +160,8 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
     const Rows r = make_rows<CF>(g, a.q, a.k, a.gg, a.b, b, h, t0, rq_s, rk_s);
     const int qdt = r.qkv_dt, gdt = r.gate_dt;           // compile-time constants in the fixed modes
     const int wC = CF::fixed ? g.V : g.wC;
-    {
-      float sq = 0.f, sk = 0.f;
-      if (l2) {                       // rows past the end read as zero
-#pragma unroll
-        for (int it = 0; it < 4; ++it) {
-          float qv[8], kv[8];
-          raw_q8(r, myrow, it * 4 + lgrp, qv);
-          raw_k8(r, myrow, it * 4 + lgrp, kv);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) { sq = fmaf(qv[i], qv[i], sq); sk = fmaf(kv[i], kv[i], sk); }
-        }
-      }
-      sq += __shfl_xor_sync(0xffffffffu, sq, 8);  sk += __shfl_xor_sync(0xffffffffu, sk, 8);
-      sq += __shfl_xor_sync(0xffffffffu, sq, 16); sk += __shfl_xor_sync(0xffffffffu, sk, 16);
-      if (lgrp == 0) {
-        rq_s[myrow] = l2 ? rsqrtf(sq + 1e-6f) : 1.f;
-        rk_s[myrow] = l2 ? rsqrtf(sk + 1e-6f) : 1.f;
-      }
-    }
-    {
-      // cumulative log-decay: thread (channel c, quarter qd) scans 32 rows in registers, the quarters
-      // are chained through shared memory
-      const int c = tid & 127, qd = tid >> 7, x0 = qd * 32;
-      const size_t gcol = r.gC == 1 ? 0 : c;
-      float v[32];
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const int x = x0 + i;
-        const bool live = x < r.rows_valid;
-        float gv = ldf_ro(r.gg, r.g_row0 + (size_t)(live ? x : 0) * r.g_pitch + gcol, gdt);
-        if (fuse) { gv = -expf(fminf(gv, 5.f)); if (guard) gv = fminf(gv, -1e-6f); }
-        else gv = gv <= 0.f ? gv : 0.f;
-        v[i] = live ? gv : 0.f;
-      }
-      float run = 0.f;
-      int nr = 32;                                   // first row of the quarter that starts a document
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const int x = x0 + i;
-        if (x > 0 && seg_s[x] != seg_s[x - 1]) { run = 0.f; if (nr == 32) nr = i; }
-        run += v[i];
-        v[i] = run;
-      }
-      TOTL[qd * 128 + c] = run;
-      if (c == 0) reset_s[qd] = nr < 32;
-      __syncthreads();
-      float carry = 0.f;
-      for (int q2 = qd - 1; q2 >= 0; --q2) {
-        carry += TOTL[q2 * 128 + c];
-        if (reset_s[q2]) break;
-      }
-#pragma unroll
-      for (int i = 0; i < 32; ++i) LAM[(x0 + i) * LP + c] = v[i] + (i < nr ? carry : 0.f);
-    }
+    row_norms_8x4(r, myrow, lgrp, rq_s, rk_s);
+    lambda_scan_512(r, seg_s, LAM, TOTL, reset_s);
     __syncthreads();
 
     DN_MARK(8);

@@ -39,7 +39,7 @@ __device__ __forceinline__ int p4v(int row, int col) { return ((col >> 2) << 7) 
 __device__ __forceinline__ int p4f(int row, int col) { return ((((col >> 2) << 7) + row) << 2) + (col & 3); }
 
 struct BwdTcIo {
-  const __nv_bfloat16 *W, *U;          // this item's (128,128) and (128,VW) tiles
+  const __nv_bfloat16 *W, *U;          // this item's (128,128) and (128,VW) tiles, image layout
   const float *S, *dH, *dV, *T;        // this item's fp32 arrays: (128,VW), (128,VW), (128,VW), (128,128)
   const float* lam_end;                // this item's (128) log-decay to the chunk end
   const void* d_out;                   // whole tensor
@@ -76,17 +76,15 @@ __device__ __forceinline__ void stage_f32(uint4* dst, const float* src, int pitc
     dst[p * R + x] = v;
   }
 }
-// bf16 sources need no conversion: asynchronous 16-byte copies, no registers.  The caller waits
-// (umma::cp_async_wait<0>) before the operands are handed to the tensor core.
-template <int R, int PANELS, int NT>
-__device__ __forceinline__ void stage_bf16_async(uint4* dst, const __nv_bfloat16* src, int pitch) {
-  static_assert((PANELS * R) % NT == 0, "whole passes");
+// W and U lie in global memory as operand images already: asynchronous 16-byte copies of a
+// contiguous range, no registers.  The caller waits (umma::cp_async_wait<0>) before the operands are
+// handed to the tensor core.
+template <int N_U4, int NT>
+__device__ __forceinline__ void copy_image_async(uint4* dst, const __nv_bfloat16* src) {
+  static_assert(N_U4 % NT == 0, "whole passes");
+  const uint4* s = reinterpret_cast<const uint4*>(src);
 #pragma unroll
-  for (int it = 0; it < PANELS * R / NT; ++it) {
-    int p, x;
-    stage_coords<R>(it * NT + threadIdx.x, p, x);
-    umma::cp_async16(dst + p * R + x, src + (size_t)x * pitch + 8 * p);
-  }
+  for (int it = 0; it < N_U4 / NT; ++it) umma::cp_async16(dst + it * NT + threadIdx.x, s + it * NT + threadIdx.x);
   umma::cp_async_commit();
 }
 
@@ -112,8 +110,8 @@ __device__ __forceinline__ void bwd_gemms_tc(umma::Ctx& cx, uint8_t* img, const 
   DN_MARK(1);
   // ---- 1. V_new = U - W S, as W (-S) + I U so that U arrives through the tensor core as well.
   //         The image X holds -S from here to step 3.
-  stage_bf16_async<128, 16, NT>(P, io.W, 128);
-  stage_bf16_async<128, PV, NT>(Z, io.U, VW);
+  copy_image_async<128 * 16, NT>(P, io.W);
+  copy_image_async<128 * PV, NT>(Z, io.U);
   stage_f32<128, PV, NT, true>(X, io.S, VW);
   for (int e = threadIdx.x; e < 128 * 16; e += NT) {          // identity, K-major
     const int p = e >> 7, x = e & 127;
@@ -241,8 +239,8 @@ __device__ __forceinline__ void bwd_gemms_tc(umma::Ctx& cx, uint8_t* img, const 
 
   DN_MARK(6);
   // ---- 6. dA = -(dX W^T + dY U^T), strictly lower and same document
-  stage_bf16_async<128, 16, NT>(P, io.W, 128);
-  stage_bf16_async<128, PV, NT>(Z, io.U, VW);
+  copy_image_async<128 * 16, NT>(P, io.W);
+  copy_image_async<128 * PV, NT>(Z, io.U);
   umma::cp_async_wait<0>();
   umma::pre_issue_sync();
   umma::issue<128, false, false>(cx, Y2, P, 128, 0, false);

@@ -281,7 +281,7 @@ size_t prepass_fwd_scratch_per_cta(const Geo& g) { return (size_t)5 * g.C * g.K 
 int launch_prepass_fwd(const Geo& g, const void* q, const void* k, const void* v, const void* gg,
                        const void* b, const void* w, const int32_t* seg, const dn_residuals& res,
                        float* scratch, size_t scratch_floats, cudaStream_t st) {
-  if (prepass_fwd_tc_eligible(g) && !force_simt())
+  if (prepass_fwd_tc_eligible(g))
     return launch_prepass_fwd_tc(g, q, k, v, gg, b, w, seg, res, scratch, scratch_floats, st);
   PrepassFwdArgs a;
   a.g = g; a.q = q; a.k = k; a.v = v; a.gg = gg; a.b = b; a.w = w; a.seg = seg; a.res = res;

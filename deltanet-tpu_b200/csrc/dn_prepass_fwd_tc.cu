@@ -1,27 +1,34 @@
 // Prepass forward on the tcgen05 tensor cores (bf16 precision, chunk = K = 128, value width
 // 128 or 256).  Produces the same outputs as the fp32 formulation in dn_prepass_fwd.cu
-// (reference body: src/deltanet_tpu/gdn2.py:115-240).
+// (reference body: src/deltanet_tpu/gdn2.py:115-240), with the bf16 tiles W, U, M, qe, ke written
+// as tensor-core operand images ([col / 8][row][8], see Geo::img).
 //
 // A and M.  A_ij = sum_c beta_ic exp(Lam_ic - Lam_jc) k_jc cannot be one matrix product because
-// the decay couples i, j and the channel c.  It is built hierarchically: at level s in {64,32,16}
+// the decay couples i, j and the channel c.  It is built hierarchically: at level s in {16,32,64}
 // the chunk is cut into pairs of adjacent s-row blocks, and for a pair with rows I (lower block),
 // columns J (upper block) and reference row r = first row of I
 //     A[I,J] = (beta_I * exp(Lam_I - Lam_r)) (k_J * exp(Lam_r - Lam_J))^T ,
 // with both scale factors <= 1 (the cumulative decay is monotone inside a document), so nothing
-// can overflow however strong the decay.  Scaling EVERY row by its own pair's factors turns each
-// level into ONE 128x128x128 MMA (per matrix); entries outside the level's blocks are finite
-// garbage that the drain ignores (entry (i,j) belongs to the level of the highest bit in which
-// i>>4 and j>>4 differ).  The 16x16 diagonal blocks are evaluated exactly, pair by pair, on the
-// CUDA cores.  The reference does the same with 32-row blocks and one reference per block row
-// (gdn2.py:162-197).
+// can overflow however strong the decay.  In one level every row is either a row of its pair
+// (lower block) or a column (upper block), so two images suffice: KR holds the beta-images on lower
+// rows and the k-images on upper rows, QK the q-images and the k-images, and
+//     level part of A = KR KR^T,   level part of M = QK KR^T       (one 128^3 MMA each);
+// entries outside the level's blocks are finite garbage that the drain ignores (entry (i,j) belongs
+// to the level of the highest bit in which i>>4 and j>>4 differ).  Levels alternate between two
+// halves of tensor memory, so a level's drain overlaps the next level's image build.  The 16x16
+// diagonal blocks are evaluated exactly, pair by pair, on the CUDA cores.  The reference does the
+// same with 32-row blocks and one reference per block row (gdn2.py:162-197).
 //
 // T = (I+A)^-1 is obtained as in the fp32 formulation (substitution on 16x16 blocks + block
 // merges, fp32 in shared memory); W = T X and U = T Y are tcgen05 MMAs on bf16 operands, which
 // is also where the reference rounds to bf16 (gdn2.py:226-230).
 //
-// 512 threads per CTA, one CTA per SM, looping over (batch, exec head, chunk) items.  The
-// cumulative decay stays in shared memory; q, k, b, g, v, w are read straight from the user's
-// tensors in 16/32-byte pieces (no staging copy in global memory).
+// 512 threads per CTA, one CTA per SM, looping over (batch, exec head, chunk) items.  Phases that
+// read the operator's row-major tensors let a warp cover 8 rows x 4 pieces of 8 channels (row =
+// 8 * warp + (lane & 7) fixed per thread) with every load issued unconditionally; phases that drain
+// tensor memory own one row per thread, which the image layout of the outputs (and the panel
+// layout [col / 4][row][4] of the fp32 scratch that carries A to the inverse) turns into stores of
+// 512 contiguous bytes per warp.
 #include "dn_chunkprep.cuh"
 #include "dn_kernels.cuh"
 
@@ -30,71 +37,91 @@ namespace {
 
 using namespace prep;
 constexpr int NT = 512;
-constexpr int OFF_IMG = C * LP * 4;                 // level images start after Lambda
-constexpr int OFF_XI = 3 * 65536;                   // X image: survives the inverse
+constexpr int AP = 132;                              // row pitch (floats) of A, T in shared memory
+constexpr int OFF_IMG = C * LP * 4;                  // level images / k cache / A start after Lambda
+constexpr int OFF_TM = OFF_IMG + C * AP * 4;         // merge scratch (16 KB)
+constexpr int OFF_XI = 160 * 1024;                   // X image: survives the inverse
+constexpr int OFF_TI = 192 * 1024;                   // T image
+constexpr int SMEM_BYTES = 224 * 1024;
+static_assert(OFF_TM + 16384 <= OFF_XI, "merge scratch below the X image");
+static_assert(OFF_IMG + 2 * 32768 <= OFF_XI, "level images below the X image");
 
-__device__ __forceinline__ void load4(const void* base, size_t off, int dt, float (&x)[4]) {
+__device__ __forceinline__ int p4v(int row, int col) { return ((col >> 2) << 7) + row; }
+__device__ __forceinline__ int p4f(int row, int col) { return ((((col >> 2) << 7) + row) << 2) + (col & 3); }
+
+// four channels (4*lane ..) of a row of q / k / b through the read-only path; a row past the end
+// reads row 0 (the caller zeroes it)
+__device__ __forceinline__ float4 in4(const void* base, size_t off, int dt) {
   if (dt == DN_BF16) {
-    const uint2 u = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(base) + off);
-    x[0] = __uint_as_float(u.x << 16); x[1] = __uint_as_float(u.x & 0xffff0000u);
-    x[2] = __uint_as_float(u.y << 16); x[3] = __uint_as_float(u.y & 0xffff0000u);
-  } else {
-    const float4 a = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + off);
-    x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w;
+    const uint2 u = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(base) + off));
+    return make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xffff0000u),
+                       __uint_as_float(u.y << 16), __uint_as_float(u.y & 0xffff0000u));
   }
+  return __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + off));
 }
 
-// four channels (4*lane ..) of k_hat, q_hat, beta for chunk row x
-__device__ __forceinline__ void row4(const Rows& r, int x, int lane, float (&kh)[4], float (&qh)[4], float (&be)[4],
-                                     bool want_q) {
+// One merge level of the inverse: for every pair of adjacent S-row blocks (lower rows I, upper rows J)
+//   T[I,J] = -T[I,I] (A[I,J] T[J,J]).
+// 512 threads = (row of I) x (8 column groups of S/8 columns) x pairs, each thread S/8 outputs.
+template <int S>
+__device__ __forceinline__ void merge_level(const float* As, float* Ts, float* Tm) {
+  constexpr int NJ = S / 8;
+  const int cg = threadIdx.x & 7, rest = threadIdx.x >> 3;      // rest = pair * S + row in I
+  const int p = rest / S, il = rest - p * S;
+  const int i = 2 * p * S + S + il, j0 = 2 * p * S + cg * NJ, m0 = 2 * p * S;
+  float acc[NJ];
 #pragma unroll
-  for (int i = 0; i < 4; ++i) kh[i] = qh[i] = be[i] = 0.f;
-  if (x >= r.rows_valid) return;
-  const size_t off = r.qk_row0 + (size_t)x * r.qk_pitch + 4 * lane;
-  load4(r.k, off, r.qkv_dt, kh);
-  if (r.l2) {
+  for (int u = 0; u < NJ; ++u) acc[u] = 0.f;
+#pragma unroll 4
+  for (int m = 0; m < S; ++m) {
+    const float av = As[i * AP + m0 + m];
+    const float* t = Ts + (m0 + m) * AP + j0;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) { kh[i] *= r.rk[x]; if (r.round_in) kh[i] = bf16r(kh[i]); }
-  }
-  if (!want_q) return;
-  load4(r.q, off, r.qkv_dt, qh);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) { qh[i] = (qh[i] * r.rq[x]) * r.scale; if (r.round_in) qh[i] = bf16r(qh[i]); }
-  if (r.bC == 1) {
-    const float v = ldf(r.b, r.b_row0 + (size_t)x * r.b_pitch, r.gate_dt);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) be[i] = v;
-  } else {
-    load4(r.b, r.b_row0 + (size_t)x * r.b_pitch + 4 * lane, r.gate_dt, be);
+    for (int u = 0; u < NJ; ++u) acc[u] = fmaf(av, t[u], acc[u]);
   }
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    if (r.fuse) be[i] = 1.f / (1.f + expf(-be[i]));
-    be[i] *= kh[i];
+  for (int u = 0; u < NJ; ++u) Tm[rest * S + cg * NJ + u] = acc[u];
+  __syncthreads();
+#pragma unroll
+  for (int u = 0; u < NJ; ++u) acc[u] = 0.f;
+#pragma unroll 4
+  for (int m = 0; m < S; ++m) {
+    const float tv = Ts[i * AP + m0 + S + m];
+    const float* t = Tm + (p * S + m) * S + cg * NJ;
+#pragma unroll
+    for (int u = 0; u < NJ; ++u) acc[u] = fmaf(tv, t[u], acc[u]);
   }
+#pragma unroll
+  for (int u = 0; u < NJ; ++u) Ts[i * AP + j0 + u] = -acc[u];
+  __syncthreads();
 }
 
-template <int VW>
+template <int VW, int MODE>
 __global__ void __launch_bounds__(NT, 1) prepass_fwd_tc_kernel(PrepassFwdArgs a, int* err) {
+  using CF = InCfg<MODE>;
   extern __shared__ __align__(128) uint8_t smraw[];
   __shared__ uint64_t mma_bar;
   __shared__ uint32_t tmem_base;
   __shared__ int seg_s[C];
+  __shared__ int reset_s[4];
   __shared__ float rq_s[C], rk_s[C];
   const Geo& g = a.g;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int myrow = warp * 8 + (lane & 7), lgrp = lane >> 3;
   float* LAM = reinterpret_cast<float*>(smraw);
-  uint4* RB = reinterpret_cast<uint4*>(smraw + OFF_IMG);
-  uint4* RQ = RB + IMG;
-  uint4* KC = RQ + IMG;
+  uint4* KR = reinterpret_cast<uint4*>(smraw + OFF_IMG);
+  uint4* QK = KR + IMG;
+  float* KHs = reinterpret_cast<float*>(smraw + OFF_IMG);          // k_hat cache (pitch AP), diagonal pass
+  float* TOTL = reinterpret_cast<float*>(smraw + OFF_IMG);         // partial sums of the decay scan
   uint4* XI = reinterpret_cast<uint4*>(smraw + OFF_XI);
-  float* As = reinterpret_cast<float*>(smraw);
-  float* Ts = As + C * C;
-  float* Tm = Ts + C * C;
-  uint4* TI = reinterpret_cast<uint4*>(smraw);
-  uint4* YI = reinterpret_cast<uint4*>(Tm);
+  float* Ts = reinterpret_cast<float*>(smraw);                     // inverse: T over Lambda,
+  float* As = reinterpret_cast<float*>(smraw + OFF_IMG);           //          A over the images / cache
+  float* Tm = reinterpret_cast<float*>(smraw + OFF_TM);
+  uint4* TI = reinterpret_cast<uint4*>(smraw + OFF_TI);
+  uint4* YI = reinterpret_cast<uint4*>(smraw + OFF_IMG);           // Y image over A, after the inverse
 
-  float* Ag = a.scratch + (size_t)blockIdx.x * a.scratch_per_cta;     // A (fp32), masked
+  float* Ag = a.scratch + (size_t)blockIdx.x * a.scratch_per_cta;     // A (fp32, masked), panel layout
+  float4* Ag4 = reinterpret_cast<float4*>(Ag);
 
   if (tid == 0) { umma::mbar_init(&mma_bar, 1); umma::fence_mbar_init(); }
   if (warp == 0) umma::tmem_alloc(&tmem_base, 512);
@@ -103,218 +130,275 @@ __global__ void __launch_bounds__(NT, 1) prepass_fwd_tc_kernel(PrepassFwdArgs a,
   umma::tc_fence_after();
   umma::Ctx cx{tmem_base, &mma_bar, 0u, err, false};
 
-  __nv_bfloat16* Wg = reinterpret_cast<__nv_bfloat16*>(a.res.W);
-  __nv_bfloat16* Ug = reinterpret_cast<__nv_bfloat16*>(a.res.U);
-  __nv_bfloat16* Mg = reinterpret_cast<__nv_bfloat16*>(a.res.M);
-  __nv_bfloat16* QEg = reinterpret_cast<__nv_bfloat16*>(a.res.qe);
-  __nv_bfloat16* KEg = reinterpret_cast<__nv_bfloat16*>(a.res.ke);
   const bool fuse = g.flags & DN_FUSE_PROLOGUE;
 
   for (int item = blockIdx.x; item < a.items; item += gridDim.x) {
     const int c_idx = item % g.NC, h = (item / g.NC) % g.H, b = item / (g.NC * g.H);
     const int t0 = c_idx * C;
     const size_t ibase = (size_t)item;
+    uint4* Wimg = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.res.W) + ibase * C * K);
+    uint4* Uimg = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.res.U) + ibase * C * VW);
+    uint4* Mimg = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.res.M) + ibase * C * C);
+    __nv_bfloat16* Mel = reinterpret_cast<__nv_bfloat16*>(a.res.M) + ibase * C * C;
+    uint4* QEimg = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.res.qe) + ibase * C * K);
+    uint4* KEimg = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.res.ke) + ibase * C * K);
+
     for (int i = tid; i < C; i += NT) seg_s[i] = seg_at(a.seg, b, t0 + i, g.L);
-    const Rows r = make_rows(g, a.q, a.k, a.gg, a.b, b, h, t0, rq_s, rk_s);
-    row_norms<NT>(r, rq_s, rk_s);
+    const Rows r = make_rows<CF>(g, a.q, a.k, a.gg, a.b, b, h, t0, rq_s, rk_s);
+    const int qdt = r.qkv_dt, gdt = r.gate_dt;           // compile-time constants in the fixed modes
+    const int wC = CF::fixed ? g.V : g.wC;
+    row_norms_8x4(r, myrow, lgrp, rq_s, rk_s);
     __syncthreads();
     const int seg0 = seg_s[0], segL = seg_s[C - 1];
-    build_lambda<NT>(r, seg_s, LAM);
+    lambda_scan_512(r, seg_s, LAM, TOTL, reset_s);
+    __syncthreads();
 
     // ---- qe, ke, Lambda_end and the X = [first doc] beta e^Lam operand image
-    for (int e = tid; e < IMG; e += NT) {
-      const int x = e >> 4, p = e & 15;
-      float qh[8], kh[8], lam[8], o[8];
-      qhat8(r, x, p, qh);
-      khat8(r, x, p, kh);
-      const float4 l0 = *reinterpret_cast<const float4*>(LAM + x * LP + 8 * p), l1 = *reinterpret_cast<const float4*>(LAM + x * LP + 8 * p + 4);
-      lam[0] = l0.x; lam[1] = l0.y; lam[2] = l0.z; lam[3] = l0.w; lam[4] = l1.x; lam[5] = l1.y; lam[6] = l1.z; lam[7] = l1.w;
+    {
+      const int x = myrow;
       const bool first = seg_s[x] == seg0, last = seg_s[x] == segL;
+#pragma unroll 2
+      for (int it = 0; it < 4; ++it) {
+        const int p = it * 4 + lgrp;
+        float qh[8], kh[8], be[8], lam[8], lend[8], o[8];
+        qhat8(r, x, p, qh);
+        khat8(r, x, p, kh);
+        bact8(r, x, p, be);
+        *reinterpret_cast<float4*>(lam) = *reinterpret_cast<const float4*>(LAM + x * LP + 8 * p);
+        *reinterpret_cast<float4*>(lam + 4) = *reinterpret_cast<const float4*>(LAM + x * LP + 8 * p + 4);
+        *reinterpret_cast<float4*>(lend) = *reinterpret_cast<const float4*>(LAM + (C - 1) * LP + 8 * p);
+        *reinterpret_cast<float4*>(lend + 4) = *reinterpret_cast<const float4*>(LAM + (C - 1) * LP + 8 * p + 4);
+        float el[8];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) o[i] = first ? qh[i] * expf(fminf(lam[i], 0.f)) : 0.f;
-      *reinterpret_cast<uint4*>(QEg + ibase * C * K + (size_t)x * K + 8 * p) = umma::pack8(o);
+        for (int i = 0; i < 8; ++i) el[i] = expf(fminf(lam[i], 0.f));
 #pragma unroll
-      for (int i = 0; i < 8; ++i) o[i] = last ? kh[i] * expf(fminf(LAM[(C - 1) * LP + 8 * p + i] - lam[i], 0.f)) : 0.f;
-      *reinterpret_cast<uint4*>(KEg + ibase * C * K + (size_t)x * K + 8 * p) = umma::pack8(o);
-      if (x == C - 1) {
+        for (int i = 0; i < 8; ++i) o[i] = first ? qh[i] * el[i] : 0.f;
+        QEimg[p * 128 + x] = umma::pack8(o);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) a.res.lam_end[ibase * K + 8 * p + i] = lam[i];
+        for (int i = 0; i < 8; ++i) o[i] = last ? kh[i] * expf(fminf(lend[i] - lam[i], 0.f)) : 0.f;
+        KEimg[p * 128 + x] = umma::pack8(o);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = first ? be[i] * kh[i] * el[i] : 0.f;
+        XI[p * 128 + x] = umma::pack8(o);
       }
-      float be[8];
-      bact8(r, x, p, be);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) o[i] = first ? be[i] * kh[i] * expf(fminf(lam[i], 0.f)) : 0.f;
-      XI[p * 128 + x] = umma::pack8(o);
+      if (tid < K) a.res.lam_end[ibase * K + tid] = LAM[(C - 1) * LP + tid];
     }
 
-    // ---- A and M, level by level: three images, two MMAs, one predicated drain per level
-    for (int lv = 0; lv < 3; ++lv) {
-      build_level<NT>(r, LAM, 16 << lv, RB, RQ, KC);
-      umma::pre_issue_sync();
-      umma::issue<128, false, false>(cx, RB, KC, K, 0, false);
-      umma::issue<128, false, false>(cx, RQ, KC, K, 128, false);
-      umma::commit_wait(cx);
-      {
-        const int quarter = warp & 3, group = warp >> 2;
-        const int row = quarter * 32 + lane, bi = row >> 4, bi0 = quarter * 2;
-        const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
-        for (int c = 0; c < 32; c += 16) {
-          const int col = group * 32 + c, bj = col >> 4;
-          // warp-uniform skip: neither of the warp's two row blocks has this piece at this level
-          const bool own0 = bj < bi0 && owner_level(bi0, bj) == lv, own1 = bj < bi0 + 1 && owner_level(bi0 + 1, bj) == lv;
-          const bool upper = lv == 0 && bj > bi0;                  // zero fill, once
-          if (!own0 && !own1 && !upper) continue;
-          float va[16], vm[16];
-          if (!cx.dead && (own0 || own1)) {
-            umma::tmem_ld16(cx.tmem + lane_base + col, va);
-            umma::tmem_ld16(cx.tmem + lane_base + 128 + col, vm);
-          } else {
+    // ---- A and M, level by level: two images, two MMAs, one predicated drain per level
+    auto build = [&](int lv) {
+#pragma unroll 2
+      for (int it = 0; it < 4; ++it) build_level_piece(r, LAM, 16 << lv, myrow, it * 4 + lgrp, KR, QK);
+    };
+    auto drain_level = [&](int lv) {
+      const int quarter = warp & 3, group = warp >> 2;
+      const int row = quarter * 32 + lane, bi = row >> 4, bi0 = quarter * 2;
+      const uint32_t tbase = cx.tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)((lv & 1) * 256);
+#pragma unroll 1
+      for (int cc = 0; cc < 32; cc += 16) {
+        const int col = group * 32 + cc, bj = col >> 4;
+        // warp-uniform skip: neither of the warp's two row blocks has this piece at this level
+        const bool own0 = bj < bi0 && owner_level(bi0, bj) == lv, own1 = bj < bi0 + 1 && owner_level(bi0 + 1, bj) == lv;
+        const bool upper = lv == 0 && bj > bi0;                  // zero fill, once
+        if (!own0 && !own1 && !upper) continue;
+        float va[16], vm[16];
+        if (!cx.dead && (own0 || own1)) {
+          umma::tmem_ld16(tbase + col, va);
+          umma::tmem_ld16(tbase + 128 + col, vm);
+        } else {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) va[i] = vm[i] = 0.f;
-          }
-          const bool mine = bj < bi && owner_level(bi, bj) == lv;
-          const bool zero_fill = lv == 0 && bj > bi;
-          if (!mine && !zero_fill) continue;
-          float oa[16], om[16];
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const bool keep = mine && seg_s[row] == seg_s[col + i];
-            oa[i] = keep ? va[i] : 0.f;
-            om[i] = keep ? vm[i] : 0.f;
-          }
-          float4* da = reinterpret_cast<float4*>(Ag + row * C + col);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) da[i] = make_float4(oa[4 * i], oa[4 * i + 1], oa[4 * i + 2], oa[4 * i + 3]);
-          float lo[8], hi[8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) { lo[i] = om[i]; hi[i] = om[8 + i]; }
-          uint4* dm = reinterpret_cast<uint4*>(Mg + ibase * C * C + (size_t)row * C + col);
-          dm[0] = umma::pack8(lo);
-          dm[1] = umma::pack8(hi);
+          for (int i = 0; i < 16; ++i) va[i] = vm[i] = 0.f;
         }
-        umma::tc_fence_before();
+        const bool mine = bj < bi && owner_level(bi, bj) == lv;
+        const bool zero_fill = lv == 0 && bj > bi;
+        if (!mine && !zero_fill) continue;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const bool keep = mine && seg_s[row] == seg_s[col + i];
+          va[i] = keep ? va[i] : 0.f;
+          vm[i] = keep ? vm[i] : 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) __stcg(Ag4 + p4v(row, col + 4 * i), make_float4(va[4 * i], va[4 * i + 1], va[4 * i + 2], va[4 * i + 3]));
+        Mimg[(col / 8) * 128 + row] = umma::pack8p(vm);
+        Mimg[(col / 8 + 1) * 128 + row] = umma::pack8p(vm + 8);
+      }
+      umma::tc_fence_before();
+    };
+    build(0);
+    for (int lv = 0; lv < 3; ++lv) {
+      const uint32_t tcol = (uint32_t)((lv & 1) * 256);
+      umma::pre_issue_sync();
+      umma::issue<128, false, false>(cx, KR, KR, K, tcol, false);          // A: KR KR^T
+      umma::issue<128, false, false>(cx, QK, KR, K, tcol + 128, false);    // M: QK KR^T
+      umma::commit_wait(cx);
+      if (lv < 2) build(lv + 1);
+      drain_level(lv);
+    }
+    __syncthreads();
+
+    // ---- 16x16 diagonal blocks, exact.  k_hat of the chunk is cached in shared memory (fp32, one
+    //      row per 8x4 thread); two warps per block take alternate rows i, lanes own 4 channels, and
+    //      the q / b of the warp's next row are in flight while the current row is reduced.
+    {
+#pragma unroll
+      for (int it = 0; it < 4; ++it) {
+        const int p = it * 4 + lgrp;
+        float kh[8];
+        khat8(r, myrow, p, kh);
+        *reinterpret_cast<float4*>(KHs + myrow * AP + 8 * p) = make_float4(kh[0], kh[1], kh[2], kh[3]);
+        *reinterpret_cast<float4*>(KHs + myrow * AP + 8 * p + 4) = make_float4(kh[4], kh[5], kh[6], kh[7]);
       }
       __syncthreads();
-    }
-
-    // ---- 16x16 diagonal blocks, exact: two warps per block (alternate rows), lanes own 4 channels
-    {
       const int r0 = (warp >> 1) * 16;
+      const size_t bcol = r.bC == 1 ? 0 : 4 * lane;
+      auto fetch = [&](int ri, float4& q4, float4& b4) {
+        const bool live = ri < r.rows_valid;
+        const int rr = live ? ri : 0;
+        q4 = in4(r.q, r.qk_row0 + (size_t)rr * r.qk_pitch + 4 * lane, qdt);
+        if (r.bC == 1) { const float v = ldf_ro(r.b, r.b_row0 + (size_t)rr * r.b_pitch, gdt); b4 = make_float4(v, v, v, v); }
+        else b4 = in4(r.b, r.b_row0 + (size_t)rr * r.b_pitch + bcol, gdt);
+      };
+      float4 nq, nb;
+      fetch(r0 + (warp & 1), nq, nb);
+#pragma unroll 1
       for (int i = warp & 1; i < 16; i += 2) {
         const int ri = r0 + i;
-        float ki[4], qi[4], bi4[4];
-        row4(r, ri, lane, ki, qi, bi4, true);
+        const bool live = ri < r.rows_valid;
+        float4 q4 = nq, b4 = nb;
+        if (i + 2 < 16) fetch(ri + 2, nq, nb);
+        const float4 k4 = *reinterpret_cast<const float4*>(KHs + ri * AP + 4 * lane);
         const float4 li = *reinterpret_cast<const float4*>(LAM + ri * LP + 4 * lane);
+        float qi[4] = {q4.x, q4.y, q4.z, q4.w}, bi4[4] = {b4.x, b4.y, b4.z, b4.w};
+        const float ki[4] = {k4.x, k4.y, k4.z, k4.w};
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          qi[u] = (qi[u] * rq_s[ri]) * r.scale;
+          if (r.round_in) qi[u] = bf16r(qi[u]);
+          if (fuse) bi4[u] = 1.f / (1.f + expf(-bi4[u]));
+          bi4[u] *= ki[u];
+          if (!live) { qi[u] = 0.f; bi4[u] = 0.f; }
+        }
         float arow = 0.f, mrow = 0.f;                  // lane j (< 16) keeps entry (ri, r0 + j)
-        for (int j = 0; j <= i; ++j) {
+#pragma unroll 1
+        for (int j = 0; j <= i; j += 2) {              // two columns per step: four independent reductions
           const int rj = r0 + j;
-          float kj[4], dq[4], db[4];
-          row4(r, rj, lane, kj, dq, db, false);
-          const float4 lj = *reinterpret_cast<const float4*>(LAM + rj * LP + 4 * lane);
-          const float e0 = kj[0] * exp2f(fminf(li.x - lj.x, 0.f) * DN_LOG2E), e1 = kj[1] * exp2f(fminf(li.y - lj.y, 0.f) * DN_LOG2E);
-          const float e2 = kj[2] * exp2f(fminf(li.z - lj.z, 0.f) * DN_LOG2E), e3 = kj[3] * exp2f(fminf(li.w - lj.w, 0.f) * DN_LOG2E);
-          float pa = bi4[0] * e0 + bi4[1] * e1 + bi4[2] * e2 + bi4[3] * e3;
-          float pm = qi[0] * e0 + qi[1] * e1 + qi[2] * e2 + qi[3] * e3;
-          pa = warp_sum(pa);
-          pm = warp_sum(pm);
-          const bool same = seg_s[ri] == seg_s[rj];
-          if (lane == j) { arow = (j < i && same) ? pa : 0.f; mrow = same ? pm : 0.f; }
+          const float4 ka = *reinterpret_cast<const float4*>(KHs + rj * AP + 4 * lane);
+          const float4 kb = *reinterpret_cast<const float4*>(KHs + (rj + 1) * AP + 4 * lane);
+          const float4 la = *reinterpret_cast<const float4*>(LAM + rj * LP + 4 * lane);
+          const float4 lb = *reinterpret_cast<const float4*>(LAM + (rj + 1) * LP + 4 * lane);
+          const float a0 = ka.x * umma::ex2_fast(fminf(li.x - la.x, 0.f) * DN_LOG2E), a1 = ka.y * umma::ex2_fast(fminf(li.y - la.y, 0.f) * DN_LOG2E);
+          const float a2 = ka.z * umma::ex2_fast(fminf(li.z - la.z, 0.f) * DN_LOG2E), a3 = ka.w * umma::ex2_fast(fminf(li.w - la.w, 0.f) * DN_LOG2E);
+          const float b0 = kb.x * umma::ex2_fast(fminf(li.x - lb.x, 0.f) * DN_LOG2E), b1 = kb.y * umma::ex2_fast(fminf(li.y - lb.y, 0.f) * DN_LOG2E);
+          const float b2 = kb.z * umma::ex2_fast(fminf(li.z - lb.z, 0.f) * DN_LOG2E), b3 = kb.w * umma::ex2_fast(fminf(li.w - lb.w, 0.f) * DN_LOG2E);
+          float pa0 = bi4[0] * a0 + bi4[1] * a1 + bi4[2] * a2 + bi4[3] * a3;
+          float pm0 = qi[0] * a0 + qi[1] * a1 + qi[2] * a2 + qi[3] * a3;
+          float pa1 = bi4[0] * b0 + bi4[1] * b1 + bi4[2] * b2 + bi4[3] * b3;
+          float pm1 = qi[0] * b0 + qi[1] * b1 + qi[2] * b2 + qi[3] * b3;
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) {
+            pa0 += __shfl_xor_sync(0xffffffffu, pa0, o); pm0 += __shfl_xor_sync(0xffffffffu, pm0, o);
+            pa1 += __shfl_xor_sync(0xffffffffu, pa1, o); pm1 += __shfl_xor_sync(0xffffffffu, pm1, o);
+          }
+          if (lane == j) {
+            const bool same = seg_s[ri] == seg_s[rj];
+            arow = (j < i && same) ? pa0 : 0.f;
+            mrow = same ? pm0 : 0.f;
+          }
+          if (lane == j + 1 && j + 1 <= i) {
+            const bool same = seg_s[ri] == seg_s[rj + 1];
+            arow = (j + 1 < i && same) ? pa1 : 0.f;
+            mrow = same ? pm1 : 0.f;
+          }
         }
         if (lane < 16) {
-          Ag[ri * C + r0 + lane] = arow;
-          Mg[ibase * C * C + (size_t)ri * C + r0 + lane] = __float2bfloat16_rn(mrow);
+          Ag[p4f(ri, r0 + lane)] = arow;
+          Mel[rix(true, ri, r0 + lane, C)] = __float2bfloat16_rn(mrow);
         }
       }
     }
     __syncthreads();
 
     // ---- T = (I + A)^-1 in fp32: substitution on the diagonal blocks, then block merges
-    for (int e = tid; e < C * C / 4; e += NT) {
-      reinterpret_cast<float4*>(As)[e] = reinterpret_cast<const float4*>(Ag)[e];
-      reinterpret_cast<float4*>(Ts)[e] = make_float4(0.f, 0.f, 0.f, 0.f);
+    {
+      float4* As4 = reinterpret_cast<float4*>(As);
+      float4* Ts4 = reinterpret_cast<float4*>(Ts);
+#pragma unroll 4
+      for (int e = tid; e < 32 * C; e += NT) {
+        const int q = e >> 7, i = e & 127;
+        As4[i * (AP / 4) + q] = __ldcg(Ag4 + e);
+      }
+      for (int e = tid; e < C * AP / 4; e += NT) Ts4[e] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
     __syncthreads();
     if (tid < C) {
-      const int j = tid, blk0 = j & ~15;
-      Ts[j * C + j] = 1.f;
-      for (int i = j + 1; i < blk0 + 16; ++i) {
+      const int j = tid, blk0 = j & ~15, jl = j & 15;
+      float col[16];
+#pragma unroll
+      for (int m = 0; m < 16; ++m) col[m] = m == jl ? 1.f : 0.f;
+#pragma unroll
+      for (int i = 1; i < 16; ++i) {
+        float av[16];
+#pragma unroll
+        for (int u = 0; u < (i + 3) / 4; ++u)
+          *reinterpret_cast<float4*>(av + 4 * u) = *reinterpret_cast<const float4*>(As + (blk0 + i) * AP + blk0 + 4 * u);
         float s = 0.f;
-        for (int m = j; m < i; ++m) s = fmaf(As[i * C + m], Ts[m * C + j], s);
-        Ts[i * C + j] = -s;
+#pragma unroll
+        for (int m = 0; m < i; ++m) s = fmaf(av[m], col[m], s);
+        if (i > jl) col[i] = -s;
       }
+#pragma unroll
+      for (int i = 0; i < 16; ++i) Ts[(blk0 + i) * AP + j] = col[i];
     }
     __syncthreads();
-    for (int s = 16; s < C; s <<= 1) {
-      const int total = C * s / 2;
-      for (int e = tid; e < total; e += NT) {
-        const int p = e / (s * s), rem = e - p * s * s, il = rem / s, jl = rem - il * s;
-        const int i = 2 * p * s + s + il, j = 2 * p * s + jl, mend = 2 * p * s + s;
-        float acc = 0.f;
-        for (int m = j; m < mend; ++m) acc = fmaf(As[i * C + m], Ts[m * C + j], acc);
-        Tm[i * C + j] = acc;
-      }
-      __syncthreads();
-      for (int e = tid; e < total; e += NT) {
-        const int p = e / (s * s), rem = e - p * s * s, il = rem / s, jl = rem - il * s;
-        const int i = 2 * p * s + s + il, j = 2 * p * s + jl, m0 = 2 * p * s + s;
-        float acc = 0.f;
-        for (int m = m0; m <= i; ++m) acc = fmaf(Ts[i * C + m], Tm[m * C + j], acc);
-        Ts[i * C + j] = -acc;
-      }
-      __syncthreads();
+    merge_level<16>(As, Ts, Tm);
+    merge_level<32>(As, Ts, Tm);
+    merge_level<64>(As, Ts, Tm);
+    if (a.res.T) {
+      float4* Tg = reinterpret_cast<float4*>(a.res.T + ibase * C * C);
+      for (int e = tid; e < C * C / 4; e += NT) Tg[e] = *reinterpret_cast<const float4*>(Ts + (e >> 5) * AP + 4 * (e & 31));
     }
-    if (a.res.T)
-      for (int e = tid; e < C * C / 4; e += NT)
-        reinterpret_cast<float4*>(a.res.T + ibase * C * C)[e] = reinterpret_cast<const float4*>(Ts)[e];
 
     // ---- W = T X, U = T Y on the tensor cores
     for (int e = tid; e < IMG; e += NT) {                       // T as K-major A: piece (p = j/8, x = i)
       const int p = e >> 7, x = e & 127;
-      TI[e] = umma::ld8_f32(Ts + x * C + 8 * p);
+      TI[e] = umma::ld8_f32(Ts + x * AP + 8 * p);
     }
-    for (int e = tid; e < (VW / 8) * 128; e += NT) {            // Y = w*v as MN-major B
-      const int p = e >> 7, x = e & 127, t = t0 + x;
-      float f[8];
-      zero8(f);
-      if (t < g.L) {
+    {                                                           // Y = w*v as MN-major B
+      const int x = myrow, t = t0 + x;
+      const bool live = t < g.L;
+      const size_t tokr = (size_t)b * g.L + (live ? t : t0);
+#pragma unroll 4
+      for (int it = 0; it < VW / 32; ++it) {
+        const int p = it * 4 + lgrp;
         const int col0 = h * VW + 8 * p, hv = col0 / g.V, cv = col0 - hv * g.V;
-        float vv[8], ww[8];
-        load8(a.v, (size_t)(b * (size_t)g.L + t) * g.Hv * g.V + col0, g.qkv_dt, vv);
-        const size_t wrow = ((size_t)(b * (size_t)g.L + t) * g.wH + g.w_head(hv)) * g.wC;
-        if (g.wC == 1) {
-          const float w1 = ldf(a.w, wrow, g.gate_dt);
+        float vv[8], ww[8], f[8];
+        load8(a.v, tokr * g.Hv * g.V + col0, qdt, vv);
+        if (wC == 1) {
+          const float w1 = ldf_ro(a.w, tokr * g.wH + g.w_head(hv), gdt);
 #pragma unroll
           for (int i = 0; i < 8; ++i) ww[i] = w1;
         } else {
-          load8(a.w, wrow + cv, g.gate_dt, ww);
+          load8(a.w, (tokr * g.wH + g.w_head(hv)) * wC + cv, gdt, ww);
         }
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           const float wa = fuse ? 1.f / (1.f + expf(-ww[i])) : ww[i];
-          f[i] = wa * vv[i];
+          f[i] = live ? wa * vv[i] : 0.f;
         }
+        YI[p * 128 + x] = umma::pack8(f);
       }
-      YI[p * 128 + x] = umma::pack8(f);
     }
     umma::pre_issue_sync();
     umma::issue<128, false, true>(cx, TI, XI, C, 0, false);
     umma::issue<VW, false, true>(cx, TI, YI, C, 128, false);
     umma::commit_wait(cx);
     umma::drain<NT, 128>(cx, 0, [&](int row, int col, const float (&v)[16]) {
-      float lo[8], hi[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) { lo[i] = v[i]; hi[i] = v[8 + i]; }
-      uint4* d = reinterpret_cast<uint4*>(Wg + ibase * C * K + (size_t)row * K + col);
-      d[0] = umma::pack8(lo);
-      d[1] = umma::pack8(hi);
+      Wimg[(col / 8) * 128 + row] = umma::pack8p(v);
+      Wimg[(col / 8 + 1) * 128 + row] = umma::pack8p(v + 8);
     });
     umma::drain<NT, VW>(cx, 128, [&](int row, int col, const float (&v)[16]) {
-      float lo[8], hi[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) { lo[i] = v[i]; hi[i] = v[8 + i]; }
-      uint4* d = reinterpret_cast<uint4*>(Ug + ibase * C * VW + (size_t)row * VW + col);
-      d[0] = umma::pack8(lo);
-      d[1] = umma::pack8(hi);
+      Uimg[(col / 8) * 128 + row] = umma::pack8p(v);
+      Uimg[(col / 8 + 1) * 128 + row] = umma::pack8p(v + 8);
     });
     __syncthreads();
   }
@@ -325,9 +409,7 @@ __global__ void __launch_bounds__(NT, 1) prepass_fwd_tc_kernel(PrepassFwdArgs a,
 
 }  // namespace
 
-bool prepass_fwd_tc_eligible(const Geo& g) {
-  return g.prec == DN_PREC_BF16 && g.C == 128 && g.K == 128 && (g.Vw == 128 || g.Vw == 256);
-}
+bool prepass_fwd_tc_eligible(const Geo& g) { return g.img; }
 
 size_t prepass_fwd_tc_scratch_per_cta() { return (size_t)C * C; }
 
@@ -342,14 +424,16 @@ int launch_prepass_fwd_tc(const Geo& g, const void* q, const void* k, const void
   const int grid = a.items < 148 ? a.items : 148;
   if (scratch_floats < (size_t)grid * a.scratch_per_cta) return DN_ERR_SCRATCH_TOO_SMALL;
   a.scratch = scratch;
-  const size_t smem = 3 * 65536 + 32768;
   int* err = device_error_ptr();
+  auto go = [&](auto kernel) {
+    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    kernel<<<grid, NT, SMEM_BYTES, st>>>(a, err);
+  };
+  const int mode = input_mode(g);
   if (g.Vw == 256) {
-    cudaFuncSetAttribute(prepass_fwd_tc_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    prepass_fwd_tc_kernel<256><<<grid, NT, smem, st>>>(a, err);
+    if (mode == 0) go(prepass_fwd_tc_kernel<256, 0>); else if (mode == 1) go(prepass_fwd_tc_kernel<256, 1>); else go(prepass_fwd_tc_kernel<256, 2>);
   } else {
-    cudaFuncSetAttribute(prepass_fwd_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    prepass_fwd_tc_kernel<128><<<grid, NT, smem, st>>>(a, err);
+    if (mode == 0) go(prepass_fwd_tc_kernel<128, 0>); else if (mode == 1) go(prepass_fwd_tc_kernel<128, 1>); else go(prepass_fwd_tc_kernel<128, 2>);
   }
   return cudaGetLastError() == cudaSuccess ? DN_OK : DN_ERR_CUDA_LAUNCH;
 }

@@ -57,10 +57,10 @@ __global__ void __launch_bounds__(DN_THREADS) state_fwd_kernel(StateArgs a) {
     const size_t bW = item * C * K, bU = item * C * Vw, bM = item * C * C;
     // V_new = U - W S
     cta_gemm<true, true>(C, VS, K,
-        [&](int i, int kk) { return ldf(a.res.W, bW + (size_t)i * K + kk, pre); },
+        [&](int i, int kk) { return ldf(a.res.W, bW + rix(g.img, i, kk, K), pre); },
         [&](int kk, int j) { float s = S[kk * VS + j]; return sbf ? bf16r(s) : s; },
         [&](int i, int j, float acc) {
-          const float u = a.res.U ? ldf(a.res.U, bU + (size_t)i * Vw + v0 + j, pre) : 0.f;   // U == NULL: transition pass
+          const float u = a.res.U ? ldf(a.res.U, bU + rix(g.img, i, v0 + j, Vw), pre) : 0.f;   // U == NULL: transition pass
           Vn[i * VS + j] = u - acc;
         },
         tile);
@@ -68,8 +68,8 @@ __global__ void __launch_bounds__(DN_THREADS) state_fwd_kernel(StateArgs a) {
       // O = [qe | M] [S ; V_new]
       cta_gemm<true, true>(C, VS, K + C,
           [&](int i, int kk) {
-            return kk < K ? ldf(a.res.qe, bW + (size_t)i * K + kk, pre)
-                          : ldf(a.res.M, bM + (size_t)i * C + (kk - K), pre);
+            return kk < K ? ldf(a.res.qe, bW + rix(g.img, i, kk, K), pre)
+                          : ldf(a.res.M, bM + rix(g.img, i, kk - K, C), pre);
           },
           [&](int kk, int j) {
             if (kk < K) { float s = S[kk * VS + j]; return sbf ? bf16r(s) : s; }
@@ -84,7 +84,7 @@ __global__ void __launch_bounds__(DN_THREADS) state_fwd_kernel(StateArgs a) {
     }
     // S <- decay * S + ke^T V_new
     cta_gemm<false, true>(K, VS, C,
-        [&](int i, int kk) { return ldf(a.res.ke, bW + (size_t)kk * K + i, pre); },
+        [&](int i, int kk) { return ldf(a.res.ke, bW + rix(g.img, kk, i, K), pre); },
         [&](int kk, int j) { float x = Vn[kk * VS + j]; return sbf ? bf16r(x) : x; },
         [&](int i, int j, float acc) {
           float carried = 0.f;
@@ -130,8 +130,8 @@ __global__ void __launch_bounds__(DN_THREADS) state_bwd_kernel(StateArgs a) {
     // dV = M^T dO + ke dH
     cta_gemm<false, true>(C, VS, C + K,
         [&](int i, int kk) {
-          return kk < C ? ldf(a.res.M, bM + (size_t)kk * C + i, pre)
-                        : ldf(a.res.ke, bW + (size_t)i * K + (kk - C), pre);
+          return kk < C ? ldf(a.res.M, bM + rix(g.img, kk, i, C), pre)
+                        : ldf(a.res.ke, bW + rix(g.img, i, kk - C, K), pre);
         },
         [&](int kk, int j) {
           if (kk < C) { float x = dOs[kk * VS + j]; return ibf ? bf16r(x) : x; }
@@ -146,8 +146,8 @@ __global__ void __launch_bounds__(DN_THREADS) state_bwd_kernel(StateArgs a) {
     // dH <- decay * dH + qe^T dO - W^T dV, cleared at a document start
     cta_gemm<false, true>(K, VS, 2 * C,
         [&](int i, int kk) {
-          return kk < C ? ldf(a.res.qe, bW + (size_t)kk * K + i, pre)
-                        : -ldf(a.res.W, bW + (size_t)(kk - C) * K + i, pre);
+          return kk < C ? ldf(a.res.qe, bW + rix(g.img, kk, i, K), pre)
+                        : -ldf(a.res.W, bW + rix(g.img, kk - C, i, K), pre);
         },
         [&](int kk, int j) {
           float x = kk < C ? dOs[kk * VS + j] : dVs[(kk - C) * VS + j];

@@ -42,11 +42,19 @@ __device__ __forceinline__ size_t native_state_index_tc(const Geo& g, int b, int
   return (((size_t)b * g.Hv + hv) * g.K + k) * g.V + cv;
 }
 
-// Thread `row` copies its 256-byte row of a (128,128) bf16 tile into the panel image.
-__device__ __forceinline__ void copy_tile_async(uint4* dst, const __nv_bfloat16* src, int row) {
-  const uint4* s = reinterpret_cast<const uint4*>(src + (size_t)row * 128);
+// Thread `row` copies its share of a (128,128) bf16 tile into the panel image: its 256-byte row of
+// a row-major tile, or (img) piece `row` of each of the 16 panels of a tile that already lies in
+// global memory as the image -- then a warp's 32 copies are 512 contiguous bytes.
+__device__ __forceinline__ void copy_tile_async(uint4* dst, const __nv_bfloat16* src, int row, bool img) {
+  if (img) {
+    const uint4* s = reinterpret_cast<const uint4*>(src) + row;
 #pragma unroll
-  for (int p = 0; p < 16; ++p) umma::cp_async16(dst + p * 128 + row, s + p);
+    for (int p = 0; p < 16; ++p) umma::cp_async16(dst + p * 128 + row, s + p * 128);
+  } else {
+    const uint4* s = reinterpret_cast<const uint4*>(src + (size_t)row * 128);
+#pragma unroll
+    for (int p = 0; p < 16; ++p) umma::cp_async16(dst + p * 128 + row, s + p);
+  }
 }
 
 template <int VS>
@@ -107,11 +115,11 @@ __global__ void __launch_bounds__(128, 1) state_fwd_tc_kernel(StateArgs a) {
   const __nv_bfloat16* Ug = reinterpret_cast<const __nv_bfloat16*>(a.res.U);
   const size_t item0 = ((size_t)b * g.H + h) * g.NC;
 
-  copy_tile_async(sW, Wg + item0 * C * K, row);
+  copy_tile_async(sW, Wg + item0 * C * K, row, g.img);
   umma::cp_async_commit();
-  copy_tile_async(sQE, QEg + item0 * C * K, row);
-  copy_tile_async(sM, Mg + item0 * C * C, row);
-  copy_tile_async(sKE, KEg + item0 * C * K, row);
+  copy_tile_async(sQE, QEg + item0 * C * K, row, g.img);
+  copy_tile_async(sM, Mg + item0 * C * C, row, g.img);
+  copy_tile_async(sKE, KEg + item0 * C * K, row, g.img);
   umma::cp_async_commit();
 
   float S[VS];
@@ -137,9 +145,15 @@ __global__ void __launch_bounds__(128, 1) state_fwd_tc_kernel(StateArgs a) {
     stage_rows<VS>(sS, row, S);
     uint4 ureg[VS / 8];
     if (Ug) {
-      const uint4* up = reinterpret_cast<const uint4*>(Ug + item * C * Vw + (size_t)row * Vw + v0);
+      if (g.img) {
+        const uint4* up = reinterpret_cast<const uint4*>(Ug + item * C * Vw) + (size_t)(v0 / 8) * 128 + row;
 #pragma unroll
-      for (int p = 0; p < VS / 8; ++p) ureg[p] = up[p];
+        for (int p = 0; p < VS / 8; ++p) ureg[p] = up[p * 128];
+      } else {
+        const uint4* up = reinterpret_cast<const uint4*>(Ug + item * C * Vw + (size_t)row * Vw + v0);
+#pragma unroll
+        for (int p = 0; p < VS / 8; ++p) ureg[p] = up[p];
+      }
     } else {                                            // U == NULL: transition pass (U = 0)
 #pragma unroll
       for (int p = 0; p < VS / 8; ++p) ureg[p] = make_uint4(0, 0, 0, 0);
@@ -150,7 +164,7 @@ __global__ void __launch_bounds__(128, 1) state_fwd_tc_kernel(StateArgs a) {
     umma::pre_issue_sync();
     umma::issue<VS, false, true>(cx, sW, sS, K, colP, false);          // P = W S
     umma::commit_wait(cx);
-    if (c + 1 < g.NC) copy_tile_async(sW, Wg + (item + 1) * C * K, row);
+    if (c + 1 < g.NC) copy_tile_async(sW, Wg + (item + 1) * C * K, row, g.img);
     umma::cp_async_commit();
 
     float vn[VS];
@@ -173,9 +187,9 @@ __global__ void __launch_bounds__(128, 1) state_fwd_tc_kernel(StateArgs a) {
     umma::issue<VS, true, true>(cx, sKE, sVn, C, colS, false);         // ke^T V_new
     umma::commit_wait(cx);
     if (c + 1 < g.NC) {
-      copy_tile_async(sQE, QEg + (item + 1) * C * K, row);
-      copy_tile_async(sM, Mg + (item + 1) * C * C, row);
-      copy_tile_async(sKE, KEg + (item + 1) * C * K, row);
+      copy_tile_async(sQE, QEg + (item + 1) * C * K, row, g.img);
+      copy_tile_async(sM, Mg + (item + 1) * C * C, row, g.img);
+      copy_tile_async(sKE, KEg + (item + 1) * C * K, row, g.img);
     }
     umma::cp_async_commit();
 
@@ -247,11 +261,11 @@ __global__ void __launch_bounds__(128, 1) state_bwd_tc_kernel(StateArgs a) {
   const size_t item0 = ((size_t)b * g.H + h) * g.NC;
   const size_t last = item0 + g.NC - 1;
 
-  copy_tile_async(sM, Mg + last * C * C, row);
-  copy_tile_async(sKE, KEg + last * C * K, row);
+  copy_tile_async(sM, Mg + last * C * C, row, g.img);
+  copy_tile_async(sKE, KEg + last * C * K, row, g.img);
   umma::cp_async_commit();
-  copy_tile_async(sQE, QEg + last * C * K, row);
-  copy_tile_async(sW, Wg + last * C * K, row);
+  copy_tile_async(sQE, QEg + last * C * K, row, g.img);
+  copy_tile_async(sW, Wg + last * C * K, row, g.img);
   umma::cp_async_commit();
 
   float dH[VS];
@@ -306,8 +320,8 @@ __global__ void __launch_bounds__(128, 1) state_bwd_tc_kernel(StateArgs a) {
     umma::issue<VS, false, true>(cx, sKE, sdH, K, colV, true);         //     + ke dH
     umma::commit_wait(cx);
     if (c > 0) {
-      copy_tile_async(sM, Mg + (item - 1) * C * C, row);
-      copy_tile_async(sKE, KEg + (item - 1) * C * K, row);
+      copy_tile_async(sM, Mg + (item - 1) * C * C, row, g.img);
+      copy_tile_async(sKE, KEg + (item - 1) * C * K, row, g.img);
     }
     umma::cp_async_commit();
 
@@ -326,8 +340,8 @@ __global__ void __launch_bounds__(128, 1) state_bwd_tc_kernel(StateArgs a) {
     umma::issue<VS, true, true>(cx, sW, sdV, C, colH, true);           // - W^T dV
     umma::commit_wait(cx);
     if (c > 0) {
-      copy_tile_async(sQE, QEg + (item - 1) * C * K, row);
-      copy_tile_async(sW, Wg + (item - 1) * C * K, row);
+      copy_tile_async(sQE, QEg + (item - 1) * C * K, row, g.img);
+      copy_tile_async(sW, Wg + (item - 1) * C * K, row, g.img);
     }
     umma::cp_async_commit();
 
