@@ -15,15 +15,16 @@ constexpr int LP = 132;                // row pitch (floats) of the shared-memor
                                        // shifts between rows keep row-strided float4 reads conflict-free
 
 // What a kernel instantiation knows about its inputs at compile time.  MODE 0: q/k/v in bf16, gates
-// in fp32, every gate with one value per channel; MODE 1: the same with q/k/v in fp32; MODE 2:
-// nothing (dtypes and gate widths are run-time properties, every load sits behind a branch).
+// in fp32 and already activated (no fused prologue), every gate with one value per channel; MODE 1:
+// the same with q/k/v in fp32; MODE 2: nothing (dtypes, gate widths and the prologue are run-time
+// properties, every load sits behind a branch and both activation paths are compiled in).
 template <int MODE>
 struct InCfg {
   static constexpr bool fixed = MODE != 2;
   static constexpr int qkv_dt = MODE == 0 ? DN_BF16 : DN_F32;
 };
 inline int input_mode(const Geo& g) {
-  const bool full = g.gC == g.K && g.bC == g.K && g.wC == g.V && g.gate_dt == DN_F32;
+  const bool full = g.gC == g.K && g.bC == g.K && g.wC == g.V && g.gate_dt == DN_F32 && !(g.flags & DN_FUSE_PROLOGUE);
   if (!full) return 2;
   return g.qkv_dt == DN_BF16 ? 0 : 1;
 }
@@ -246,7 +247,9 @@ __device__ __forceinline__ Rows make_rows(const Geo& g, const void* q, const voi
   r.b_pitch = (size_t)g.bH * g.bC;
   r.b_row0 = tok0 * r.b_pitch + (size_t)g.gate_head(h, g.bH) * g.bC;
   r.rows_valid = g.L - t0 < C ? g.L - t0 : C;
-  r.l2 = g.flags & DN_QK_L2NORM; r.fuse = g.flags & DN_FUSE_PROLOGUE; r.guard = g.flags & DN_STABILITY_GUARD;
+  r.l2 = g.flags & DN_QK_L2NORM;
+  r.fuse = CF::fixed ? false : (g.flags & DN_FUSE_PROLOGUE) != 0;
+  r.guard = CF::fixed ? false : (g.flags & DN_STABILITY_GUARD) != 0;
   r.round_in = !r.fuse && g.qkv_dt == DN_BF16;
   r.scale = g.scale;
   r.rq = rq; r.rk = rk;

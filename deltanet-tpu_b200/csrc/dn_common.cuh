@@ -79,6 +79,15 @@ __host__ __device__ __forceinline__ size_t rix(bool img, int row, int col, int n
   return img ? ((size_t)((col >> 3) * 128 + row) << 3) + (col & 7) : (size_t)row * ncols + col;
 }
 
+// Optional phase clock (compile with -DDN_PHASE_TIMING): CTA 0 records clock64 at marked points of
+// its first item and prints the differences.  Compiled out otherwise.
+#ifdef DN_PHASE_TIMING
+static __device__ long long g_phase_marks[48];
+#define DN_MARK(i) do { if (blockIdx.x == 0 && threadIdx.x == 0) g_phase_marks[i] = clock64(); } while (0)
+#else
+#define DN_MARK(i) do { } while (0)
+#endif
+
 // --------------------------------------------------------------------------- dtype helpers
 __device__ __forceinline__ float bf16r(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 

@@ -121,8 +121,9 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
   umma::tc_fence_after();
   umma::Ctx cx{tmem_base, &mma_bar, 0u, a.err, false};
 
-  const bool l2 = g.flags & DN_QK_L2NORM, fuse = g.flags & DN_FUSE_PROLOGUE;
-  const bool guard = g.flags & DN_STABILITY_GUARD;
+  const bool l2 = g.flags & DN_QK_L2NORM;
+  const bool fuse = CF::fixed ? false : (g.flags & DN_FUSE_PROLOGUE) != 0;     // the fixed modes have no fused prologue
+  const bool guard = CF::fixed ? false : (g.flags & DN_STABILITY_GUARD) != 0;
   const bool trunc = g.flags & DN_TRUNC_DT_BF16;
 
   for (int item = blockIdx.x; item < a.items; item += gridDim.x) {
@@ -135,6 +136,29 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
     chunk_flags(a.seg, g, b, c_idx, is_new, all_same);
     __syncthreads();
     const int seg0 = seg_s[0], segL = seg_s[C - 1];
+    {
+      // everything this item streams from global memory is asked into L2 now: the later phases then
+      // pay an L2 hit instead of a DRAM access for their first touch
+      const int rows = g.L - t0 < C ? g.L - t0 : C;
+      const size_t tok0 = (size_t)b * g.L + t0;
+      const size_t qsz = dt_size(g.qkv_dt), gsz = dt_size(g.gate_dt);
+      if (tid == 0) {
+        umma::prefetch_l2_bulk(a.dV + ibase * CV, (uint32_t)(CV * 4));
+        umma::prefetch_l2_bulk(a.dH + ibase * K * VW, (uint32_t)(K * VW * 4));
+        umma::prefetch_l2_bulk(a.res.T + ibase * CC, (uint32_t)(CC * 4));
+      }
+      const int hq = h / g.qk_div;
+      umma::prefetch_rows_l2<NT>(reinterpret_cast<const uint8_t*>(a.d_out) + (tok0 * g.Hv * g.V + (size_t)h * VW) * qsz, rows, (size_t)g.Hv * g.V * qsz, (int)(VW * qsz));
+      umma::prefetch_rows_l2<NT>(reinterpret_cast<const uint8_t*>(a.v) + (tok0 * g.Hv * g.V + (size_t)h * VW) * qsz, rows, (size_t)g.Hv * g.V * qsz, (int)(VW * qsz));
+      umma::prefetch_rows_l2<NT>(reinterpret_cast<const uint8_t*>(a.q) + (tok0 * g.Hk + hq) * K * qsz, rows, (size_t)g.Hk * K * qsz, (int)(K * qsz));
+      umma::prefetch_rows_l2<NT>(reinterpret_cast<const uint8_t*>(a.k) + (tok0 * g.Hk + hq) * K * qsz, rows, (size_t)g.Hk * K * qsz, (int)(K * qsz));
+      umma::prefetch_rows_l2<NT>(reinterpret_cast<const uint8_t*>(a.gg) + (tok0 * g.gH + g.gate_head(h, g.gH)) * g.gC * gsz, rows, (size_t)g.gH * g.gC * gsz, (int)(g.gC * gsz));
+      umma::prefetch_rows_l2<NT>(reinterpret_cast<const uint8_t*>(a.b) + (tok0 * g.bH + g.gate_head(h, g.bH)) * g.bC * gsz, rows, (size_t)g.bH * g.bC * gsz, (int)(g.bC * gsz));
+      if (g.wC != 1) {
+        const int hv0 = h * VW / g.V;
+        umma::prefetch_rows_l2<NT>(reinterpret_cast<const uint8_t*>(a.w) + (tok0 * g.wH + g.w_head(hv0)) * g.wC * gsz, rows, (size_t)g.wH * g.wC * gsz, (int)((g.wH == g.Hv ? VW : g.V) * gsz));
+      }
+    }
 
     // ---- G. the matrix products (and dLambda_end from the carried state)
     {
@@ -166,67 +190,81 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
 
     DN_MARK(8);
     // ---- D. diagonal 16x16 blocks, exact.  The blocks of dA and dM are staged in shared memory
-    //         (all lanes of a warp read the same entry); one thread per (block, channel) walks the
-    //         rows i of the block with the next row's q, k, b already in flight, and for every
-    //         earlier row j adds to dbeta'_i, dq'_i (scalars) and dk'_j (one register per j).
+    //         (all lanes of a warp read the same entry), and so are k_hat, q_hat and beta of 64 rows
+    //         at a time (fp32, one global round trip per half); one thread per (block, channel)
+    //         then walks the rows i of its block and, for every earlier row j, adds to dbeta'_i,
+    //         dq'_i (scalars) and dk'_j (one register per j), reading shared memory only.
     //         This pass initialises DBP / DQP / DKP; the levels of phase H add to them.
     {
-      float4* DG4 = reinterpret_cast<float4*>(smraw + OFF_IMG);      // [2][8 blocks][16 rows][4]
+      constexpr int CP = 132;                                        // row pitch of the caches
+      float* KC = reinterpret_cast<float*>(smraw + OFF_IMG);         // [64][CP] k_hat
+      float* QC = KC + 64 * CP;                                      // q_hat
+      float* BC = QC + 64 * CP;                                      // beta = b_act * k_hat
+      float4* DG4 = reinterpret_cast<float4*>(BC + 64 * CP);         // [2][8 blocks][16 rows][4]
       for (int e = tid; e < 512; e += NT) {
         const int blk = e >> 6, q4 = (e >> 4) & 3, row = e & 15;
         DG4[(blk * 16 + row) * 4 + q4] = __ldcg(DA4 + p4v(blk * 16 + row, blk * 16 + 4 * q4));
         DG4[512 + (blk * 16 + row) * 4 + q4] = __ldcg(DM4 + p4v(blk * 16 + row, blk * 16 + 4 * q4));
       }
-      __syncthreads();
-      for (int task = tid; task < 8 * K; task += NT) {
-        const int blk = task >> 7, r0 = blk * 16, c = task & 127;
-        const size_t bcol = r.bC == 1 ? 0 : c;
-        float lam[16], kh[16], sk[16];
+#pragma unroll 1
+      for (int half = 0; half < 2; ++half) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const int x = r0 + i;
-          lam[i] = LAM[x * LP + c] * DN_LOG2E;
-          const bool live = x < r.rows_valid;
-          float kv = ldf_ro(r.k, r.qk_row0 + (size_t)(live ? x : 0) * r.qk_pitch + c, qdt);
-          if (!live) kv = 0.f;
-          if (l2) { kv *= rk_s[x]; if (r.round_in) kv = bf16r(kv); }
-          kh[i] = kv;
-          sk[i] = 0.f;
+        for (int it = 0; it < 2; ++it) {
+          const int w = it * 16 + warp, xr = (w & 7) * 8 + (lane & 7), p = (w >> 3) * 4 + lgrp, x = half * 64 + xr;
+          float kh[8], qh[8], ba[8];
+          khat8(r, x, p, kh);
+          qhat8(r, x, p, qh);
+          bact8(r, x, p, ba);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) ba[i] *= kh[i];
+          *reinterpret_cast<float4*>(KC + xr * CP + 8 * p) = make_float4(kh[0], kh[1], kh[2], kh[3]);
+          *reinterpret_cast<float4*>(KC + xr * CP + 8 * p + 4) = make_float4(kh[4], kh[5], kh[6], kh[7]);
+          *reinterpret_cast<float4*>(QC + xr * CP + 8 * p) = make_float4(qh[0], qh[1], qh[2], qh[3]);
+          *reinterpret_cast<float4*>(QC + xr * CP + 8 * p + 4) = make_float4(qh[4], qh[5], qh[6], qh[7]);
+          *reinterpret_cast<float4*>(BC + xr * CP + 8 * p) = make_float4(ba[0], ba[1], ba[2], ba[3]);
+          *reinterpret_cast<float4*>(BC + xr * CP + 8 * p + 4) = make_float4(ba[4], ba[5], ba[6], ba[7]);
         }
-        DBP[p4f(r0, c)] = 0.f;
-        DQP[p4f(r0, c)] = 0.f;
-        auto row_inputs = [&](int i, float kv, float& be, float& qv) {
-          const int x = r0 + i;
-          const bool live = x < r.rows_valid;
-          qv = ldf_ro(r.q, r.qk_row0 + (size_t)(live ? x : 0) * r.qk_pitch + c, qdt);
-          float bv = ldf_ro(r.b, r.b_row0 + (size_t)(live ? x : 0) * r.b_pitch + bcol, gdt);
-          qv = (qv * rq_s[x]) * r.scale;
-          if (r.round_in) qv = bf16r(qv);
-          if (fuse) bv = 1.f / (1.f + expf(-bv));
-          if (!live) { bv = 0.f; qv = 0.f; }
-          be = bv * kv;
-        };
+        __syncthreads();
+        DN_MARK(20 + 3 * half);
+        {
+          const int lb = tid >> 7, blk = half * 4 + lb, r0 = blk * 16, c = tid & 127;
+          const float* kc = KC + lb * 16 * CP + c;
+          const float* qc = QC + lb * 16 * CP + c;
+          const float* bc = BC + lb * 16 * CP + c;
+          float lam[16], kh[16], sk[16];
 #pragma unroll
-        for (int i = 1; i < 8; ++i) {                 // upper-left triangle: static row index
-          float be, qv, sb, sq;
-          row_inputs(i, kh[i], be, qv);
-          diag_row<0, 7>(i, lam[i], lam, kh, sk, DG4 + (r0 + i) * 4, DG4 + 512 + (r0 + i) * 4, be, qv, sb, sq);
-          DBP[p4f(r0 + i, c)] = sb;
-          DQP[p4f(r0 + i, c)] = sq;
+          for (int i = 0; i < 16; ++i) {
+            lam[i] = LAM[(r0 + i) * LP + c] * DN_LOG2E;
+            kh[i] = kc[i * CP];
+            sk[i] = 0.f;
+          }
+          DBP[p4f(r0, c)] = 0.f;
+          DQP[p4f(r0, c)] = 0.f;
+          // rolled over the rows (the body is executed 15 times, which keeps the code small enough
+          // to stay in the instruction cache): rows 1..7 see columns j < i <= 7, rows 8..15 see
+          // columns 0..7 unconditionally and columns 8..14 while j < i
+#pragma unroll 1
+          for (int i = 1; i < 8; ++i) {
+            float sb, sq;
+            diag_row<0, 7>(i, LAM[(r0 + i) * LP + c] * DN_LOG2E, lam, kh, sk, DG4 + (r0 + i) * 4, DG4 + 512 + (r0 + i) * 4, bc[i * CP], qc[i * CP], sb, sq);
+            DBP[p4f(r0 + i, c)] = sb;
+            DQP[p4f(r0 + i, c)] = sq;
+          }
+#pragma unroll 1
+          for (int i = 8; i < 16; ++i) {
+            float sb, sq;
+            diag_row<8, 7>(i, LAM[(r0 + i) * LP + c] * DN_LOG2E, lam, kh, sk, DG4 + (r0 + i) * 4, DG4 + 512 + (r0 + i) * 4, bc[i * CP], qc[i * CP], sb, sq);
+            DBP[p4f(r0 + i, c)] = sb;
+            DQP[p4f(r0 + i, c)] = sq;
+          }
+#pragma unroll
+          for (int j = 0; j < 16; ++j) DKP[p4f(r0 + j, c)] = sk[j];
         }
-#pragma unroll
-        for (int i = 8; i < 16; ++i) {                // square below it, then the lower-right triangle
-          float be, qv, sb, sq;
-          row_inputs(i, kh[i], be, qv);
-          diag_row<8, 7>(i, lam[i], lam, kh, sk, DG4 + (r0 + i) * 4, DG4 + 512 + (r0 + i) * 4, be, qv, sb, sq);
-          DBP[p4f(r0 + i, c)] = sb;
-          DQP[p4f(r0 + i, c)] = sq;
-        }
-#pragma unroll
-        for (int j = 0; j < 16; ++j) DKP[p4f(r0 + j, c)] = sk[j];
+        DN_MARK(21 + 3 * half);
+        __syncthreads();
+        DN_MARK(22 + 3 * half);
       }
     }
-    __syncthreads();
 
     DN_MARK(9);
     // ---- H. three levels
@@ -238,19 +276,18 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
         float4 a0[2], a1[2], m0[2], m1[2];
         bool own[2];
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {                  // loads are unconditional: entries of other levels are discarded
+        for (int u = 0; u < 2; ++u) {                  // predicated, branch-free loads: only the level's own entries
           const int e = (2 * half + u) * NT + tid, p = e >> 7, x = e & 127;
           const int bi = x >> 4, bj = p >> 1;
           own[u] = bj < bi && owner_level(bi, bj) == lv;
-          a0[u] = __ldcg(DA4 + p4v(x, 8 * p)); a1[u] = __ldcg(DA4 + p4v(x, 8 * p + 4));
-          m0[u] = __ldcg(DM4 + p4v(x, 8 * p)); m1[u] = __ldcg(DM4 + p4v(x, 8 * p + 4));
+          a0[u] = umma::ldcg_pred(DA4 + p4v(x, 8 * p), own[u]); a1[u] = umma::ldcg_pred(DA4 + p4v(x, 8 * p + 4), own[u]);
+          m0[u] = umma::ldcg_pred(DM4 + p4v(x, 8 * p), own[u]); m1[u] = umma::ldcg_pred(DM4 + p4v(x, 8 * p + 4), own[u]);
         }
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
           const int e = (2 * half + u) * NT + tid;
           uint4 va = make_uint4(umma::pack2(a0[u].x, a0[u].y), umma::pack2(a0[u].z, a0[u].w), umma::pack2(a1[u].x, a1[u].y), umma::pack2(a1[u].z, a1[u].w));
           uint4 vm = make_uint4(umma::pack2(m0[u].x, m0[u].y), umma::pack2(m0[u].z, m0[u].w), umma::pack2(m1[u].x, m1[u].y), umma::pack2(m1[u].z, m1[u].w));
-          if (!own[u]) va = vm = make_uint4(0, 0, 0, 0);
           I_DA[e] = va;
           I_DM[e] = vm;
         }
@@ -274,7 +311,7 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
         const int col = group * 32 + cc;
         float4 ob[4], oq[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) { ob[i] = __ldcg(pb + p4v(x, col + 4 * i)); oq[i] = __ldcg(DQP4 + p4v(x, col + 4 * i)); }
+        for (int i = 0; i < 4; ++i) { ob[i] = __ldcg(pb + p4v(x, col + 4 * i)); oq[i] = umma::ldcg_pred(DQP4 + p4v(x, col + 4 * i), lower); }
         float t1[16], t2[16];
         if (!cx.dead) {
           umma::tmem_ld16(tbase + col, t1);
@@ -544,6 +581,9 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
     if (blockIdx.x == 0 && tid == 0 && item == 0) {
       for (int i = 1; i < 18; ++i) printf("mark %d -> %d: %lld\n", i - 1, i, g_phase_marks[i] - g_phase_marks[i - 1]);
       printf("item total %lld\n", g_phase_marks[17] - g_phase_marks[0]);
+      printf("D: stage0 %lld compute0(warp0) %lld wait0 %lld stage1 %lld compute1 %lld wait1 %lld\n", g_phase_marks[20] - g_phase_marks[8],
+             g_phase_marks[21] - g_phase_marks[20], g_phase_marks[22] - g_phase_marks[21], g_phase_marks[23] - g_phase_marks[22],
+             g_phase_marks[24] - g_phase_marks[23], g_phase_marks[25] - g_phase_marks[24]);
     }
 #endif
   }

@@ -24,15 +24,6 @@
 
 namespace dn {
 
-// Optional phase clock (compile with -DDN_PHASE_TIMING): CTA 0 records clock64 at marked points of
-// its first item and prints the differences.  Compiled out otherwise.
-#ifdef DN_PHASE_TIMING
-__device__ long long g_phase_marks[48];
-#define DN_MARK(i) do { if (blockIdx.x == 0 && threadIdx.x == 0) g_phase_marks[i] = clock64(); } while (0)
-#else
-#define DN_MARK(i) do { } while (0)
-#endif
-
 // float4 index of (row, col) in a panel-layout array (col a multiple of 4)
 __device__ __forceinline__ int p4v(int row, int col) { return ((col >> 2) << 7) + row; }
 // float index of (row, col) in a panel-layout array

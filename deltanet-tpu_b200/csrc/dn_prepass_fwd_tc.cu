@@ -29,6 +29,7 @@
 // tensor memory own one row per thread, which the image layout of the outputs (and the panel
 // layout [col / 4][row][4] of the fp32 scratch that carries A to the inverse) turns into stores of
 // 512 contiguous bytes per warp.
+#include <cstdio>
 #include "dn_chunkprep.cuh"
 #include "dn_kernels.cuh"
 
@@ -49,50 +50,44 @@ static_assert(OFF_IMG + 2 * 32768 <= OFF_XI, "level images below the X image");
 __device__ __forceinline__ int p4v(int row, int col) { return ((col >> 2) << 7) + row; }
 __device__ __forceinline__ int p4f(int row, int col) { return ((((col >> 2) << 7) + row) << 2) + (col & 3); }
 
-// four channels (4*lane ..) of a row of q / k / b through the read-only path; a row past the end
-// reads row 0 (the caller zeroes it)
-__device__ __forceinline__ float4 in4(const void* base, size_t off, int dt) {
-  if (dt == DN_BF16) {
-    const uint2 u = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(base) + off));
-    return make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xffff0000u),
-                       __uint_as_float(u.y << 16), __uint_as_float(u.y & 0xffff0000u));
-  }
-  return __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + off));
-}
-
 // One merge level of the inverse: for every pair of adjacent S-row blocks (lower rows I, upper rows J)
 //   T[I,J] = -T[I,I] (A[I,J] T[J,J]).
-// 512 threads = (row of I) x (8 column groups of S/8 columns) x pairs, each thread S/8 outputs.
+// 512 threads = (row pair of I) x (16 column groups of S/16 columns) x pairs; a thread owns a
+// 2 x (S/16) tile of outputs, so one step of the contraction costs two scalar loads and one
+// vector load from shared memory for 2 * S/16 multiply-adds.
 template <int S>
 __device__ __forceinline__ void merge_level(const float* As, float* Ts, float* Tm) {
-  constexpr int NJ = S / 8;
-  const int cg = threadIdx.x & 7, rest = threadIdx.x >> 3;      // rest = pair * S + row in I
-  const int p = rest / S, il = rest - p * S;
+  constexpr int NJ = S / 16;
+  const int cg = threadIdx.x & 15, rest = threadIdx.x >> 4;     // rest = pair * (S/2) + row pair in I
+  const int p = rest / (S / 2), il = 2 * (rest - p * (S / 2));
   const int i = 2 * p * S + S + il, j0 = 2 * p * S + cg * NJ, m0 = 2 * p * S;
-  float acc[NJ];
+  float acc0[NJ], acc1[NJ];
 #pragma unroll
-  for (int u = 0; u < NJ; ++u) acc[u] = 0.f;
+  for (int u = 0; u < NJ; ++u) acc0[u] = acc1[u] = 0.f;
 #pragma unroll 4
   for (int m = 0; m < S; ++m) {
-    const float av = As[i * AP + m0 + m];
+    const float a0 = As[i * AP + m0 + m], a1 = As[(i + 1) * AP + m0 + m];
     const float* t = Ts + (m0 + m) * AP + j0;
 #pragma unroll
-    for (int u = 0; u < NJ; ++u) acc[u] = fmaf(av, t[u], acc[u]);
+    for (int u = 0; u < NJ; ++u) { acc0[u] = fmaf(a0, t[u], acc0[u]); acc1[u] = fmaf(a1, t[u], acc1[u]); }
   }
 #pragma unroll
-  for (int u = 0; u < NJ; ++u) Tm[rest * S + cg * NJ + u] = acc[u];
+  for (int u = 0; u < NJ; ++u) {
+    Tm[(p * S + il) * S + cg * NJ + u] = acc0[u];
+    Tm[(p * S + il + 1) * S + cg * NJ + u] = acc1[u];
+  }
   __syncthreads();
 #pragma unroll
-  for (int u = 0; u < NJ; ++u) acc[u] = 0.f;
+  for (int u = 0; u < NJ; ++u) acc0[u] = acc1[u] = 0.f;
 #pragma unroll 4
   for (int m = 0; m < S; ++m) {
-    const float tv = Ts[i * AP + m0 + S + m];
+    const float t0 = Ts[i * AP + m0 + S + m], t1 = Ts[(i + 1) * AP + m0 + S + m];
     const float* t = Tm + (p * S + m) * S + cg * NJ;
 #pragma unroll
-    for (int u = 0; u < NJ; ++u) acc[u] = fmaf(tv, t[u], acc[u]);
+    for (int u = 0; u < NJ; ++u) { acc0[u] = fmaf(t0, t[u], acc0[u]); acc1[u] = fmaf(t1, t[u], acc1[u]); }
   }
 #pragma unroll
-  for (int u = 0; u < NJ; ++u) Ts[i * AP + j0 + u] = -acc[u];
+  for (int u = 0; u < NJ; ++u) { Ts[i * AP + j0 + u] = -acc0[u]; Ts[(i + 1) * AP + j0 + u] = -acc1[u]; }
   __syncthreads();
 }
 
@@ -130,7 +125,7 @@ __global__ void __launch_bounds__(NT, 1) prepass_fwd_tc_kernel(PrepassFwdArgs a,
   umma::tc_fence_after();
   umma::Ctx cx{tmem_base, &mma_bar, 0u, err, false};
 
-  const bool fuse = g.flags & DN_FUSE_PROLOGUE;
+  const bool fuse = CF::fixed ? false : (g.flags & DN_FUSE_PROLOGUE) != 0;     // the fixed modes have no fused prologue
 
   for (int item = blockIdx.x; item < a.items; item += gridDim.x) {
     const int c_idx = item % g.NC, h = (item / g.NC) % g.H, b = item / (g.NC * g.H);
@@ -143,7 +138,19 @@ __global__ void __launch_bounds__(NT, 1) prepass_fwd_tc_kernel(PrepassFwdArgs a,
     uint4* QEimg = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.res.qe) + ibase * C * K);
     uint4* KEimg = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.res.ke) + ibase * C * K);
 
+    DN_MARK(0);
     for (int i = tid; i < C; i += NT) seg_s[i] = seg_at(a.seg, b, t0 + i, g.L);
+    {
+      // the rows of v and w are needed only at the end of the item: ask them into L2 now
+      const int rows = g.L - t0 < C ? g.L - t0 : C;
+      const size_t tok0 = (size_t)b * g.L + t0;
+      const size_t qsz = dt_size(g.qkv_dt), gsz = dt_size(g.gate_dt);
+      umma::prefetch_rows_l2<NT>(reinterpret_cast<const uint8_t*>(a.v) + (tok0 * g.Hv * g.V + (size_t)h * VW) * qsz, rows, (size_t)g.Hv * g.V * qsz, (int)(VW * qsz));
+      if (g.wC != 1) {
+        const int hv0 = h * VW / g.V;
+        umma::prefetch_rows_l2<NT>(reinterpret_cast<const uint8_t*>(a.w) + (tok0 * g.wH + g.w_head(hv0)) * g.wC * gsz, rows, (size_t)g.wH * g.wC * gsz, (int)((g.wH == g.Hv ? VW : g.V) * gsz));
+      }
+    }
     const Rows r = make_rows<CF>(g, a.q, a.k, a.gg, a.b, b, h, t0, rq_s, rk_s);
     const int qdt = r.qkv_dt, gdt = r.gate_dt;           // compile-time constants in the fixed modes
     const int wC = CF::fixed ? g.V : g.wC;
@@ -153,6 +160,7 @@ __global__ void __launch_bounds__(NT, 1) prepass_fwd_tc_kernel(PrepassFwdArgs a,
     lambda_scan_512(r, seg_s, LAM, TOTL, reset_s);
     __syncthreads();
 
+    DN_MARK(1);
     // ---- qe, ke, Lambda_end and the X = [first doc] beta e^Lam operand image
     {
       const int x = myrow;
@@ -184,6 +192,7 @@ __global__ void __launch_bounds__(NT, 1) prepass_fwd_tc_kernel(PrepassFwdArgs a,
       if (tid < K) a.res.lam_end[ibase * K + tid] = LAM[(C - 1) * LP + tid];
     }
 
+    DN_MARK(2);
     // ---- A and M, level by level: two images, two MMAs, one predicated drain per level
     auto build = [&](int lv) {
 #pragma unroll 2
@@ -231,59 +240,51 @@ __global__ void __launch_bounds__(NT, 1) prepass_fwd_tc_kernel(PrepassFwdArgs a,
       umma::issue<128, false, false>(cx, KR, KR, K, tcol, false);          // A: KR KR^T
       umma::issue<128, false, false>(cx, QK, KR, K, tcol + 128, false);    // M: QK KR^T
       umma::commit_wait(cx);
+      DN_MARK(3 + lv);
       if (lv < 2) build(lv + 1);
       drain_level(lv);
     }
     __syncthreads();
 
-    // ---- 16x16 diagonal blocks, exact.  k_hat of the chunk is cached in shared memory (fp32, one
-    //      row per 8x4 thread); two warps per block take alternate rows i, lanes own 4 channels, and
-    //      the q / b of the warp's next row are in flight while the current row is reduced.
-    {
+    DN_MARK(6);
+    // ---- 16x16 diagonal blocks, exact.  k_hat, q_hat and beta of 64 rows at a time are cached in
+    //      shared memory (fp32; one global round trip per half); four warps per block take every
+    //      fourth row i, lanes own 4 channels, and every pair (i, j <= i) is one warp reduction.
+#pragma unroll 1
+    for (int half = 0; half < 2; ++half) {
+      float* QHs = KHs + 64 * AP;                                       // q_hat (pitch AP)
+      float* BEs = reinterpret_cast<float*>(smraw + OFF_TI);            // beta (pitch 128)
 #pragma unroll
-      for (int it = 0; it < 4; ++it) {
-        const int p = it * 4 + lgrp;
-        float kh[8];
-        khat8(r, myrow, p, kh);
-        *reinterpret_cast<float4*>(KHs + myrow * AP + 8 * p) = make_float4(kh[0], kh[1], kh[2], kh[3]);
-        *reinterpret_cast<float4*>(KHs + myrow * AP + 8 * p + 4) = make_float4(kh[4], kh[5], kh[6], kh[7]);
+      for (int it = 0; it < 2; ++it) {
+        const int w = it * 16 + warp, xr = (w & 7) * 8 + (lane & 7), p = (w >> 3) * 4 + lgrp, x = half * 64 + xr;
+        float kh[8], qh[8], ba[8];
+        khat8(r, x, p, kh);
+        qhat8(r, x, p, qh);
+        bact8(r, x, p, ba);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ba[i] *= kh[i];
+        *reinterpret_cast<float4*>(KHs + xr * AP + 8 * p) = make_float4(kh[0], kh[1], kh[2], kh[3]);
+        *reinterpret_cast<float4*>(KHs + xr * AP + 8 * p + 4) = make_float4(kh[4], kh[5], kh[6], kh[7]);
+        *reinterpret_cast<float4*>(QHs + xr * AP + 8 * p) = make_float4(qh[0], qh[1], qh[2], qh[3]);
+        *reinterpret_cast<float4*>(QHs + xr * AP + 8 * p + 4) = make_float4(qh[4], qh[5], qh[6], qh[7]);
+        *reinterpret_cast<float4*>(BEs + xr * 128 + 8 * p) = make_float4(ba[0], ba[1], ba[2], ba[3]);
+        *reinterpret_cast<float4*>(BEs + xr * 128 + 8 * p + 4) = make_float4(ba[4], ba[5], ba[6], ba[7]);
       }
       __syncthreads();
-      const int r0 = (warp >> 1) * 16;
-      const size_t bcol = r.bC == 1 ? 0 : 4 * lane;
-      auto fetch = [&](int ri, float4& q4, float4& b4) {
-        const bool live = ri < r.rows_valid;
-        const int rr = live ? ri : 0;
-        q4 = in4(r.q, r.qk_row0 + (size_t)rr * r.qk_pitch + 4 * lane, qdt);
-        if (r.bC == 1) { const float v = ldf_ro(r.b, r.b_row0 + (size_t)rr * r.b_pitch, gdt); b4 = make_float4(v, v, v, v); }
-        else b4 = in4(r.b, r.b_row0 + (size_t)rr * r.b_pitch + bcol, gdt);
-      };
-      float4 nq, nb;
-      fetch(r0 + (warp & 1), nq, nb);
+      const int lb = warp >> 2, r0 = (half * 4 + lb) * 16, c0 = lb * 16;   // block rows in the chunk / in the caches
 #pragma unroll 1
-      for (int i = warp & 1; i < 16; i += 2) {
+      for (int i = warp & 3; i < 16; i += 4) {
         const int ri = r0 + i;
-        const bool live = ri < r.rows_valid;
-        float4 q4 = nq, b4 = nb;
-        if (i + 2 < 16) fetch(ri + 2, nq, nb);
-        const float4 k4 = *reinterpret_cast<const float4*>(KHs + ri * AP + 4 * lane);
+        const float4 q4 = *reinterpret_cast<const float4*>(QHs + (c0 + i) * AP + 4 * lane);
+        const float4 b4 = *reinterpret_cast<const float4*>(BEs + (c0 + i) * 128 + 4 * lane);
         const float4 li = *reinterpret_cast<const float4*>(LAM + ri * LP + 4 * lane);
-        float qi[4] = {q4.x, q4.y, q4.z, q4.w}, bi4[4] = {b4.x, b4.y, b4.z, b4.w};
-        const float ki[4] = {k4.x, k4.y, k4.z, k4.w};
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          qi[u] = (qi[u] * rq_s[ri]) * r.scale;
-          if (r.round_in) qi[u] = bf16r(qi[u]);
-          if (fuse) bi4[u] = 1.f / (1.f + expf(-bi4[u]));
-          bi4[u] *= ki[u];
-          if (!live) { qi[u] = 0.f; bi4[u] = 0.f; }
-        }
+        const float qi[4] = {q4.x, q4.y, q4.z, q4.w}, bi4[4] = {b4.x, b4.y, b4.z, b4.w};
         float arow = 0.f, mrow = 0.f;                  // lane j (< 16) keeps entry (ri, r0 + j)
 #pragma unroll 1
         for (int j = 0; j <= i; j += 2) {              // two columns per step: four independent reductions
           const int rj = r0 + j;
-          const float4 ka = *reinterpret_cast<const float4*>(KHs + rj * AP + 4 * lane);
-          const float4 kb = *reinterpret_cast<const float4*>(KHs + (rj + 1) * AP + 4 * lane);
+          const float4 ka = *reinterpret_cast<const float4*>(KHs + (c0 + j) * AP + 4 * lane);
+          const float4 kb = *reinterpret_cast<const float4*>(KHs + (c0 + j + 1) * AP + 4 * lane);
           const float4 la = *reinterpret_cast<const float4*>(LAM + rj * LP + 4 * lane);
           const float4 lb = *reinterpret_cast<const float4*>(LAM + (rj + 1) * LP + 4 * lane);
           const float a0 = ka.x * umma::ex2_fast(fminf(li.x - la.x, 0.f) * DN_LOG2E), a1 = ka.y * umma::ex2_fast(fminf(li.y - la.y, 0.f) * DN_LOG2E);
@@ -315,9 +316,10 @@ __global__ void __launch_bounds__(NT, 1) prepass_fwd_tc_kernel(PrepassFwdArgs a,
           Mel[rix(true, ri, r0 + lane, C)] = __float2bfloat16_rn(mrow);
         }
       }
+      __syncthreads();
     }
-    __syncthreads();
 
+    DN_MARK(7);
     // ---- T = (I + A)^-1 in fp32: substitution on the diagonal blocks, then block merges
     {
       float4* As4 = reinterpret_cast<float4*>(As);
@@ -350,6 +352,7 @@ __global__ void __launch_bounds__(NT, 1) prepass_fwd_tc_kernel(PrepassFwdArgs a,
       for (int i = 0; i < 16; ++i) Ts[(blk0 + i) * AP + j] = col[i];
     }
     __syncthreads();
+    DN_MARK(8);
     merge_level<16>(As, Ts, Tm);
     merge_level<32>(As, Ts, Tm);
     merge_level<64>(As, Ts, Tm);
@@ -358,6 +361,7 @@ __global__ void __launch_bounds__(NT, 1) prepass_fwd_tc_kernel(PrepassFwdArgs a,
       for (int e = tid; e < C * C / 4; e += NT) Tg[e] = *reinterpret_cast<const float4*>(Ts + (e >> 5) * AP + 4 * (e & 31));
     }
 
+    DN_MARK(9);
     // ---- W = T X, U = T Y on the tensor cores
     for (int e = tid; e < IMG; e += NT) {                       // T as K-major A: piece (p = j/8, x = i)
       const int p = e >> 7, x = e & 127;
@@ -392,6 +396,7 @@ __global__ void __launch_bounds__(NT, 1) prepass_fwd_tc_kernel(PrepassFwdArgs a,
     umma::issue<128, false, true>(cx, TI, XI, C, 0, false);
     umma::issue<VW, false, true>(cx, TI, YI, C, 128, false);
     umma::commit_wait(cx);
+    DN_MARK(10);
     umma::drain<NT, 128>(cx, 0, [&](int row, int col, const float (&v)[16]) {
       Wimg[(col / 8) * 128 + row] = umma::pack8p(v);
       Wimg[(col / 8 + 1) * 128 + row] = umma::pack8p(v + 8);
@@ -401,6 +406,13 @@ __global__ void __launch_bounds__(NT, 1) prepass_fwd_tc_kernel(PrepassFwdArgs a,
       Uimg[(col / 8 + 1) * 128 + row] = umma::pack8p(v + 8);
     });
     __syncthreads();
+#ifdef DN_PHASE_TIMING
+    DN_MARK(11);
+    if (blockIdx.x == 0 && tid == 0 && item == 0) {
+      for (int i = 1; i < 12; ++i) printf("fwd mark %d -> %d: %lld\n", i - 1, i, g_phase_marks[i] - g_phase_marks[i - 1]);
+      printf("fwd item total %lld\n", g_phase_marks[11] - g_phase_marks[0]);
+    }
+#endif
   }
   umma::tc_fence_before();
   __syncthreads();
