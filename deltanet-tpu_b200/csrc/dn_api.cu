@@ -1,10 +1,60 @@
 // extern "C" surface declared in include/deltanet_b200.h: argument checks, buffer carving,
-// and the order in which the kernels are enqueued.  Nothing here allocates or synchronises.
+// and the order in which the kernels are enqueued.  Nothing here allocates device memory or
+// synchronises.
+#include <cstdlib>
+#include <mutex>
+
 #include "dn_kernels.cuh"
 
 using namespace dn;
 
 static inline size_t align_up(size_t x, size_t a = 256) { return (x + a - 1) / a * a; }
+
+// ---- overlap of the chunk-parallel kernels with the chains ------------------------------------
+// The chunk-parallel kernels run one CTA per SM over B*H*NC work items; when that count leaves the
+// last round of CTAs mostly empty (192 items on 148 SMs), dn_chunk_fwd / dn_chunk_bwd cut the chunk
+// axis in two and run the chain of one part on a side stream next to the chunk-parallel kernel of
+// the other part.  The side stream forks from and joins back into the caller's stream through
+// events, so the caller still sees one stream-ordered operation.  The stream and its events are
+// created on the first such call per device (host objects; do that call outside stream capture).
+// DN_NO_OVERLAP=1 turns the split off.
+namespace {
+struct Overlap {
+  cudaStream_t side = nullptr;
+  cudaEvent_t ev[2] = {nullptr, nullptr};
+  bool tried = false, ok = false;
+};
+Overlap* overlap_for_device() {
+  static Overlap table[64];
+  static std::mutex mu;
+  static const bool off = [] { const char* e = std::getenv("DN_NO_OVERLAP"); return e && e[0] == '1'; }();
+  if (off) return nullptr;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  Overlap& o = table[dev];
+  if (!o.tried) {
+    o.tried = true;
+    o.ok = cudaStreamCreateWithFlags(&o.side, cudaStreamNonBlocking) == cudaSuccess &&
+           cudaEventCreateWithFlags(&o.ev[0], cudaEventDisableTiming) == cudaSuccess &&
+           cudaEventCreateWithFlags(&o.ev[1], cudaEventDisableTiming) == cudaSuccess;
+    if (!o.ok) cudaGetLastError();
+  }
+  return o.ok ? &o : nullptr;
+}
+// First chunk of the second part, or 0 for "do not split": the first part [0, cut) holds the whole
+// rounds of CTAs, the second part [cut, NC) the last, partly filled round.
+int overlap_cut(const Geo& g) {
+  if (!g.img || !state_tc_eligible(g) || (g.flags & DN_STATE_FP32_MM)) return 0;
+  const int per_chunk = g.B * g.H, n = per_chunk * g.NC;
+  if (g.NC < 4 || n <= 148 || n > 4 * 148) return 0;
+  const int rounds = (n + 147) / 148, tail = n - (rounds - 1) * 148;
+  if (tail * 4 > 148 * 3) return 0;                       // the last round is well filled already
+  const int cut = ((rounds - 1) * 148) / per_chunk;
+  return (cut >= 1 && cut < g.NC) ? cut : 0;
+}
+size_t carry_bytes(const Geo& g) { return align_up((size_t)g.B * g.H * g.K * g.Vw * sizeof(float)); }
+}  // namespace
 
 extern "C" {
 
@@ -107,12 +157,13 @@ size_t dn_scratch_bytes(const dn_shape* s, int for_backward, int recompute) {
   const size_t n = (size_t)g.B * g.H * g.NC;
   if (!for_backward) {
     // forward without residuals keeps the prepass outputs in scratch
-    return fwd_kernel_scratch(g) + align_up(dn_residual_bytes(s));
+    return fwd_kernel_scratch(g) + align_up(dn_residual_bytes(s)) + carry_bytes(g);
   }
   size_t tot = bwd_kernel_scratch(g) > fwd_kernel_scratch(g) ? bwd_kernel_scratch(g) : fwd_kernel_scratch(g);
   tot += align_up(n * g.C * g.Vw * sizeof(float));   // dV
   tot += align_up(n * g.K * g.Vw * sizeof(float));   // dH
   tot += staging_bytes(g);
+  tot += carry_bytes(g);
   if (recompute) tot += align_up(full_residual_bytes(s));
   return tot;
 }
@@ -176,37 +227,66 @@ int dn_state_bwd(const dn_shape* s, const dn_residuals* res, const int32_t* seg,
   return launch_state_bwd(a, (cudaStream_t)stream);
 }
 
-// Carves gradient staging out of `p`, runs the chunk-parallel backward, then the head sums.
+// The chunk-parallel backward in three steps: carve the gradient staging out of `p` and fill the
+// argument block; launch (a chunk range, on a stream); the head sums.
+namespace {
+struct BwdPlan {
+  PrepassBwdArgs a{};
+  float *sq = nullptr, *sk = nullptr, *sg = nullptr, *sb = nullptr, *sw = nullptr;
+  size_t scratch_floats = 0;
+  void *dq, *dk, *dg, *db, *dw;
+};
+int plan_prepass_bwd(const Geo& g, const void* q, const void* k, const void* v, const void* g_,
+                     const void* b, const void* w, const int32_t* seg, const dn_residuals& res,
+                     const void* d_out, const float* dV, const float* dH,
+                     void* dq, void* dk, void* dv, void* dg, void* db, void* dw,
+                     char* p, size_t bytes, BwdPlan& pl) {
+  const size_t rows = (size_t)g.B * g.L;
+  char* end = p + bytes;
+  PrepassBwdArgs& a = pl.a;
+  a.g = g; a.q = q; a.k = k; a.v = v; a.gg = g_; a.b = b; a.w = w; a.seg = seg; a.res = res;
+  a.d_out = d_out; a.dV = dV; a.dH = dH;
+  a.dq = dq; a.dk = dk; a.dv = dv; a.dg = dg; a.db = db; a.dw = dw;
+  pl.dq = dq; pl.dk = dk; pl.dg = dg; pl.db = db; pl.dw = dw;
+  a.dq_dt = g.qkv_dt; a.dg_dt = a.db_dt = a.dw_dt = g.gate_dt;
+  auto take = [&](size_t nfl) { float* r = reinterpret_cast<float*>(p); p += align_up(nfl * sizeof(float)); return r; };
+  if (g.qk_div > 1) { pl.sq = take(rows * g.H * g.K); pl.sk = take(rows * g.H * g.K); a.dq = pl.sq; a.dk = pl.sk; a.dq_dt = DN_F32; }
+  if (g.gH != g.H) { pl.sg = take(rows * g.H * g.gC); a.dg = pl.sg; a.dg_dt = DN_F32; }
+  if (g.bH != g.H) { pl.sb = take(rows * g.H * g.bC); a.db = pl.sb; a.db_dt = DN_F32; }
+  if (g.wH != g.Hv) { pl.sw = take(rows * g.Hv * g.wC); a.dw = pl.sw; a.dw_dt = DN_F32; }
+  if (p > end) return DN_ERR_SCRATCH_TOO_SMALL;
+  a.scratch = reinterpret_cast<float*>(p);
+  pl.scratch_floats = (size_t)(end - p) / sizeof(float);
+  return DN_OK;
+}
+int launch_plan(BwdPlan& pl, int c_begin, int c_end, cudaStream_t st) {
+  pl.a.c_begin = c_begin; pl.a.c_end = c_end;
+  return launch_prepass_bwd(pl.a, pl.scratch_floats, st);
+}
+int finish_plan(const Geo& g, const BwdPlan& pl, cudaStream_t st) {
+  const size_t rows = (size_t)g.B * g.L;
+  int rc;
+  if (pl.sq) {
+    if ((rc = launch_group_sum(pl.sq, pl.dq, g.qkv_dt, rows, g.Hk, g.qk_div, g.K, st))) return rc;
+    if ((rc = launch_group_sum(pl.sk, pl.dk, g.qkv_dt, rows, g.Hk, g.qk_div, g.K, st))) return rc;
+  }
+  if (pl.sg && (rc = launch_group_sum(pl.sg, pl.dg, g.gate_dt, rows, g.gH, g.H / g.gH, g.gC, st))) return rc;
+  if (pl.sb && (rc = launch_group_sum(pl.sb, pl.db, g.gate_dt, rows, g.bH, g.H / g.bH, g.bC, st))) return rc;
+  if (pl.sw && (rc = launch_group_sum(pl.sw, pl.dw, g.gate_dt, rows, g.wH, g.Hv / g.wH, g.wC, st))) return rc;
+  return DN_OK;
+}
+}  // namespace
+
 static int run_prepass_bwd(const Geo& g, const void* q, const void* k, const void* v, const void* g_,
                            const void* b, const void* w, const int32_t* seg, const dn_residuals& res,
                            const void* d_out, const float* dV, const float* dH,
                            void* dq, void* dk, void* dv, void* dg, void* db, void* dw,
                            char* p, size_t bytes, cudaStream_t st) {
-  const size_t rows = (size_t)g.B * g.L;
-  char* end = p + bytes;
-  PrepassBwdArgs a{};
-  a.g = g; a.q = q; a.k = k; a.v = v; a.gg = g_; a.b = b; a.w = w; a.seg = seg; a.res = res;
-  a.d_out = d_out; a.dV = dV; a.dH = dH;
-  a.dq = dq; a.dk = dk; a.dv = dv; a.dg = dg; a.db = db; a.dw = dw;
-  a.dq_dt = g.qkv_dt; a.dg_dt = a.db_dt = a.dw_dt = g.gate_dt;
-  float *sq = nullptr, *sk = nullptr, *sg = nullptr, *sb = nullptr, *sw = nullptr;
-  auto take = [&](size_t nfl) { float* r = reinterpret_cast<float*>(p); p += align_up(nfl * sizeof(float)); return r; };
-  if (g.qk_div > 1) { sq = take(rows * g.H * g.K); sk = take(rows * g.H * g.K); a.dq = sq; a.dk = sk; a.dq_dt = DN_F32; }
-  if (g.gH != g.H) { sg = take(rows * g.H * g.gC); a.dg = sg; a.dg_dt = DN_F32; }
-  if (g.bH != g.H) { sb = take(rows * g.H * g.bC); a.db = sb; a.db_dt = DN_F32; }
-  if (g.wH != g.Hv) { sw = take(rows * g.Hv * g.wC); a.dw = sw; a.dw_dt = DN_F32; }
-  if (p > end) return DN_ERR_SCRATCH_TOO_SMALL;
-  a.scratch = reinterpret_cast<float*>(p);
-  int rc = launch_prepass_bwd(a, (size_t)(end - p) / sizeof(float), st);
+  BwdPlan pl;
+  int rc = plan_prepass_bwd(g, q, k, v, g_, b, w, seg, res, d_out, dV, dH, dq, dk, dv, dg, db, dw, p, bytes, pl);
   if (rc) return rc;
-  if (sq) {
-    if ((rc = launch_group_sum(sq, dq, g.qkv_dt, rows, g.Hk, g.qk_div, g.K, st))) return rc;
-    if ((rc = launch_group_sum(sk, dk, g.qkv_dt, rows, g.Hk, g.qk_div, g.K, st))) return rc;
-  }
-  if (sg && (rc = launch_group_sum(sg, dg, g.gate_dt, rows, g.gH, g.H / g.gH, g.gC, st))) return rc;
-  if (sb && (rc = launch_group_sum(sb, db, g.gate_dt, rows, g.bH, g.H / g.bH, g.bC, st))) return rc;
-  if (sw && (rc = launch_group_sum(sw, dw, g.gate_dt, rows, g.wH, g.Hv / g.wH, g.wC, st))) return rc;
-  return DN_OK;
+  if ((rc = launch_plan(pl, 0, 0, st))) return rc;
+  return finish_plan(g, pl, st);
 }
 
 int dn_prepass_bwd(const dn_shape* s, const void* q, const void* k, const void* v,
@@ -246,6 +326,31 @@ int dn_chunk_fwd(const dn_shape* s, const void* q, const void* k, const void* v,
     p += need;
     res = &local;
   }
+  const int cut = overlap_cut(g);
+  Overlap* ov = cut ? overlap_for_device() : nullptr;
+  if (ov && p + carry_bytes(g) <= end) {
+    // prepass of chunks [0, cut); then the chain over those chunks (side stream) next to the
+    // prepass of chunks [cut, NC); then the rest of the chain
+    if (!res->W || !res->U || !res->M || !res->qe || !res->ke || !res->lam_end) return DN_ERR_NULL_POINTER;
+    cudaStream_t st = (cudaStream_t)stream;
+    float* carry = reinterpret_cast<float*>(p);
+    p += carry_bytes(g);
+    float* sc = reinterpret_cast<float*>(p);
+    const size_t scf = (size_t)(end - p) / sizeof(float);
+    StateArgs a{};
+    a.g = g; a.res = *res; a.seg = seg; a.init_state = (g.flags & DN_HAS_INIT) ? init_state : nullptr;
+    a.out = out; a.final_state = final_state; a.states = res->states; a.carry = carry;
+    if ((rc = launch_prepass_fwd_tc(g, q, k, v, g_, b, w, seg, *res, sc, scf, st, 0, cut))) return rc;
+    cudaEventRecord(ov->ev[0], st);
+    cudaStreamWaitEvent(ov->side, ov->ev[0], 0);
+    a.c_begin = 0; a.c_end = cut;
+    if ((rc = launch_state_fwd_tc(a, ov->side))) return rc;
+    cudaEventRecord(ov->ev[1], ov->side);
+    if ((rc = launch_prepass_fwd_tc(g, q, k, v, g_, b, w, seg, *res, sc, scf, st, cut, g.NC))) return rc;
+    cudaStreamWaitEvent(st, ov->ev[1], 0);
+    a.c_begin = cut; a.c_end = g.NC;
+    return launch_state_fwd_tc(a, st);
+  }
   if ((rc = dn_prepass_fwd(s, q, k, v, g_, b, w, seg, res, p, (size_t)(end - p), stream))) return rc;
   return dn_state_fwd(s, res, seg, init_state, out, final_state, stream);
 }
@@ -282,6 +387,33 @@ int dn_chunk_bwd(const dn_shape* s, const void* q, const void* k, const void* v,
     res = &local;
   }
   if (!res->T || !res->states) return DN_ERR_NULL_POINTER;
+  const int cut = prepass_bwd_tc_eligible(g) ? overlap_cut(g) : 0;
+  Overlap* ov = cut ? overlap_for_device() : nullptr;
+  if (ov && p + carry_bytes(g) <= end) {
+    // reverse chain over chunks [cut, NC); then the chunk-parallel backward of those chunks (side
+    // stream, the partly filled round of CTAs) next to the rest of the chain; then the
+    // chunk-parallel backward of chunks [0, cut) and the head sums
+    if (!res->W || !res->U || !res->lam_end) return DN_ERR_NULL_POINTER;
+    float* carry = reinterpret_cast<float*>(p);
+    p += carry_bytes(g);
+    BwdPlan pl;
+    if ((rc = plan_prepass_bwd(g, q, k, v, g_, b, w, seg, *res, d_out, dV, dH, dq, dk, dv, dg, db, dw,
+                               p, (size_t)(end - p), pl))) return rc;
+    StateArgs a{};
+    a.g = g; a.res = *res; a.seg = seg; a.d_out = d_out; a.d_final = d_final_state;
+    a.dV = dV; a.dH = dH; a.d_init = (g.flags & DN_HAS_INIT) ? d_init : nullptr; a.carry = carry;
+    a.c_begin = cut; a.c_end = g.NC;
+    if ((rc = launch_state_bwd_tc(a, st))) return rc;
+    cudaEventRecord(ov->ev[0], st);
+    cudaStreamWaitEvent(ov->side, ov->ev[0], 0);
+    if ((rc = launch_plan(pl, cut, g.NC, ov->side))) return rc;
+    cudaEventRecord(ov->ev[1], ov->side);
+    a.c_begin = 0; a.c_end = cut;
+    if ((rc = launch_state_bwd_tc(a, st))) return rc;
+    cudaStreamWaitEvent(st, ov->ev[1], 0);
+    if ((rc = launch_plan(pl, 0, cut, st))) return rc;
+    return finish_plan(g, pl, st);
+  }
   if ((rc = dn_state_bwd(s, res, seg, d_out, d_final_state, dV, dH, d_init, stream))) return rc;
   return run_prepass_bwd(g, q, k, v, g_, b, w, seg, *res, d_out, dV, dH, dq, dk, dv, dg, db, dw,
                          p, (size_t)(end - p), st);

@@ -13,6 +13,7 @@ struct PrepassFwdArgs {
   size_t scratch_per_cta;
   int items;
   int smem_tile_off;
+  int c_begin, c_end;          // chunk range [c_begin, c_end) of every (batch, head); tensor-core path only
 };
 
 struct StateArgs {
@@ -29,6 +30,11 @@ struct StateArgs {
   float* dV;                 // (B,H,NC,C,Vw)
   float* dH;                 // (B,H,NC,K,Vw)
   float* d_init;             // (B,Hv,K,V) or null
+  // Chunk range [c_begin, c_end) of the chain (tensor-core path only; 0, NC = the whole chain).  A
+  // forward pass that starts at c_begin > 0 reads its state from `carry`, one that stops before NC
+  // leaves it there; the backward pass uses it the other way round.  (B,H,K,Vw) fp32.
+  int c_begin, c_end;
+  float* carry;
 };
 
 struct PrepassBwdArgs {
@@ -45,6 +51,7 @@ struct PrepassBwdArgs {
   size_t scratch_per_cta;
   int items;
   int* err;                        // device error word (bounded waits report here)
+  int c_begin, c_end;              // chunk range [c_begin, c_end) of every (batch, head); tensor-core path only
 };
 
 size_t prepass_fwd_scratch_per_cta(const Geo& g);
@@ -57,7 +64,7 @@ bool prepass_fwd_tc_eligible(const Geo& g);
 size_t prepass_fwd_tc_scratch_per_cta();
 int launch_prepass_fwd_tc(const Geo& g, const void* q, const void* k, const void* v, const void* gg,
                           const void* b, const void* w, const int32_t* seg, const dn_residuals& res,
-                          float* scratch, size_t scratch_floats, cudaStream_t st);
+                          float* scratch, size_t scratch_floats, cudaStream_t st, int c_begin = 0, int c_end = -1);
 int launch_state_fwd(const StateArgs& a, cudaStream_t st);
 // tensor-core (tcgen05) variants of the chain kernels, used when state_tc_eligible()
 bool state_tc_eligible(const Geo& g);
@@ -68,6 +75,7 @@ int* device_error_ptr();
 int launch_state_bwd(const StateArgs& a, cudaStream_t st);
 int launch_prepass_bwd(PrepassBwdArgs& a, size_t scratch_floats, cudaStream_t st);
 int launch_prepass_bwd_tc(PrepassBwdArgs& a, size_t scratch_floats, cudaStream_t st);
+bool prepass_bwd_tc_eligible(const Geo& g);
 size_t prepass_bwd_tc_scratch_per_cta(const Geo& g);
 int launch_canonical_segments(const int32_t* raw, const int32_t* first_is_new, int32_t* out,
                               int B, int L, cudaStream_t st);

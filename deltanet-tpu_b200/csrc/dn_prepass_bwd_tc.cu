@@ -126,8 +126,11 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
   const bool guard = CF::fixed ? false : (g.flags & DN_STABILITY_GUARD) != 0;
   const bool trunc = g.flags & DN_TRUNC_DT_BF16;
 
-  for (int item = blockIdx.x; item < a.items; item += gridDim.x) {
-    const int c_idx = item % g.NC, h = (item / g.NC) % g.H, b = item / (g.NC * g.H);
+  // work items in chunk-major order inside the chunk range: all heads of chunk c_begin first
+  for (int e_item = blockIdx.x; e_item < a.items; e_item += gridDim.x) {
+    const int bh = e_item % (g.B * g.H), c_idx = a.c_begin + e_item / (g.B * g.H);
+    const int h = bh % g.H, b = bh / g.H;
+    const int item = bh * g.NC + c_idx;
     const int t0 = c_idx * C;
     const size_t ibase = (size_t)item;
     DN_MARK(0);
@@ -578,7 +581,7 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
     __syncthreads();
 #ifdef DN_PHASE_TIMING
     DN_MARK(17);
-    if (blockIdx.x == 0 && tid == 0 && item == 0) {
+    if (blockIdx.x == 0 && tid == 0 && e_item == 0) {
       for (int i = 1; i < 18; ++i) printf("mark %d -> %d: %lld\n", i - 1, i, g_phase_marks[i] - g_phase_marks[i - 1]);
       printf("item total %lld\n", g_phase_marks[17] - g_phase_marks[0]);
       printf("D: stage0 %lld compute0(warp0) %lld wait0 %lld stage1 %lld compute1 %lld wait1 %lld\n", g_phase_marks[20] - g_phase_marks[8],
@@ -600,7 +603,9 @@ size_t prepass_bwd_tc_scratch_per_cta(const Geo& g) {
 
 int launch_prepass_bwd_tc(PrepassBwdArgs& a, size_t scratch_floats, cudaStream_t st) {
   const Geo& g = a.g;
-  a.items = g.B * g.H * g.NC;
+  if (a.c_end <= 0) { a.c_begin = 0; a.c_end = g.NC; }
+  a.items = g.B * g.H * (a.c_end - a.c_begin);
+  if (a.items <= 0) return DN_OK;
   a.scratch_per_cta = prepass_bwd_tc_scratch_per_cta(g);
   a.err = device_error_ptr();
   const int grid = a.items < 148 ? a.items : 148;

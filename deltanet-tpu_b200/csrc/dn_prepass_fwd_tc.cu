@@ -127,8 +127,11 @@ __global__ void __launch_bounds__(NT, 1) prepass_fwd_tc_kernel(PrepassFwdArgs a,
 
   const bool fuse = CF::fixed ? false : (g.flags & DN_FUSE_PROLOGUE) != 0;     // the fixed modes have no fused prologue
 
-  for (int item = blockIdx.x; item < a.items; item += gridDim.x) {
-    const int c_idx = item % g.NC, h = (item / g.NC) % g.H, b = item / (g.NC * g.H);
+  // work items in chunk-major order inside the chunk range: all heads of chunk c_begin first
+  for (int e_item = blockIdx.x; e_item < a.items; e_item += gridDim.x) {
+    const int bh = e_item % (g.B * g.H), c_idx = a.c_begin + e_item / (g.B * g.H);
+    const int h = bh % g.H, b = bh / g.H;
+    const int item = bh * g.NC + c_idx;
     const int t0 = c_idx * C;
     const size_t ibase = (size_t)item;
     uint4* Wimg = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.res.W) + ibase * C * K);
@@ -408,7 +411,7 @@ __global__ void __launch_bounds__(NT, 1) prepass_fwd_tc_kernel(PrepassFwdArgs a,
     __syncthreads();
 #ifdef DN_PHASE_TIMING
     DN_MARK(11);
-    if (blockIdx.x == 0 && tid == 0 && item == 0) {
+    if (blockIdx.x == 0 && tid == 0 && e_item == 0) {
       for (int i = 1; i < 12; ++i) printf("fwd mark %d -> %d: %lld\n", i - 1, i, g_phase_marks[i] - g_phase_marks[i - 1]);
       printf("fwd item total %lld\n", g_phase_marks[11] - g_phase_marks[0]);
     }
@@ -427,10 +430,12 @@ size_t prepass_fwd_tc_scratch_per_cta() { return (size_t)C * C; }
 
 int launch_prepass_fwd_tc(const Geo& g, const void* q, const void* k, const void* v, const void* gg,
                           const void* b, const void* w, const int32_t* seg, const dn_residuals& res,
-                          float* scratch, size_t scratch_floats, cudaStream_t st) {
+                          float* scratch, size_t scratch_floats, cudaStream_t st, int c_begin, int c_end) {
   PrepassFwdArgs a;
   a.g = g; a.q = q; a.k = k; a.v = v; a.gg = gg; a.b = b; a.w = w; a.seg = seg; a.res = res;
-  a.items = g.B * g.H * g.NC;
+  a.c_begin = c_begin; a.c_end = c_end < 0 ? g.NC : c_end;
+  a.items = g.B * g.H * (a.c_end - a.c_begin);
+  if (a.items <= 0) return DN_OK;
   a.scratch_per_cta = prepass_fwd_tc_scratch_per_cta();
   a.smem_tile_off = 0;
   const int grid = a.items < 148 ? a.items : 148;

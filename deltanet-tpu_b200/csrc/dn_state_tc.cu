@@ -115,20 +115,22 @@ __global__ void __launch_bounds__(128, 1) state_fwd_tc_kernel(StateArgs a) {
   const __nv_bfloat16* Ug = reinterpret_cast<const __nv_bfloat16*>(a.res.U);
   const size_t item0 = ((size_t)b * g.H + h) * g.NC;
 
-  copy_tile_async(sW, Wg + item0 * C * K, row, g.img);
+  const int cb = a.c_begin, ce = a.c_end;               // chunk range of this launch
+  float* carry = a.carry ? a.carry + (((size_t)b * g.H + h) * K + row) * Vw + v0 : nullptr;
+  copy_tile_async(sW, Wg + (item0 + cb) * C * K, row, g.img);
   umma::cp_async_commit();
-  copy_tile_async(sQE, QEg + item0 * C * K, row, g.img);
-  copy_tile_async(sM, Mg + item0 * C * C, row, g.img);
-  copy_tile_async(sKE, KEg + item0 * C * K, row, g.img);
+  copy_tile_async(sQE, QEg + (item0 + cb) * C * K, row, g.img);
+  copy_tile_async(sM, Mg + (item0 + cb) * C * C, row, g.img);
+  copy_tile_async(sKE, KEg + (item0 + cb) * C * K, row, g.img);
   umma::cp_async_commit();
 
   float S[VS];
 #pragma unroll
-  for (int j = 0; j < VS; ++j) S[j] = 0.f;
+  for (int j = 0; j < VS; ++j) S[j] = cb > 0 ? carry[j] : 0.f;
 
-  for (int c = 0; c < g.NC; ++c) {
-    bool is_new, all_same;
-    chunk_flags(a.seg, g, b, c, is_new, all_same);
+  bool is_new, all_same;
+  chunk_flags(a.seg, g, b, cb, is_new, all_same);
+  for (int c = cb; c < ce; ++c) {
     const size_t item = item0 + c;
     if (c == 0 && !is_new && a.init_state) {
 #pragma unroll
@@ -158,13 +160,16 @@ __global__ void __launch_bounds__(128, 1) state_fwd_tc_kernel(StateArgs a) {
 #pragma unroll
       for (int p = 0; p < VS / 8; ++p) ureg[p] = make_uint4(0, 0, 0, 0);
     }
-    const float dec = all_same ? expf(fminf(a.res.lam_end[item * K + row], 0.f)) : 0.f;
+    const float dec = all_same ? expf(fminf(__ldg(a.res.lam_end + item * K + row), 0.f)) : 0.f;
+    // the next chunk's document flags: their (dependent) global loads overlap this chunk's products
+    bool nis_new = false, nall_same = false;
+    if (c + 1 < ce) chunk_flags(a.seg, g, b, c + 1, nis_new, nall_same);
 
     umma::cp_async_wait<1>();                           // this chunk's W has landed
     umma::pre_issue_sync();
     umma::issue<VS, false, true>(cx, sW, sS, K, colP, false);          // P = W S
     umma::commit_wait(cx);
-    if (c + 1 < g.NC) copy_tile_async(sW, Wg + (item + 1) * C * K, row, g.img);
+    if (c + 1 < ce) copy_tile_async(sW, Wg + (item + 1) * C * K, row, g.img);
     umma::cp_async_commit();
 
     float vn[VS];
@@ -186,7 +191,7 @@ __global__ void __launch_bounds__(128, 1) state_fwd_tc_kernel(StateArgs a) {
     }
     umma::issue<VS, true, true>(cx, sKE, sVn, C, colS, false);         // ke^T V_new
     umma::commit_wait(cx);
-    if (c + 1 < g.NC) {
+    if (c + 1 < ce) {
       copy_tile_async(sQE, QEg + (item + 1) * C * K, row, g.img);
       copy_tile_async(sM, Mg + (item + 1) * C * C, row, g.img);
       copy_tile_async(sKE, KEg + (item + 1) * C * K, row, g.img);
@@ -220,8 +225,12 @@ __global__ void __launch_bounds__(128, 1) state_fwd_tc_kernel(StateArgs a) {
 #pragma unroll
     for (int j = 0; j < VS; ++j) S[j] = fmaf(dec, S[j], sn[j]);       // S <- decay * S + ke^T V_new
     umma::tc_fence_before();
+    is_new = nis_new; all_same = nall_same;
   }
-  if (a.final_state) {
+  if (ce < g.NC) {
+#pragma unroll
+    for (int j = 0; j < VS; ++j) carry[j] = S[j];
+  } else if (a.final_state) {
 #pragma unroll
     for (int j = 0; j < VS; ++j) a.final_state[native_state_index_tc(g, b, h, row, v0 + j)] = S[j];
   }
@@ -259,7 +268,9 @@ __global__ void __launch_bounds__(128, 1) state_bwd_tc_kernel(StateArgs a) {
   const __nv_bfloat16* KEg = reinterpret_cast<const __nv_bfloat16*>(a.res.ke);
   const __nv_bfloat16* Mg = reinterpret_cast<const __nv_bfloat16*>(a.res.M);
   const size_t item0 = ((size_t)b * g.H + h) * g.NC;
-  const size_t last = item0 + g.NC - 1;
+  const int cb = a.c_begin, ce = a.c_end;               // chunk range of this launch, walked from ce - 1 down
+  float* carry = a.carry ? a.carry + (((size_t)b * g.H + h) * K + row) * Vw + v0 : nullptr;
+  const size_t last = item0 + ce - 1;
 
   copy_tile_async(sM, Mg + last * C * C, row, g.img);
   copy_tile_async(sKE, KEg + last * C * K, row, g.img);
@@ -271,40 +282,53 @@ __global__ void __launch_bounds__(128, 1) state_bwd_tc_kernel(StateArgs a) {
   float dH[VS];
 #pragma unroll
   for (int j = 0; j < VS; ++j)
-    dH[j] = a.d_final ? a.d_final[native_state_index_tc(g, b, h, row, v0 + j)] : 0.f;
+    dH[j] = ce < g.NC ? carry[j] : (a.d_final ? a.d_final[native_state_index_tc(g, b, h, row, v0 + j)] : 0.f);
 
-  for (int c = g.NC - 1; c >= 0; --c) {
-    bool is_new, all_same;
-    chunk_flags(a.seg, g, b, c, is_new, all_same);
+  // This thread's row of dO of one chunk as raw 16-byte vectors (token c*C+row; zero past the end).
+  // They are fetched one chunk ahead so that the chain never waits for them.
+  constexpr int NV = VS / 8;                            // bf16 vectors per row slice; fp32 needs 2 * NV
+  uint4 raw[2 * NV];
+  const bool dobf = g.qkv_dt == DN_BF16;
+  auto fetch_dO = [&](int c) {
+    const int t = c * C + row;
+    const bool live = c >= cb && t < g.L;
+    const size_t off = ((size_t)b * g.L + (live ? t : 0)) * g.Hv * g.V + (size_t)h * Vw + v0;
+    if (dobf) {
+      const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(a.d_out) + off);
+#pragma unroll
+      for (int p = 0; p < NV; ++p) raw[p] = live ? __ldg(src + p) : make_uint4(0, 0, 0, 0);
+    } else {
+      const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const float*>(a.d_out) + off);
+#pragma unroll
+      for (int p = 0; p < 2 * NV; ++p) raw[p] = live ? __ldg(src + p) : make_uint4(0, 0, 0, 0);
+    }
+  };
+  fetch_dO(ce - 1);
+  bool is_new, all_same;
+  chunk_flags(a.seg, g, b, ce - 1, is_new, all_same);
+
+  for (int c = ce - 1; c >= cb; --c) {
     const size_t item = item0 + c;
-    // this thread's row of dO (token c*C+row), rounded to bf16 as the reference does (gdn2.py:731)
+    // dO of this chunk, rounded to bf16 as the reference does (gdn2.py:731)
     float dO[VS];
-    {
-      const int t = c * C + row;
-      if (t < g.L) {
-        const size_t off = ((size_t)b * g.L + t) * g.Hv * g.V + (size_t)h * Vw + v0;
-        if (g.qkv_dt == DN_BF16) {
-          const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(a.d_out) + off);
+    if (dobf) {
 #pragma unroll
-          for (int p = 0; p < VS / 8; ++p) {
-            float t8[8];
-            umma::unpack8(src[p], t8);
+      for (int p = 0; p < NV; ++p) {
+        float t8[8];
+        umma::unpack8(raw[p], t8);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) dO[p * 8 + i] = t8[i];
-          }
-        } else {
-          const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.d_out) + off);
+        for (int i = 0; i < 8; ++i) dO[p * 8 + i] = t8[i];
+      }
+    } else {
 #pragma unroll
-          for (int j = 0; j < VS / 4; ++j) {
-            const float4 f = src[j];
-            dO[4 * j] = f.x; dO[4 * j + 1] = f.y; dO[4 * j + 2] = f.z; dO[4 * j + 3] = f.w;
-          }
-        }
-      } else {
-#pragma unroll
-        for (int j = 0; j < VS; ++j) dO[j] = 0.f;
+      for (int p = 0; p < 2 * NV; ++p) {
+        dO[4 * p] = __uint_as_float(raw[p].x); dO[4 * p + 1] = __uint_as_float(raw[p].y);
+        dO[4 * p + 2] = __uint_as_float(raw[p].z); dO[4 * p + 3] = __uint_as_float(raw[p].w);
       }
     }
+    fetch_dO(c - 1);                                    // in flight during this chunk's products
+    bool nis_new = false, nall_same = false;
+    if (c > cb) chunk_flags(a.seg, g, b, c - 1, nis_new, nall_same);
     stage_rows<VS>(sdO, row, dO);
     stage_rows<VS>(sdH, row, dH);
     {
@@ -312,14 +336,14 @@ __global__ void __launch_bounds__(128, 1) state_bwd_tc_kernel(StateArgs a) {
 #pragma unroll
       for (int j = 0; j < VS / 4; ++j) dst[j] = make_float4(dH[4 * j], dH[4 * j + 1], dH[4 * j + 2], dH[4 * j + 3]);
     }
-    const float dec = all_same ? expf(fminf(a.res.lam_end[item * K + row], 0.f)) : 0.f;
+    const float dec = all_same ? expf(fminf(__ldg(a.res.lam_end + item * K + row), 0.f)) : 0.f;
 
     umma::cp_async_wait<1>();                           // M, ke of this chunk
     umma::pre_issue_sync();
     umma::issue<VS, true, true>(cx, sM, sdO, C, colV, false);          // dV  = M^T dO
     umma::issue<VS, false, true>(cx, sKE, sdH, K, colV, true);         //     + ke dH
     umma::commit_wait(cx);
-    if (c > 0) {
+    if (c > cb) {
       copy_tile_async(sM, Mg + (item - 1) * C * C, row, g.img);
       copy_tile_async(sKE, KEg + (item - 1) * C * K, row, g.img);
     }
@@ -339,7 +363,7 @@ __global__ void __launch_bounds__(128, 1) state_bwd_tc_kernel(StateArgs a) {
     umma::issue<VS, true, true>(cx, sQE, sdO, C, colH, false);         // qe^T dO
     umma::issue<VS, true, true>(cx, sW, sdV, C, colH, true);           // - W^T dV
     umma::commit_wait(cx);
-    if (c > 0) {
+    if (c > cb) {
       copy_tile_async(sQE, QEg + (item - 1) * C * K, row, g.img);
       copy_tile_async(sW, Wg + (item - 1) * C * K, row, g.img);
     }
@@ -350,8 +374,12 @@ __global__ void __launch_bounds__(128, 1) state_bwd_tc_kernel(StateArgs a) {
 #pragma unroll
     for (int j = 0; j < VS; ++j) dH[j] = is_new ? 0.f : fmaf(dec, dH[j], dn_[j]);
     umma::tc_fence_before();
+    is_new = nis_new; all_same = nall_same;
   }
-  if (a.d_init) {
+  if (cb > 0) {
+#pragma unroll
+    for (int j = 0; j < VS; ++j) carry[j] = dH[j];
+  } else if (a.d_init) {
 #pragma unroll
     for (int j = 0; j < VS; ++j) a.d_init[native_state_index_tc(g, b, h, row, v0 + j)] = dH[j];
   }
@@ -398,14 +426,22 @@ bool state_tc_eligible(const Geo& g) {
   return g.prec == DN_PREC_BF16 && !(g.flags & DN_STATE_FP32_MM) && g.C == 128 && g.K == 128 && g.Vw % 32 == 0;
 }
 
-int launch_state_fwd_tc(const StateArgs& a, cudaStream_t st) {
+static StateArgs with_range(const StateArgs& in) {
+  StateArgs a = in;
+  if (a.c_end <= 0) { a.c_begin = 0; a.c_end = a.g.NC; }
+  return a;
+}
+
+int launch_state_fwd_tc(const StateArgs& in, cudaStream_t st) {
+  const StateArgs a = with_range(in);
   switch (pick_vs(a.g)) {
     case 64: return launch_fwd_vs<64>(a, st);
     default: return launch_fwd_vs<32>(a, st);
   }
 }
 
-int launch_state_bwd_tc(const StateArgs& a, cudaStream_t st) {
+int launch_state_bwd_tc(const StateArgs& in, cudaStream_t st) {
+  const StateArgs a = with_range(in);
   switch (pick_vs(a.g)) {
     case 64: return launch_bwd_vs<64>(a, st);
     default: return launch_bwd_vs<32>(a, st);

@@ -206,6 +206,26 @@ def test_oracle_parity_bf16_training_shape_small(dn):
                  precision="bf16", qk_l2norm=True, recompute_states=rc)
 
 
+def test_oracle_parity_split_chains(dn):
+    """A shape whose work items (2 batches x 10 heads x 8 chunks = 160) leave the last round of CTAs
+    almost empty, which makes the library cut the chunk axis (here after chunk 7) and run a part of
+    the chain next to the chunk-parallel kernels on a second stream.  A document crosses the cut and
+    an initial state, a final state and the state cotangent flow through the carried state."""
+    B, L, Hk, Hv, K, V = 2, 1024, 10, 10, 128, 128
+    q, k, v, g, b, w = O.make_inputs(410, B, L, Hk, Hv, K, V, qkv_dtype=torch.bfloat16)
+    seg = torch.zeros(B, L, dtype=torch.int32)
+    seg[0, 300:] = 1
+    seg[0, 950:] = 2                      # starts inside the last chunk, after the cut at token 896
+    seg[1, 640:] = 1
+    gen = torch.Generator().manual_seed(7)
+    init = torch.randn(B, Hv, K, V, generator=gen) * 0.1
+    do = torch.randn(B, L, Hv, V, generator=gen).to(torch.bfloat16).float()
+    for rc in (False, True):
+        run_both(dn, q, k, v, g, b, w, do=do, tol=BF16_TOL, segment_ids=seg, chunk_size=128, precision="bf16",
+                 qk_l2norm=True, initial_state=init, initial_state_segment_id=0,
+                 recompute_states=rc)
+
+
 def test_many_small_documents_and_cu_seqlens(dn):
     """Length-1 documents, reused ids, cu_seqlens (reference: tests/test_document_boundaries.py:33-141)."""
     B, L, Hk, Hv, K, V = 1, 192, 1, 1, 64, 64
