@@ -72,6 +72,25 @@ def alg_flops(c):
     return dict(prepass_fwd=pre_fwd, state_fwd=st_fwd, state_bwd=chain_bwd, prepass_bwd=par_bwd)
 
 
+def alg_bytes(c):
+    """Algorithmic HBM bytes per (batch, exec head, chunk) item and kernel: every array the kernel must
+    read or write, once (bf16 q/k/v/out/dO and residual tiles, fp32 gates, T, states, dV, dH)."""
+    C, K, Vw = c["chunk"], c["K"], (c["Hv"] // c["Hk"]) * c["V"]
+    qk, gb, vv, ww = 2 * C * K * 2, 2 * C * K * 4, C * Vw * 2, C * Vw * 4
+    tiles = 3 * C * K * 2 + C * C * 2 + C * Vw * 2              # W, qe, ke, M, U
+    pre_fwd = qk + gb + vv + ww + tiles + C * C * 4 + K * 4
+    st_fwd = tiles + C * Vw * 2 + K * Vw * 4                     # + out, chunk-entry state
+    chain_bwd = 3 * C * K * 2 + C * C * 2 + C * Vw * 2 + C * Vw * 4 + K * Vw * 4    # tiles, dO -> dV, dH
+    par_bwd = (C * K * 2 + C * Vw * 2 + K * Vw * 4 + C * C * 4 + C * Vw * 2 + C * Vw * 4 + K * Vw * 4
+               + qk + gb + vv + ww + qk + gb + vv + ww)          # W,U,S,T,dO,dV,dH, inputs, six gradients
+    return dict(prepass_fwd=pre_fwd, state_fwd=st_fwd, state_bwd=chain_bwd, prepass_bwd=par_bwd)
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch on the headline workload, from the ncu captures
+# summarised under profiles/ (None where no capture of the current kernel exists)
+NCU_DRAM_BYTES = {"prepass_bwd": None, "prepass_fwd": None, "state_fwd": None, "state_bwd": None}
+
+
 # ------------------------------------------------------------------------------------------ inputs
 def make_training_inputs(seed, c, device=None, pin=False):
     gen = torch.Generator().manual_seed(seed)
@@ -364,11 +383,23 @@ def main():
     for name in ("prepass_fwd", "state_fwd", "state_bwd", "prepass_bwd"):
         per[name] = time_steps(lambda: job.phase(name), 10, 3) / 10
     dom = max(per, key=per.get)
-    ach = fl[dom] * items / (per[dom] * 1e-3) / 1e12
-    roofline = dict(kernel=dom, bound="tensor", achieved=ach, peak=peaks["bf16_tflops"], unit="TFLOP/s",
-                    frac=ach / peaks["bf16_tflops"], traffic=None, peak_source=peaks["source"],
+    by = alg_bytes(CFG)
+    t_hbm = by[dom] * items / (peaks["hbm_gbs"] * 1e9)          # seconds at the measured copy bandwidth
+    t_tc = fl[dom] * items / (peaks["bf16_tflops"] * 1e12)      # seconds at the measured dense bf16 rate
+    sec = per[dom] * 1e-3
+    if t_hbm >= t_tc:
+        ach = by[dom] * items / sec / 1e9
+        roofline = dict(kernel=dom, bound="hbm", achieved=ach, peak=peaks["hbm_gbs"], unit="GB/s", frac=ach / peaks["hbm_gbs"])
+    else:
+        ach = fl[dom] * items / sec / 1e12
+        roofline = dict(kernel=dom, bound="tensor", achieved=ach, peak=peaks["bf16_tflops"], unit="TFLOP/s",
+                        frac=ach / peaks["bf16_tflops"])
+    roofline.update(traffic=NCU_DRAM_BYTES.get(dom), peak_source=peaks["source"],
+                    tensor_frac=fl[dom] * items / sec / 1e12 / peaks["bf16_tflops"],
+                    hbm_frac=by[dom] * items / sec / 1e9 / peaks["hbm_gbs"],
                     kernel_ms={k_: round(v_, 4) for k_, v_ in per.items()},
-                    alg_gflop={k_: round(v_ * items / 1e9, 3) for k_, v_ in fl.items()})
+                    alg_gflop={k_: round(v_ * items / 1e9, 3) for k_, v_ in fl.items()},
+                    alg_mbytes={k_: round(v_ * items / 1e6, 1) for k_, v_ in by.items()})
 
     # ---- end to end through the public operator with host buffers
     host = make_training_inputs(2000 + rank, CFG, pin=True)
@@ -423,7 +454,9 @@ def main():
         config=dict(workload="chunk_gdn2 fwd+bwd B=1 L=2048 Hk=12 Hv=24 K=V=128 chunk=128 precision=bf16 qk_l2norm "
                              "docs split at L/2 (per GPU)", global_batch=world, parallelism=f"batch-sharded x{world}, no collective",
                     l2=f"no flush: the step touches {job.bytes / 1e6:.0f} MB (inputs, residuals, scratch, grads) > 126 MB L2"),
-        roofline=roofline, e2e=e2e, decode=decode, cpu_baseline=cpu, gpu_launches=4 * args.steps, clocks=clocks)
+        roofline=roofline, e2e=e2e, decode=decode, cpu_baseline=cpu,
+        gpu_launches=(job.lib.dn_launch_count(job.shape, 0, 0) + job.lib.dn_launch_count(job.shape, 1, 0)) * args.steps,
+        clocks=clocks)
     print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()

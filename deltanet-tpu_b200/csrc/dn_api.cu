@@ -438,6 +438,18 @@ int dn_sp_transition(const dn_shape* s, const dn_residuals* res, const int32_t* 
   return launch_state_fwd(a, (cudaStream_t)stream);
 }
 
+int dn_launch_count(const dn_shape* s, int backward, int recompute) {
+  Geo g;
+  if (make_geo(s, &g)) return 0;
+  const bool split_f = overlap_cut(g) && overlap_for_device();
+  const bool split_b = split_f && prepass_bwd_tc_eligible(g);
+  if (!backward) return split_f ? 4 : 2;
+  int n = split_b ? 4 : 2;
+  if (recompute) n += 2;
+  n += (g.qk_div > 1 ? 2 : 0) + (g.gH != g.H) + (g.bH != g.H) + (g.wH != g.Hv);   // head sums
+  return n;
+}
+
 int dn_sp_apply(const float* P, const float* S_in, const float* Q, float* S_out, int32_t B, int32_t H,
                 int32_t G, int32_t K, int32_t V, int32_t transpose, void* stream) {
   if (!P || !S_in || !S_out) return DN_ERR_NULL_POINTER;

@@ -103,7 +103,7 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
   float* sc = a.scratch + (size_t)blockIdx.x * a.scratch_per_cta;
   float* DQE = sc;          float* DKE = DQE + CK;   float* DX = DKE + CK;
   float* DBP = DX + CK;     float* DQP = DBP + CK;   float* DKP = DQP + CK;
-  float* DY = DKP + CK;     float* DM = DY + CV;     float* DA = DM + CC;
+  float* DM = DKP + CK;     float* DA = DM + CC;
   float4* DA4 = reinterpret_cast<float4*>(DA);
   float4* DM4 = reinterpret_cast<float4*>(DM);
   float4* DBP4 = reinterpret_cast<float4*>(DBP);
@@ -112,7 +112,6 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
   const float4* DX4 = reinterpret_cast<const float4*>(DX);
   const float4* DQE4 = reinterpret_cast<const float4*>(DQE);
   const float4* DKE4 = reinterpret_cast<const float4*>(DKE);
-  const float4* DY4 = reinterpret_cast<const float4*>(DY);
 
   if (tid == 0) { umma::mbar_init(&mma_bar, 1); umma::fence_mbar_init(); }
   if (warp == 0) umma::tmem_alloc(&tmem_base, 512);
@@ -163,6 +162,10 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
       }
     }
 
+    const Rows r = make_rows<CF>(g, a.q, a.k, a.gg, a.b, b, h, t0, rq_s, rk_s);
+    const int qdt = r.qkv_dt, gdt = r.gate_dt;           // compile-time constants in the fixed modes
+    const int wC = CF::fixed ? g.V : g.wC;
+
     // ---- G. the matrix products (and dLambda_end from the carried state)
     {
       BwdTcIo io;
@@ -176,17 +179,63 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
       io.dO_off = ((size_t)b * g.L + t0) * g.Hv * g.V + (size_t)h * VW;
       io.dO_pitch = (size_t)g.Hv * g.V;
       io.rows_valid = g.L - t0 < C ? g.L - t0 : C;
-      io.DQE = DQE; io.DKE = DKE; io.DX = DX; io.DY = DY; io.DM = DM; io.DA = DA;
+      io.DQE = DQE; io.DKE = DKE; io.DX = DX; io.DM = DM; io.DA = DA;
       io.dlend_s = dlend_s; io.all_same = all_same;
       io.seg_s = seg_s; io.trunc = trunc;
       bwd_gemms_tc<VW, NT>(cx, smraw, io);
     }
 
+    // ---- V. dv = dY * w_act, dw = dY * v (+ sigmoid adjoint; summed over a value head's columns
+    //         when w is one scalar per head): 8 rows x 4 pieces per warp step.  dY is read from the
+    //         bf16 operand image the products left in shared memory (slot X), i.e. rounded to bf16
+    //         like every other operand of this precision mode.
+    {
+      constexpr int PV = VW / 8;
+      const int x = myrow, t = t0 + x;
+      const bool live = t < g.L;
+      const size_t tok = (size_t)b * g.L + t;
+      const int steps_per_head = g.V / 32;            // warp steps that cover one value head
+      float sw = 0.f;
+      const size_t tokr = live ? tok : (size_t)b * g.L + t0;      // row read when this one does not exist
+#pragma unroll 4
+      for (int it = 0; it < PV / 4; ++it) {
+        const int p = it * 4 + lgrp;
+        const int col0 = h * VW + 8 * p, hv = col0 / g.V, cv = col0 - hv * g.V;
+        float vv[8], ww[8], dy[8], dv8[8], dw8[8];
+        load8(a.v, tokr * g.Hv * g.V + col0, qdt, vv);
+        if (wC == 1) {
+          const float w1 = ldf_ro(a.w, tokr * g.wH + g.w_head(hv), gdt);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) ww[i] = w1;
+        } else {
+          load8(a.w, (tokr * g.wH + g.w_head(hv)) * wC + cv, gdt, ww);
+        }
+        umma::unpack8(reinterpret_cast<const uint4*>(smraw)[p * 128 + x], dy);
+        if (live) {
+          const size_t vrow = tok * g.Hv * g.V + col0;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            float wa = ww[i], dwv = dy[i] * vv[i];
+            if (fuse) { wa = 1.f / (1.f + expf(-ww[i])); dwv *= wa * (1.f - wa); }
+            dv8[i] = dy[i] * wa;
+            dw8[i] = dwv;
+            sw += dwv;
+          }
+          out8(a.dv, vrow, qdt, dv8);
+          if (wC != 1) out8(a.dw, (tok * g.Hv + hv) * wC + cv, a.dw_dt, dw8);
+        }
+        if (wC == 1 && (it + 1) % steps_per_head == 0) {
+          sw += __shfl_xor_sync(0xffffffffu, sw, 8);
+          sw += __shfl_xor_sync(0xffffffffu, sw, 16);
+          if (live && lgrp == 0) stf(a.dw, tok * g.Hv + hv, sw, a.dw_dt);
+          sw = 0.f;
+        }
+      }
+    }
+    __syncthreads();
+
     DN_MARK(7);
     // ---- L. rows, normalisers, cumulative decay
-    const Rows r = make_rows<CF>(g, a.q, a.k, a.gg, a.b, b, h, t0, rq_s, rk_s);
-    const int qdt = r.qkv_dt, gdt = r.gate_dt;           // compile-time constants in the fixed modes
-    const int wC = CF::fixed ? g.V : g.wC;
     row_norms_8x4(r, myrow, lgrp, rq_s, rk_s);
     lambda_scan_512(r, seg_s, LAM, TOTL, reset_s);
     __syncthreads();
@@ -357,10 +406,14 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
 
     DN_MARK(13);
     // ---- E. combination (8 rows x 4 pieces per warp step; a thread keeps row `myrow`):
-    //         dLambda and dke*ke to shared memory, d b written, d q_hat / d k_hat back in place;
-    //         then the l2norm adjoint needs each row's <q_n, dq_n> and <k_n, dk_n>: partial sums per
-    //         thread, the four threads of a row sit 8 lanes apart.
+    //         dLambda and dke*ke to shared memory, d b written.  The l2norm adjoint needs each row's
+    //         <q_n, dq_n> and <k_n, dk_n> (partial sums per thread, the four threads of a row sit 8
+    //         lanes apart) before dq, dk can be written: until then a thread parks its d q_n, d k_n,
+    //         q_n, k_n in tensor memory, which is idle in this phase (128 columns per group of four
+    //         warps, the thread's own lane), so nothing goes through global memory twice.
     {
+      umma::tc_fence_after();
+      const uint32_t stash = cx.tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)((warp >> 2) * 128);
       const int x = myrow, t = t0 + x;
       const bool live = x < r.rows_valid;
       const bool first = seg_s[x] == seg0, last = seg_s[x] == segL;
@@ -408,11 +461,15 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
           sb2 += dbv;
           dqp[i] = dq * g.scale;                                // d q_n (before the l2norm adjoint)
           dkp[i] = dk;
-          dq_dot = fmaf(qr[i] * rq, dqp[i], dq_dot);
-          dk_dot = fmaf(kr[i] * rk, dkp[i], dk_dot);
+          qr[i] *= rq;                                          // q_n, k_n
+          kr[i] *= rk;
+          dq_dot = fmaf(qr[i], dqp[i], dq_dot);
+          dk_dot = fmaf(kr[i], dkp[i], dk_dot);
         }
-        st2x4(DQP4 + p4v(x, 8 * p), dqp);
-        st2x4(DKP4 + p4v(x, 8 * p), dkp);
+        umma::tmem_st8(stash + it * 32, dqp);
+        umma::tmem_st8(stash + it * 32 + 8, dkp);
+        umma::tmem_st8(stash + it * 32 + 16, qr);
+        umma::tmem_st8(stash + it * 32 + 24, kr);
         *reinterpret_cast<float4*>(DLs + x * LP + 8 * p) = make_float4(odl[0], odl[1], odl[2], odl[3]);
         *reinterpret_cast<float4*>(DLs + x * LP + 8 * p + 4) = make_float4(odl[4], odl[5], odl[6], odl[7]);
         *reinterpret_cast<float4*>(DKs + x * LP + 8 * p) = make_float4(odk[0], odk[1], odk[2], odk[3]);
@@ -426,26 +483,28 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
         sb2 += __shfl_xor_sync(0xffffffffu, sb2, 16);
         if (live && lgrp == 0) stf(a.db, outb, sb2, a.db_dt);
       }
-      if (live) {
+      umma::tmem_wait_st();
 #pragma unroll 2
-        for (int it = 0; it < 4; ++it) {
-          const int p = it * 4 + lgrp;
-          float qr[8], kr[8], dqn[8], dkn[8];
-          raw_q8(r, x, p, qr);
-          raw_k8(r, x, p, kr);
-          ld2x4(DQP4 + p4v(x, 8 * p), dqn);
-          ld2x4(DKP4 + p4v(x, 8 * p), dkn);
-          if (l2) {
+      for (int it = 0; it < 4; ++it) {                        // every thread takes part: the loads are warp-wide
+        const int p = it * 4 + lgrp;
+        float qn[8], kn[8], dqn[8], dkn[8];
+        umma::tmem_ld8(stash + it * 32, dqn);
+        umma::tmem_ld8(stash + it * 32 + 8, dkn);
+        umma::tmem_ld8(stash + it * 32 + 16, qn);
+        umma::tmem_ld8(stash + it * 32 + 24, kn);
+        if (l2) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              dqn[i] = rq * (dqn[i] - (qr[i] * rq) * dq_dot);
-              dkn[i] = rk * (dkn[i] - (kr[i] * rk) * dk_dot);
-            }
+          for (int i = 0; i < 8; ++i) {
+            dqn[i] = rq * (dqn[i] - qn[i] * dq_dot);
+            dkn[i] = rk * (dkn[i] - kn[i] * dk_dot);
           }
+        }
+        if (live) {
           out8(a.dq, outqk + 8 * p, a.dq_dt, dqn);
           out8(a.dk, outqk + 8 * p, a.dq_dt, dkn);
         }
       }
+      umma::tc_fence_before();
       (void)rowqk;
     }
     __syncthreads();
@@ -533,51 +592,6 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
     }
 
     DN_MARK(16);
-    // ---- V. dv = dY * w_act, dw = dY * v (+ sigmoid adjoint; summed over a value head's columns
-    //         when w is one scalar per head): 8 rows x 4 pieces per warp step
-    {
-      constexpr int PV = VW / 8;
-      const int x = myrow, t = t0 + x;
-      const bool live = t < g.L;
-      const size_t tok = (size_t)b * g.L + t;
-      const int steps_per_head = g.V / 32;            // warp steps that cover one value head
-      float sw = 0.f;
-      const size_t tokr = live ? tok : (size_t)b * g.L + t0;      // row read when this one does not exist
-#pragma unroll 4
-      for (int it = 0; it < PV / 4; ++it) {
-        const int p = it * 4 + lgrp;
-        const int col0 = h * VW + 8 * p, hv = col0 / g.V, cv = col0 - hv * g.V;
-        float vv[8], ww[8], dy[8], dv8[8], dw8[8];
-        load8(a.v, tokr * g.Hv * g.V + col0, qdt, vv);
-        if (wC == 1) {
-          const float w1 = ldf_ro(a.w, tokr * g.wH + g.w_head(hv), gdt);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) ww[i] = w1;
-        } else {
-          load8(a.w, (tokr * g.wH + g.w_head(hv)) * wC + cv, gdt, ww);
-        }
-        ld2x4(DY4 + p4v(x, 8 * p), dy);
-        if (live) {
-          const size_t vrow = tok * g.Hv * g.V + col0;
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            float wa = ww[i], dwv = dy[i] * vv[i];
-            if (fuse) { wa = 1.f / (1.f + expf(-ww[i])); dwv *= wa * (1.f - wa); }
-            dv8[i] = dy[i] * wa;
-            dw8[i] = dwv;
-            sw += dwv;
-          }
-          out8(a.dv, vrow, qdt, dv8);
-          if (wC != 1) out8(a.dw, (tok * g.Hv + hv) * wC + cv, a.dw_dt, dw8);
-        }
-        if (wC == 1 && (it + 1) % steps_per_head == 0) {
-          sw += __shfl_xor_sync(0xffffffffu, sw, 8);
-          sw += __shfl_xor_sync(0xffffffffu, sw, 16);
-          if (live && lgrp == 0) stf(a.dw, tok * g.Hv + hv, sw, a.dw_dt);
-          sw = 0.f;
-        }
-      }
-    }
     __syncthreads();
 #ifdef DN_PHASE_TIMING
     DN_MARK(17);
@@ -597,9 +611,7 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
 
 }  // namespace
 
-size_t prepass_bwd_tc_scratch_per_cta(const Geo& g) {
-  return (size_t)6 * C * K + (size_t)C * g.Vw + (size_t)2 * C * C;
-}
+size_t prepass_bwd_tc_scratch_per_cta(const Geo&) { return (size_t)6 * C * K + (size_t)2 * C * C; }
 
 int launch_prepass_bwd_tc(PrepassBwdArgs& a, size_t scratch_floats, cudaStream_t st) {
   const Geo& g = a.g;

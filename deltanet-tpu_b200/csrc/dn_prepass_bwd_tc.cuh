@@ -11,6 +11,7 @@
 //   3. dW    = -dV S^T                       A = dV (Z)         B = -S (X)        -> image P
 //   4. dke   = V_new dH^T                    A = V_new (Y)      B = dH (X)
 //   5. dX    = T^T dW ; dY = T^T dV          A = T^T (Y)        B = dW (P), dV (Z) -> images Y', X
+//      (dY leaves the function as the image X: the caller forms dv, dw from it)
 //   6. dA    = -(dX W^T + dY U^T)            A = dX (Y'), dY (X)   B = W (P), U (Z)
 //
 // Global memory is touched in two patterns only.  Inputs are read by warps that cover 8 rows x 4
@@ -38,7 +39,7 @@ struct BwdTcIo {
   size_t dO_off;                       // element offset of (row 0, column 0) of this item's dO block
   size_t dO_pitch;                     // elements between token rows
   int rows_valid;                      // rows of the chunk that exist (others read as 0)
-  float *DQE, *DKE, *DX, *DY, *DM, *DA;  // fp32 results in scratch, panel layout
+  float *DQE, *DKE, *DX, *DM, *DA;       // fp32 results in scratch, panel layout
   float* dlend_s;                      // out (shared, 128): [one doc] exp(lam_end) * sum_v dH * S
   bool all_same;
   const int* seg_s;
@@ -94,7 +95,6 @@ __device__ __forceinline__ void bwd_gemms_tc(umma::Ctx& cx, uint8_t* img, const 
   float4* DQE4 = reinterpret_cast<float4*>(io.DQE);
   float4* DKE4 = reinterpret_cast<float4*>(io.DKE);
   float4* DX4 = reinterpret_cast<float4*>(io.DX);
-  float4* DY4 = reinterpret_cast<float4*>(io.DY);
   float4* DM4 = reinterpret_cast<float4*>(io.DM);
   float4* DA4 = reinterpret_cast<float4*>(io.DA);
 
@@ -218,14 +218,10 @@ __device__ __forceinline__ void bwd_gemms_tc(umma::Ctx& cx, uint8_t* img, const 
     Y2[(col / 8) * 128 + row] = umma::pack8p(r);
     Y2[(col / 8 + 1) * 128 + row] = umma::pack8p(r + 8);
   });
+  // dY is kept only as its bf16 image X: operand of step 6, and read again by the caller for dv, dw
   umma::drain<NT, VW>(cx, 256, [&](int row, int col, const float (&v)[16]) {
-    float r[16];
-#pragma unroll
-    for (int i = 0; i < 16; ++i) r[i] = io.trunc ? bf16r(v[i]) : v[i];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) DY4[p4v(row, col + 4 * i)] = make_float4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
-    X[(col / 8) * 128 + row] = umma::pack8p(r);
-    X[(col / 8 + 1) * 128 + row] = umma::pack8p(r + 8);
+    X[(col / 8) * 128 + row] = umma::pack8p(v);
+    X[(col / 8 + 1) * 128 + row] = umma::pack8p(v + 8);
   });
 
   DN_MARK(6);

@@ -257,6 +257,10 @@ __global__ void __launch_bounds__(NT, 1) prepass_fwd_tc_kernel(PrepassFwdArgs a,
     for (int half = 0; half < 2; ++half) {
       float* QHs = KHs + 64 * AP;                                       // q_hat (pitch AP)
       float* BEs = reinterpret_cast<float*>(smraw + OFF_TI);            // beta (pitch 128)
+#ifdef DN_STAGE_TWICE
+#pragma unroll 1
+      for (int rep = 0; rep < 2; ++rep)
+#endif
 #pragma unroll
       for (int it = 0; it < 2; ++it) {
         const int w = it * 16 + warp, xr = (w & 7) * 8 + (lane & 7), p = (w >> 3) * 4 + lgrp, x = half * 64 + xr;
@@ -274,6 +278,7 @@ __global__ void __launch_bounds__(NT, 1) prepass_fwd_tc_kernel(PrepassFwdArgs a,
         *reinterpret_cast<float4*>(BEs + xr * 128 + 8 * p + 4) = make_float4(ba[4], ba[5], ba[6], ba[7]);
       }
       __syncthreads();
+      DN_MARK(20 + 3 * half);
       const int lb = warp >> 2, r0 = (half * 4 + lb) * 16, c0 = lb * 16;   // block rows in the chunk / in the caches
 #pragma unroll 1
       for (int i = warp & 3; i < 16; i += 4) {
@@ -319,7 +324,9 @@ __global__ void __launch_bounds__(NT, 1) prepass_fwd_tc_kernel(PrepassFwdArgs a,
           Mel[rix(true, ri, r0 + lane, C)] = __float2bfloat16_rn(mrow);
         }
       }
+      DN_MARK(21 + 3 * half);
       __syncthreads();
+      DN_MARK(22 + 3 * half);
     }
 
     DN_MARK(7);
@@ -414,6 +421,9 @@ __global__ void __launch_bounds__(NT, 1) prepass_fwd_tc_kernel(PrepassFwdArgs a,
     if (blockIdx.x == 0 && tid == 0 && e_item == 0) {
       for (int i = 1; i < 12; ++i) printf("fwd mark %d -> %d: %lld\n", i - 1, i, g_phase_marks[i] - g_phase_marks[i - 1]);
       printf("fwd item total %lld\n", g_phase_marks[11] - g_phase_marks[0]);
+      printf("fwd D: stage0 %lld compute0(warp0) %lld wait0 %lld stage1 %lld compute1 %lld wait1 %lld\n", g_phase_marks[20] - g_phase_marks[6],
+             g_phase_marks[21] - g_phase_marks[20], g_phase_marks[22] - g_phase_marks[21], g_phase_marks[23] - g_phase_marks[22],
+             g_phase_marks[24] - g_phase_marks[23], g_phase_marks[25] - g_phase_marks[24]);
     }
 #endif
   }

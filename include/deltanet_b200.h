@@ -92,13 +92,19 @@ int dn_exec_view(const dn_shape* s, dn_exec* out);
 /*
  * Residuals written by the forward and read by the backward: the reference's residual tuple
  * (gdn2.py:1384-1388).  All in exec-head layout; NC = ceil(L/chunk), C = chunk.
+ *
+ * The five pre_dtype tiles are opaque to the caller: only the library's own entry points read
+ * them.  Each (batch, head, chunk) tile holds rows x cols elements, row-major in general; for shapes
+ * that take the tensor-core path (precision bf16, chunk = K = 128, Vw in {128,256}, DN_FORCE_SIMT
+ * unset) a tile is stored as the tensor cores' operand image, [col / 8][row][8 elements], so that
+ * every kernel copies it into shared memory as it lies.  The sizes are the same in both layouts.
  */
 typedef struct dn_residuals {
-  void*  W;        /* (B,H,NC,C,K)   pre_dtype */
-  void*  U;        /* (B,H,NC,C,Vw)  pre_dtype */
-  void*  M;        /* (B,H,NC,C,C)   pre_dtype */
-  void*  qe;       /* (B,H,NC,C,K)   pre_dtype */
-  void*  ke;       /* (B,H,NC,C,K)   pre_dtype */
+  void*  W;        /* (B,H,NC) tiles of C x K    pre_dtype */
+  void*  U;        /* (B,H,NC) tiles of C x Vw   pre_dtype */
+  void*  M;        /* (B,H,NC) tiles of C x C    pre_dtype */
+  void*  qe;       /* (B,H,NC) tiles of C x K    pre_dtype */
+  void*  ke;       /* (B,H,NC) tiles of C x K    pre_dtype */
   float* lam_end;  /* (B,H,NC,K)     */
   float* T;        /* (B,H,NC,C,C)   or NULL (inference) */
   float* states;   /* (B,H,NC,K,Vw)  chunk-entry states, or NULL (inference) */
@@ -120,6 +126,15 @@ int dn_canonical_segments(const int32_t* raw, const int32_t* first_is_new, int32
  * (B,Hv,K,V) f32 is read when DN_HAS_INIT.  final_state (B,Hv,K,V) f32 may be NULL.
  * res == NULL means "keep nothing" (inference, or recompute_states): the prepass
  * outputs then live in scratch only.
+ *
+ * Streams: all work is ordered on `stream`.  For shapes whose B*H*NC work items leave the last
+ * round of the one-CTA-per-SM kernels mostly empty, dn_chunk_fwd and dn_chunk_bwd cut the chunk
+ * axis in two and run part of the inter-chunk chain on a library-owned side stream next to the
+ * chunk-parallel kernel of the other part; the side stream forks from `stream` and joins back into
+ * it through events before the call's last kernel, so the caller still sees one stream-ordered
+ * operation (and may capture it in a graph).  The side stream and its two events are created on the
+ * first such call per device; make that call outside stream capture.  DN_NO_OVERLAP=1 in the
+ * environment turns the split off.
  */
 int dn_chunk_fwd(const dn_shape* s,
                  const void* q, const void* k, const void* v,
@@ -248,6 +263,13 @@ int dn_selftest_umma(int32_t a_mn, int32_t b_mn, int32_t N, int32_t Kc, const vo
  * affected products).  Synchronises with the device; meant for tests and debugging.
  */
 int dn_device_error(void);
+
+/*
+ * Diagnostic (no reference counterpart): the number of kernels dn_chunk_fwd (backward = 0) or
+ * dn_chunk_bwd (backward = 1; recompute = 1 adds the rebuilt prepass and states) enqueues for this
+ * shape.  0 for an invalid shape.
+ */
+int dn_launch_count(const dn_shape* s, int backward, int recompute);
 
 const char* dn_status_string(int status);
 int dn_version(void);
