@@ -86,9 +86,9 @@ def alg_bytes(c):
     return dict(prepass_fwd=pre_fwd, state_fwd=st_fwd, state_bwd=chain_bwd, prepass_bwd=par_bwd)
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch on the headline workload, from the ncu captures
-# summarised under profiles/ (None where no capture of the current kernel exists)
-NCU_DRAM_BYTES = {"prepass_bwd": None, "prepass_fwd": None, "state_fwd": None, "state_bwd": None}
+# dram__bytes_read.sum + dram__bytes_write.sum of a kernel's launches in one step of the headline workload
+# (both chunk ranges together), from the ncu capture summarised in profiles/chunk_step_kernels_headline.md
+NCU_DRAM_BYTES = {"prepass_bwd": 397.7e6, "prepass_fwd": 92.9e6, "state_fwd": 39.6e6, "state_bwd": 40.5e6}
 
 
 # ------------------------------------------------------------------------------------------ inputs
