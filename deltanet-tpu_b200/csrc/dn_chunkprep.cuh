@@ -205,22 +205,27 @@ __device__ __forceinline__ void decay8(const float* la, const float* lb, float (
 // k_hat * exp(Lam_ref - Lam_x) in BOTH images; rows of the lower blocks carry
 // beta * exp(Lam_x - Lam_ref) in KR and q_hat * exp(Lam_x - Lam_ref) in QK.  All scale factors are
 // <= 1.  One piece (row x, channel group p) per call, stored at image[p*128 + x].
-__device__ __forceinline__ void build_level_piece(const Rows& r, const float* LAM, int s, int x, int p, uint4* KR, uint4* QK) {
+__device__ __forceinline__ void build_level_from(const float (&kh)[8], const float (&ba)[8], const float (&qh)[8],
+                                                 const float* LAM, int s, int x, int p, uint4* KR, uint4* QK) {
   const int ref = level_ref(x, s);
   const bool lower = x >= ref;
-  float f[8], kh[8], ba[8], qh[8];
-  khat8(r, x, p, kh);              // all three loads are issued before the role is looked at
-  bact8(r, x, p, ba);
-  qhat8(r, x, p, qh);
+  float f[8], o1[8], o2[8];
   decay8(LAM + (lower ? x : ref) * LP + 8 * p, LAM + (lower ? ref : x) * LP + 8 * p, f);
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     const float kf = kh[i] * f[i];
-    ba[i] = lower ? (ba[i] * kh[i]) * f[i] : kf;
-    qh[i] = lower ? qh[i] * f[i] : kf;
+    o1[i] = lower ? (ba[i] * kh[i]) * f[i] : kf;
+    o2[i] = lower ? qh[i] * f[i] : kf;
   }
-  KR[p * 128 + x] = umma::pack8(ba);
-  QK[p * 128 + x] = umma::pack8(qh);
+  KR[p * 128 + x] = umma::pack8(o1);
+  QK[p * 128 + x] = umma::pack8(o2);
+}
+__device__ __forceinline__ void build_level_piece(const Rows& r, const float* LAM, int s, int x, int p, uint4* KR, uint4* QK) {
+  float kh[8], ba[8], qh[8];
+  khat8(r, x, p, kh);              // all three loads are issued before the role is looked at
+  bact8(r, x, p, ba);
+  qhat8(r, x, p, qh);
+  build_level_from(kh, ba, qh, LAM, s, x, p, KR, QK);
 }
 
 // Which level owns entry (row block bi, column block bj) of the strictly lower block triangle:

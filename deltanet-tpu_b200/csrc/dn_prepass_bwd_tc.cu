@@ -138,30 +138,6 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
     chunk_flags(a.seg, g, b, c_idx, is_new, all_same);
     __syncthreads();
     const int seg0 = seg_s[0], segL = seg_s[C - 1];
-    {
-      // everything this item streams from global memory is asked into L2 now: the later phases then
-      // pay an L2 hit instead of a DRAM access for their first touch
-      const int rows = g.L - t0 < C ? g.L - t0 : C;
-      const size_t tok0 = (size_t)b * g.L + t0;
-      const size_t qsz = dt_size(g.qkv_dt), gsz = dt_size(g.gate_dt);
-      if (tid == 0) {
-        umma::prefetch_l2_bulk(a.dV + ibase * CV, (uint32_t)(CV * 4));
-        umma::prefetch_l2_bulk(a.dH + ibase * K * VW, (uint32_t)(K * VW * 4));
-        umma::prefetch_l2_bulk(a.res.T + ibase * CC, (uint32_t)(CC * 4));
-      }
-      const int hq = h / g.qk_div;
-      umma::prefetch_rows_l2<NT>(reinterpret_cast<const uint8_t*>(a.d_out) + (tok0 * g.Hv * g.V + (size_t)h * VW) * qsz, rows, (size_t)g.Hv * g.V * qsz, (int)(VW * qsz));
-      umma::prefetch_rows_l2<NT>(reinterpret_cast<const uint8_t*>(a.v) + (tok0 * g.Hv * g.V + (size_t)h * VW) * qsz, rows, (size_t)g.Hv * g.V * qsz, (int)(VW * qsz));
-      umma::prefetch_rows_l2<NT>(reinterpret_cast<const uint8_t*>(a.q) + (tok0 * g.Hk + hq) * K * qsz, rows, (size_t)g.Hk * K * qsz, (int)(K * qsz));
-      umma::prefetch_rows_l2<NT>(reinterpret_cast<const uint8_t*>(a.k) + (tok0 * g.Hk + hq) * K * qsz, rows, (size_t)g.Hk * K * qsz, (int)(K * qsz));
-      umma::prefetch_rows_l2<NT>(reinterpret_cast<const uint8_t*>(a.gg) + (tok0 * g.gH + g.gate_head(h, g.gH)) * g.gC * gsz, rows, (size_t)g.gH * g.gC * gsz, (int)(g.gC * gsz));
-      umma::prefetch_rows_l2<NT>(reinterpret_cast<const uint8_t*>(a.b) + (tok0 * g.bH + g.gate_head(h, g.bH)) * g.bC * gsz, rows, (size_t)g.bH * g.bC * gsz, (int)(g.bC * gsz));
-      if (g.wC != 1) {
-        const int hv0 = h * VW / g.V;
-        umma::prefetch_rows_l2<NT>(reinterpret_cast<const uint8_t*>(a.w) + (tok0 * g.wH + g.w_head(hv0)) * g.wC * gsz, rows, (size_t)g.wH * g.wC * gsz, (int)((g.wH == g.Hv ? VW : g.V) * gsz));
-      }
-    }
-
     const Rows r = make_rows<CF>(g, a.q, a.k, a.gg, a.b, b, h, t0, rq_s, rk_s);
     const int qdt = r.qkv_dt, gdt = r.gate_dt;           // compile-time constants in the fixed modes
     const int wC = CF::fixed ? g.V : g.wC;

@@ -143,28 +143,18 @@ __global__ void __launch_bounds__(NT, 1) prepass_fwd_tc_kernel(PrepassFwdArgs a,
 
     DN_MARK(0);
     for (int i = tid; i < C; i += NT) seg_s[i] = seg_at(a.seg, b, t0 + i, g.L);
-    {
-      // the rows of v and w are needed only at the end of the item: ask them into L2 now
-      const int rows = g.L - t0 < C ? g.L - t0 : C;
-      const size_t tok0 = (size_t)b * g.L + t0;
-      const size_t qsz = dt_size(g.qkv_dt), gsz = dt_size(g.gate_dt);
-      umma::prefetch_rows_l2<NT>(reinterpret_cast<const uint8_t*>(a.v) + (tok0 * g.Hv * g.V + (size_t)h * VW) * qsz, rows, (size_t)g.Hv * g.V * qsz, (int)(VW * qsz));
-      if (g.wC != 1) {
-        const int hv0 = h * VW / g.V;
-        umma::prefetch_rows_l2<NT>(reinterpret_cast<const uint8_t*>(a.w) + (tok0 * g.wH + g.w_head(hv0)) * g.wC * gsz, rows, (size_t)g.wH * g.wC * gsz, (int)((g.wH == g.Hv ? VW : g.V) * gsz));
-      }
-    }
     const Rows r = make_rows<CF>(g, a.q, a.k, a.gg, a.b, b, h, t0, rq_s, rk_s);
     const int qdt = r.qkv_dt, gdt = r.gate_dt;           // compile-time constants in the fixed modes
     const int wC = CF::fixed ? g.V : g.wC;
-    row_norms_8x4(r, myrow, lgrp, rq_s, rk_s);
     __syncthreads();
     const int seg0 = seg_s[0], segL = seg_s[C - 1];
-    lambda_scan_512(r, seg_s, LAM, TOTL, reset_s);
+    row_norms_8x4(r, myrow, lgrp, rq_s, rk_s);             // no barrier in between: the loads of q, k and g
+    lambda_scan_512(r, seg_s, LAM, TOTL, reset_s);         // are all in flight together
     __syncthreads();
 
     DN_MARK(1);
-    // ---- qe, ke, Lambda_end and the X = [first doc] beta e^Lam operand image
+    // ---- qe, ke, Lambda_end, the X = [first doc] beta e^Lam operand image, and (same pass over q, k,
+    //      b) the images of the first level
     {
       const int x = myrow;
       const bool first = seg_s[x] == seg0, last = seg_s[x] == segL;
@@ -191,6 +181,7 @@ __global__ void __launch_bounds__(NT, 1) prepass_fwd_tc_kernel(PrepassFwdArgs a,
 #pragma unroll
         for (int i = 0; i < 8; ++i) o[i] = first ? be[i] * kh[i] * el[i] : 0.f;
         XI[p * 128 + x] = umma::pack8(o);
+        build_level_from(kh, be, qh, LAM, 16, x, p, KR, QK);
       }
       if (tid < K) a.res.lam_end[ibase * K + tid] = LAM[(C - 1) * LP + tid];
     }
@@ -236,8 +227,7 @@ __global__ void __launch_bounds__(NT, 1) prepass_fwd_tc_kernel(PrepassFwdArgs a,
       }
       umma::tc_fence_before();
     };
-    build(0);
-    for (int lv = 0; lv < 3; ++lv) {
+    for (int lv = 0; lv < 3; ++lv) {                       // (the images of level 0 were built above)
       const uint32_t tcol = (uint32_t)((lv & 1) * 256);
       umma::pre_issue_sync();
       umma::issue<128, false, false>(cx, KR, KR, K, tcol, false);          // A: KR KR^T

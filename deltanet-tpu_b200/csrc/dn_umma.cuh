@@ -127,21 +127,7 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int PENDING>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(PENDING) : "memory"); }
 
-// ---- L2 prefetch ---------------------------------------------------------------------------
-// One 128-byte line / a contiguous range (bytes a multiple of 16, address 16-byte aligned) into L2.
-__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
-__device__ __forceinline__ void prefetch_l2_bulk(const void* p, uint32_t bytes) {
-  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
-}
-// Rows of a strided tensor: `rows` rows of `row_bytes` bytes, `pitch_bytes` apart, one line per thread step.
-template <int NT>
-__device__ __forceinline__ void prefetch_rows_l2(const void* base, int rows, size_t pitch_bytes, int row_bytes) {
-  const int lines = (row_bytes + 127) / 128;
-  for (int e = threadIdx.x; e < rows * lines; e += NT) {
-    const int r = e / lines, l = e - r * lines;
-    prefetch_l2(reinterpret_cast<const uint8_t*>(base) + (size_t)r * pitch_bytes + (size_t)l * 128);
-  }
-}
+// ---- predicated loads ------------------------------------------------------------------------
 // 16-byte global load through L2 only, skipped (zeros returned) when `pred` is false: no branch, so
 // the loads of an unrolled group stay back to back
 __device__ __forceinline__ float4 ldcg_pred(const float4* p, bool pred) {
