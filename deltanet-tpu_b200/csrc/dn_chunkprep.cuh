@@ -197,7 +197,7 @@ __device__ __forceinline__ void decay8(const float* la, const float* lb, float (
   const float4 b0 = *reinterpret_cast<const float4*>(lb), b1 = *reinterpret_cast<const float4*>(lb + 4);
   const float d[8] = {a0.x - b0.x, a0.y - b0.y, a0.z - b0.z, a0.w - b0.w, a1.x - b1.x, a1.y - b1.y, a1.z - b1.z, a1.w - b1.w};
 #pragma unroll
-  for (int i = 0; i < 8; ++i) f[i] = exp2f(fminf(d[i], 0.f) * DN_LOG2E);
+  for (int i = 0; i < 8; ++i) f[i] = umma::ex2_fast(fminf(d[i], 0.f) * DN_LOG2E);
 }
 
 // Operand images of level s (pairs of adjacent s-row blocks; reference row = first row of the

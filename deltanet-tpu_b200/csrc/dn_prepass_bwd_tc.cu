@@ -423,7 +423,7 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
           float qh = (qr[i] * rq) * r.scale, kh = kr[i];
           if (r.round_in) qh = bf16r(qh);
           if (l2) { kh *= rk; if (r.round_in) kh = bf16r(kh); }
-          const float el = expf(fminf(lam[i], 0.f)), eke = expf(fminf(lend[i] - lam[i], 0.f));
+          const float el = umma::exp_neg(fminf(lam[i], 0.f)), eke = umma::exp_neg(fminf(lend[i] - lam[i], 0.f));
           const float be = ba[i] * kh;
           const float X = first ? be * el : 0.f, qe = first ? qh * el : 0.f, ke = last ? kh * eke : 0.f;
           const float dbeta = dbp[i] + (first ? dx[i] * el : 0.f);

@@ -171,12 +171,12 @@ __global__ void __launch_bounds__(NT, 1) prepass_fwd_tc_kernel(PrepassFwdArgs a,
         *reinterpret_cast<float4*>(lend + 4) = *reinterpret_cast<const float4*>(LAM + (C - 1) * LP + 8 * p + 4);
         float el[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) el[i] = expf(fminf(lam[i], 0.f));
+        for (int i = 0; i < 8; ++i) el[i] = umma::exp_neg(fminf(lam[i], 0.f));
 #pragma unroll
         for (int i = 0; i < 8; ++i) o[i] = first ? qh[i] * el[i] : 0.f;
         QEimg[p * 128 + x] = umma::pack8(o);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) o[i] = last ? kh[i] * expf(fminf(lend[i] - lam[i], 0.f)) : 0.f;
+        for (int i = 0; i < 8; ++i) o[i] = last ? kh[i] * umma::exp_neg(fminf(lend[i] - lam[i], 0.f)) : 0.f;
         KEimg[p * 128 + x] = umma::pack8(o);
 #pragma unroll
         for (int i = 0; i < 8; ++i) o[i] = first ? be[i] * kh[i] * el[i] : 0.f;
