@@ -96,7 +96,7 @@ static void residual_sizes(const Geo& g, size_t sz[8]) {
   sz[4] = sz[0];
   sz[5] = n * g.K * sizeof(float);
   sz[6] = keep ? n * g.C * g.C * sizeof(float) : 0;
-  sz[7] = keep ? n * g.K * g.Vw * sizeof(float) : 0;
+  sz[7] = keep ? n * g.K * g.Vw * (sizeof(float) + (g.img ? 2 : 0)) : 0;      // + the bf16 image copy (states_img)
 }
 
 size_t dn_residual_bytes(const dn_shape* s) {
@@ -221,6 +221,7 @@ int dn_state_bwd(const dn_shape* s, const dn_residuals* res, const int32_t* seg,
   int rc = make_geo(s, &g);
   if (rc) return rc;
   if (!res || !d_out || !dV || !dH) return DN_ERR_NULL_POINTER;
+  if (g.img && !res->states) return DN_ERR_NULL_POINTER;      // dLambda_end is reduced in the reverse chain on this path
   StateArgs a{};
   a.g = g; a.res = *res; a.seg = seg; a.d_out = d_out; a.d_final = d_final_state;
   a.dV = dV; a.dH = dH; a.d_init = (g.flags & DN_HAS_INIT) ? d_init : nullptr;

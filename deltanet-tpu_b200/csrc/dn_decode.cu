@@ -206,6 +206,222 @@ __global__ void __launch_bounds__(NTH) decode_kernel(DecodeArgs a) {
   for (int r = 0; r < R; ++r) store_row<CPT>(Sout + (size_t)(rg + r * RG) * V + col0, S[r]);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Bulk-copy pipeline for the common serving case: K = V = 128, bf16 state in and out, bf16 q/k/v,
+// fp32 per-channel gates.  The (128,128) bf16 state of one (sequence, value head) is 32 KB of
+// contiguous global memory, so it moves with ONE bulk asynchronous copy each way
+// (cp.async.bulk, completion on an mbarrier / a bulk group); the token vectors ride on the same
+// barrier.  A persistent CTA keeps a ring of STAGES tiles: while tile i is updated in place in
+// shared memory, tiles i+1 .. i+STAGES-1 are in flight and tile i-1 drains to global memory.  No
+// register ever holds a byte that is waiting for memory, which is what limited the slab kernel.
+// Every barrier wait is bounded; a wait that gives up sets the library's error word and the CTA
+// stops taking tiles.
+namespace bulk {
+
+constexpr int NT = 256, STAGES = 3, KD = 128, VD = 128;
+constexpr int OFF_Q = KD * VD * 2, OFF_K = OFF_Q + 256, OFF_V = OFF_K + 256, OFF_G = OFF_V + 256,
+              OFF_B = OFF_G + 512, OFF_W = OFF_B + 512, STAGE_BYTES = OFF_W + 512;     // 35072, a multiple of 128
+constexpr uint32_t TX_BYTES = STAGE_BYTES;
+constexpr uint32_t SPIN = 1u << 22;
+
+__device__ __forceinline__ uint32_t s32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void bar_init(uint64_t* b, uint32_t n) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s32(b)), "r"(n) : "memory");
+}
+__device__ __forceinline__ void bar_expect(uint64_t* b, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(s32(b)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool bar_wait(uint64_t* b, uint32_t parity) {
+  for (uint32_t it = 0; it < SPIN; ++it) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(s32(b)), "r"(parity) : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* b) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(s32(dst)), "l"(src), "r"(bytes), "r"(s32(b)) : "memory");
+}
+__device__ __forceinline__ void bulk_store(void* dst, const void* src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(s32(src)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void fence_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__global__ void __launch_bounds__(NT, 2) decode_bulk_kernel(DecodeArgs a, int tiles, int* err) {
+  extern __shared__ __align__(128) uint8_t ring[];
+  __shared__ __align__(8) uint64_t full[STAGES];
+  __shared__ float qs[KD], ks[KD], dec[KD], beta[KD], wv[VD], vnew[VD];
+  __shared__ float red[NT / 32][VD];
+  __shared__ int dead_s;
+  const dn_decode_shape& s = a.s;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int G = s.Hv / s.Hk;
+  const bool l2 = s.flags & DN_QK_L2NORM, guard = s.flags & DN_STABILITY_GUARD;
+
+  auto issue = [&](int tile, int st) {               // one thread: the tile's state and token vectors
+    const int hv = tile % s.Hv, b = tile / s.Hv, hk = hv / G;
+    uint8_t* dst = ring + (size_t)st * STAGE_BYTES;
+    bar_expect(&full[st], TX_BYTES);
+    bulk_load(dst, reinterpret_cast<const __nv_bfloat16*>(a.state_in) + (size_t)tile * KD * VD, KD * VD * 2, &full[st]);
+    bulk_load(dst + OFF_Q, reinterpret_cast<const __nv_bfloat16*>(a.q) + ((size_t)b * s.Hk + hk) * KD, 256, &full[st]);
+    bulk_load(dst + OFF_K, reinterpret_cast<const __nv_bfloat16*>(a.k) + ((size_t)b * s.Hk + hk) * KD, 256, &full[st]);
+    bulk_load(dst + OFF_V, reinterpret_cast<const __nv_bfloat16*>(a.v) + ((size_t)b * s.Hv + hv) * VD, 256, &full[st]);
+    bulk_load(dst + OFF_G, reinterpret_cast<const float*>(a.g) + ((size_t)b * s.g_heads + dec_gate_head(hv, s.g_heads, s.Hk, s.Hv)) * KD, 512, &full[st]);
+    bulk_load(dst + OFF_B, reinterpret_cast<const float*>(a.b) + ((size_t)b * s.b_heads + dec_gate_head(hv, s.b_heads, s.Hk, s.Hv)) * KD, 512, &full[st]);
+    bulk_load(dst + OFF_W, reinterpret_cast<const float*>(a.w) + ((size_t)b * s.w_heads + dec_gate_head(hv, s.w_heads, s.Hk, s.Hv)) * VD, 512, &full[st]);
+  };
+
+  if (tid == 0) {
+    for (int i = 0; i < STAGES; ++i) bar_init(&full[i], 1);
+    dead_s = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  const int first = blockIdx.x, stride = gridDim.x;
+  if (tid == NT - 1)
+    for (int i = 0; i < STAGES - 1; ++i)
+      if (first + i * stride < tiles) issue(first + i * stride, i);
+
+  const int vc = tid & 15, rg = tid >> 4;              // 8 columns, rows rg + 16 r
+  int it = 0;
+  for (int tile = first; tile < tiles; tile += stride, ++it) {
+    const int st = it % STAGES;
+    const uint32_t parity = (uint32_t)(it / STAGES) & 1u;
+    if (!bar_wait(&full[st], parity)) { dead_s = 1; if (err) atomicExch(err, 1); }
+    __syncthreads();
+    if (dead_s) break;
+    uint8_t* buf = ring + (size_t)st * STAGE_BYTES;
+    const int hv = tile % s.Hv, b = tile / s.Hv;
+    const bool zero = a.reset && a.reset[b];
+
+    // ---- token vectors: q, k normalised (warps 0, 1), w*v (threads 128..255)
+    if (warp < 2) {
+      const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(buf + (warp == 0 ? OFF_Q : OFF_K));
+      float x[4], ss = 0.f;
+#pragma unroll
+      for (int u = 0; u < 4; ++u) { x[u] = __bfloat162float(src[lane + 32 * u]); ss += x[u] * x[u]; }
+      ss = warp_sum(ss);
+      const float r = l2 ? 1.f / sqrtf(ss + 1e-6f) : 1.f;
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (warp == 0) qs[lane + 32 * u] = x[u] * r * s.scale;
+        else ks[lane + 32 * u] = x[u] * r;
+      }
+    } else if (tid >= 128) {
+      const int j = tid - 128;
+      wv[j] = reinterpret_cast<const float*>(buf + OFF_W)[j] * __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(buf + OFF_V)[j]);
+    }
+    __syncthreads();
+    if (tid < KD) {
+      float gg = fminf(reinterpret_cast<const float*>(buf + OFF_G)[tid], 0.f), bb = reinterpret_cast<const float*>(buf + OFF_B)[tid];
+      if (guard) { bb = fmaxf(bb, 0.f); gg = fminf(gg, -1e-6f); }
+      dec[tid] = expf(gg);
+      beta[tid] = bb * ks[tid];
+    }
+    // refill the stage that tile it-1 used: its store (issued a while ago) must have finished reading
+    // shared memory
+    if (tid == NT - 1) {
+      bulk_wait_read<0>();
+      const int nxt = tile + (STAGES - 1) * stride;
+      if (nxt < tiles) issue(nxt, (it + STAGES - 1) % STAGES);
+    }
+    __syncthreads();
+
+    // ---- decay, erase projection e = Sd^T beta
+    uint4* tile4 = reinterpret_cast<uint4*>(buf);          // row kk: 16 vectors of 8 columns
+    float S[8][8], part[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) part[c] = 0.f;
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+      const int kk = rg + 16 * r;
+      const uint4 v = tile4[kk * 16 + vc];
+      const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+      const float d = dec[kk], be = beta[kk];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {                          // a reset sequence starts from zeros whatever the buffer holds
+        S[r][2 * j] = zero ? 0.f : __uint_as_float(u[j] << 16) * d;
+        S[r][2 * j + 1] = zero ? 0.f : __uint_as_float(u[j] & 0xffff0000u) * d;
+      }
+#pragma unroll
+      for (int c = 0; c < 8; ++c) part[c] = fmaf(be, S[r][c], part[c]);
+    }
+#pragma unroll
+    for (int c = 0; c < 8; ++c) part[c] += __shfl_xor_sync(0xffffffffu, part[c], 16);    // the warp's two row groups
+    if (lane < 16) {
+#pragma unroll
+      for (int c = 0; c < 8; ++c) red[warp][8 * vc + c] = part[c];
+    }
+    __syncthreads();
+    if (tid < VD) {
+      float e = 0.f;
+#pragma unroll
+      for (int w8 = 0; w8 < NT / 32; ++w8) e += red[w8][tid];
+      vnew[tid] = wv[tid] - e;
+    }
+    __syncthreads();
+    // ---- rank-one write, output projection o = S'^T q, new state back into the tile
+    float vn[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) { vn[c] = vnew[8 * vc + c]; part[c] = 0.f; }
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+      const int kk = rg + 16 * r;
+      const float kx = ks[kk], qx = qs[kk];
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        S[r][c] = fmaf(kx, vn[c], S[r][c]);
+        part[c] = fmaf(qx, S[r][c], part[c]);
+      }
+      uint32_t u[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        __nv_bfloat162 h2 = __floats2bfloat162_rn(S[r][2 * j], S[r][2 * j + 1]);
+        u[j] = *reinterpret_cast<uint32_t*>(&h2);
+      }
+      tile4[kk * 16 + vc] = make_uint4(u[0], u[1], u[2], u[3]);
+    }
+#pragma unroll
+    for (int c = 0; c < 8; ++c) part[c] += __shfl_xor_sync(0xffffffffu, part[c], 16);
+    if (lane < 16) {
+#pragma unroll
+      for (int c = 0; c < 8; ++c) red[warp][8 * vc + c] = part[c];
+    }
+    fence_async();                                           // the tile was written through the generic proxy
+    __syncthreads();
+    if (tid == NT - 1) {                                     // the thread that also waits on the bulk groups
+      bulk_store(reinterpret_cast<__nv_bfloat16*>(a.state_out) + (size_t)tile * KD * VD, buf, KD * VD * 2);
+      bulk_commit();
+    }
+    if (tid < VD) {
+      float o = 0.f;
+#pragma unroll
+      for (int w8 = 0; w8 < NT / 32; ++w8) o += red[w8][tid];
+      reinterpret_cast<__nv_bfloat16*>(a.out)[((size_t)b * s.Hv + hv) * VD + tid] = __float2bfloat16_rn(o);
+    }
+    // the next tile's first barrier orders these reads of red / vnew before they are rewritten
+  }
+  if (tid == NT - 1) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
+
+inline bool eligible(const DecodeArgs& a) {
+  const dn_decode_shape& s = a.s;
+  if (s.K != KD || s.V != VD) return false;
+  if (s.state_in_dtype != DN_BF16 || s.state_out_dtype != DN_BF16 || s.qkv_dtype != DN_BF16 || s.gate_dtype != DN_F32) return false;
+  if (s.g_cols != KD || s.b_cols != KD || s.w_cols != VD) return false;
+  const void* ptrs[] = {a.q, a.k, a.v, a.g, a.b, a.w, a.state_in, a.state_out};
+  for (const void* p : ptrs)
+    if (reinterpret_cast<uintptr_t>(p) & 15) return false;
+  return true;
+}
+
+}  // namespace bulk
+
 // Frobenius cap of the returned state (gdn2.py:2484-2487): one CTA per (sequence, value head).
 template <typename SO>
 __global__ void __launch_bounds__(256) decode_cap_kernel(SO* state, int KV, float tau) {
@@ -242,6 +458,19 @@ int launch_decode(const dn_decode_shape& s, const void* q, const void* k, const 
                   const void* g, const void* b, const void* w, const void* state_in,
                   const uint8_t* reset, void* out, void* state_out, cudaStream_t st) {
   DecodeArgs a{s, q, k, v, g, b, w, state_in, reset, out, state_out};
+  if (bulk::eligible(a) && !force_simt()) {
+    const int tiles = s.B * s.Hv;
+    const int grid = tiles < 2 * 148 ? tiles : 2 * 148;
+    const size_t smem = (size_t)bulk::STAGES * bulk::STAGE_BYTES;
+    cudaFuncSetAttribute(bulk::decode_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    bulk::decode_bulk_kernel<<<grid, bulk::NT, smem, st>>>(a, tiles, device_error_ptr());
+    if (cudaGetLastError() != cudaSuccess) return DN_ERR_CUDA_LAUNCH;
+    if (s.flags & DN_STABILITY_GUARD) {
+      decode_cap_kernel<__nv_bfloat16><<<s.B * s.Hv, 256, 0, st>>>(reinterpret_cast<__nv_bfloat16*>(a.state_out), s.K * s.V, s.stability_tau);
+      if (cudaGetLastError() != cudaSuccess) return DN_ERR_CUDA_LAUNCH;
+    }
+    return DN_OK;
+  }
   const bool ib = s.state_in_dtype == DN_BF16, ob = s.state_out_dtype == DN_BF16;
   if (ib && ob) return launch_decode_t<__nv_bfloat16, __nv_bfloat16>(a, st);
   if (ib && !ob) return launch_decode_t<__nv_bfloat16, float>(a, st);

@@ -169,11 +169,11 @@ __global__ void __launch_bounds__(DN_THREADS, 1) prepass_bwd_kernel(PrepassBwdAr
         [&](int i, int j, float acc) { DM[i * C + j] = (i >= j && seg_s[i] == seg_s[j]) ? acc : 0.f; }, tile);
     // ---- dX = T^T dW, dY = T^T dV
     cta_gemm<false, true>(C, K, C,
-        [&](int i, int kk) { float t = T[(size_t)kk * C + i]; return ibf ? bf16r(t) : t; },
+        [&](int i, int kk) { float t = g.img ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(T)[rix(true, kk, i, C)]) : T[(size_t)kk * C + i]; return ibf ? bf16r(t) : t; },
         [&](int kk, int j) { float x = DW[kk * K + j]; return ibf ? bf16r(x) : x; },
         [&](int i, int j, float acc) { DX[i * K + j] = trunc ? bf16r(acc) : acc; }, tile);
     cta_gemm<false, true>(C, Vw, C,
-        [&](int i, int kk) { float t = T[(size_t)kk * C + i]; return ibf ? bf16r(t) : t; },
+        [&](int i, int kk) { float t = g.img ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(T)[rix(true, kk, i, C)]) : T[(size_t)kk * C + i]; return ibf ? bf16r(t) : t; },
         [&](int kk, int j) { float x = dV[(size_t)kk * Vw + j]; return ibf ? bf16r(x) : x; },
         [&](int i, int j, float acc) { DY[i * Vw + j] = trunc ? bf16r(acc) : acc; }, tile);
     // ---- dA = -(dX W^T + dY U^T), strictly lower and same document

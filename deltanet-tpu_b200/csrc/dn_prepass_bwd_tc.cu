@@ -147,9 +147,12 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
       BwdTcIo io;
       io.W = reinterpret_cast<const __nv_bfloat16*>(a.res.W) + ibase * CK;
       io.U = reinterpret_cast<const __nv_bfloat16*>(a.res.U) + ibase * CV;
-      io.S = a.res.states + ibase * K * VW;
-      io.dH = a.dH + ibase * K * VW;
-      io.dV = a.dV + ibase * CV; io.T = a.res.T + ibase * CC;
+      io.S = states_img(g, a.res.states) + ibase * K * VW;
+      io.dH = reinterpret_cast<const __nv_bfloat16*>(a.dH) + ibase * K * VW;
+      io.dV = reinterpret_cast<const __nv_bfloat16*>(a.dV) + ibase * CV;
+      io.T = reinterpret_cast<const __nv_bfloat16*>(a.res.T + ibase * CC);
+      io.slices = VW / 32;
+      io.dlend_part = dlend_part(g, const_cast<float*>(a.dH)) + ibase * (VW / 32) * K;
       io.lam_end = a.res.lam_end + ibase * K;
       io.d_out = a.d_out; io.qkv_dt = CF::fixed ? CF::qkv_dt : g.qkv_dt;
       io.dO_off = ((size_t)b * g.L + t0) * g.Hv * g.V + (size_t)h * VW;

@@ -6,19 +6,21 @@
 // and are drained one row per thread.  An image written once serves as a matrix and as its
 // transpose (the descriptor says which), which is why S, V_new, dV, W and U are staged only once
 // per use group:
-//   1. V_new = W (-S) + I U                  A = W (P), I (Y)   B = -S (X), U (Z) -> image Y
-//   2. dqe   = dO S^T ; dM = dO V_new^T      A = dO (Z)         B = -S (X), V_new (Y)
-//   3. dW    = -dV S^T                       A = dV (Z)         B = -S (X)        -> image P
+//   1. V_new = U - W S                       A = W (P)          B = S (X); U (Z) read by the drain -> image Y
+//   2. dqe   = dO S^T ; dM = dO V_new^T      A = dO (Z)         B = S (X), V_new (Y)
+//   3. dW    = -dV S^T                       A = dV (Z)         B = S (X)         -> image P
 //   4. dke   = V_new dH^T                    A = V_new (Y)      B = dH (X)
 //   5. dX    = T^T dW ; dY = T^T dV          A = T^T (Y)        B = dW (P), dV (Z) -> images Y', X
 //      (dY leaves the function as the image X: the caller forms dv, dw from it)
 //   6. dA    = -(dX W^T + dY U^T)            A = dX (Y'), dY (X)   B = W (P), U (Z)
 //
-// Global memory is touched in two patterns only.  Inputs are read by warps that cover 8 rows x 4
-// pieces of 8 elements per step (stage_coords), through the read-only path so that several loads
-// stay in flight.  fp32 results go to the per-CTA scratch in a PANEL layout, [column / 4][row][4]:
-// a thread that owns one row of tensor memory then writes 16 bytes next to its neighbours' and a
-// warp store covers 512 contiguous bytes.
+// Every operand except dO arrives as a bf16 operand image that its producer wrote in exactly this
+// layout (W, U: forward prepass; the chunk-entry state S: forward chain; dV, dH: reverse chain; T:
+// forward prepass), so staging is a contiguous asynchronous copy with no register in between.  dO is
+// the operator's row-major tensor: warps cover 8 rows x 4 pieces of 8 elements per step
+// (stage_coords).  fp32 results go to the per-CTA scratch in a PANEL layout, [column / 4][row][4]: a
+// thread that owns one row of tensor memory then writes 16 bytes next to its neighbours' and a warp
+// store covers 512 contiguous bytes.
 #pragma once
 #include "dn_common.cuh"
 #include "dn_umma.cuh"
@@ -32,7 +34,10 @@ __device__ __forceinline__ int p4f(int row, int col) { return ((((col >> 2) << 7
 
 struct BwdTcIo {
   const __nv_bfloat16 *W, *U;          // this item's (128,128) and (128,VW) tiles, image layout
-  const float *S, *dH, *dV, *T;        // this item's fp32 arrays: (128,VW), (128,VW), (128,VW), (128,128)
+  const __nv_bfloat16 *S, *dH, *dV;    // this item's (128,VW) images: chunk-entry state, state cotangent, dV
+  const __nv_bfloat16* T;              // this item's (128,128) image
+  const float* dlend_part;             // this item's (slices, 128) partial sums of sum_v dH * S
+  int slices;
   const float* lam_end;                // this item's (128) log-decay to the chunk end
   const void* d_out;                   // whole tensor
   int qkv_dt;
@@ -46,31 +51,18 @@ struct BwdTcIo {
   bool trunc;
 };
 
-// Operand staging.  A warp covers 8 rows x 4 panels per step: its 32 global loads fall in 8 row
+// dO staging.  A warp covers 8 rows x 4 panels per step: its 32 global loads fall in 8 row
 // segments of 128 B (fp32) or 64 B (bf16), and each quarter-warp writes 8 consecutive rows of one
-// panel (128 contiguous bytes of shared memory).  With 512 threads and 128 rows a thread keeps the
-// same row over all its steps: row = 8 * warp + (lane & 7).
+// panel (128 contiguous bytes of shared memory).
 template <int R>
 __device__ __forceinline__ void stage_coords(int e, int& p, int& x) {
   const int lane = e & 31, w = e >> 5;
   x = (w % (R / 8)) * 8 + (lane & 7);
   p = (w / (R / 8)) * 4 + (lane >> 3);
 }
-template <int R, int PANELS, int NT, bool NEGATE = false>
-__device__ __forceinline__ void stage_f32(uint4* dst, const float* src, int pitch) {
-  static_assert((PANELS * R) % NT == 0, "whole passes");
-#pragma unroll 8
-  for (int it = 0; it < PANELS * R / NT; ++it) {
-    int p, x;
-    stage_coords<R>(it * NT + threadIdx.x, p, x);
-    uint4 v = umma::ld8_f32_ro(src + (size_t)x * pitch + 8 * p);
-    if (NEGATE) { v.x ^= 0x80008000u; v.y ^= 0x80008000u; v.z ^= 0x80008000u; v.w ^= 0x80008000u; }
-    dst[p * R + x] = v;
-  }
-}
-// W and U lie in global memory as operand images already: asynchronous 16-byte copies of a
-// contiguous range, no registers.  The caller waits (umma::cp_async_wait<0>) before the operands are
-// handed to the tensor core.
+// An operand that lies in global memory as its image: asynchronous 16-byte copies of a contiguous
+// range, no registers.  The caller waits (umma::cp_async_wait<0>) before the operands are handed to
+// the tensor core.
 template <int N_U4, int NT>
 __device__ __forceinline__ void copy_image_async(uint4* dst, const __nv_bfloat16* src) {
   static_assert(N_U4 % NT == 0, "whole passes");
@@ -82,7 +74,6 @@ __device__ __forceinline__ void copy_image_async(uint4* dst, const __nv_bfloat16
 
 template <int VW, int NT>
 __device__ __forceinline__ void bwd_gemms_tc(umma::Ctx& cx, uint8_t* img, const BwdTcIo& io) {
-  static_assert(NT == 512, "a thread keeps one row while staging");
   constexpr int SLOT = 128 * VW * 2;
   uint4* X = reinterpret_cast<uint4*>(img);
   uint4* Y = reinterpret_cast<uint4*>(img + SLOT);
@@ -99,29 +90,34 @@ __device__ __forceinline__ void bwd_gemms_tc(umma::Ctx& cx, uint8_t* img, const 
   float4* DA4 = reinterpret_cast<float4*>(io.DA);
 
   DN_MARK(1);
-  // ---- 1. V_new = U - W S, as W (-S) + I U so that U arrives through the tensor core as well.
-  //         The image X holds -S from here to step 3.
+  // ---- 1. V_new = U - W S: the product in tensor memory, U taken from its image by the drain
   copy_image_async<128 * 16, NT>(P, io.W);
+  copy_image_async<128 * PV, NT>(X, io.S);
   copy_image_async<128 * PV, NT>(Z, io.U);
-  stage_f32<128, PV, NT, true>(X, io.S, VW);
-  for (int e = threadIdx.x; e < 128 * 16; e += NT) {          // identity, K-major
-    const int p = e >> 7, x = e & 127;
-    uint32_t w[4] = {0u, 0u, 0u, 0u};
-    if ((x >> 3) == p) w[(x & 7) >> 1] = 0x3F80u << (16 * (x & 1));
-    Y[e] = make_uint4(w[0], w[1], w[2], w[3]);
+  // dLambda_end = [one doc] exp(Lambda_end) sum_v dH * S  (gdn2.py:759-762) from the reverse chain's
+  // per-slice partial sums, added in a fixed order
+  if (threadIdx.x < 128) {
+    float acc = 0.f;
+    for (int sl = 0; sl < io.slices; ++sl) acc += __ldg(io.dlend_part + sl * 128 + threadIdx.x);
+    io.dlend_s[threadIdx.x] = io.all_same ? acc * expf(fminf(__ldg(io.lam_end + threadIdx.x), 0.f)) : 0.f;
   }
   umma::cp_async_wait<0>();
   umma::pre_issue_sync();
   umma::issue<VW, false, true>(cx, P, X, 128, 0, false);
-  umma::issue<VW, false, true>(cx, Y, Z, 128, 0, true);
   umma::commit_wait(cx);
   umma::drain<NT, VW>(cx, 0, [&](int row, int col, const float (&v)[16]) {
-    Y[(col / 8) * 128 + row] = umma::pack8p(v);
-    Y[(col / 8 + 1) * 128 + row] = umma::pack8p(v + 8);
+    float u0[8], u1[8];
+    umma::unpack8(Z[(col / 8) * 128 + row], u0);
+    umma::unpack8(Z[(col / 8 + 1) * 128 + row], u1);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { u0[i] -= v[i]; u1[i] -= v[8 + i]; }
+    Y[(col / 8) * 128 + row] = umma::pack8(u0);
+    Y[(col / 8 + 1) * 128 + row] = umma::pack8(u1);
   });
+  __syncthreads();                                // every row of U has been read before dO overwrites Z
 
   DN_MARK(2);
-  // ---- 2. dqe = dO S^T (= -(dO X^T)), dM = dO V_new^T
+  // ---- 2. dqe = dO S^T, dM = dO V_new^T
   if (io.qkv_dt == DN_BF16) {
 #pragma unroll
     for (int it = 0; it < PV * 128 / NT; ++it) {
@@ -149,9 +145,10 @@ __device__ __forceinline__ void bwd_gemms_tc(umma::Ctx& cx, uint8_t* img, const 
   umma::issue<128, false, false>(cx, Z, X, VW, 256, false);
   umma::issue<128, false, false>(cx, Z, Y, VW, 384, false);
   umma::commit_wait(cx);
+  copy_image_async<128 * PV, NT>(Z, io.dV);          // dO has been consumed: dV for step 3 travels during the drains
   umma::drain<NT, 128>(cx, 256, [&](int row, int col, const float (&v)[16]) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) DQE4[p4v(row, col + 4 * i)] = make_float4(-v[4 * i], -v[4 * i + 1], -v[4 * i + 2], -v[4 * i + 3]);
+    for (int i = 0; i < 4; ++i) DQE4[p4v(row, col + 4 * i)] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
   });
   umma::drain<NT, 128>(cx, 384, [&](int row, int col, const float (&v)[16]) {
     float m[16];
@@ -162,41 +159,27 @@ __device__ __forceinline__ void bwd_gemms_tc(umma::Ctx& cx, uint8_t* img, const 
   });
 
   DN_MARK(3);
-  // ---- 3. dW = -dV S^T = dV X^T (kept only as the operand image of step 5)
-  stage_f32<128, PV, NT>(Z, io.dV, VW);
+  // ---- 3. dW = -dV S^T (kept only as the operand image of step 5)
+  umma::cp_async_wait<0>();
   umma::pre_issue_sync();
   umma::issue<128, false, false>(cx, Z, X, VW, 0, false);
   umma::commit_wait(cx);
+  copy_image_async<128 * PV, NT>(X, io.dH);          // S has been consumed: dH for step 4 travels during the drain
   umma::drain<NT, 128>(cx, 0, [&](int row, int col, const float (&v)[16]) {
-    P[(col / 8) * 128 + row] = umma::pack8p(v);
-    P[(col / 8 + 1) * 128 + row] = umma::pack8p(v + 8);
+    float n[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) n[i] = -v[i];
+    P[(col / 8) * 128 + row] = umma::pack8p(n);
+    P[(col / 8 + 1) * 128 + row] = umma::pack8p(n + 8);
   });
 
   DN_MARK(4);
-  // ---- 4. dke = V_new dH^T.  While dH is staged, the same threads read S once more in fp32 and
-  //         reduce dLambda_end = [one doc] exp(Lambda_end) sum_v dH * S  (gdn2.py:759-762): a thread
-  //         keeps one row, the four threads of a row sit 8 lanes apart.
-  {
-    float part = 0.f;
-    int row = 0;
-#pragma unroll 4
-    for (int it = 0; it < PV * 128 / NT; ++it) {
-      int p, x;
-      stage_coords<128>(it * NT + threadIdx.x, p, x);
-      row = x;
-      const float4* ph = reinterpret_cast<const float4*>(io.dH + (size_t)x * VW + 8 * p);
-      const float4* ps = reinterpret_cast<const float4*>(io.S + (size_t)x * VW + 8 * p);
-      const float4 h0 = __ldg(ph), h1 = __ldg(ph + 1), s0 = __ldg(ps), s1 = __ldg(ps + 1);
-      part += h0.x * s0.x + h0.y * s0.y + h0.z * s0.z + h0.w * s0.w + h1.x * s1.x + h1.y * s1.y + h1.z * s1.z + h1.w * s1.w;
-      X[p * 128 + x] = make_uint4(umma::pack2(h0.x, h0.y), umma::pack2(h0.z, h0.w), umma::pack2(h1.x, h1.y), umma::pack2(h1.z, h1.w));
-    }
-    part += __shfl_xor_sync(0xffffffffu, part, 8);
-    part += __shfl_xor_sync(0xffffffffu, part, 16);
-    if ((threadIdx.x & 31) < 8) io.dlend_s[row] = io.all_same ? part * expf(fminf(__ldg(io.lam_end + row), 0.f)) : 0.f;
-  }
+  // ---- 4. dke = V_new dH^T
+  umma::cp_async_wait<0>();
   umma::pre_issue_sync();
   umma::issue<128, false, false>(cx, Y, X, VW, 128, false);
   umma::commit_wait(cx);
+  copy_image_async<128 * 16, NT>(Y, io.T);            // V_new has been consumed: T for step 5
   umma::drain<NT, 128>(cx, 128, [&](int row, int col, const float (&v)[16]) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) DKE4[p4v(row, col + 4 * i)] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
@@ -204,11 +187,13 @@ __device__ __forceinline__ void bwd_gemms_tc(umma::Ctx& cx, uint8_t* img, const 
 
   DN_MARK(5);
   // ---- 5. dX = T^T dW, dY = T^T dV
-  stage_f32<128, 16, NT>(Y, io.T, 128);
+  umma::cp_async_wait<0>();
   umma::pre_issue_sync();
   umma::issue<128, true, true>(cx, Y, P, 128, 0, false);
   umma::issue<VW, true, true>(cx, Y, Z, 128, 256, false);
   umma::commit_wait(cx);
+  copy_image_async<128 * 16, NT>(P, io.W);            // dW and dV have been consumed: W, U for step 6
+  copy_image_async<128 * PV, NT>(Z, io.U);
   umma::drain<NT, 128>(cx, 0, [&](int row, int col, const float (&v)[16]) {
     float r[16];
 #pragma unroll
@@ -226,8 +211,6 @@ __device__ __forceinline__ void bwd_gemms_tc(umma::Ctx& cx, uint8_t* img, const 
 
   DN_MARK(6);
   // ---- 6. dA = -(dX W^T + dY U^T), strictly lower and same document
-  copy_image_async<128 * 16, NT>(P, io.W);
-  copy_image_async<128 * PV, NT>(Z, io.U);
   umma::cp_async_wait<0>();
   umma::pre_issue_sync();
   umma::issue<128, false, false>(cx, Y2, P, 128, 0, false);

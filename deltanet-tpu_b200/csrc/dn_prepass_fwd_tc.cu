@@ -356,16 +356,18 @@ __global__ void __launch_bounds__(NT, 1) prepass_fwd_tc_kernel(PrepassFwdArgs a,
     merge_level<16>(As, Ts, Tm);
     merge_level<32>(As, Ts, Tm);
     merge_level<64>(As, Ts, Tm);
-    if (a.res.T) {
-      float4* Tg = reinterpret_cast<float4*>(a.res.T + ibase * C * C);
-      for (int e = tid; e < C * C / 4; e += NT) Tg[e] = *reinterpret_cast<const float4*>(Ts + (e >> 5) * AP + 4 * (e & 31));
-    }
-
     DN_MARK(9);
     // ---- W = T X, U = T Y on the tensor cores
-    for (int e = tid; e < IMG; e += NT) {                       // T as K-major A: piece (p = j/8, x = i)
-      const int p = e >> 7, x = e & 127;
-      TI[e] = umma::ld8_f32(Ts + x * AP + 8 * p);
+    {
+      // T as K-major A: piece (p = j/8, x = i).  The same image is the residual the backward reads
+      // (bf16, in the first half of T's fp32-sized slot): it rounds T to bf16 there anyway.
+      uint4* Tg = a.res.T ? reinterpret_cast<uint4*>(a.res.T + ibase * C * C) : nullptr;
+      for (int e = tid; e < IMG; e += NT) {
+        const int p = e >> 7, x = e & 127;
+        const uint4 v = umma::ld8_f32(Ts + x * AP + 8 * p);
+        TI[e] = v;
+        if (Tg) Tg[e] = v;
+      }
     }
     {                                                           // Y = w*v as MN-major B
       const int x = myrow, t = t0 + x;

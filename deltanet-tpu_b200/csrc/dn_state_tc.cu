@@ -145,6 +145,11 @@ __global__ void __launch_bounds__(128, 1) state_fwd_tc_kernel(StateArgs a) {
       for (int j = 0; j < VS / 4; ++j) dst[j] = make_float4(S[4 * j], S[4 * j + 1], S[4 * j + 2], S[4 * j + 3]);
     }
     stage_rows<VS>(sS, row, S);
+    if (a.states && g.img) {                            // the same bf16 rows, as an operand image for the backward
+      uint4* simg = reinterpret_cast<uint4*>(const_cast<__nv_bfloat16*>(states_img(g, a.states)) + item * K * Vw) + (size_t)(v0 / 8) * 128 + row;
+#pragma unroll
+      for (int p = 0; p < VS / 8; ++p) simg[p * 128] = sS[p * 128 + row];
+    }
     uint4 ureg[VS / 8];
     if (Ug) {
       if (g.img) {
@@ -255,6 +260,8 @@ __global__ void __launch_bounds__(128, 1) state_bwd_tc_kernel(StateArgs a) {
   uint4* sdO = sW + TILE_U4;
   uint4* sdH = sdO + (VS / 8) * 128;
   uint4* sdV = sdH + (VS / 8) * 128;
+  float4* sSl = reinterpret_cast<float4*>(sdV + (VS / 8) * 128) + row;   // this thread's row of S (image path): piece j at sSl[j * 128]
+  const bool img = g.img;
   if (row == 0) { umma::mbar_init(&bar, 1); umma::fence_mbar_init(); }
   if (warp == 0) umma::tmem_alloc(&tmem_base, tmem_cols(VS));
   umma::tc_fence_before();
@@ -272,8 +279,16 @@ __global__ void __launch_bounds__(128, 1) state_bwd_tc_kernel(StateArgs a) {
   float* carry = a.carry ? a.carry + (((size_t)b * g.H + h) * K + row) * Vw + v0 : nullptr;
   const size_t last = item0 + ce - 1;
 
+  // image path: the thread's own row of the chunk-entry state (fp32) travels with M and ke, one chunk
+  // ahead, into a private strip of shared memory; it is needed for dLambda_end = sum_v dH * S
+  auto copy_S_row = [&](size_t it_) {
+    const float4* src = reinterpret_cast<const float4*>(a.res.states + it_ * K * Vw + (size_t)row * Vw + v0);
+#pragma unroll
+    for (int j = 0; j < VS / 4; ++j) umma::cp_async16(sSl + j * 128, src + j);
+  };
   copy_tile_async(sM, Mg + last * C * C, row, g.img);
   copy_tile_async(sKE, KEg + last * C * K, row, g.img);
+  if (img) copy_S_row(last);
   umma::cp_async_commit();
   copy_tile_async(sQE, QEg + last * C * K, row, g.img);
   copy_tile_async(sW, Wg + last * C * K, row, g.img);
@@ -331,14 +346,27 @@ __global__ void __launch_bounds__(128, 1) state_bwd_tc_kernel(StateArgs a) {
     if (c > cb) chunk_flags(a.seg, g, b, c - 1, nis_new, nall_same);
     stage_rows<VS>(sdO, row, dO);
     stage_rows<VS>(sdH, row, dH);
-    {
+    if (img) {                                           // dH as a bf16 operand image
+      uint4* dst = reinterpret_cast<uint4*>(a.dH) + item * (K * Vw / 8) + (size_t)(v0 / 8) * 128 + row;
+#pragma unroll
+      for (int p = 0; p < VS / 8; ++p) dst[p * 128] = sdH[p * 128 + row];
+    } else {
       float4* dst = reinterpret_cast<float4*>(a.dH + item * K * Vw + (size_t)row * Vw + v0);
 #pragma unroll
       for (int j = 0; j < VS / 4; ++j) dst[j] = make_float4(dH[4 * j], dH[4 * j + 1], dH[4 * j + 2], dH[4 * j + 3]);
     }
     const float dec = all_same ? expf(fminf(__ldg(a.res.lam_end + item * K + row), 0.f)) : 0.f;
 
-    umma::cp_async_wait<1>();                           // M, ke of this chunk
+    umma::cp_async_wait<1>();                           // M, ke (and the S row) of this chunk
+    if (img) {                                          // partial sum of dLambda_end over this CTA's columns
+      float part = 0.f;
+#pragma unroll
+      for (int j = 0; j < VS / 4; ++j) {
+        const float4 sv = sSl[j * 128];
+        part += dH[4 * j] * sv.x + dH[4 * j + 1] * sv.y + dH[4 * j + 2] * sv.z + dH[4 * j + 3] * sv.w;
+      }
+      dlend_part(g, a.dH)[(item * gridDim.x + blockIdx.x) * K + row] = part;
+    }
     umma::pre_issue_sync();
     umma::issue<VS, true, true>(cx, sM, sdO, C, colV, false);          // dV  = M^T dO
     umma::issue<VS, false, true>(cx, sKE, sdH, K, colV, true);         //     + ke dH
@@ -346,12 +374,22 @@ __global__ void __launch_bounds__(128, 1) state_bwd_tc_kernel(StateArgs a) {
     if (c > cb) {
       copy_tile_async(sM, Mg + (item - 1) * C * C, row, g.img);
       copy_tile_async(sKE, KEg + (item - 1) * C * K, row, g.img);
+      if (img) copy_S_row(item - 1);
     }
     umma::cp_async_commit();
 
     float dv[VS];
     read_acc<VS>(cx, colV, warp, dv);
-    {
+    if (img) {                                           // dV as a bf16 operand image
+      uint4* dst = reinterpret_cast<uint4*>(a.dV) + item * (C * Vw / 8) + (size_t)(v0 / 8) * 128 + row;
+#pragma unroll
+      for (int p = 0; p < VS / 8; ++p) {
+        float t8[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) t8[i] = dv[p * 8 + i];
+        dst[p * 128] = umma::pack8(t8);
+      }
+    } else {
       float4* dst = reinterpret_cast<float4*>(a.dV + item * C * Vw + (size_t)row * Vw + v0);
 #pragma unroll
       for (int j = 0; j < VS / 4; ++j) dst[j] = make_float4(dv[4 * j], dv[4 * j + 1], dv[4 * j + 2], dv[4 * j + 3]);
@@ -395,7 +433,9 @@ int pick_vs(const Geo& g) {
 }
 
 template <int VS>
-size_t tc_smem(bool bwd) { return (size_t)4 * TILE_U4 * 16 + (size_t)(bwd ? 3 : 2) * (VS / 8) * 128 * 16; }
+size_t tc_smem(bool bwd) {
+  return (size_t)4 * TILE_U4 * 16 + (size_t)(bwd ? 3 : 2) * (VS / 8) * 128 * 16 + (bwd ? (size_t)128 * VS * 4 : 0);
+}
 
 template <int VS>
 int launch_fwd_vs(const StateArgs& a, cudaStream_t st) {
@@ -442,7 +482,9 @@ int launch_state_fwd_tc(const StateArgs& in, cudaStream_t st) {
 
 int launch_state_bwd_tc(const StateArgs& in, cudaStream_t st) {
   const StateArgs a = with_range(in);
-  switch (pick_vs(a.g)) {
+  // image path: slices of 32 columns (the dLambda_end partial sums are laid out per slice of 32, and the
+  // S strip of a 64-column slice would not fit in shared memory)
+  switch (a.g.img ? 32 : pick_vs(a.g)) {
     case 64: return launch_bwd_vs<64>(a, st);
     default: return launch_bwd_vs<32>(a, st);
   }
