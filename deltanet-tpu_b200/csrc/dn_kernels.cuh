@@ -52,6 +52,7 @@ struct PrepassBwdArgs {
   int items;
   int* err;                        // device error word (bounded waits report here)
   int c_begin, c_end;              // chunk range [c_begin, c_end) of every (batch, head); tensor-core path only
+  bool bulk_v;                     // v, w, dv, dw move by bulk copies (set by the launcher)
 };
 
 size_t prepass_fwd_scratch_per_cta(const Geo& g);

@@ -80,7 +80,7 @@ template <int VW, int MODE>
 __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a) {
   using CF = InCfg<MODE>;
   extern __shared__ __align__(128) uint8_t smraw[];
-  __shared__ uint64_t mma_bar;
+  __shared__ uint64_t mma_bar, v_bar;
   __shared__ uint32_t tmem_base;
   __shared__ int seg_s[C];
   __shared__ int reset_s[8];                 // per 32-row quarter: a document starts inside it
@@ -113,7 +113,9 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
   const float4* DQE4 = reinterpret_cast<const float4*>(DQE);
   const float4* DKE4 = reinterpret_cast<const float4*>(DKE);
 
-  if (tid == 0) { umma::mbar_init(&mma_bar, 1); umma::fence_mbar_init(); }
+  if (tid == 0) { umma::mbar_init(&mma_bar, 1); umma::mbar_init(&v_bar, 1); umma::fence_mbar_init(); }
+  uint32_t v_phase = 0;
+  const bool bulk_v = MODE == 0 && a.bulk_v;
   if (warp == 0) umma::tmem_alloc(&tmem_base, 512);
   umma::tc_fence_before();
   __syncthreads();
@@ -168,6 +170,54 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
     //         when w is one scalar per head): 8 rows x 4 pieces per warp step.  dY is read from the
     //         bf16 operand image the products left in shared memory (slot X), i.e. rounded to bf16
     //         like every other operand of this precision mode.
+    //         In the headline mode (bf16 v, fp32 per-channel w, V = 128) the rows of v and w come in
+    //         and the rows of dv and dw go out by bulk asynchronous copies, one per row and tensor,
+    //         through padded staging rows in shared memory: a 128-column pass (one value head) moves
+    //         384 KB without a single load or store instruction of the CUDA cores touching global memory.
+    if (bulk_v) {
+      constexpr int VP = 256 + 16, WP = 512 + 16;          // row pitches in bytes (padding: no bank conflicts)
+      uint8_t* VB = smraw + 68 * 1024;
+      uint8_t* WB = VB + 128 * VP;
+      const int rows = g.L - t0 < C ? g.L - t0 : C;
+      const uint4* Ximg = reinterpret_cast<const uint4*>(smraw);
+#pragma unroll 1
+      for (int pass = 0; pass < VW / 128; ++pass) {
+        const int hv = h * (VW / 128) + pass;                // V == 128: one value head per pass
+        const size_t tok = (size_t)b * g.L + t0 + tid;
+        if (tid == 0) umma::mbar_expect_tx(&v_bar, (uint32_t)rows * (256 + 512));
+        __syncthreads();
+        if (tid < rows) {
+          umma::bulk_load(VB + tid * VP, reinterpret_cast<const __nv_bfloat16*>(a.v) + (tok * g.Hv + hv) * 128, 256, &v_bar);
+          umma::bulk_load(WB + tid * WP, reinterpret_cast<const float*>(a.w) + (tok * g.wH + g.w_head(hv)) * 128, 512, &v_bar);
+        }
+        if (!umma::mbar_wait(&v_bar, v_phase) && a.err) atomicExch(a.err, 1);
+        v_phase ^= 1u;
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+          const int p = it * 4 + lgrp, x = myrow;
+          uint4* pv = reinterpret_cast<uint4*>(VB + x * VP + 16 * p);
+          float4* pw = reinterpret_cast<float4*>(WB + x * WP + 32 * p);
+          float vv[8], dy[8], dv8[8];
+          umma::unpack8(*pv, vv);
+          const float4 w0 = pw[0], w1 = pw[1];
+          const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+          umma::unpack8(Ximg[(pass * 16 + p) * 128 + x], dy);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) { dv8[i] = dy[i] * ww[i]; vv[i] *= dy[i]; }
+          *pv = umma::pack8(dv8);
+          pw[0] = make_float4(vv[0], vv[1], vv[2], vv[3]);
+          pw[1] = make_float4(vv[4], vv[5], vv[6], vv[7]);
+        }
+        umma::fence_async_smem();
+        __syncthreads();
+        if (tid < rows) {
+          umma::bulk_store(reinterpret_cast<__nv_bfloat16*>(a.dv) + (tok * g.Hv + hv) * 128, VB + tid * VP, 256);
+          umma::bulk_store(reinterpret_cast<float*>(a.dw) + (tok * g.Hv + hv) * 128, WB + tid * WP, 512);
+          umma::bulk_commit();
+          if (pass + 1 < VW / 128) umma::bulk_wait_read<0>();      // the staging rows are reused by the next pass
+        }
+      }
+    } else
     {
       constexpr int PV = VW / 8;
       const int x = myrow, t = t0 + x;
@@ -217,6 +267,7 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
     // ---- L. rows, normalisers, cumulative decay
     row_norms_8x4(r, myrow, lgrp, rq_s, rk_s);
     lambda_scan_512(r, seg_s, LAM, TOTL, reset_s);
+    if (bulk_v && tid < C) umma::bulk_wait_read<0>();      // dv, dw have left their staging rows (reused below)
     __syncthreads();
 
     DN_MARK(8);
@@ -610,6 +661,8 @@ int launch_prepass_bwd_tc(PrepassBwdArgs& a, size_t scratch_floats, cudaStream_t
     kernel<<<grid, NT, smem, st>>>(a);
   };
   const int mode = input_mode(g);
+  auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  a.bulk_v = mode == 0 && g.V == 128 && a.dw_dt == DN_F32 && al16(a.v) && al16(a.w) && al16(a.dv) && al16(a.dw);
   if (g.Vw == 256) {
     if (mode == 0) go(prepass_bwd_tc_kernel<256, 0>); else if (mode == 1) go(prepass_bwd_tc_kernel<256, 1>); else go(prepass_bwd_tc_kernel<256, 2>);
   } else {

@@ -232,6 +232,19 @@ def test_oracle_parity_bf16_training_shape_small(dn):
                  precision="bf16", qk_l2norm=True, recompute_states=rc)
 
 
+def test_oracle_parity_bf16_ragged_length(dn):
+    """bf16 inputs on the tensor-core path with a last chunk of 44 rows (L = 300) and two batch rows:
+    every bulk and asynchronous copy of the chunk kernels has to stop at the end of the sequence."""
+    B, L, Hk, Hv, K, V = 2, 300, 2, 4, 128, 128
+    q, k, v, g, b, w = O.make_inputs(405, B, L, Hk, Hv, K, V, qkv_dtype=torch.bfloat16)
+    seg = torch.zeros(B, L, dtype=torch.int32)
+    seg[0, 130:] = 1
+    seg[1, 290:] = 1
+    gen = torch.Generator().manual_seed(8)
+    do = torch.randn(B, L, Hv, V, generator=gen).to(torch.bfloat16).float()
+    run_both(dn, q, k, v, g, b, w, do=do, tol=BF16_TOL, segment_ids=seg, chunk_size=128, precision="bf16", qk_l2norm=True)
+
+
 def test_oracle_parity_split_chains(dn):
     """A shape whose work items (2 batches x 10 heads x 8 chunks = 160) leave the last round of CTAs
     almost empty, which makes the library cut the chunk axis (here after chunk 7) and run a part of
