@@ -223,6 +223,22 @@ __device__ __forceinline__ void build_level_from(const float (&kh)[8], const flo
   KR[p * 128 + x] = umma::pack8(o1);
   QK[p * 128 + x] = umma::pack8(o2);
 }
+// The same from beta = b_act * k_hat already formed (operands cached on chip).
+__device__ __forceinline__ void build_level_from_beta(const float (&kh)[8], const float (&be)[8], const float (&qh)[8],
+                                                      const float* LAM, int s, int x, int p, uint4* KR, uint4* QK) {
+  const int ref = level_ref(x, s);
+  const bool lower = x >= ref;
+  float f[8], o1[8], o2[8];
+  decay8(LAM + (lower ? x : ref) * LP + 8 * p, LAM + (lower ? ref : x) * LP + 8 * p, f);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float kf = kh[i] * f[i];
+    o1[i] = lower ? be[i] * f[i] : kf;
+    o2[i] = lower ? qh[i] * f[i] : kf;
+  }
+  KR[p * 128 + x] = umma::pack8(o1);
+  QK[p * 128 + x] = umma::pack8(o2);
+}
 __device__ __forceinline__ void build_level_piece(const Rows& r, const float* LAM, int s, int x, int p, uint4* KR, uint4* QK) {
   float kh[8], ba[8], qh[8];
   khat8(r, x, p, kh);              // all three loads are issued before the role is looked at

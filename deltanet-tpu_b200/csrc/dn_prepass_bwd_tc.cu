@@ -116,6 +116,9 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
   if (tid == 0) { umma::mbar_init(&mma_bar, 1); umma::mbar_init(&v_bar, 1); umma::fence_mbar_init(); }
   uint32_t v_phase = 0;
   const bool bulk_v = MODE == 0 && a.bulk_v;
+  // tensor-memory columns: level products T1 | T2 at [0, 256); operand cache of the level sweep at
+  // [256, 384) (k_hat | q_hat, two bf16 per column) and [384, 512) (beta, fp32)
+  constexpr uint32_t COL_KQ = 256, COL_BE = 384;
   if (warp == 0) umma::tmem_alloc(&tmem_base, 512);
   umma::tc_fence_before();
   __syncthreads();
@@ -143,6 +146,7 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
     const Rows r = make_rows<CF>(g, a.q, a.k, a.gg, a.b, b, h, t0, rq_s, rk_s);
     const int qdt = r.qkv_dt, gdt = r.gate_dt;           // compile-time constants in the fixed modes
     const int wC = CF::fixed ? (CF::scalar_gates ? 1 : g.V) : g.wC;
+    const bool tm_cache = r.round_in;                    // k_hat, q_hat exactly bf16: they can be packed two per column
 
     // ---- G. the matrix products (and dLambda_end from the carried state)
     {
@@ -308,6 +312,28 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
         }
         __syncthreads();
         DN_MARK(20 + 3 * half);
+        if (tm_cache && ((warp & 3) >> 1) == half) {
+          // the level sweep reads k_hat, q_hat and beta from tensor memory instead of global memory:
+          // thread = row (its own lane), the four warps of a lane quarter take 32 channels each
+          const int xr = (warp & 3) * 32 + lane - 64 * half, cg0 = (warp >> 2) * 32;
+          const uint32_t tl = cx.tmem + ((uint32_t)((warp & 3) * 32) << 16);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int c0 = cg0 + 8 * j;
+            float kq[8], be8[8];
+            const float4 k0 = *reinterpret_cast<const float4*>(KC + xr * CP + c0), k1 = *reinterpret_cast<const float4*>(KC + xr * CP + c0 + 4);
+            const float4 q0 = *reinterpret_cast<const float4*>(QC + xr * CP + c0), q1 = *reinterpret_cast<const float4*>(QC + xr * CP + c0 + 4);
+            const float4 b0 = *reinterpret_cast<const float4*>(BC + xr * CP + c0), b1 = *reinterpret_cast<const float4*>(BC + xr * CP + c0 + 4);
+            const float kk[8] = {k0.x, k0.y, k0.z, k0.w, k1.x, k1.y, k1.z, k1.w}, qq[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i)                 // both are exactly representable in bf16 here
+              kq[i] = __uint_as_float((__float_as_uint(kk[i]) >> 16) | (__float_as_uint(qq[i]) & 0xffff0000u));
+            be8[0] = b0.x; be8[1] = b0.y; be8[2] = b0.z; be8[3] = b0.w; be8[4] = b1.x; be8[5] = b1.y; be8[6] = b1.z; be8[7] = b1.w;
+            umma::tmem_st8(tl + COL_KQ + c0, kq);
+            umma::tmem_st8(tl + COL_BE + c0, be8);
+          }
+          umma::tmem_wait_st();
+        }
         {
           const int lb = tid >> 7, blk = half * 4 + lb, r0 = blk * 16, c = tid & 127;
           const float* kc = KC + lb * 16 * CP + c;
@@ -374,15 +400,33 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
           I_DM[e] = vm;
         }
       }
+      if (tm_cache) {
+        const int x = (warp & 3) * 32 + lane;
+        const uint32_t tl = cx.tmem + ((uint32_t)((warp & 3) * 32) << 16);
 #pragma unroll 2
-      for (int it = 0; it < 4; ++it) build_level_piece(r, LAM, s, myrow, it * 4 + lgrp, I_KR, I_QK);
+        for (int j = 0; j < 4; ++j) {
+          const int p = (warp >> 2) * 4 + j;
+          float kq[8], be8[8], kh[8], qh[8];
+          umma::tmem_ld8(tl + COL_KQ + 8 * p, kq);
+          umma::tmem_ld8(tl + COL_BE + 8 * p, be8);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            kh[i] = __uint_as_float(__float_as_uint(kq[i]) << 16);
+            qh[i] = __uint_as_float(__float_as_uint(kq[i]) & 0xffff0000u);
+          }
+          build_level_from_beta(kh, be8, qh, LAM, s, x, p, I_KR, I_QK);
+        }
+      } else {
+#pragma unroll 2
+        for (int it = 0; it < 4; ++it) build_level_piece(r, LAM, s, myrow, it * 4 + lgrp, I_KR, I_QK);
+      }
     };
     auto drain_level = [&](int lv) {
       const int s = 16 << lv;
       const int quarter = warp & 3, group = warp >> 2;
       const int x = quarter * 32 + lane, ref = level_ref(x, s);
       const bool lower = x >= ref;
-      const uint32_t tbase = cx.tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)((lv & 1) * 256);
+      const uint32_t tbase = cx.tmem + ((uint32_t)(quarter * 32) << 16);
       // one code path for both roles: a lower row adds rowfac * T1 to dbeta' and rowfac * T2 to dq',
       // an upper row adds colfac * (T1 + T2) to dk'
       float4* const pb = lower ? DBP4 : DKP4;
@@ -421,7 +465,7 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
     };
     build(0);
     for (int lv = 0; lv < 3; ++lv) {
-      const uint32_t tcol = (uint32_t)((lv & 1) * 256);
+      const uint32_t tcol = 0;                             // the drain of level lv is over before level lv + 1 is issued
       umma::pre_issue_sync();
       umma::issue<128, false, true>(cx, I_DA, I_KR, C, tcol, false);        // dA_s   KR
       umma::issue<128, true, true>(cx, I_DA, I_KR, C, tcol, true);          // dA_s^T KR
