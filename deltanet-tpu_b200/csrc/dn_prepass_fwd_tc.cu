@@ -126,6 +126,9 @@ __global__ void __launch_bounds__(NT, 1) prepass_fwd_tc_kernel(PrepassFwdArgs a,
   umma::Ctx cx{tmem_base, &mma_bar, 0u, err, false};
 
   const bool fuse = CF::fixed ? false : (g.flags & DN_FUSE_PROLOGUE) != 0;     // the fixed modes have no fused prologue
+  // tensor-memory columns: level products at [0, 256); operand cache at [256, 384) (k_hat | q_hat, two
+  // bf16 per column) and [384, 512) (beta, fp32)
+  constexpr uint32_t COL_KQ = 256, COL_BE = 384;
 
   // work items in chunk-major order inside the chunk range: all heads of chunk c_begin first
   for (int e_item = blockIdx.x; e_item < a.items; e_item += gridDim.x) {
@@ -146,103 +149,18 @@ __global__ void __launch_bounds__(NT, 1) prepass_fwd_tc_kernel(PrepassFwdArgs a,
     const Rows r = make_rows<CF>(g, a.q, a.k, a.gg, a.b, b, h, t0, rq_s, rk_s);
     const int qdt = r.qkv_dt, gdt = r.gate_dt;           // compile-time constants in the fixed modes
     const int wC = CF::fixed ? (CF::scalar_gates ? 1 : g.V) : g.wC;
+    const bool tm_cache = r.round_in;                    // k_hat, q_hat exactly bf16: they can be packed two per column
     __syncthreads();
     const int seg0 = seg_s[0], segL = seg_s[C - 1];
     row_norms_8x4(r, myrow, lgrp, rq_s, rk_s);             // no barrier in between: the loads of q, k and g
     lambda_scan_512(r, seg_s, LAM, TOTL, reset_s);         // are all in flight together
     __syncthreads();
 
-    DN_MARK(1);
-    // ---- qe, ke, Lambda_end, the X = [first doc] beta e^Lam operand image, and (same pass over q, k,
-    //      b) the images of the first level
-    {
-      const int x = myrow;
-      const bool first = seg_s[x] == seg0, last = seg_s[x] == segL;
-#pragma unroll 2
-      for (int it = 0; it < 4; ++it) {
-        const int p = it * 4 + lgrp;
-        float qh[8], kh[8], be[8], lam[8], lend[8], o[8];
-        qhat8(r, x, p, qh);
-        khat8(r, x, p, kh);
-        bact8(r, x, p, be);
-        *reinterpret_cast<float4*>(lam) = *reinterpret_cast<const float4*>(LAM + x * LP + 8 * p);
-        *reinterpret_cast<float4*>(lam + 4) = *reinterpret_cast<const float4*>(LAM + x * LP + 8 * p + 4);
-        *reinterpret_cast<float4*>(lend) = *reinterpret_cast<const float4*>(LAM + (C - 1) * LP + 8 * p);
-        *reinterpret_cast<float4*>(lend + 4) = *reinterpret_cast<const float4*>(LAM + (C - 1) * LP + 8 * p + 4);
-        float el[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) el[i] = umma::exp_neg(fminf(lam[i], 0.f));
-#pragma unroll
-        for (int i = 0; i < 8; ++i) o[i] = first ? qh[i] * el[i] : 0.f;
-        QEimg[p * 128 + x] = umma::pack8(o);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) o[i] = last ? kh[i] * umma::exp_neg(fminf(lend[i] - lam[i], 0.f)) : 0.f;
-        KEimg[p * 128 + x] = umma::pack8(o);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) o[i] = first ? be[i] * kh[i] * el[i] : 0.f;
-        XI[p * 128 + x] = umma::pack8(o);
-        build_level_from(kh, be, qh, LAM, 16, x, p, KR, QK);
-      }
-      if (tid < K) a.res.lam_end[ibase * K + tid] = LAM[(C - 1) * LP + tid];
-    }
-
-    DN_MARK(2);
-    // ---- A and M, level by level: two images, two MMAs, one predicated drain per level
-    auto build = [&](int lv) {
-#pragma unroll 2
-      for (int it = 0; it < 4; ++it) build_level_piece(r, LAM, 16 << lv, myrow, it * 4 + lgrp, KR, QK);
-    };
-    auto drain_level = [&](int lv) {
-      const int quarter = warp & 3, group = warp >> 2;
-      const int row = quarter * 32 + lane, bi = row >> 4, bi0 = quarter * 2;
-      const uint32_t tbase = cx.tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)((lv & 1) * 256);
-#pragma unroll 1
-      for (int cc = 0; cc < 32; cc += 16) {
-        const int col = group * 32 + cc, bj = col >> 4;
-        // warp-uniform skip: neither of the warp's two row blocks has this piece at this level
-        const bool own0 = bj < bi0 && owner_level(bi0, bj) == lv, own1 = bj < bi0 + 1 && owner_level(bi0 + 1, bj) == lv;
-        const bool upper = lv == 0 && bj > bi0;                  // zero fill, once
-        if (!own0 && !own1 && !upper) continue;
-        float va[16], vm[16];
-        if (!cx.dead && (own0 || own1)) {
-          umma::tmem_ld16(tbase + col, va);
-          umma::tmem_ld16(tbase + 128 + col, vm);
-        } else {
-#pragma unroll
-          for (int i = 0; i < 16; ++i) va[i] = vm[i] = 0.f;
-        }
-        const bool mine = bj < bi && owner_level(bi, bj) == lv;
-        const bool zero_fill = lv == 0 && bj > bi;
-        if (!mine && !zero_fill) continue;
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const bool keep = mine && seg_s[row] == seg_s[col + i];
-          va[i] = keep ? va[i] : 0.f;
-          vm[i] = keep ? vm[i] : 0.f;
-        }
-#pragma unroll
-        for (int i = 0; i < 4; ++i) __stcg(Ag4 + p4v(row, col + 4 * i), make_float4(va[4 * i], va[4 * i + 1], va[4 * i + 2], va[4 * i + 3]));
-        Mimg[(col / 8) * 128 + row] = umma::pack8p(vm);
-        Mimg[(col / 8 + 1) * 128 + row] = umma::pack8p(vm + 8);
-      }
-      umma::tc_fence_before();
-    };
-    for (int lv = 0; lv < 3; ++lv) {                       // (the images of level 0 were built above)
-      const uint32_t tcol = (uint32_t)((lv & 1) * 256);
-      umma::pre_issue_sync();
-      umma::issue<128, false, false>(cx, KR, KR, K, tcol, false);          // A: KR KR^T
-      umma::issue<128, false, false>(cx, QK, KR, K, tcol + 128, false);    // M: QK KR^T
-      umma::commit_wait(cx);
-      DN_MARK(3 + lv);
-      if (lv < 2) build(lv + 1);
-      drain_level(lv);
-    }
-    __syncthreads();
-
-    DN_MARK(6);
     // ---- 16x16 diagonal blocks, exact.  k_hat, q_hat and beta of 64 rows at a time are cached in
     //      shared memory (fp32; one global round trip per half); four warps per block take every
     //      fourth row i, lanes own 4 channels, and every pair (i, j <= i) is one warp reduction.
+    const uint32_t tm_lane = cx.tmem + ((uint32_t)((warp & 3) * 32) << 16);
+    auto diag_pass = [&]() {
 #pragma unroll 1
     for (int half = 0; half < 2; ++half) {
       float* QHs = KHs + 64 * AP;                                       // q_hat (pitch AP)
@@ -269,6 +187,27 @@ __global__ void __launch_bounds__(NT, 1) prepass_fwd_tc_kernel(PrepassFwdArgs a,
       }
       __syncthreads();
       DN_MARK(20 + 3 * half);
+      if (tm_cache && ((warp & 3) >> 1) == half) {
+        // every later pass (qe / ke / X, the three levels) reads k_hat, q_hat and beta from tensor
+        // memory: thread = row (its own lane), the four warps of a lane quarter take 32 channels each
+        const int xr = (warp & 3) * 32 + lane - 64 * half, cg0 = (warp >> 2) * 32;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int c0 = cg0 + 8 * j;
+          float kq[8], be8[8];
+          const float4 k0 = *reinterpret_cast<const float4*>(KHs + xr * AP + c0), k1 = *reinterpret_cast<const float4*>(KHs + xr * AP + c0 + 4);
+          const float4 q0 = *reinterpret_cast<const float4*>(QHs + xr * AP + c0), q1 = *reinterpret_cast<const float4*>(QHs + xr * AP + c0 + 4);
+          const float4 b0 = *reinterpret_cast<const float4*>(BEs + xr * 128 + c0), b1 = *reinterpret_cast<const float4*>(BEs + xr * 128 + c0 + 4);
+          const float kk[8] = {k0.x, k0.y, k0.z, k0.w, k1.x, k1.y, k1.z, k1.w}, qq[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+          for (int i = 0; i < 8; ++i)                   // both are exactly representable in bf16 here
+            kq[i] = __uint_as_float((__float_as_uint(kk[i]) >> 16) | (__float_as_uint(qq[i]) & 0xffff0000u));
+          be8[0] = b0.x; be8[1] = b0.y; be8[2] = b0.z; be8[3] = b0.w; be8[4] = b1.x; be8[5] = b1.y; be8[6] = b1.z; be8[7] = b1.w;
+          umma::tmem_st8(tm_lane + COL_KQ + c0, kq);
+          umma::tmem_st8(tm_lane + COL_BE + c0, be8);
+        }
+        umma::tmem_wait_st();
+      }
       const int lb = warp >> 2, r0 = (half * 4 + lb) * 16, c0 = lb * 16;   // block rows in the chunk / in the caches
 #pragma unroll 1
       for (int i = warp & 3; i < 16; i += 4) {
@@ -318,6 +257,137 @@ __global__ void __launch_bounds__(NT, 1) prepass_fwd_tc_kernel(PrepassFwdArgs a,
       __syncthreads();
       DN_MARK(22 + 3 * half);
     }
+    };
+
+    // ---- qe, ke, the X = [first doc] beta e^Lam operand image and the images of the first level for
+    //      one piece (row x, channels 8p..8p+7), from k_hat, q_hat and beta = b_act * k_hat
+    auto xi_piece = [&](int x, int p, const float (&kh)[8], const float (&qh)[8], const float (&be)[8]) {
+      const bool first = seg_s[x] == seg0, last = seg_s[x] == segL;
+      float lam[8], lend[8], o[8], el[8];
+      *reinterpret_cast<float4*>(lam) = *reinterpret_cast<const float4*>(LAM + x * LP + 8 * p);
+      *reinterpret_cast<float4*>(lam + 4) = *reinterpret_cast<const float4*>(LAM + x * LP + 8 * p + 4);
+      *reinterpret_cast<float4*>(lend) = *reinterpret_cast<const float4*>(LAM + (C - 1) * LP + 8 * p);
+      *reinterpret_cast<float4*>(lend + 4) = *reinterpret_cast<const float4*>(LAM + (C - 1) * LP + 8 * p + 4);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) el[i] = umma::exp_neg(fminf(lam[i], 0.f));
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = first ? qh[i] * el[i] : 0.f;
+      QEimg[p * 128 + x] = umma::pack8(o);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = last ? kh[i] * umma::exp_neg(fminf(lend[i] - lam[i], 0.f)) : 0.f;
+      KEimg[p * 128 + x] = umma::pack8(o);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = first ? be[i] * el[i] : 0.f;
+      XI[p * 128 + x] = umma::pack8(o);
+      build_level_from_beta(kh, be, qh, LAM, 16, x, p, KR, QK);
+    };
+    // the cached operands of row x = this thread's tensor-memory lane, piece p
+    auto cached_piece = [&](int p, float (&kh)[8], float (&qh)[8], float (&be)[8]) {
+      float kq[8];
+      umma::tmem_ld8(tm_lane + COL_KQ + 8 * p, kq);
+      umma::tmem_ld8(tm_lane + COL_BE + 8 * p, be);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        kh[i] = __uint_as_float(__float_as_uint(kq[i]) << 16);
+        qh[i] = __uint_as_float(__float_as_uint(kq[i]) & 0xffff0000u);
+      }
+    };
+    auto xi_pass = [&]() {
+      if (tm_cache) {
+        const int x = (warp & 3) * 32 + lane;
+#pragma unroll 2
+        for (int j = 0; j < 4; ++j) {
+          const int p = (warp >> 2) * 4 + j;
+          float kh[8], qh[8], be[8];
+          cached_piece(p, kh, qh, be);
+          xi_piece(x, p, kh, qh, be);
+        }
+      } else {
+#pragma unroll 2
+        for (int it = 0; it < 4; ++it) {
+          const int p = it * 4 + lgrp;
+          float qh[8], kh[8], be[8];
+          qhat8(r, myrow, p, qh);
+          khat8(r, myrow, p, kh);
+          bact8(r, myrow, p, be);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) be[i] *= kh[i];
+          xi_piece(myrow, p, kh, qh, be);
+        }
+      }
+      if (tid < K) a.res.lam_end[ibase * K + tid] = LAM[(C - 1) * LP + tid];
+    };
+
+    DN_MARK(1);
+    if (tm_cache) diag_pass();                 // first: it also fills the tensor-memory operand cache
+    xi_pass();
+
+    DN_MARK(2);
+    // ---- A and M, level by level: two images, two MMAs, one predicated drain per level
+    auto build = [&](int lv) {
+      if (tm_cache) {
+        const int x = (warp & 3) * 32 + lane;
+#pragma unroll 2
+        for (int j = 0; j < 4; ++j) {
+          const int p = (warp >> 2) * 4 + j;
+          float kh[8], qh[8], be[8];
+          cached_piece(p, kh, qh, be);
+          build_level_from_beta(kh, be, qh, LAM, 16 << lv, x, p, KR, QK);
+        }
+      } else {
+#pragma unroll 2
+        for (int it = 0; it < 4; ++it) build_level_piece(r, LAM, 16 << lv, myrow, it * 4 + lgrp, KR, QK);
+      }
+    };
+    auto drain_level = [&](int lv) {
+      const int quarter = warp & 3, group = warp >> 2;
+      const int row = quarter * 32 + lane, bi = row >> 4, bi0 = quarter * 2;
+      const uint32_t tbase = cx.tmem + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+      for (int cc = 0; cc < 32; cc += 16) {
+        const int col = group * 32 + cc, bj = col >> 4;
+        // warp-uniform skip: neither of the warp's two row blocks has this piece at this level
+        const bool own0 = bj < bi0 && owner_level(bi0, bj) == lv, own1 = bj < bi0 + 1 && owner_level(bi0 + 1, bj) == lv;
+        const bool upper = lv == 0 && bj > bi0;                  // zero fill, once
+        if (!own0 && !own1 && !upper) continue;
+        float va[16], vm[16];
+        if (!cx.dead && (own0 || own1)) {
+          umma::tmem_ld16(tbase + col, va);
+          umma::tmem_ld16(tbase + 128 + col, vm);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) va[i] = vm[i] = 0.f;
+        }
+        const bool mine = bj < bi && owner_level(bi, bj) == lv;
+        const bool zero_fill = lv == 0 && bj > bi;
+        if (!mine && !zero_fill) continue;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const bool keep = mine && seg_s[row] == seg_s[col + i];
+          va[i] = keep ? va[i] : 0.f;
+          vm[i] = keep ? vm[i] : 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) __stcg(Ag4 + p4v(row, col + 4 * i), make_float4(va[4 * i], va[4 * i + 1], va[4 * i + 2], va[4 * i + 3]));
+        Mimg[(col / 8) * 128 + row] = umma::pack8p(vm);
+        Mimg[(col / 8 + 1) * 128 + row] = umma::pack8p(vm + 8);
+      }
+      umma::tc_fence_before();
+    };
+    for (int lv = 0; lv < 3; ++lv) {                       // (the images of level 0 were built above)
+      const uint32_t tcol = 0;                             // the drain of level lv is over before level lv + 1 is issued
+      umma::pre_issue_sync();
+      umma::issue<128, false, false>(cx, KR, KR, K, tcol, false);          // A: KR KR^T
+      umma::issue<128, false, false>(cx, QK, KR, K, tcol + 128, false);    // M: QK KR^T
+      umma::commit_wait(cx);
+      DN_MARK(3 + lv);
+      if (lv < 2) build(lv + 1);
+      drain_level(lv);
+    }
+    __syncthreads();
+
+    DN_MARK(6);
+    if (!tm_cache) diag_pass();
 
     DN_MARK(7);
     // ---- T = (I + A)^-1 in fp32: substitution on the diagonal blocks, then block merges
