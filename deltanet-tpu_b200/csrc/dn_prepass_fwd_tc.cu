@@ -217,35 +217,47 @@ __global__ void __launch_bounds__(NT, 1) prepass_fwd_tc_kernel(PrepassFwdArgs a,
         const float4 li = *reinterpret_cast<const float4*>(LAM + ri * LP + 4 * lane);
         const float qi[4] = {q4.x, q4.y, q4.z, q4.w}, bi4[4] = {b4.x, b4.y, b4.z, b4.w};
         float arow = 0.f, mrow = 0.f;                  // lane j (< 16) keeps entry (ri, r0 + j)
+        const bool hi16 = lane & 16, hi8 = lane & 8, hi4 = lane & 4;
 #pragma unroll 1
-        for (int j = 0; j <= i; j += 2) {              // two columns per step: four independent reductions
-          const int rj = r0 + j;
-          const float4 ka = *reinterpret_cast<const float4*>(KHs + (c0 + j) * AP + 4 * lane);
-          const float4 kb = *reinterpret_cast<const float4*>(KHs + (c0 + j + 1) * AP + 4 * lane);
-          const float4 la = *reinterpret_cast<const float4*>(LAM + rj * LP + 4 * lane);
-          const float4 lb = *reinterpret_cast<const float4*>(LAM + (rj + 1) * LP + 4 * lane);
-          const float a0 = ka.x * umma::ex2_fast(fminf(li.x - la.x, 0.f) * DN_LOG2E), a1 = ka.y * umma::ex2_fast(fminf(li.y - la.y, 0.f) * DN_LOG2E);
-          const float a2 = ka.z * umma::ex2_fast(fminf(li.z - la.z, 0.f) * DN_LOG2E), a3 = ka.w * umma::ex2_fast(fminf(li.w - la.w, 0.f) * DN_LOG2E);
-          const float b0 = kb.x * umma::ex2_fast(fminf(li.x - lb.x, 0.f) * DN_LOG2E), b1 = kb.y * umma::ex2_fast(fminf(li.y - lb.y, 0.f) * DN_LOG2E);
-          const float b2 = kb.z * umma::ex2_fast(fminf(li.z - lb.z, 0.f) * DN_LOG2E), b3 = kb.w * umma::ex2_fast(fminf(li.w - lb.w, 0.f) * DN_LOG2E);
-          float pa0 = bi4[0] * a0 + bi4[1] * a1 + bi4[2] * a2 + bi4[3] * a3;
-          float pm0 = qi[0] * a0 + qi[1] * a1 + qi[2] * a2 + qi[3] * a3;
-          float pa1 = bi4[0] * b0 + bi4[1] * b1 + bi4[2] * b2 + bi4[3] * b3;
-          float pm1 = qi[0] * b0 + qi[1] * b1 + qi[2] * b2 + qi[3] * b3;
+        for (int j = 0; j <= i; j += 4) {              // four columns per step, reduced together (see below)
+          float v[8];
 #pragma unroll
-          for (int o = 16; o > 0; o >>= 1) {
-            pa0 += __shfl_xor_sync(0xffffffffu, pa0, o); pm0 += __shfl_xor_sync(0xffffffffu, pm0, o);
-            pa1 += __shfl_xor_sync(0xffffffffu, pa1, o); pm1 += __shfl_xor_sync(0xffffffffu, pm1, o);
+          for (int u = 0; u < 4; ++u) {
+            const int cj = j + u < 16 ? j + u : 15;    // (a column past the block is computed and dropped)
+            const float4 kk = *reinterpret_cast<const float4*>(KHs + (c0 + cj) * AP + 4 * lane);
+            const float4 ll = *reinterpret_cast<const float4*>(LAM + (r0 + cj) * LP + 4 * lane);
+            const float e0 = kk.x * umma::ex2_fast(fminf(li.x - ll.x, 0.f) * DN_LOG2E), e1 = kk.y * umma::ex2_fast(fminf(li.y - ll.y, 0.f) * DN_LOG2E);
+            const float e2 = kk.z * umma::ex2_fast(fminf(li.z - ll.z, 0.f) * DN_LOG2E), e3 = kk.w * umma::ex2_fast(fminf(li.w - ll.w, 0.f) * DN_LOG2E);
+            v[2 * u] = bi4[0] * e0 + bi4[1] * e1 + bi4[2] * e2 + bi4[3] * e3;
+            v[2 * u + 1] = qi[0] * e0 + qi[1] * e1 + qi[2] * e2 + qi[3] * e3;
           }
-          if (lane == j) {
-            const bool same = seg_s[ri] == seg_s[rj];
-            arow = (j < i && same) ? pa0 : 0.f;
-            mrow = same ? pm0 : 0.f;
+          // eight sums over the 32 lanes in 9 shuffles: at each of the first three steps a lane hands
+          // over the half it drops and adds what it receives to the half it keeps
+          float w4[4], u2[2], z;
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            const float got = __shfl_xor_sync(0xffffffffu, hi16 ? v[t] : v[4 + t], 16);
+            w4[t] = (hi16 ? v[4 + t] : v[t]) + got;
           }
-          if (lane == j + 1 && j + 1 <= i) {
-            const bool same = seg_s[ri] == seg_s[rj + 1];
-            arow = (j + 1 < i && same) ? pa1 : 0.f;
-            mrow = same ? pm1 : 0.f;
+#pragma unroll
+          for (int t = 0; t < 2; ++t) {
+            const float got = __shfl_xor_sync(0xffffffffu, hi8 ? w4[t] : w4[2 + t], 8);
+            u2[t] = (hi8 ? w4[2 + t] : w4[t]) + got;
+          }
+          {
+            const float got = __shfl_xor_sync(0xffffffffu, hi4 ? u2[0] : u2[1], 4);
+            z = (hi4 ? u2[1] : u2[0]) + got;
+          }
+          z += __shfl_xor_sync(0xffffffffu, z, 2);
+          z += __shfl_xor_sync(0xffffffffu, z, 1);
+          // lane 16*(u>>1) + 8*(u&1) + 4*t now holds column j+u's sum of kind t (0: A, 1: M)
+          const int u = lane - j;                      // the column this lane keeps, if 0 <= u < 4
+          const int src = (u >= 0 && u < 4) ? 16 * (u >> 1) + 8 * (u & 1) : 0;
+          const float pa = __shfl_sync(0xffffffffu, z, src), pm = __shfl_sync(0xffffffffu, z, src + 4);
+          if (u >= 0 && u < 4 && lane <= i) {
+            const bool same = seg_s[ri] == seg_s[r0 + lane];
+            arow = (lane < i && same) ? pa : 0.f;
+            mrow = same ? pm : 0.f;
           }
         }
         if (lane < 16) {
