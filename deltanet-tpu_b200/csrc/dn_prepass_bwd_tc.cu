@@ -80,7 +80,7 @@ template <int VW, int MODE>
 __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a) {
   using CF = InCfg<MODE>;
   extern __shared__ __align__(128) uint8_t smraw[];
-  __shared__ uint64_t mma_bar, v_bar;
+  __shared__ uint64_t mma_bar, v_bar, g_bar;
   __shared__ uint32_t tmem_base;
   __shared__ int seg_s[C];
   __shared__ int reset_s[8];                 // per 32-row quarter: a document starts inside it
@@ -113,8 +113,9 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
   const float4* DQE4 = reinterpret_cast<const float4*>(DQE);
   const float4* DKE4 = reinterpret_cast<const float4*>(DKE);
 
-  if (tid == 0) { umma::mbar_init(&mma_bar, 1); umma::mbar_init(&v_bar, 1); umma::fence_mbar_init(); }
+  if (tid == 0) { umma::mbar_init(&mma_bar, 1); umma::mbar_init(&v_bar, 1); umma::mbar_init(&g_bar, 1); umma::fence_mbar_init(); }
   uint32_t v_phase = 0;
+  ImgLoader imgld{&g_bar, 0u, a.err};
   const bool bulk_v = MODE == 0 && a.bulk_v;
   // tensor-memory columns: level products T1 | T2 at [0, 256); operand cache of the level sweep at
   // [256, 384) (k_hat | q_hat, two bf16 per column) and [384, 512) (beta, fp32)
@@ -167,7 +168,7 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
       io.DQE = DQE; io.DKE = DKE; io.DX = DX; io.DM = DM; io.DA = DA;
       io.dlend_s = dlend_s; io.all_same = all_same;
       io.seg_s = seg_s; io.trunc = trunc;
-      bwd_gemms_tc<VW, NT>(cx, smraw, io);
+      bwd_gemms_tc<VW, NT>(cx, smraw, io, imgld);
     }
 
     // ---- V. dv = dY * w_act, dw = dY * v (+ sigmoid adjoint; summed over a value head's columns

@@ -72,8 +72,27 @@ __device__ __forceinline__ void copy_image_async(uint4* dst, const __nv_bfloat16
   umma::cp_async_commit();
 }
 
+// Operand images by bulk asynchronous copies: one thread announces the bytes on the mbarrier and
+// issues one copy per image; everybody waits on the barrier (bounded) before the tensor core reads.
+struct ImgLoader {
+  uint64_t* bar;
+  uint32_t phase;
+  int* err;
+  // (the proxy fence orders the CTA's earlier ordinary accesses to the slot before the copy engine's writes)
+  __device__ __forceinline__ void expect(uint32_t bytes) {
+    if (threadIdx.x == 0) { umma::fence_async_smem(); umma::mbar_expect_tx(bar, bytes); }
+  }
+  __device__ __forceinline__ void load(void* dst, const void* src, uint32_t bytes) {
+    if (threadIdx.x == 0) umma::bulk_load(dst, src, bytes, bar);
+  }
+  __device__ __forceinline__ void wait() {
+    if (!umma::mbar_wait(bar, phase) && err) atomicExch(err, 1);
+    phase ^= 1u;
+  }
+};
+
 template <int VW, int NT>
-__device__ __forceinline__ void bwd_gemms_tc(umma::Ctx& cx, uint8_t* img, const BwdTcIo& io) {
+__device__ __forceinline__ void bwd_gemms_tc(umma::Ctx& cx, uint8_t* img, const BwdTcIo& io, ImgLoader& ld) {
   constexpr int SLOT = 128 * VW * 2;
   uint4* X = reinterpret_cast<uint4*>(img);
   uint4* Y = reinterpret_cast<uint4*>(img + SLOT);
@@ -91,9 +110,11 @@ __device__ __forceinline__ void bwd_gemms_tc(umma::Ctx& cx, uint8_t* img, const 
 
   DN_MARK(1);
   // ---- 1. V_new = U - W S: the product in tensor memory, U taken from its image by the drain
-  copy_image_async<128 * 16, NT>(P, io.W);
-  copy_image_async<128 * PV, NT>(X, io.S);
-  copy_image_async<128 * PV, NT>(Z, io.U);
+  constexpr uint32_t B_KK = 128 * 128 * 2, B_KV = 128 * VW * 2;     // bytes of a (128,128) / (128,VW) image
+  ld.expect(B_KK + 2 * B_KV);
+  ld.load(P, io.W, B_KK);
+  ld.load(X, io.S, B_KV);
+  ld.load(Z, io.U, B_KV);
   // dLambda_end = [one doc] exp(Lambda_end) sum_v dH * S  (gdn2.py:759-762) from the reverse chain's
   // per-slice partial sums, added in a fixed order
   if (threadIdx.x < 128) {
@@ -101,7 +122,7 @@ __device__ __forceinline__ void bwd_gemms_tc(umma::Ctx& cx, uint8_t* img, const 
     for (int sl = 0; sl < io.slices; ++sl) acc += __ldg(io.dlend_part + sl * 128 + threadIdx.x);
     io.dlend_s[threadIdx.x] = io.all_same ? acc * expf(fminf(__ldg(io.lam_end + threadIdx.x), 0.f)) : 0.f;
   }
-  umma::cp_async_wait<0>();
+  ld.wait();
   umma::pre_issue_sync();
   umma::issue<VW, false, true>(cx, P, X, 128, 0, false);
   umma::commit_wait(cx);
@@ -145,7 +166,8 @@ __device__ __forceinline__ void bwd_gemms_tc(umma::Ctx& cx, uint8_t* img, const 
   umma::issue<128, false, false>(cx, Z, X, VW, 256, false);
   umma::issue<128, false, false>(cx, Z, Y, VW, 384, false);
   umma::commit_wait(cx);
-  copy_image_async<128 * PV, NT>(Z, io.dV);          // dO has been consumed: dV for step 3 travels during the drains
+  ld.expect(B_KV);
+  ld.load(Z, io.dV, B_KV);                           // dO has been consumed: dV for step 3 travels during the drains
   umma::drain<NT, 128>(cx, 256, [&](int row, int col, const float (&v)[16]) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) DQE4[p4v(row, col + 4 * i)] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
@@ -160,11 +182,12 @@ __device__ __forceinline__ void bwd_gemms_tc(umma::Ctx& cx, uint8_t* img, const 
 
   DN_MARK(3);
   // ---- 3. dW = -dV S^T (kept only as the operand image of step 5)
-  umma::cp_async_wait<0>();
+  ld.wait();
   umma::pre_issue_sync();
   umma::issue<128, false, false>(cx, Z, X, VW, 0, false);
   umma::commit_wait(cx);
-  copy_image_async<128 * PV, NT>(X, io.dH);          // S has been consumed: dH for step 4 travels during the drain
+  ld.expect(B_KV);
+  ld.load(X, io.dH, B_KV);                           // S has been consumed: dH for step 4 travels during the drain
   umma::drain<NT, 128>(cx, 0, [&](int row, int col, const float (&v)[16]) {
     float n[16];
 #pragma unroll
@@ -175,11 +198,12 @@ __device__ __forceinline__ void bwd_gemms_tc(umma::Ctx& cx, uint8_t* img, const 
 
   DN_MARK(4);
   // ---- 4. dke = V_new dH^T
-  umma::cp_async_wait<0>();
+  ld.wait();
   umma::pre_issue_sync();
   umma::issue<128, false, false>(cx, Y, X, VW, 128, false);
   umma::commit_wait(cx);
-  copy_image_async<128 * 16, NT>(Y, io.T);            // V_new has been consumed: T for step 5
+  ld.expect(B_KK);
+  ld.load(Y, io.T, B_KK);                             // V_new has been consumed: T for step 5
   umma::drain<NT, 128>(cx, 128, [&](int row, int col, const float (&v)[16]) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) DKE4[p4v(row, col + 4 * i)] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
@@ -187,13 +211,14 @@ __device__ __forceinline__ void bwd_gemms_tc(umma::Ctx& cx, uint8_t* img, const 
 
   DN_MARK(5);
   // ---- 5. dX = T^T dW, dY = T^T dV
-  umma::cp_async_wait<0>();
+  ld.wait();
   umma::pre_issue_sync();
   umma::issue<128, true, true>(cx, Y, P, 128, 0, false);
   umma::issue<VW, true, true>(cx, Y, Z, 128, 256, false);
   umma::commit_wait(cx);
-  copy_image_async<128 * 16, NT>(P, io.W);            // dW and dV have been consumed: W, U for step 6
-  copy_image_async<128 * PV, NT>(Z, io.U);
+  ld.expect(B_KK + B_KV);
+  ld.load(P, io.W, B_KK);                             // dW and dV have been consumed: W, U for step 6
+  ld.load(Z, io.U, B_KV);
   umma::drain<NT, 128>(cx, 0, [&](int row, int col, const float (&v)[16]) {
     float r[16];
 #pragma unroll
@@ -211,7 +236,7 @@ __device__ __forceinline__ void bwd_gemms_tc(umma::Ctx& cx, uint8_t* img, const 
 
   DN_MARK(6);
   // ---- 6. dA = -(dX W^T + dY U^T), strictly lower and same document
-  umma::cp_async_wait<0>();
+  ld.wait();
   umma::pre_issue_sync();
   umma::issue<128, false, false>(cx, Y2, P, 128, 0, false);
   umma::issue<128, false, false>(cx, X, Z, VW, 0, true);
