@@ -2,11 +2,15 @@
 // width 128 or 256): the adjoint of the state step's value-width contractions, of the prepass
 // (reference: src/deltanet_tpu/gdn2.py:243-493, 750-762) and of the fused prologue (558-575).
 //
-// Per (batch, exec head, chunk), 512 threads, one CTA per SM:
-//   G. nine matrix products (bwd_gemms_tc): V_new, dqe, dM, dW, dke, dX, dY, dA.
+// Per (batch, exec head, chunk), 512 threads, one CTA per SM, in this order:
+//   G. nine matrix products (bwd_gemms_tc): V_new, dqe, dM, dW, dke, dX, dY, dA.  Every operand is a
+//      bf16 image fetched by one bulk copy; dLambda_end comes from the reverse chain's partial sums.
+//   V. dv and dw from the bf16 image of dY that G leaves in shared memory; in the headline mode the
+//      rows of v, w, dv, dw move by bulk copies through padded staging rows.
 //   L. row normalisers and the cumulative log-decay of the chunk in shared memory.
-//   D. the 16x16 diagonal blocks of dA and dM, exact, one thread per (block, channel); this pass
-//      initialises dbeta', dq', dk'.
+//   D. the 16x16 diagonal blocks of dA and dM, exact, one thread per (block, channel), from
+//      shared-memory caches of k_hat, q_hat, beta (64 rows at a time); this pass initialises dbeta',
+//      dq', dk' and parks k_hat | q_hat (two bf16 per column) and beta in tensor memory.
 //   H. adjoints of A and M through the same three-level factorisation as the forward.  In one level
 //      every row is either a ROW of the level's entries (lower block of its pair) or a COLUMN (upper
 //      block), so with dA_s / dM_s the entries the level owns, KR the image holding beta-images on
@@ -14,15 +18,17 @@
 //        T1 = (dA_s + dA_s^T) KR,   T2 = (dM_s + dM_s^T) QK        (four MMAs, one drain)
 //        lower rows:  dbeta' += rowfac * T1,  dq' += rowfac * T2
 //        upper rows:  dk'    += colfac * (T1 + T2)
-//      with the same exp(Lam - Lam_ref) factors (all <= 1) as the forward.  Levels alternate between
-//      two halves of tensor memory, so a level's drain overlaps the next level's image build.
-//   E. combination into dLambda, d q_hat, d k_hat, d b (written), the l2norm adjoint and dq, dk.
+//      with the same exp(Lam - Lam_ref) factors (all <= 1) as the forward.  KR and QK are built from
+//      the tensor-memory cache; a level's drain overlaps the next level's image build.
+//   E. combination into dLambda, d q_hat, d k_hat, d b (written), the l2norm adjoint and dq, dk; the
+//      operands of the second half wait in tensor memory.
 //   R. dg by a within-document reverse cumulative sum plus the Lambda_end path; written with the
-//      gate adjoint.   V. dv and dw.
+//      gate adjoint.
 //
 // Thread mappings: phases that touch the operator's row-major tensors let a warp cover 8 rows x 4
-// pieces of 8 channels (row = 8 * warp + (lane & 7) is fixed per thread); phases that drain tensor
-// memory own one row per thread and use the panel layout of the scratch (see the header).
+// pieces of 8 channels (row = 8 * warp + (lane & 7) is fixed per thread); phases that drain or use
+// tensor memory own one row per thread (row = the thread's lane of its warp's lane quarter) and use
+// the panel layout of the scratch (see the header).
 #include <cstdio>
 #include "dn_chunkprep.cuh"
 #include "dn_kernels.cuh"
@@ -37,10 +43,6 @@ constexpr int NT = 512;
 __device__ __forceinline__ void ld2x4(const float4* p, float (&o)[8]) {      // scratch written by this CTA
   const float4 a = __ldcg(p), b = __ldcg(p + 128);
   o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
-}
-__device__ __forceinline__ void st2x4(float4* p, const float (&v)[8]) {
-  __stcg(p, make_float4(v[0], v[1], v[2], v[3]));
-  __stcg(p + 128, make_float4(v[4], v[5], v[6], v[7]));
 }
 __device__ __forceinline__ void out8(void* base, size_t off, int dt, const float (&v)[8]) {
   if (dt == DN_BF16) *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(base) + off) = umma::pack8(v);

@@ -16,7 +16,8 @@
 //
 // Every operand except dO arrives as a bf16 operand image that its producer wrote in exactly this
 // layout (W, U: forward prepass; the chunk-entry state S: forward chain; dV, dH: reverse chain; T:
-// forward prepass), so staging is a contiguous asynchronous copy with no register in between.  dO is
+// forward prepass), so staging is one bulk asynchronous copy per operand (cp.async.bulk, completion
+// counted on an mbarrier), issued while the previous accumulator drains.  dO is
 // the operator's row-major tensor: warps cover 8 rows x 4 pieces of 8 elements per step
 // (stage_coords).  fp32 results go to the per-CTA scratch in a PANEL layout, [column / 4][row][4]: a
 // thread that owns one row of tensor memory then writes 16 bytes next to its neighbours' and a warp
@@ -60,18 +61,6 @@ __device__ __forceinline__ void stage_coords(int e, int& p, int& x) {
   x = (w % (R / 8)) * 8 + (lane & 7);
   p = (w / (R / 8)) * 4 + (lane >> 3);
 }
-// An operand that lies in global memory as its image: asynchronous 16-byte copies of a contiguous
-// range, no registers.  The caller waits (umma::cp_async_wait<0>) before the operands are handed to
-// the tensor core.
-template <int N_U4, int NT>
-__device__ __forceinline__ void copy_image_async(uint4* dst, const __nv_bfloat16* src) {
-  static_assert(N_U4 % NT == 0, "whole passes");
-  const uint4* s = reinterpret_cast<const uint4*>(src);
-#pragma unroll
-  for (int it = 0; it < N_U4 / NT; ++it) umma::cp_async16(dst + it * NT + threadIdx.x, s + it * NT + threadIdx.x);
-  umma::cp_async_commit();
-}
-
 // Operand images by bulk asynchronous copies: one thread announces the bytes on the mbarrier and
 // issues one copy per image; everybody waits on the barrier (bounded) before the tensor core reads.
 struct ImgLoader {

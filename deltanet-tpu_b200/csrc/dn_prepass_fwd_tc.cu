@@ -165,10 +165,6 @@ __global__ void __launch_bounds__(NT, 1) prepass_fwd_tc_kernel(PrepassFwdArgs a,
     for (int half = 0; half < 2; ++half) {
       float* QHs = KHs + 64 * AP;                                       // q_hat (pitch AP)
       float* BEs = reinterpret_cast<float*>(smraw + OFF_TI);            // beta (pitch 128)
-#ifdef DN_STAGE_TWICE
-#pragma unroll 1
-      for (int rep = 0; rep < 2; ++rep)
-#endif
 #pragma unroll
       for (int it = 0; it < 2; ++it) {
         const int w = it * 16 + warp, xr = (w & 7) * 8 + (lane & 7), p = (w >> 3) * 4 + lgrp, x = half * 64 + xr;
