@@ -23,6 +23,9 @@ struct Overlap {
   cudaStream_t side = nullptr;
   cudaEvent_t ev[2] = {nullptr, nullptr};
   bool tried = false, ok = false;
+  // Held while one call enqueues its fork/join: a record and the wait that refers to it must not be
+  // separated by another host thread's record of the same event.
+  std::mutex enqueue;
 };
 Overlap* overlap_for_device() {
   static Overlap table[64];
@@ -333,6 +336,7 @@ int dn_chunk_fwd(const dn_shape* s, const void* q, const void* k, const void* v,
     // prepass of chunks [0, cut); then the chain over those chunks (side stream) next to the
     // prepass of chunks [cut, NC); then the rest of the chain
     if (!res->W || !res->U || !res->M || !res->qe || !res->ke || !res->lam_end) return DN_ERR_NULL_POINTER;
+    std::lock_guard<std::mutex> lock(ov->enqueue);
     cudaStream_t st = (cudaStream_t)stream;
     float* carry = reinterpret_cast<float*>(p);
     p += carry_bytes(g);
@@ -395,6 +399,7 @@ int dn_chunk_bwd(const dn_shape* s, const void* q, const void* k, const void* v,
     // stream, the partly filled round of CTAs) next to the rest of the chain; then the
     // chunk-parallel backward of chunks [0, cut) and the head sums
     if (!res->W || !res->U || !res->lam_end) return DN_ERR_NULL_POINTER;
+    std::lock_guard<std::mutex> lock(ov->enqueue);
     float* carry = reinterpret_cast<float*>(p);
     p += carry_bytes(g);
     BwdPlan pl;

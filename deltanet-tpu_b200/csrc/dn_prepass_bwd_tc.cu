@@ -274,8 +274,11 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
     // ---- L. rows, normalisers, cumulative decay
     row_norms_8x4(r, myrow, lgrp, rq_s, rk_s);
     lambda_scan_512(r, seg_s, LAM, TOTL, reset_s);
-    if (bulk_v && tid < C) umma::bulk_wait_read<0>();      // dv, dw have left their staging rows (reused below)
     __syncthreads();
+    if (bulk_v) {                                          // dv, dw have left their staging rows (reused below);
+      if (tid < C) umma::bulk_wait_read<0>();              // the copies had the whole of phase L to do so
+      __syncthreads();
+    }
 
     DN_MARK(8);
     // ---- D. diagonal 16x16 blocks, exact.  The blocks of dA and dM are staged in shared memory

@@ -57,6 +57,12 @@ __device__ __forceinline__ void copy_tile_async(uint4* dst, const __nv_bfloat16*
   }
 }
 
+// A (128,128) bf16 tile that lies in global memory as its operand image: one bulk copy, issued by
+// one thread, completion counted on an mbarrier (image layout only).
+__device__ __forceinline__ void bulk_tile(uint4* dst, const __nv_bfloat16* src, uint64_t* bar) {
+  umma::bulk_load(dst, src, TILE_U4 * 16, bar);
+}
+
 template <int VS>
 __device__ __forceinline__ void stage_rows(uint4* dst, int row, const float (&x)[VS], float sign = 1.f) {
 #pragma unroll
@@ -88,7 +94,7 @@ __host__ __device__ constexpr uint32_t tmem_cols(int vs) { return 3 * vs <= 128 
 template <int VS, bool WITH_OUT>
 __global__ void __launch_bounds__(128, 1) state_fwd_tc_kernel(StateArgs a) {
   extern __shared__ __align__(128) uint8_t sm[];
-  __shared__ uint64_t bar;
+  __shared__ uint64_t bar, tb[2];                       // MMA completion; tile arrival: W | qe, M, ke
   __shared__ uint32_t tmem_base;
   const Geo& g = a.g;
   constexpr int C = 128, K = 128;
@@ -100,13 +106,19 @@ __global__ void __launch_bounds__(128, 1) state_fwd_tc_kernel(StateArgs a) {
   uint4* sKE = sM + TILE_U4;
   uint4* sS = sKE + TILE_U4;
   uint4* sVn = sS + (VS / 8) * 128;
-  if (row == 0) { umma::mbar_init(&bar, 1); umma::fence_mbar_init(); }
+  if (row == 0) { umma::mbar_init(&bar, 1); umma::mbar_init(&tb[0], 1); umma::mbar_init(&tb[1], 1); umma::fence_mbar_init(); }
   if (warp == 0) umma::tmem_alloc(&tmem_base, tmem_cols(VS));
   umma::tc_fence_before();
   __syncthreads();
   umma::tc_fence_after();
   umma::Ctx cx{tmem_base, &bar, 0u, &g_device_error, false};
   constexpr uint32_t colP = 0, colO = VS, colS = 2 * VS;
+  const bool img = g.img;
+  uint32_t tph[2] = {0u, 0u};
+  auto tile_wait = [&](int i) {                         // bounded, like every wait here
+    if (!umma::mbar_wait(&tb[i], tph[i])) atomicExch(&g_device_error, 1);
+    tph[i] ^= 1u;
+  };
 
   const __nv_bfloat16* Wg = reinterpret_cast<const __nv_bfloat16*>(a.res.W);
   const __nv_bfloat16* QEg = reinterpret_cast<const __nv_bfloat16*>(a.res.qe);
@@ -117,12 +129,31 @@ __global__ void __launch_bounds__(128, 1) state_fwd_tc_kernel(StateArgs a) {
 
   const int cb = a.c_begin, ce = a.c_end;               // chunk range of this launch
   float* carry = a.carry ? a.carry + (((size_t)b * g.H + h) * K + row) * Vw + v0 : nullptr;
-  copy_tile_async(sW, Wg + (item0 + cb) * C * K, row, g.img);
-  umma::cp_async_commit();
-  copy_tile_async(sQE, QEg + (item0 + cb) * C * K, row, g.img);
-  copy_tile_async(sM, Mg + (item0 + cb) * C * C, row, g.img);
-  copy_tile_async(sKE, KEg + (item0 + cb) * C * K, row, g.img);
-  umma::cp_async_commit();
+  auto fetch_W = [&](size_t it_) {
+    if (img) {
+      if (row == 0) { umma::mbar_expect_tx(&tb[0], TILE_U4 * 16); bulk_tile(sW, Wg + it_ * C * K, &tb[0]); }
+    } else {
+      copy_tile_async(sW, Wg + it_ * C * K, row, false);
+    }
+    umma::cp_async_commit();
+  };
+  auto fetch_QMK = [&](size_t it_) {
+    if (img) {
+      if (row == 0) {
+        umma::mbar_expect_tx(&tb[1], 3 * TILE_U4 * 16);
+        bulk_tile(sQE, QEg + it_ * C * K, &tb[1]);
+        bulk_tile(sM, Mg + it_ * C * C, &tb[1]);
+        bulk_tile(sKE, KEg + it_ * C * K, &tb[1]);
+      }
+    } else {
+      copy_tile_async(sQE, QEg + it_ * C * K, row, false);
+      copy_tile_async(sM, Mg + it_ * C * C, row, false);
+      copy_tile_async(sKE, KEg + it_ * C * K, row, false);
+    }
+    umma::cp_async_commit();
+  };
+  fetch_W(item0 + cb);
+  fetch_QMK(item0 + cb);
 
   float S[VS];
 #pragma unroll
@@ -170,12 +201,11 @@ __global__ void __launch_bounds__(128, 1) state_fwd_tc_kernel(StateArgs a) {
     bool nis_new = false, nall_same = false;
     if (c + 1 < ce) chunk_flags(a.seg, g, b, c + 1, nis_new, nall_same);
 
-    umma::cp_async_wait<1>();                           // this chunk's W has landed
+    if (img) tile_wait(0); else umma::cp_async_wait<1>();      // this chunk's W has landed
     umma::pre_issue_sync();
     umma::issue<VS, false, true>(cx, sW, sS, K, colP, false);          // P = W S
     umma::commit_wait(cx);
-    if (c + 1 < ce) copy_tile_async(sW, Wg + (item + 1) * C * K, row, g.img);
-    umma::cp_async_commit();
+    if (c + 1 < ce) fetch_W(item + 1); else umma::cp_async_commit();
 
     float vn[VS];
     read_acc<VS>(cx, colP, warp, vn);
@@ -188,7 +218,7 @@ __global__ void __launch_bounds__(128, 1) state_fwd_tc_kernel(StateArgs a) {
     }
     stage_rows<VS>(sVn, row, vn);
 
-    umma::cp_async_wait<1>();                           // this chunk's qe, M, ke have landed
+    if (img) tile_wait(1); else umma::cp_async_wait<1>();      // this chunk's qe, M, ke have landed
     umma::pre_issue_sync();
     if (WITH_OUT) {
       umma::issue<VS, false, true>(cx, sQE, sS, K, colO, false);       // O  = qe S
@@ -196,12 +226,7 @@ __global__ void __launch_bounds__(128, 1) state_fwd_tc_kernel(StateArgs a) {
     }
     umma::issue<VS, true, true>(cx, sKE, sVn, C, colS, false);         // ke^T V_new
     umma::commit_wait(cx);
-    if (c + 1 < ce) {
-      copy_tile_async(sQE, QEg + (item + 1) * C * K, row, g.img);
-      copy_tile_async(sM, Mg + (item + 1) * C * C, row, g.img);
-      copy_tile_async(sKE, KEg + (item + 1) * C * K, row, g.img);
-    }
-    umma::cp_async_commit();
+    if (c + 1 < ce) fetch_QMK(item + 1); else umma::cp_async_commit();
 
     if (WITH_OUT) {
       float o[VS];
@@ -247,7 +272,7 @@ __global__ void __launch_bounds__(128, 1) state_fwd_tc_kernel(StateArgs a) {
 template <int VS>
 __global__ void __launch_bounds__(128, 1) state_bwd_tc_kernel(StateArgs a) {
   extern __shared__ __align__(128) uint8_t sm[];
-  __shared__ uint64_t bar;
+  __shared__ uint64_t bar, tb[2];                       // MMA completion; tile arrival: M, ke | qe, W
   __shared__ uint32_t tmem_base;
   const Geo& g = a.g;
   constexpr int C = 128, K = 128;
@@ -262,7 +287,12 @@ __global__ void __launch_bounds__(128, 1) state_bwd_tc_kernel(StateArgs a) {
   uint4* sdV = sdH + (VS / 8) * 128;
   float4* sSl = reinterpret_cast<float4*>(sdV + (VS / 8) * 128) + row;   // this thread's row of S (image path): piece j at sSl[j * 128]
   const bool img = g.img;
-  if (row == 0) { umma::mbar_init(&bar, 1); umma::fence_mbar_init(); }
+  if (row == 0) { umma::mbar_init(&bar, 1); umma::mbar_init(&tb[0], 1); umma::mbar_init(&tb[1], 1); umma::fence_mbar_init(); }
+  uint32_t tph[2] = {0u, 0u};
+  auto tile_wait = [&](int i) {                         // bounded, like every wait here
+    if (!umma::mbar_wait(&tb[i], tph[i])) atomicExch(&g_device_error, 1);
+    tph[i] ^= 1u;
+  };
   if (warp == 0) umma::tmem_alloc(&tmem_base, tmem_cols(VS));
   umma::tc_fence_before();
   __syncthreads();
@@ -286,13 +316,37 @@ __global__ void __launch_bounds__(128, 1) state_bwd_tc_kernel(StateArgs a) {
 #pragma unroll
     for (int j = 0; j < VS / 4; ++j) umma::cp_async16(sSl + j * 128, src + j);
   };
-  copy_tile_async(sM, Mg + last * C * C, row, g.img);
-  copy_tile_async(sKE, KEg + last * C * K, row, g.img);
-  if (img) copy_S_row(last);
-  umma::cp_async_commit();
-  copy_tile_async(sQE, QEg + last * C * K, row, g.img);
-  copy_tile_async(sW, Wg + last * C * K, row, g.img);
-  umma::cp_async_commit();
+  // image path: whole tiles by bulk copies on tb[], the S row by this thread's own cp.async group;
+  // otherwise everything by cp.async groups (two per chunk)
+  auto fetch_MK = [&](size_t it_) {
+    if (img) {
+      if (row == 0) {
+        umma::mbar_expect_tx(&tb[0], 2 * TILE_U4 * 16);
+        bulk_tile(sM, Mg + it_ * C * C, &tb[0]);
+        bulk_tile(sKE, KEg + it_ * C * K, &tb[0]);
+      }
+      copy_S_row(it_);
+    } else {
+      copy_tile_async(sM, Mg + it_ * C * C, row, false);
+      copy_tile_async(sKE, KEg + it_ * C * K, row, false);
+    }
+    umma::cp_async_commit();
+  };
+  auto fetch_QW = [&](size_t it_) {
+    if (img) {
+      if (row == 0) {
+        umma::mbar_expect_tx(&tb[1], 2 * TILE_U4 * 16);
+        bulk_tile(sQE, QEg + it_ * C * K, &tb[1]);
+        bulk_tile(sW, Wg + it_ * C * K, &tb[1]);
+      }
+    } else {
+      copy_tile_async(sQE, QEg + it_ * C * K, row, false);
+      copy_tile_async(sW, Wg + it_ * C * K, row, false);
+    }
+    umma::cp_async_commit();
+  };
+  fetch_MK(last);
+  fetch_QW(last);
 
   float dH[VS];
 #pragma unroll
@@ -357,7 +411,8 @@ __global__ void __launch_bounds__(128, 1) state_bwd_tc_kernel(StateArgs a) {
     }
     const float dec = all_same ? expf(fminf(__ldg(a.res.lam_end + item * K + row), 0.f)) : 0.f;
 
-    umma::cp_async_wait<1>();                           // M, ke (and the S row) of this chunk
+    umma::cp_async_wait<1>();                           // M, ke of this chunk (cp.async path); the S row (image path)
+    if (img) tile_wait(0);
     if (img) {                                          // partial sum of dLambda_end over this CTA's columns
       float part = 0.f;
 #pragma unroll
@@ -371,12 +426,7 @@ __global__ void __launch_bounds__(128, 1) state_bwd_tc_kernel(StateArgs a) {
     umma::issue<VS, true, true>(cx, sM, sdO, C, colV, false);          // dV  = M^T dO
     umma::issue<VS, false, true>(cx, sKE, sdH, K, colV, true);         //     + ke dH
     umma::commit_wait(cx);
-    if (c > cb) {
-      copy_tile_async(sM, Mg + (item - 1) * C * C, row, g.img);
-      copy_tile_async(sKE, KEg + (item - 1) * C * K, row, g.img);
-      if (img) copy_S_row(item - 1);
-    }
-    umma::cp_async_commit();
+    if (c > cb) fetch_MK(item - 1); else umma::cp_async_commit();
 
     float dv[VS];
     read_acc<VS>(cx, colV, warp, dv);
@@ -396,16 +446,12 @@ __global__ void __launch_bounds__(128, 1) state_bwd_tc_kernel(StateArgs a) {
     }
     stage_rows<VS>(sdV, row, dv, -1.f);                 // staged negated: the product below is -W^T dV
 
-    umma::cp_async_wait<1>();                           // qe, W of this chunk
+    if (img) tile_wait(1); else umma::cp_async_wait<1>();      // qe, W of this chunk
     umma::pre_issue_sync();
     umma::issue<VS, true, true>(cx, sQE, sdO, C, colH, false);         // qe^T dO
     umma::issue<VS, true, true>(cx, sW, sdV, C, colH, true);           // - W^T dV
     umma::commit_wait(cx);
-    if (c > cb) {
-      copy_tile_async(sQE, QEg + (item - 1) * C * K, row, g.img);
-      copy_tile_async(sW, Wg + (item - 1) * C * K, row, g.img);
-    }
-    umma::cp_async_commit();
+    if (c > cb) fetch_QW(item - 1); else umma::cp_async_commit();
 
     float dn_[VS];
     read_acc<VS>(cx, colH, warp, dn_);
