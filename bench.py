@@ -88,7 +88,7 @@ def alg_bytes(c):
 
 # dram__bytes_read.sum + dram__bytes_write.sum of a kernel's launches in one step of the headline workload
 # (both chunk ranges together), from the ncu capture summarised in profiles/chunk_step_kernels_headline.md
-NCU_DRAM_BYTES = {"prepass_bwd": 300.7e6, "prepass_fwd": 82.0e6, "state_fwd": 40.2e6, "state_bwd": 66.3e6}
+NCU_DRAM_BYTES = {"prepass_bwd": 301.1e6, "prepass_fwd": 82.1e6, "state_fwd": 40.5e6, "state_bwd": 66.2e6}
 
 
 # ------------------------------------------------------------------------------------------ inputs
