@@ -469,18 +469,21 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
       }
       umma::tc_fence_before();
     };
-    build(0);
-    for (int lv = 0; lv < 3; ++lv) {
-      const uint32_t tcol = 0;                             // the drain of level lv is over before level lv + 1 is issued
-      umma::pre_issue_sync();
-      umma::issue<128, false, true>(cx, I_DA, I_KR, C, tcol, false);        // dA_s   KR
-      umma::issue<128, true, true>(cx, I_DA, I_KR, C, tcol, true);          // dA_s^T KR
-      umma::issue<128, false, true>(cx, I_DM, I_QK, C, tcol + 128, false);  // dM_s   QK
-      umma::issue<128, true, true>(cx, I_DM, I_QK, C, tcol + 128, true);    // dM_s^T QK
-      umma::commit_wait(cx);
-      DN_MARK(10 + lv);
-      if (lv < 2) build(lv + 1);
-      drain_level(lv);
+    // one rolled loop, one call site each: build(lv) and drain(lv - 1) share a barrier interval (the
+    // images are free once the products of lv - 1 have completed), then the products of lv are issued
+#pragma unroll 1
+    for (int lv = 0; lv <= 3; ++lv) {
+      if (lv < 3) build(lv);
+      if (lv > 0) drain_level(lv - 1);
+      if (lv < 3) {
+        umma::pre_issue_sync();
+        umma::issue<128, false, true>(cx, I_DA, I_KR, C, 0, false);        // dA_s   KR
+        umma::issue<128, true, true>(cx, I_DA, I_KR, C, 0, true);          // dA_s^T KR
+        umma::issue<128, false, true>(cx, I_DM, I_QK, C, 128, false);      // dM_s   QK
+        umma::issue<128, true, true>(cx, I_DM, I_QK, C, 128, true);        // dM_s^T QK
+        umma::commit_wait(cx);
+        DN_MARK(10 + lv);
+      }
     }
     __syncthreads();
 

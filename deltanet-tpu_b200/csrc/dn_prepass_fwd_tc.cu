@@ -382,6 +382,7 @@ __global__ void __launch_bounds__(NT, 1) prepass_fwd_tc_kernel(PrepassFwdArgs a,
       }
       umma::tc_fence_before();
     };
+#pragma unroll 1
     for (int lv = 0; lv < 3; ++lv) {                       // (the images of level 0 were built above)
       const uint32_t tcol = 0;                             // the drain of level lv is over before level lv + 1 is issued
       umma::pre_issue_sync();
