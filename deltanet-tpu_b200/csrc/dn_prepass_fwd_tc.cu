@@ -14,10 +14,13 @@
 // rows and the k-images on upper rows, QK the q-images and the k-images, and
 //     level part of A = KR KR^T,   level part of M = QK KR^T       (one 128^3 MMA each);
 // entries outside the level's blocks are finite garbage that the drain ignores (entry (i,j) belongs
-// to the level of the highest bit in which i>>4 and j>>4 differ).  Levels alternate between two
-// halves of tensor memory, so a level's drain overlaps the next level's image build.  The 16x16
-// diagonal blocks are evaluated exactly, pair by pair, on the CUDA cores.  The reference does the
-// same with 32-row blocks and one reference per block row (gdn2.py:162-197).
+// to the level of the highest bit in which i>>4 and j>>4 differ).  A level's drain shares a barrier
+// interval with the next level's image build (the images are free once the level's products have
+// completed).  The 16x16 diagonal blocks are evaluated exactly, pair by pair, on the CUDA cores;
+// when k_hat and q_hat are exactly bf16 this pass runs first and parks k_hat | q_hat (two bf16 per
+// column) and beta in tensor memory, from where the qe / ke / X pass and all level images are built
+// without touching global memory again.  The reference does the same with 32-row blocks and one
+// reference per block row (gdn2.py:162-197).
 //
 // T = (I+A)^-1 is obtained as in the fp32 formulation (substitution on 16x16 blocks + block
 // merges, fp32 in shared memory); W = T X and U = T Y are tcgen05 MMAs on bf16 operands, which
