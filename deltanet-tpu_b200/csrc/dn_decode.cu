@@ -208,7 +208,7 @@ __global__ void __launch_bounds__(NTH) decode_kernel(DecodeArgs a) {
 
 // ---------------------------------------------------------------------------------------------
 // Bulk-copy pipeline for the common serving case: K = V = 128, bf16 state in and out, bf16 q/k/v,
-// fp32 per-channel gates.  The (128,128) bf16 state of one (sequence, value head) is 32 KB of
+// fp32 gates, each either per channel or one scalar per head.  The (128,128) bf16 state of one (sequence, value head) is 32 KB of
 // contiguous global memory, so it moves with ONE bulk asynchronous copy each way
 // (cp.async.bulk, completion on an mbarrier / a bulk group); the token vectors ride on the same
 // barrier.  A persistent CTA keeps a ring of STAGES tiles: while tile i is updated in place in
@@ -221,7 +221,6 @@ namespace bulk {
 constexpr int NT = 256, STAGES = 3, KD = 128, VD = 128;
 constexpr int OFF_Q = KD * VD * 2, OFF_K = OFF_Q + 256, OFF_V = OFF_K + 256, OFF_G = OFF_V + 256,
               OFF_B = OFF_G + 512, OFF_W = OFF_B + 512, STAGE_BYTES = OFF_W + 512;     // 35072, a multiple of 128
-constexpr uint32_t TX_BYTES = STAGE_BYTES;
 constexpr uint32_t SPIN = 1u << 22;
 
 __device__ __forceinline__ uint32_t s32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -263,18 +262,29 @@ __global__ void __launch_bounds__(NT, 2) decode_bulk_kernel(DecodeArgs a, int ti
   const int G = s.Hv / s.Hk;
   const bool l2 = s.flags & DN_QK_L2NORM, guard = s.flags & DN_STABILITY_GUARD;
 
+  // a gate that is one scalar per head cannot travel as a bulk copy (16 bytes at least): it comes by a
+  // 4-byte cp.async of the issuing thread, one committed group per issued tile
+  const bool gs = s.g_cols == 1, bs = s.b_cols == 1, ws = s.w_cols == 1, any_scalar = gs || bs || ws;
+  const uint32_t tx_bytes = KD * VD * 2 + 3 * 256 + (gs ? 0 : 512) + (bs ? 0 : 512) + (ws ? 0 : 512);
+  auto gate = [&](uint8_t* dst, const void* base, int b, int heads, int hv, bool scalar, uint64_t* bar) {
+    const float* src = reinterpret_cast<const float*>(base) + ((size_t)b * heads + dec_gate_head(hv, heads, s.Hk, s.Hv)) * (scalar ? 1 : KD);
+    if (scalar) asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(s32(dst)), "l"(src) : "memory");
+    else bulk_load(dst, src, 512, bar);
+  };
   auto issue = [&](int tile, int st) {               // one thread: the tile's state and token vectors
     const int hv = tile % s.Hv, b = tile / s.Hv, hk = hv / G;
     uint8_t* dst = ring + (size_t)st * STAGE_BYTES;
-    bar_expect(&full[st], TX_BYTES);
+    bar_expect(&full[st], tx_bytes);
     bulk_load(dst, reinterpret_cast<const __nv_bfloat16*>(a.state_in) + (size_t)tile * KD * VD, KD * VD * 2, &full[st]);
     bulk_load(dst + OFF_Q, reinterpret_cast<const __nv_bfloat16*>(a.q) + ((size_t)b * s.Hk + hk) * KD, 256, &full[st]);
     bulk_load(dst + OFF_K, reinterpret_cast<const __nv_bfloat16*>(a.k) + ((size_t)b * s.Hk + hk) * KD, 256, &full[st]);
     bulk_load(dst + OFF_V, reinterpret_cast<const __nv_bfloat16*>(a.v) + ((size_t)b * s.Hv + hv) * VD, 256, &full[st]);
-    bulk_load(dst + OFF_G, reinterpret_cast<const float*>(a.g) + ((size_t)b * s.g_heads + dec_gate_head(hv, s.g_heads, s.Hk, s.Hv)) * KD, 512, &full[st]);
-    bulk_load(dst + OFF_B, reinterpret_cast<const float*>(a.b) + ((size_t)b * s.b_heads + dec_gate_head(hv, s.b_heads, s.Hk, s.Hv)) * KD, 512, &full[st]);
-    bulk_load(dst + OFF_W, reinterpret_cast<const float*>(a.w) + ((size_t)b * s.w_heads + dec_gate_head(hv, s.w_heads, s.Hk, s.Hv)) * VD, 512, &full[st]);
+    gate(dst + OFF_G, a.g, b, s.g_heads, hv, gs, &full[st]);
+    gate(dst + OFF_B, a.b, b, s.b_heads, hv, bs, &full[st]);
+    gate(dst + OFF_W, a.w, b, s.w_heads, hv, ws, &full[st]);
   };
+  // (a group is committed whether or not a tile was issued, so that the count below stays in step)
+  auto commit_scalars = [&]() { if (any_scalar) asm volatile("cp.async.commit_group;" ::: "memory"); };
 
   if (tid == 0) {
     for (int i = 0; i < STAGES; ++i) bar_init(&full[i], 1);
@@ -284,8 +294,10 @@ __global__ void __launch_bounds__(NT, 2) decode_bulk_kernel(DecodeArgs a, int ti
   __syncthreads();
   const int first = blockIdx.x, stride = gridDim.x;
   if (tid == NT - 1)
-    for (int i = 0; i < STAGES - 1; ++i)
+    for (int i = 0; i < STAGES - 1; ++i) {
       if (first + i * stride < tiles) issue(first + i * stride, i);
+      commit_scalars();
+    }
 
   const int vc = tid & 15, rg = tid >> 4;              // 8 columns, rows rg + 16 r
   int it = 0;
@@ -293,6 +305,8 @@ __global__ void __launch_bounds__(NT, 2) decode_bulk_kernel(DecodeArgs a, int ti
     const int st = it % STAGES;
     const uint32_t parity = (uint32_t)(it / STAGES) & 1u;
     if (!bar_wait(&full[st], parity)) { dead_s = 1; if (err) atomicExch(err, 1); }
+    // STAGES - 1 + it groups are committed by now and this tile's is number it: all but the newest STAGES - 2
+    if (any_scalar && tid == NT - 1) asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 2) : "memory");
     __syncthreads();
     if (dead_s) break;
     uint8_t* buf = ring + (size_t)st * STAGE_BYTES;
@@ -314,11 +328,11 @@ __global__ void __launch_bounds__(NT, 2) decode_bulk_kernel(DecodeArgs a, int ti
       }
     } else if (tid >= 128) {
       const int j = tid - 128;
-      wv[j] = reinterpret_cast<const float*>(buf + OFF_W)[j] * __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(buf + OFF_V)[j]);
+      wv[j] = reinterpret_cast<const float*>(buf + OFF_W)[ws ? 0 : j] * __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(buf + OFF_V)[j]);
     }
     __syncthreads();
     if (tid < KD) {
-      float gg = fminf(reinterpret_cast<const float*>(buf + OFF_G)[tid], 0.f), bb = reinterpret_cast<const float*>(buf + OFF_B)[tid];
+      float gg = fminf(reinterpret_cast<const float*>(buf + OFF_G)[gs ? 0 : tid], 0.f), bb = reinterpret_cast<const float*>(buf + OFF_B)[bs ? 0 : tid];
       if (guard) { bb = fmaxf(bb, 0.f); gg = fminf(gg, -1e-6f); }
       dec[tid] = expf(gg);
       beta[tid] = bb * ks[tid];
@@ -329,6 +343,7 @@ __global__ void __launch_bounds__(NT, 2) decode_bulk_kernel(DecodeArgs a, int ti
       bulk_wait_read<0>();
       const int nxt = tile + (STAGES - 1) * stride;
       if (nxt < tiles) issue(nxt, (it + STAGES - 1) % STAGES);
+      commit_scalars();
     }
     __syncthreads();
 
@@ -406,14 +421,17 @@ __global__ void __launch_bounds__(NT, 2) decode_bulk_kernel(DecodeArgs a, int ti
     }
     // the next tile's first barrier orders these reads of red / vnew before they are rewritten
   }
-  if (tid == NT - 1) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  if (tid == NT - 1) {
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    if (any_scalar) asm volatile("cp.async.wait_all;" ::: "memory");
+  }
 }
 
 inline bool eligible(const DecodeArgs& a) {
   const dn_decode_shape& s = a.s;
   if (s.K != KD || s.V != VD) return false;
   if (s.state_in_dtype != DN_BF16 || s.state_out_dtype != DN_BF16 || s.qkv_dtype != DN_BF16 || s.gate_dtype != DN_F32) return false;
-  if (s.g_cols != KD || s.b_cols != KD || s.w_cols != VD) return false;
+  if ((s.g_cols != KD && s.g_cols != 1) || (s.b_cols != KD && s.b_cols != 1) || (s.w_cols != VD && s.w_cols != 1)) return false;
   const void* ptrs[] = {a.q, a.k, a.v, a.g, a.b, a.w, a.state_in, a.state_out};
   for (const void* p : ptrs)
     if (reinterpret_cast<uintptr_t>(p) & 15) return false;

@@ -169,6 +169,32 @@ def test_decode_bulk_pipeline_against_oracle(dn, B):
     assert dn._lib.lib().dn_device_error() == 0
 
 
+@pytest.mark.parametrize("layout", ["scalar", "scalar_at_value_heads", "mixed"])
+def test_decode_bulk_pipeline_scalar_gates(dn, layout):
+    """Per-head scalar gates (Gated DeltaNet's layout) on the bulk-copy pipelined decode kernel:
+    the scalars travel beside the bulk copies, one small asynchronous copy per gate and tile.
+    400 sequences x 4 value heads = 1600 tiles, more than five trips round every CTA's ring."""
+    B, Hk, Hv, K, V = 400, 2, 4, 128, 128
+    gen = torch.Generator().manual_seed(123)
+    rn = lambda *s: torch.randn(*s, generator=gen)
+    st_cpu = (rn(B, Hv, K, V) * 0.1).to(torch.bfloat16)
+    st_gpu = st_cpu.cuda()
+    for step in range(2):
+        q, k, v = (rn(B, Hk, K).to(torch.bfloat16), rn(B, Hk, K).to(torch.bfloat16), rn(B, Hv, V).to(torch.bfloat16))
+        if layout == "scalar":
+            g, b, w = -torch.exp(rn(B, Hk) * 0.39 - 1.0), torch.sigmoid(rn(B, Hk) * 0.39), torch.sigmoid(rn(B, Hv) * 0.39)
+        elif layout == "scalar_at_value_heads":
+            g, b, w = -torch.exp(rn(B, Hv) * 0.39 - 1.0), torch.sigmoid(rn(B, Hv) * 0.39), torch.sigmoid(rn(B, Hv) * 0.39)
+        else:
+            g, b, w = -torch.exp(rn(B, Hk, K) * 0.39 - 1.0), torch.sigmoid(rn(B, Hk) * 0.39), torch.sigmoid(rn(B, Hv) * 0.39)
+        o_ref, st_cpu = O.decode_step(q, k, v, g, b, w, st_cpu, qk_l2norm=True, state_dtype=torch.bfloat16)
+        o, st_gpu = dn.gdn2_decode_step(q.cuda(), k.cuda(), v.cuda(), g.cuda(), b.cuda(), w.cuda(), st_gpu,
+                                        qk_l2norm=True, state_dtype="bfloat16")
+        assert O.rel_l2(o.float().cpu(), o_ref.float()) < 1e-2, step
+        assert O.rel_l2(st_gpu.float().cpu(), st_cpu.float()) < 1e-2, step
+    assert dn._lib.lib().dn_device_error() == 0
+
+
 # ------------------------------------------------------------------------------- oracle parity
 @pytest.mark.parametrize("C,K,V", [(64, 64, 64), (128, 128, 128), (64, 128, 64), (128, 64, 128)])
 @pytest.mark.parametrize("Hk,Hv", [(2, 2), (2, 4)])
