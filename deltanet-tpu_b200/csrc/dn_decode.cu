@@ -207,9 +207,9 @@ __global__ void __launch_bounds__(NTH) decode_kernel(DecodeArgs a) {
 }
 
 // ---------------------------------------------------------------------------------------------
-// Bulk-copy pipeline for the common serving case: K = V = 128, bf16 state in and out, bf16 q/k/v,
-// fp32 gates, each either per channel or one scalar per head.  The (128,128) bf16 state of one (sequence, value head) is 32 KB of
-// contiguous global memory, so it moves with ONE bulk asynchronous copy each way
+// Bulk-copy pipeline for the common serving case: K = V = 128, state in and out in one dtype, bf16 q/k/v,
+// fp32 gates, each either per channel or one scalar per head.  The (128,128) state of one (sequence, value head) is 32 KB (bf16) or 64 KB (fp32)
+// of contiguous global memory, so it moves with ONE bulk asynchronous copy each way
 // (cp.async.bulk, completion on an mbarrier / a bulk group); the token vectors ride on the same
 // barrier.  A persistent CTA keeps a ring of STAGES tiles: while tile i is updated in place in
 // shared memory, tiles i+1 .. i+STAGES-1 are in flight and tile i-1 drains to global memory.  No
@@ -219,8 +219,13 @@ __global__ void __launch_bounds__(NTH) decode_kernel(DecodeArgs a) {
 namespace bulk {
 
 constexpr int NT = 256, STAGES = 3, KD = 128, VD = 128;
-constexpr int OFF_Q = KD * VD * 2, OFF_K = OFF_Q + 256, OFF_V = OFF_K + 256, OFF_G = OFF_V + 256,
-              OFF_B = OFF_G + 512, OFF_W = OFF_B + 512, STAGE_BYTES = OFF_W + 512;     // 35072, a multiple of 128
+// one stage of the ring: the state tile (SB bytes per element), then q, k, v (bf16) and g, b, w (fp32)
+template <int SB>
+struct Stage {
+  static constexpr int TILE = KD * VD * SB;
+  static constexpr int OFF_Q = TILE, OFF_K = OFF_Q + 256, OFF_V = OFF_K + 256, OFF_G = OFF_V + 256,
+                       OFF_B = OFF_G + 512, OFF_W = OFF_B + 512, BYTES = OFF_W + 512;   // 35072 / 67840, multiples of 128
+};
 constexpr uint32_t SPIN = 1u << 22;
 
 __device__ __forceinline__ uint32_t s32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -251,7 +256,11 @@ template <int N>
 __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
 __device__ __forceinline__ void fence_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
-__global__ void __launch_bounds__(NT, 2) decode_bulk_kernel(DecodeArgs a, int tiles, int* err) {
+template <int SB>                                        // bytes per state element: 2 (bf16, two CTAs per SM) or 4 (fp32, one)
+__global__ void __launch_bounds__(NT, SB == 2 ? 2 : 1) decode_bulk_kernel(DecodeArgs a, int tiles, int* err) {
+  using LY = Stage<SB>;
+  constexpr int TILE = LY::TILE, OFF_Q = LY::OFF_Q, OFF_K = LY::OFF_K, OFF_V = LY::OFF_V, OFF_G = LY::OFF_G,
+                OFF_B = LY::OFF_B, OFF_W = LY::OFF_W, STAGE_BYTES = LY::BYTES;
   extern __shared__ __align__(128) uint8_t ring[];
   __shared__ __align__(8) uint64_t full[STAGES];
   __shared__ float qs[KD], ks[KD], dec[KD], beta[KD], wv[VD], vnew[VD];
@@ -265,7 +274,7 @@ __global__ void __launch_bounds__(NT, 2) decode_bulk_kernel(DecodeArgs a, int ti
   // a gate that is one scalar per head cannot travel as a bulk copy (16 bytes at least): it comes by a
   // 4-byte cp.async of the issuing thread, one committed group per issued tile
   const bool gs = s.g_cols == 1, bs = s.b_cols == 1, ws = s.w_cols == 1, any_scalar = gs || bs || ws;
-  const uint32_t tx_bytes = KD * VD * 2 + 3 * 256 + (gs ? 0 : 512) + (bs ? 0 : 512) + (ws ? 0 : 512);
+  const uint32_t tx_bytes = TILE + 3 * 256 + (gs ? 0 : 512) + (bs ? 0 : 512) + (ws ? 0 : 512);
   auto gate = [&](uint8_t* dst, const void* base, int b, int heads, int hv, bool scalar, uint64_t* bar) {
     const float* src = reinterpret_cast<const float*>(base) + ((size_t)b * heads + dec_gate_head(hv, heads, s.Hk, s.Hv)) * (scalar ? 1 : KD);
     if (scalar) asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(s32(dst)), "l"(src) : "memory");
@@ -275,7 +284,7 @@ __global__ void __launch_bounds__(NT, 2) decode_bulk_kernel(DecodeArgs a, int ti
     const int hv = tile % s.Hv, b = tile / s.Hv, hk = hv / G;
     uint8_t* dst = ring + (size_t)st * STAGE_BYTES;
     bar_expect(&full[st], tx_bytes);
-    bulk_load(dst, reinterpret_cast<const __nv_bfloat16*>(a.state_in) + (size_t)tile * KD * VD, KD * VD * 2, &full[st]);
+    bulk_load(dst, reinterpret_cast<const uint8_t*>(a.state_in) + (size_t)tile * TILE, TILE, &full[st]);
     bulk_load(dst + OFF_Q, reinterpret_cast<const __nv_bfloat16*>(a.q) + ((size_t)b * s.Hk + hk) * KD, 256, &full[st]);
     bulk_load(dst + OFF_K, reinterpret_cast<const __nv_bfloat16*>(a.k) + ((size_t)b * s.Hk + hk) * KD, 256, &full[st]);
     bulk_load(dst + OFF_V, reinterpret_cast<const __nv_bfloat16*>(a.v) + ((size_t)b * s.Hv + hv) * VD, 256, &full[st]);
@@ -348,20 +357,27 @@ __global__ void __launch_bounds__(NT, 2) decode_bulk_kernel(DecodeArgs a, int ti
     __syncthreads();
 
     // ---- decay, erase projection e = Sd^T beta
-    uint4* tile4 = reinterpret_cast<uint4*>(buf);          // row kk: 16 vectors of 8 columns
+    uint4* tile4 = reinterpret_cast<uint4*>(buf);          // row kk: 16 (bf16) or 32 (fp32) vectors; a thread owns 8 columns
     float S[8][8], part[8];
 #pragma unroll
     for (int c = 0; c < 8; ++c) part[c] = 0.f;
 #pragma unroll
     for (int r = 0; r < 8; ++r) {
       const int kk = rg + 16 * r;
-      const uint4 v = tile4[kk * 16 + vc];
-      const uint32_t u[4] = {v.x, v.y, v.z, v.w};
       const float d = dec[kk], be = beta[kk];
+      if (SB == 2) {
+        const uint4 v = tile4[kk * 16 + vc];
+        const uint32_t u[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {                          // a reset sequence starts from zeros whatever the buffer holds
-        S[r][2 * j] = zero ? 0.f : __uint_as_float(u[j] << 16) * d;
-        S[r][2 * j + 1] = zero ? 0.f : __uint_as_float(u[j] & 0xffff0000u) * d;
+        for (int j = 0; j < 4; ++j) {                        // a reset sequence starts from zeros whatever the buffer holds
+          S[r][2 * j] = zero ? 0.f : __uint_as_float(u[j] << 16) * d;
+          S[r][2 * j + 1] = zero ? 0.f : __uint_as_float(u[j] & 0xffff0000u) * d;
+        }
+      } else {
+        const uint4 v0 = tile4[kk * 32 + 2 * vc], v1 = tile4[kk * 32 + 2 * vc + 1];
+        const uint32_t u[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) S[r][j] = zero ? 0.f : __uint_as_float(u[j]) * d;
       }
 #pragma unroll
       for (int c = 0; c < 8; ++c) part[c] = fmaf(be, S[r][c], part[c]);
@@ -393,13 +409,18 @@ __global__ void __launch_bounds__(NT, 2) decode_bulk_kernel(DecodeArgs a, int ti
         S[r][c] = fmaf(kx, vn[c], S[r][c]);
         part[c] = fmaf(qx, S[r][c], part[c]);
       }
-      uint32_t u[4];
+      if (SB == 2) {
+        uint32_t u[4];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        __nv_bfloat162 h2 = __floats2bfloat162_rn(S[r][2 * j], S[r][2 * j + 1]);
-        u[j] = *reinterpret_cast<uint32_t*>(&h2);
+        for (int j = 0; j < 4; ++j) {
+          __nv_bfloat162 h2 = __floats2bfloat162_rn(S[r][2 * j], S[r][2 * j + 1]);
+          u[j] = *reinterpret_cast<uint32_t*>(&h2);
+        }
+        tile4[kk * 16 + vc] = make_uint4(u[0], u[1], u[2], u[3]);
+      } else {
+        tile4[kk * 32 + 2 * vc] = make_uint4(__float_as_uint(S[r][0]), __float_as_uint(S[r][1]), __float_as_uint(S[r][2]), __float_as_uint(S[r][3]));
+        tile4[kk * 32 + 2 * vc + 1] = make_uint4(__float_as_uint(S[r][4]), __float_as_uint(S[r][5]), __float_as_uint(S[r][6]), __float_as_uint(S[r][7]));
       }
-      tile4[kk * 16 + vc] = make_uint4(u[0], u[1], u[2], u[3]);
     }
 #pragma unroll
     for (int c = 0; c < 8; ++c) part[c] += __shfl_xor_sync(0xffffffffu, part[c], 16);
@@ -410,7 +431,7 @@ __global__ void __launch_bounds__(NT, 2) decode_bulk_kernel(DecodeArgs a, int ti
     fence_async();                                           // the tile was written through the generic proxy
     __syncthreads();
     if (tid == NT - 1) {                                     // the thread that also waits on the bulk groups
-      bulk_store(reinterpret_cast<__nv_bfloat16*>(a.state_out) + (size_t)tile * KD * VD, buf, KD * VD * 2);
+      bulk_store(reinterpret_cast<uint8_t*>(a.state_out) + (size_t)tile * TILE, buf, TILE);
       bulk_commit();
     }
     if (tid < VD) {
@@ -430,7 +451,7 @@ __global__ void __launch_bounds__(NT, 2) decode_bulk_kernel(DecodeArgs a, int ti
 inline bool eligible(const DecodeArgs& a) {
   const dn_decode_shape& s = a.s;
   if (s.K != KD || s.V != VD) return false;
-  if (s.state_in_dtype != DN_BF16 || s.state_out_dtype != DN_BF16 || s.qkv_dtype != DN_BF16 || s.gate_dtype != DN_F32) return false;
+  if (s.state_in_dtype != s.state_out_dtype || s.qkv_dtype != DN_BF16 || s.gate_dtype != DN_F32) return false;
   if ((s.g_cols != KD && s.g_cols != 1) || (s.b_cols != KD && s.b_cols != 1) || (s.w_cols != VD && s.w_cols != 1)) return false;
   const void* ptrs[] = {a.q, a.k, a.v, a.g, a.b, a.w, a.state_in, a.state_out};
   for (const void* p : ptrs)
@@ -478,13 +499,22 @@ int launch_decode(const dn_decode_shape& s, const void* q, const void* k, const 
   DecodeArgs a{s, q, k, v, g, b, w, state_in, reset, out, state_out};
   if (bulk::eligible(a) && !force_simt()) {
     const int tiles = s.B * s.Hv;
-    const int grid = tiles < 2 * 148 ? tiles : 2 * 148;
-    const size_t smem = (size_t)bulk::STAGES * bulk::STAGE_BYTES;
-    cudaFuncSetAttribute(bulk::decode_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    bulk::decode_bulk_kernel<<<grid, bulk::NT, smem, st>>>(a, tiles, device_error_ptr());
+    const bool sb16 = s.state_in_dtype == DN_BF16;
+    const int slots = (sb16 ? 2 : 1) * 148;
+    const int grid = tiles < slots ? tiles : slots;
+    if (sb16) {
+      const size_t smem = (size_t)bulk::STAGES * bulk::Stage<2>::BYTES;
+      cudaFuncSetAttribute(bulk::decode_bulk_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      bulk::decode_bulk_kernel<2><<<grid, bulk::NT, smem, st>>>(a, tiles, device_error_ptr());
+    } else {
+      const size_t smem = (size_t)bulk::STAGES * bulk::Stage<4>::BYTES;
+      cudaFuncSetAttribute(bulk::decode_bulk_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      bulk::decode_bulk_kernel<4><<<grid, bulk::NT, smem, st>>>(a, tiles, device_error_ptr());
+    }
     if (cudaGetLastError() != cudaSuccess) return DN_ERR_CUDA_LAUNCH;
     if (s.flags & DN_STABILITY_GUARD) {
-      decode_cap_kernel<__nv_bfloat16><<<s.B * s.Hv, 256, 0, st>>>(reinterpret_cast<__nv_bfloat16*>(a.state_out), s.K * s.V, s.stability_tau);
+      if (sb16) decode_cap_kernel<__nv_bfloat16><<<s.B * s.Hv, 256, 0, st>>>(reinterpret_cast<__nv_bfloat16*>(a.state_out), s.K * s.V, s.stability_tau);
+      else decode_cap_kernel<float><<<s.B * s.Hv, 256, 0, st>>>(reinterpret_cast<float*>(a.state_out), s.K * s.V, s.stability_tau);
       if (cudaGetLastError() != cudaSuccess) return DN_ERR_CUDA_LAUNCH;
     }
     return DN_OK;

@@ -143,15 +143,18 @@ def test_golden_decode_step(dn, golden_dir):
     assert O.rel_l2(ns2.cpu(), d["new_state_fp32"]) < 1e-5
 
 
+@pytest.mark.parametrize("state_dtype", ["bfloat16", "float32"])
 @pytest.mark.parametrize("B", [5, 256])
-def test_decode_bulk_pipeline_against_oracle(dn, B):
-    """The serving configuration (bf16 q/k/v, fp32 per-channel gates, bf16 state in and out,
+def test_decode_bulk_pipeline_against_oracle(dn, B, state_dtype):
+    """The serving configuration (bf16 q/k/v, fp32 gates, state in and out in one dtype,
     K = V = 128) takes the bulk-copy pipelined kernel; B = 256 gives 1024 tiles, i.e. several trips
     round the ring of every persistent CTA.  A reset sequence must ignore what its buffer holds."""
     Hk, Hv, K, V = 2, 4, 128, 128
+    sdt = getattr(torch, state_dtype)
+    tol = 1e-2 if sdt == torch.bfloat16 else 1e-5
     gen = torch.Generator().manual_seed(90 + B)
     rn = lambda *s: torch.randn(*s, generator=gen)
-    state = (rn(B, Hv, K, V) * 0.1).to(torch.bfloat16)
+    state = (rn(B, Hv, K, V) * 0.1).to(sdt)
     reset = torch.zeros(B, dtype=torch.bool)
     reset[1] = True
     state[1] = float("nan")
@@ -160,12 +163,12 @@ def test_decode_bulk_pipeline_against_oracle(dn, B):
         q, k, v = (rn(B, Hk, K).to(torch.bfloat16), rn(B, Hk, K).to(torch.bfloat16), rn(B, Hv, V).to(torch.bfloat16))
         g, b, w = -torch.exp(rn(B, Hk, K) * 0.39 - 1.0), torch.sigmoid(rn(B, Hk, K) * 0.39), torch.sigmoid(rn(B, Hv, V) * 0.39)
         rs = reset if step == 0 else None
-        o_ref, st_cpu = O.decode_step(q, k, v, g, b, w, st_cpu, reset=rs, qk_l2norm=True, state_dtype=torch.bfloat16)
+        o_ref, st_cpu = O.decode_step(q, k, v, g, b, w, st_cpu, reset=rs, qk_l2norm=True, state_dtype=sdt)
         o, st_gpu = dn.gdn2_decode_step(q.cuda(), k.cuda(), v.cuda(), g.cuda(), b.cuda(), w.cuda(), st_gpu,
-                                        reset=None if rs is None else rs.cuda(), qk_l2norm=True, state_dtype="bfloat16")
-        assert st_gpu.dtype == torch.bfloat16 and o.dtype == torch.bfloat16
-        assert O.rel_l2(o.float().cpu(), o_ref.float()) < 1e-2, step
-        assert O.rel_l2(st_gpu.float().cpu(), st_cpu.float()) < 1e-2, step
+                                        reset=None if rs is None else rs.cuda(), qk_l2norm=True, state_dtype=state_dtype)
+        assert st_gpu.dtype == sdt and o.dtype == torch.bfloat16
+        assert O.rel_l2(o.float().cpu(), o_ref.float()) < 1e-2, step          # the output is rounded to bf16
+        assert O.rel_l2(st_gpu.float().cpu(), st_cpu.float()) < tol, step
     assert dn._lib.lib().dn_device_error() == 0
 
 
