@@ -322,29 +322,28 @@ __global__ void __launch_bounds__(NT, SB == 2 ? 2 : 1) decode_bulk_kernel(Decode
     const int hv = tile % s.Hv, b = tile / s.Hv;
     const bool zero = a.reset && a.reset[b];
 
-    // ---- token vectors: q, k normalised (warps 0, 1), w*v (threads 128..255)
-    if (warp < 2) {
-      const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(buf + (warp == 0 ? OFF_Q : OFF_K));
-      float x[4], ss = 0.f;
+    // ---- token vectors in one phase: warps 0..3 take k (every warp computes the norm for itself),
+    //      the decay and beta = b * k_hat; warps 4..7 take q and w * v
+    {
+      const bool kside = tid < 128;
+      const int j = tid & 127;
+      const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(buf + (kside ? OFF_K : OFF_Q));
+      float ss = 0.f;
 #pragma unroll
-      for (int u = 0; u < 4; ++u) { x[u] = __bfloat162float(src[lane + 32 * u]); ss += x[u] * x[u]; }
+      for (int u = 0; u < 4; ++u) { const float x = __bfloat162float(src[lane + 32 * u]); ss += x * x; }
       ss = warp_sum(ss);
       const float r = l2 ? 1.f / sqrtf(ss + 1e-6f) : 1.f;
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        if (warp == 0) qs[lane + 32 * u] = x[u] * r * s.scale;
-        else ks[lane + 32 * u] = x[u] * r;
+      const float mine = __bfloat162float(src[j]) * r;
+      if (kside) {
+        float gg = fminf(reinterpret_cast<const float*>(buf + OFF_G)[gs ? 0 : j], 0.f), bb = reinterpret_cast<const float*>(buf + OFF_B)[bs ? 0 : j];
+        if (guard) { bb = fmaxf(bb, 0.f); gg = fminf(gg, -1e-6f); }
+        ks[j] = mine;
+        dec[j] = expf(gg);
+        beta[j] = bb * mine;
+      } else {
+        qs[j] = mine * s.scale;
+        wv[j] = reinterpret_cast<const float*>(buf + OFF_W)[ws ? 0 : j] * __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(buf + OFF_V)[j]);
       }
-    } else if (tid >= 128) {
-      const int j = tid - 128;
-      wv[j] = reinterpret_cast<const float*>(buf + OFF_W)[ws ? 0 : j] * __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(buf + OFF_V)[j]);
-    }
-    __syncthreads();
-    if (tid < KD) {
-      float gg = fminf(reinterpret_cast<const float*>(buf + OFF_G)[gs ? 0 : tid], 0.f), bb = reinterpret_cast<const float*>(buf + OFF_B)[bs ? 0 : tid];
-      if (guard) { bb = fmaxf(bb, 0.f); gg = fminf(gg, -1e-6f); }
-      dec[tid] = expf(gg);
-      beta[tid] = bb * ks[tid];
     }
     // refill the stage that tile it-1 used: its store (issued a while ago) must have finished reading
     // shared memory
