@@ -17,6 +17,10 @@ One JSON line is printed by rank 0:
   decode       state-stream GB/s of the decode step with its own roofline,
   cpu_baseline the CPU oracle (a port of the reference's chunked path) on the host cores.
 
+`--only sp` runs a different workload and prints its own line: KDA-style fwd+bwd on one packed
+sequence of 131072 tokens, split over the ranks (strong scaling; the state chain crosses the ranks
+by NCCL point-to-point).
+
 `--impl reference` times the CPU oracle instead (the reference itself needs an array
 library that is not installed on the box; the oracle restates its chunked algorithm).
 With N>1 GPUs every rank runs the same per-GPU workload on its own data (batch
@@ -330,6 +334,56 @@ def run_reference(args):
 
 
 # ------------------------------------------------------------------------------------------ main arm
+# ------------------------------------------------------------------------------------------ long sequence
+SPCFG = dict(L=131072, H=32, K=128, V=128, chunk=128)
+
+
+def sp_leg(args, dn, dist, world, rank, dev):
+    """KDA-style fwd+bwd on ONE packed sequence of 131072 tokens (channel-wise decay, per-head beta,
+    documents of 2048..32768 tokens), split into equal contiguous shards over the ranks: the state
+    chain crosses the ranks by NCCL point-to-point, everything else is local.  Total work is fixed, so
+    this is strong scaling.  chunk_size is 128, the only size the reference's operator accepts."""
+    from deltanet_b200 import sp
+    c = SPCFG
+    L, H, K, V = c["L"], c["H"], c["K"], c["V"]
+    gen = torch.Generator().manual_seed(4000)
+    lens, tot = [], 0
+    while tot < L:
+        n = int(torch.randint(2048, 32769, (1,), generator=gen))
+        lens.append(min(n, L - tot))
+        tot += lens[-1]
+    seg = torch.repeat_interleave(torch.arange(len(lens), dtype=torch.int32), torch.tensor(lens))[None]
+    lo, hi = rank * L // world, (rank + 1) * L // world
+    n = hi - lo
+    g2 = torch.Generator(device=dev).manual_seed(4100 + rank)
+    rn = lambda *sh: torch.randn(*sh, generator=g2, device=dev)
+    q, k, v = (rn(1, n, H, K).bfloat16().requires_grad_(), rn(1, n, H, K).bfloat16().requires_grad_(),
+               rn(1, n, H, V).bfloat16().requires_grad_())
+    g = (-torch.exp(rn(1, n, H, K) * 0.39 - 1.0)).requires_grad_()
+    beta = torch.sigmoid(rn(1, n, H)).requires_grad_()
+    do = rn(1, n, H, V).bfloat16()
+    seg_d = seg[:, lo:hi].contiguous().to(dev)
+
+    def step():
+        if world == 1:
+            o = dn.chunk_kda(q, k, v, g, beta, segment_ids=seg_d, chunk_size=c["chunk"], qk_l2norm=True)
+        else:
+            o, _ = sp.chunk_gdn2_sp(q, k, v, g, beta, beta, segment_ids=seg_d, chunk_size=c["chunk"],
+                                    precision="bf16", qk_l2norm=True)
+        torch.autograd.grad(o, [q, k, v, g, beta], grad_outputs=do)
+
+    steps = max(2, min(args.steps, 5))
+    ms = time_steps(step, steps, 3, dist) / steps
+    if rank == 0:
+        print(json.dumps(dict(only="sp", metric="kda fwd+bwd tokens/s, one sequence split over the GPUs",
+                              value=L / (ms * 1e-3), unit="tokens/s", n_gpus=world, steps=steps, warmup=3,
+                              ms_per_step=ms, scaling="strong", dtype="bf16", data="synthetic",
+                              config=dict(workload="chunk_kda fwd+bwd B=1 L=131072 H=32 K=V=128 chunk=128 bf16 "
+                                                   "qk_l2norm, documents of 2048..32768 tokens",
+                                          parallelism=f"sequence-sharded x{world}, state chain by NCCL send/recv"))),
+              flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -337,7 +391,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--only", default="all", choices=["all", "chunk", "decode"],
+    ap.add_argument("--only", default="all", choices=["all", "chunk", "decode", "sp"],
                     help="profiling aid: run only the chunked fwd+bwd device loop, or only the decode loop")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -358,6 +412,9 @@ def main():
     peaks = measured_peaks()
     tokens = CFG["B"] * CFG["L"]
 
+    if args.only == "sp":
+        sp_leg(args, dn, dist, world, rank, dev)
+        return
     if args.only == "decode":
         dj = DecodeJob(DEC, dev, seed=3000 + rank, heads=DEC["Hv"] // world)
         ms_dec = time_steps(dj.step, args.steps, args.warmup, dist) / args.steps
