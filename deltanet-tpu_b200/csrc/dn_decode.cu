@@ -256,7 +256,9 @@ template <int N>
 __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
 __device__ __forceinline__ void fence_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
-template <int SB>                                        // bytes per state element: 2 (bf16, two CTAs per SM) or 4 (fp32, one)
+// SB: bytes per state element, 2 (bf16, two CTAs per SM) or 4 (fp32, one).  SC: some gate is one scalar per
+// head (the all-per-channel instance carries none of that code).
+template <int SB, bool SC>
 __global__ void __launch_bounds__(NT, SB == 2 ? 2 : 1) decode_bulk_kernel(DecodeArgs a, int tiles, int* err) {
   using LY = Stage<SB>;
   constexpr int TILE = LY::TILE, OFF_Q = LY::OFF_Q, OFF_K = LY::OFF_K, OFF_V = LY::OFF_V, OFF_G = LY::OFF_G,
@@ -273,7 +275,8 @@ __global__ void __launch_bounds__(NT, SB == 2 ? 2 : 1) decode_bulk_kernel(Decode
 
   // a gate that is one scalar per head cannot travel as a bulk copy (16 bytes at least): it comes by a
   // 4-byte cp.async of the issuing thread, one committed group per issued tile
-  const bool gs = s.g_cols == 1, bs = s.b_cols == 1, ws = s.w_cols == 1, any_scalar = gs || bs || ws;
+  const bool gs = SC && s.g_cols == 1, bs = SC && s.b_cols == 1, ws = SC && s.w_cols == 1;
+  constexpr bool any_scalar = SC;
   const uint32_t tx_bytes = TILE + 3 * 256 + (gs ? 0 : 512) + (bs ? 0 : 512) + (ws ? 0 : 512);
   auto gate = [&](uint8_t* dst, const void* base, int b, int heads, int hv, bool scalar, uint64_t* bar) {
     const float* src = reinterpret_cast<const float*>(base) + ((size_t)b * heads + dec_gate_head(hv, heads, s.Hk, s.Hv)) * (scalar ? 1 : KD);
@@ -499,17 +502,16 @@ int launch_decode(const dn_decode_shape& s, const void* q, const void* k, const 
   if (bulk::eligible(a) && !force_simt()) {
     const int tiles = s.B * s.Hv;
     const bool sb16 = s.state_in_dtype == DN_BF16;
+    const bool sc = s.g_cols == 1 || s.b_cols == 1 || s.w_cols == 1;
     const int slots = (sb16 ? 2 : 1) * 148;
     const int grid = tiles < slots ? tiles : slots;
-    if (sb16) {
-      const size_t smem = (size_t)bulk::STAGES * bulk::Stage<2>::BYTES;
-      cudaFuncSetAttribute(bulk::decode_bulk_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      bulk::decode_bulk_kernel<2><<<grid, bulk::NT, smem, st>>>(a, tiles, device_error_ptr());
-    } else {
-      const size_t smem = (size_t)bulk::STAGES * bulk::Stage<4>::BYTES;
-      cudaFuncSetAttribute(bulk::decode_bulk_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      bulk::decode_bulk_kernel<4><<<grid, bulk::NT, smem, st>>>(a, tiles, device_error_ptr());
-    }
+    const size_t smem = (size_t)bulk::STAGES * (sb16 ? bulk::Stage<2>::BYTES : bulk::Stage<4>::BYTES);
+    auto go = [&](auto kern) {
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      kern<<<grid, bulk::NT, smem, st>>>(a, tiles, device_error_ptr());
+    };
+    if (sb16) { if (sc) go(bulk::decode_bulk_kernel<2, true>); else go(bulk::decode_bulk_kernel<2, false>); }
+    else      { if (sc) go(bulk::decode_bulk_kernel<4, true>); else go(bulk::decode_bulk_kernel<4, false>); }
     if (cudaGetLastError() != cudaSuccess) return DN_ERR_CUDA_LAUNCH;
     if (s.flags & DN_STABILITY_GUARD) {
       if (sb16) decode_cap_kernel<__nv_bfloat16><<<s.B * s.Hv, 256, 0, st>>>(reinterpret_cast<__nv_bfloat16*>(a.state_out), s.K * s.V, s.stability_tau);
