@@ -140,7 +140,7 @@ class DeviceJob:
         self.lib.dn_exec_view(self.shape, ex)
         self.ex = ex
         items = c["B"] * ex.H * ex.NC
-        self.dV = torch.empty(items * c["chunk"] * ex.Vw, dtype=torch.float32, device=dev)
+        self.dV = torch.empty(items * ex.chunk * ex.Vw, dtype=torch.float32, device=dev)
         self.dH = torch.empty(items * c["K"] * ex.Vw, dtype=torch.float32, device=dev)
         self.stream = torch.cuda.current_stream().cuda_stream
         self.bytes = sum(x.numel() * x.element_size() for x in (self.res_block, self.scratch, self.out)) + \

@@ -27,11 +27,14 @@ struct Overlap {
   // separated by another host thread's record of the same event.
   std::mutex enqueue;
 };
+bool overlap_disabled() {
+  static const bool off = [] { const char* e = std::getenv("DN_NO_OVERLAP"); return e && e[0] == '1'; }();
+  return off;
+}
 Overlap* overlap_for_device() {
   static Overlap table[64];
   static std::mutex mu;
-  static const bool off = [] { const char* e = std::getenv("DN_NO_OVERLAP"); return e && e[0] == '1'; }();
-  if (off) return nullptr;
+  if (overlap_disabled()) return nullptr;
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
   std::lock_guard<std::mutex> lock(mu);
@@ -49,11 +52,11 @@ Overlap* overlap_for_device() {
 // rounds of CTAs, the second part [cut, NC) the last, partly filled round.
 int overlap_cut(const Geo& g) {
   if (!g.img || !state_tc_eligible(g) || (g.flags & DN_STATE_FP32_MM)) return 0;
-  const int per_chunk = g.B * g.H, n = per_chunk * g.NC;
-  if (g.NC < 4 || n <= 148 || n > 4 * 148) return 0;
-  const int rounds = (n + 147) / 148, tail = n - (rounds - 1) * 148;
-  if (tail * 4 > 148 * 3) return 0;                       // the last round is well filled already
-  const int cut = ((rounds - 1) * 148) / per_chunk;
+  const int per_chunk = g.B * g.H, n = per_chunk * g.NC, sms = sm_count();
+  if (g.NC < 4 || n <= sms || n > 4 * sms) return 0;
+  const int rounds = (n + sms - 1) / sms, tail = n - (rounds - 1) * sms;
+  if (tail * 4 > sms * 3) return 0;                       // the last round is well filled already
+  const int cut = ((rounds - 1) * sms) / per_chunk;
   return (cut >= 1 && cut < g.NC) ? cut : 0;
 }
 size_t carry_bytes(const Geo& g) { return align_up((size_t)g.B * g.H * g.K * g.Vw * sizeof(float)); }
@@ -64,6 +67,7 @@ extern "C" {
 int dn_version(void) { return 1; }
 
 int dn_device_error(void) { return read_device_error(); }
+void dn_device_error_reset(void) { reset_device_error(); }
 
 const char* dn_status_string(int st) {
   switch (st) {
@@ -74,6 +78,7 @@ const char* dn_status_string(int st) {
     case DN_ERR_SCRATCH_TOO_SMALL: return "scratch buffer too small (see dn_scratch_bytes)";
     case DN_ERR_CUDA_LAUNCH: return "a CUDA kernel launch failed";
     case DN_ERR_UNSUPPORTED: return "unsupported combination of options";
+    case DN_ERR_DEVICE_WAIT: return "an earlier kernel gave up a bounded wait (see dn_device_error / dn_device_error_reset)";
     case DN_ERR_STATIC_SCRATCH_EXCEEDED: return "this shape needs more scratch than the built-in static array (see dn_static_scratch_bytes)";
     default: return "unknown status";
   }
@@ -84,7 +89,7 @@ int dn_exec_view(const dn_shape* s, dn_exec* out) {
   int rc = make_geo(s, &g);
   if (rc) return rc;
   if (!out) return DN_ERR_NULL_POINTER;
-  out->H = g.H; out->Vw = g.Vw; out->G = g.G; out->NC = g.NC; out->pre_dtype = g.pre_dt;
+  out->H = g.H; out->Vw = g.Vw; out->G = g.G; out->NC = g.NC; out->pre_dtype = g.pre_dt; out->chunk = g.C;
   return DN_OK;
 }
 
@@ -131,12 +136,12 @@ int dn_residual_carve(const dn_shape* s, void* block, dn_residuals* out) {
 // ---- scratch accounting -------------------------------------------------------------------
 static size_t fwd_kernel_scratch(const Geo& g) {
   size_t items = (size_t)g.B * g.H * g.NC;
-  size_t ctas = items < 148 ? items : 148;
+  size_t ctas = items < (size_t)sm_count() ? items : (size_t)sm_count();
   return align_up(ctas * prepass_fwd_scratch_per_cta(g) * sizeof(float));
 }
 static size_t bwd_kernel_scratch(const Geo& g) {
   size_t items = (size_t)g.B * g.H * g.NC;
-  size_t ctas = items < 296 ? items : 296;
+  size_t ctas = items < (size_t)2 * sm_count() ? items : (size_t)2 * sm_count();
   return align_up(ctas * prepass_bwd_scratch_per_cta(g) * sizeof(float));
 }
 static size_t staging_bytes(const Geo& g) {
@@ -178,6 +183,13 @@ int dn_canonical_segments(const int32_t* raw, const int32_t* first_is_new, int32
   return launch_canonical_segments(raw, first_is_new, out, B, L, (cudaStream_t)stream);
 }
 
+int dn_cu_seqlens_segments(const int32_t* cu_seqlens, int32_t n_cu, const int32_t* first_is_new, int32_t* out,
+                           int32_t B, int32_t L, void* stream) {
+  if (!cu_seqlens || !out) return DN_ERR_NULL_POINTER;
+  if (B < 1 || L < 1 || n_cu < 2) return DN_ERR_BAD_SHAPE;
+  return launch_cu_seqlens_segments(cu_seqlens, n_cu, first_is_new, out, B, L, (cudaStream_t)stream);
+}
+
 // ---- phases -------------------------------------------------------------------------------
 int dn_prepass_fwd(const dn_shape* s, const void* q, const void* k, const void* v,
                    const void* g_, const void* b, const void* w, const int32_t* seg,
@@ -185,6 +197,7 @@ int dn_prepass_fwd(const dn_shape* s, const void* q, const void* k, const void* 
   Geo g;
   int rc = make_geo(s, &g);
   if (rc) return rc;
+  if (peek_device_error()) return DN_ERR_DEVICE_WAIT;
   if (!q || !k || !v || !g_ || !b || !w || !res || !scratch) return DN_ERR_NULL_POINTER;
   if (!res->W || !res->U || !res->M || !res->qe || !res->ke || !res->lam_end) return DN_ERR_NULL_POINTER;
   return launch_prepass_fwd(g, q, k, v, g_, b, w, seg, *res, reinterpret_cast<float*>(scratch),
@@ -196,6 +209,7 @@ int dn_state_fwd(const dn_shape* s, const dn_residuals* res, const int32_t* seg,
   Geo g;
   int rc = make_geo(s, &g);
   if (rc) return rc;
+  if (peek_device_error()) return DN_ERR_DEVICE_WAIT;
   if (!res || (!out && !final_state && !res->states)) return DN_ERR_NULL_POINTER;
   if ((g.flags & DN_HAS_INIT) && !init_state) return DN_ERR_NULL_POINTER;
   StateArgs a{};
@@ -209,6 +223,7 @@ int dn_recompute_states(const dn_shape* s, const dn_residuals* res, const int32_
   Geo g;
   int rc = make_geo(s, &g);
   if (rc) return rc;
+  if (peek_device_error()) return DN_ERR_DEVICE_WAIT;
   if (!res || !res->states) return DN_ERR_NULL_POINTER;
   if ((g.flags & DN_HAS_INIT) && !init_state) return DN_ERR_NULL_POINTER;
   StateArgs a{};
@@ -223,6 +238,7 @@ int dn_state_bwd(const dn_shape* s, const dn_residuals* res, const int32_t* seg,
   Geo g;
   int rc = make_geo(s, &g);
   if (rc) return rc;
+  if (peek_device_error()) return DN_ERR_DEVICE_WAIT;
   if (!res || !d_out || !dV || !dH) return DN_ERR_NULL_POINTER;
   if (g.img && !res->states) return DN_ERR_NULL_POINTER;      // dLambda_end is reduced in the reverse chain on this path
   StateArgs a{};
@@ -301,6 +317,7 @@ int dn_prepass_bwd(const dn_shape* s, const void* q, const void* k, const void* 
   Geo g;
   int rc = make_geo(s, &g);
   if (rc) return rc;
+  if (peek_device_error()) return DN_ERR_DEVICE_WAIT;
   if (!q || !k || !v || !g_ || !b || !w || !res || !d_out || !dV || !dH || !scratch) return DN_ERR_NULL_POINTER;
   if (!dq || !dk || !dv || !dg || !db || !dw) return DN_ERR_NULL_POINTER;
   if (!res->W || !res->U || !res->T || !res->states || !res->lam_end) return DN_ERR_NULL_POINTER;
@@ -316,6 +333,7 @@ int dn_chunk_fwd(const dn_shape* s, const void* q, const void* k, const void* v,
   Geo g;
   int rc = make_geo(s, &g);
   if (rc) return rc;
+  if (peek_device_error()) return DN_ERR_DEVICE_WAIT;
   if (!q || !k || !v || !g_ || !b || !w || !out || !scratch) return DN_ERR_NULL_POINTER;
   if ((g.flags & DN_HAS_INIT) && !init_state) return DN_ERR_NULL_POINTER;
   char* p = reinterpret_cast<char*>(scratch);
@@ -346,13 +364,17 @@ int dn_chunk_fwd(const dn_shape* s, const void* q, const void* k, const void* v,
     a.g = g; a.res = *res; a.seg = seg; a.init_state = (g.flags & DN_HAS_INIT) ? init_state : nullptr;
     a.out = out; a.final_state = final_state; a.states = res->states; a.carry = carry;
     if ((rc = launch_prepass_fwd_tc(g, q, k, v, g_, b, w, seg, *res, sc, scf, st, 0, cut))) return rc;
-    cudaEventRecord(ov->ev[0], st);
-    cudaStreamWaitEvent(ov->side, ov->ev[0], 0);
+    if (cudaEventRecord(ov->ev[0], st) != cudaSuccess || cudaStreamWaitEvent(ov->side, ov->ev[0], 0) != cudaSuccess)
+      return DN_ERR_CUDA_LAUNCH;
+    // forked: whatever fails from here on, the side stream is joined back before returning
     a.c_begin = 0; a.c_end = cut;
-    if ((rc = launch_state_fwd_tc(a, ov->side))) return rc;
-    cudaEventRecord(ov->ev[1], ov->side);
-    if ((rc = launch_prepass_fwd_tc(g, q, k, v, g_, b, w, seg, *res, sc, scf, st, cut, g.NC))) return rc;
-    cudaStreamWaitEvent(st, ov->ev[1], 0);
+    const int rc_side = launch_state_fwd_tc(a, ov->side);
+    const cudaError_t e1 = cudaEventRecord(ov->ev[1], ov->side);
+    const int rc_main = launch_prepass_fwd_tc(g, q, k, v, g_, b, w, seg, *res, sc, scf, st, cut, g.NC);
+    const cudaError_t e2 = cudaStreamWaitEvent(st, ov->ev[1], 0);
+    if (rc_side) return rc_side;
+    if (rc_main) return rc_main;
+    if (e1 != cudaSuccess || e2 != cudaSuccess) return DN_ERR_CUDA_LAUNCH;
     a.c_begin = cut; a.c_end = g.NC;
     return launch_state_fwd_tc(a, st);
   }
@@ -369,6 +391,7 @@ int dn_chunk_bwd(const dn_shape* s, const void* q, const void* k, const void* v,
   Geo g;
   int rc = make_geo(s, &g);
   if (rc) return rc;
+  if (peek_device_error()) return DN_ERR_DEVICE_WAIT;
   if (!q || !k || !v || !g_ || !b || !w || !d_out || !scratch) return DN_ERR_NULL_POINTER;
   if (!dq || !dk || !dv || !dg || !db || !dw) return DN_ERR_NULL_POINTER;
   if (g.flags & DN_INFERENCE) return DN_ERR_UNSUPPORTED;
@@ -410,13 +433,17 @@ int dn_chunk_bwd(const dn_shape* s, const void* q, const void* k, const void* v,
     a.dV = dV; a.dH = dH; a.d_init = (g.flags & DN_HAS_INIT) ? d_init : nullptr; a.carry = carry;
     a.c_begin = cut; a.c_end = g.NC;
     if ((rc = launch_state_bwd_tc(a, st))) return rc;
-    cudaEventRecord(ov->ev[0], st);
-    cudaStreamWaitEvent(ov->side, ov->ev[0], 0);
-    if ((rc = launch_plan(pl, cut, g.NC, ov->side))) return rc;
-    cudaEventRecord(ov->ev[1], ov->side);
+    if (cudaEventRecord(ov->ev[0], st) != cudaSuccess || cudaStreamWaitEvent(ov->side, ov->ev[0], 0) != cudaSuccess)
+      return DN_ERR_CUDA_LAUNCH;
+    // forked: whatever fails from here on, the side stream is joined back before returning
+    const int rc_side = launch_plan(pl, cut, g.NC, ov->side);
+    const cudaError_t e1 = cudaEventRecord(ov->ev[1], ov->side);
     a.c_begin = 0; a.c_end = cut;
-    if ((rc = launch_state_bwd_tc(a, st))) return rc;
-    cudaStreamWaitEvent(st, ov->ev[1], 0);
+    const int rc_main = launch_state_bwd_tc(a, st);
+    const cudaError_t e2 = cudaStreamWaitEvent(st, ov->ev[1], 0);
+    if (rc_side) return rc_side;
+    if (rc_main) return rc_main;
+    if (e1 != cudaSuccess || e2 != cudaSuccess) return DN_ERR_CUDA_LAUNCH;
     if ((rc = launch_plan(pl, 0, cut, st))) return rc;
     return finish_plan(g, pl, st);
   }
@@ -434,6 +461,7 @@ int dn_sp_transition(const dn_shape* s, const dn_residuals* res, const int32_t* 
   Geo g;
   int rc = make_geo(s, &g);
   if (rc) return rc;
+  if (peek_device_error()) return DN_ERR_DEVICE_WAIT;
   if (!res || !identity || !P) return DN_ERR_NULL_POINTER;
   Geo t = g;                       // same chunks and heads, value width K, one "value head" per exec head
   t.Hv = g.H; t.G = 1; t.V = g.K; t.Vw = g.K; t.qk_div = 1;
@@ -444,10 +472,57 @@ int dn_sp_transition(const dn_shape* s, const dn_residuals* res, const int32_t* 
   return launch_state_fwd(a, (cudaStream_t)stream);
 }
 
+// One launch for a shard's affine summary: the state pass from a zero state WITH outputs and chunk
+// states (complete for every chunk after the shard's first document boundary, provisional before it),
+// carrying K extra columns that start from the identity and end as P.
+int dn_sp_summary(const dn_shape* s, const dn_residuals* res, const int32_t* seg,
+                  void* out, float* Q, float* P, void* stream) {
+  Geo g;
+  int rc = make_geo(s, &g);
+  if (rc) return rc;
+  if (peek_device_error()) return DN_ERR_DEVICE_WAIT;
+  if (!res || !Q || !P) return DN_ERR_NULL_POINTER;
+  if (!res->W || !res->U || !res->ke || !res->lam_end || (out && (!res->M || !res->qe))) return DN_ERR_NULL_POINTER;
+  StateArgs a{};
+  a.g = g; a.res = *res; a.seg = seg; a.init_state = nullptr;
+  a.out = out; a.final_state = Q; a.states = res->states; a.P_out = P;
+  return launch_state_fwd(a, (cudaStream_t)stream);
+}
+
+// The forward chain again from the shard's true incoming state, over the chunks that depend on it.
+int dn_sp_correct_fwd(const dn_shape* s, const dn_residuals* res, const int32_t* seg,
+                      const float* S_in, void* out, void* stream) {
+  Geo g;
+  int rc = make_geo(s, &g);
+  if (rc) return rc;
+  if (peek_device_error()) return DN_ERR_DEVICE_WAIT;
+  if (!res || !S_in || (!out && !res->states)) return DN_ERR_NULL_POINTER;
+  if (!(g.flags & DN_HAS_INIT)) return DN_ERR_UNSUPPORTED;
+  StateArgs a{};
+  a.g = g; a.res = *res; a.seg = seg; a.init_state = S_in;
+  a.out = out; a.states = res->states; a.until_independent = true;
+  return launch_state_fwd(a, (cudaStream_t)stream);
+}
+
+// The reverse chain again from the shard's true incoming state cotangent, over the chunks that depend on it.
+int dn_sp_correct_bwd(const dn_shape* s, const dn_residuals* res, const int32_t* seg,
+                      const void* d_out, const float* d_final_state, float* dV, float* dH, void* stream) {
+  Geo g;
+  int rc = make_geo(s, &g);
+  if (rc) return rc;
+  if (peek_device_error()) return DN_ERR_DEVICE_WAIT;
+  if (!res || !d_out || !d_final_state || !dV || !dH) return DN_ERR_NULL_POINTER;
+  if (g.img && !res->states) return DN_ERR_NULL_POINTER;
+  StateArgs a{};
+  a.g = g; a.res = *res; a.seg = seg; a.d_out = d_out; a.d_final = d_final_state;
+  a.dV = dV; a.dH = dH; a.until_independent = true;
+  return launch_state_bwd(a, (cudaStream_t)stream);
+}
+
 int dn_launch_count(const dn_shape* s, int backward, int recompute) {
   Geo g;
   if (make_geo(s, &g)) return 0;
-  const bool split_f = overlap_cut(g) && overlap_for_device();
+  const bool split_f = overlap_cut(g) && !overlap_disabled();      // (a pure query: creates no stream)
   const bool split_b = split_f && prepass_bwd_tc_eligible(g);
   if (!backward) return split_f ? 4 : 2;
   int n = split_b ? 4 : 2;
@@ -474,7 +549,14 @@ int dn_decode_step(const dn_decode_shape* s, const void* q, const void* k, const
   if ((s->g_cols != 1 && s->g_cols != s->K) || (s->b_cols != 1 && s->b_cols != s->K) ||
       (s->w_cols != 1 && s->w_cols != s->V)) return DN_ERR_BAD_SHAPE;
   if (state_in == state_out && s->state_in_dtype != s->state_out_dtype) return DN_ERR_UNSUPPORTED;
+  if (peek_device_error()) return DN_ERR_DEVICE_WAIT;
   return launch_decode(*s, q, k, v, g_, b, w, state_in, reset, out, state_out, (cudaStream_t)stream);
+}
+
+int dn_cap_state(float* state, int64_t n_states, int32_t K, int32_t V, float tau, void* stream) {
+  if (!state) return DN_ERR_NULL_POINTER;
+  if (n_states < 1 || K < 1 || V < 1 || !(tau > 0.f)) return DN_ERR_BAD_SHAPE;
+  return launch_cap_state(state, n_states, K * V, tau, (cudaStream_t)stream);
 }
 
 }  // extern "C"

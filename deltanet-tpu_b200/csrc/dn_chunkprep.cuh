@@ -26,7 +26,7 @@ struct InCfg {
   static constexpr int qkv_dt = MODE == 1 ? DN_F32 : DN_BF16;
 };
 inline int input_mode(const Geo& g) {
-  if (g.gate_dt != DN_F32 || (g.flags & DN_FUSE_PROLOGUE)) return 2;
+  if (g.gate_dt != DN_F32 || (g.flags & (DN_FUSE_PROLOGUE | DN_STABILITY_GUARD))) return 2;
   if (g.gC == g.K && g.bC == g.K && g.wC == g.V) return g.qkv_dt == DN_BF16 ? 0 : 1;
   if (g.gC == 1 && g.bC == 1 && g.wC == 1 && g.qkv_dt == DN_BF16) return 3;
   return 2;
@@ -108,6 +108,9 @@ __device__ __forceinline__ void bact8(const Rows& r, int x, int p, float (&o)[8]
   if (r.fuse) {
 #pragma unroll
     for (int i = 0; i < 8; ++i) o[i] = 1.f / (1.f + expf(-o[i]));
+  } else if (r.guard) {                       // stability_guard on a given gate: b >= 0 (gdn2.py:1973)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = fmaxf(o[i], 0.f);
   }
   if (!live) zero8(o);
 }
@@ -118,7 +121,7 @@ __device__ __forceinline__ void gact8(const Rows& r, int x, int p, float (&o)[8]
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     if (r.fuse) { o[i] = -expf(fminf(o[i], 5.f)); if (r.guard) o[i] = fminf(o[i], -1e-6f); }
-    else o[i] = o[i] <= 0.f ? o[i] : 0.f;
+    else { o[i] = o[i] <= 0.f ? o[i] : 0.f; if (r.guard) o[i] = fminf(o[i], -1e-6f); }
   }
   if (!live) zero8(o);
 }
@@ -168,7 +171,7 @@ __device__ __forceinline__ void lambda_scan_512(const Rows& r, const int* seg_s,
     const bool live = x < r.rows_valid;
     float gv = ldf_ro(r.gg, r.g_row0 + (size_t)(live ? x : 0) * r.g_pitch + gcol, r.gate_dt);
     if (r.fuse) { gv = -expf(fminf(gv, 5.f)); if (r.guard) gv = fminf(gv, -1e-6f); }
-    else gv = gv <= 0.f ? gv : 0.f;
+    else { gv = gv <= 0.f ? gv : 0.f; if (r.guard) gv = fminf(gv, -1e-6f); }
     v[i] = live ? gv : 0.f;
   }
   float run = 0.f;

@@ -14,6 +14,8 @@ namespace dn {
 
 // true when the environment asks for the fp32 SIMT kernels everywhere (DN_FORCE_SIMT=1)
 bool force_simt();
+// streaming multiprocessors of the current device (queried once per device)
+int sm_count();
 
 // --------------------------------------------------------------------------- geometry
 // Everything a kernel needs to know about where a (batch, exec head, chunk) lives.
@@ -59,18 +61,25 @@ inline int make_geo(const dn_shape* s, Geo* g) {
       (s->gate_dtype != DN_F32 && s->gate_dtype != DN_BF16)) return DN_ERR_BAD_DTYPE;
   if (s->precision != DN_PREC_FP32 && s->precision != DN_PREC_BF16) return DN_ERR_BAD_DTYPE;
   g->B = s->B; g->L = s->L; g->Hk = s->Hk; g->Hv = s->Hv; g->K = s->K; g->V = s->V;
-  g->C = s->chunk; g->NC = (s->L + s->chunk - 1) / s->chunk;
   bool at_hv = (s->Hk < s->Hv) && (s->g_heads == s->Hv || s->b_heads == s->Hv);
   if (at_hv) { g->H = s->Hv; g->Vw = s->V; g->G = 1; g->qk_div = s->Hv / s->Hk; }
   else       { g->H = s->Hk; g->G = s->Hv / s->Hk; g->Vw = g->G * s->V; g->qk_div = 1; }
   if (g->Vw > 1024) return DN_ERR_BAD_SHAPE;
+  // Rows per tile.  The tensor-core kernels work on 128-row tiles (the M of a tcgen05.mma), so in
+  // bf16 precision a request for chunk 64 is run with two requested chunks merged into one tile:
+  // the chunked form is an exact regrouping of the token recurrence, results differ only in where
+  // the state is rounded to bf16 (every 128 tokens instead of every 64).  dn_exec_view reports the
+  // tile height actually used; every buffer size follows from it.
+  const bool tc_shape = s->precision == DN_PREC_BF16 && !(s->flags & DN_STATE_FP32_MM) && s->K == 128 &&
+                        (g->Vw == 128 || g->Vw == 256) && !force_simt();
+  g->C = (tc_shape && s->chunk == 64) ? 128 : s->chunk;
+  g->NC = (s->L + g->C - 1) / g->C;
   g->gH = s->g_heads; g->gC = s->g_cols; g->bH = s->b_heads; g->bC = s->b_cols;
   g->wH = s->w_heads; g->wC = s->w_cols;
   g->qkv_dt = s->qkv_dtype; g->gate_dt = s->gate_dtype; g->prec = s->precision;
   g->pre_dt = s->precision == DN_PREC_BF16 ? DN_BF16 : DN_F32;
   g->flags = s->flags; g->scale = s->scale;
-  g->img = s->precision == DN_PREC_BF16 && g->C == 128 && g->K == 128 && (g->Vw == 128 || g->Vw == 256) &&
-           !force_simt();
+  g->img = tc_shape;
   return DN_OK;
 }
 
@@ -102,6 +111,12 @@ static __device__ long long g_phase_marks[48];
 #endif
 
 // --------------------------------------------------------------------------- dtype helpers
+// A bounded wait gave up: raise the library's error word (a plain store; the word may live in
+// host memory that the device reaches over the bus).
+__device__ __forceinline__ void report_timeout(int* err) {
+  if (err) { *reinterpret_cast<volatile int*>(err) = 1; __threadfence_system(); }
+}
+
 __device__ __forceinline__ float bf16r(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 
 __device__ __forceinline__ float ldf(const void* p, size_t i, int dt) {

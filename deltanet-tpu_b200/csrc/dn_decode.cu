@@ -97,7 +97,7 @@ __global__ void __launch_bounds__(NTH) decode_kernel(DecodeArgs a) {
   // ---- state loads first: they are the long-latency part
   const size_t sbase = ((size_t)b * s.Hv + hv) * KD * V;
   const SI* Sin = reinterpret_cast<const SI*>(a.state_in) + sbase;
-  const bool zero = a.reset && a.reset[b];
+  const bool zero = a.reset && a.reset[(s.flags & DN_RESET_PER_HEAD) ? b * s.Hv + hv : b];
   float S[R][CPT];
 #pragma unroll
   for (int r = 0; r < R; ++r) {
@@ -316,14 +316,14 @@ __global__ void __launch_bounds__(NT, SB == 2 ? 2 : 1) decode_bulk_kernel(Decode
   for (int tile = first; tile < tiles; tile += stride, ++it) {
     const int st = it % STAGES;
     const uint32_t parity = (uint32_t)(it / STAGES) & 1u;
-    if (!bar_wait(&full[st], parity)) { dead_s = 1; if (err) atomicExch(err, 1); }
+    if (!bar_wait(&full[st], parity)) { dead_s = 1; report_timeout(err); }
     // STAGES - 1 + it groups are committed by now and this tile's is number it: all but the newest STAGES - 2
     if (any_scalar && tid == NT - 1) asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 2) : "memory");
     __syncthreads();
     if (dead_s) break;
     uint8_t* buf = ring + (size_t)st * STAGE_BYTES;
     const int hv = tile % s.Hv, b = tile / s.Hv;
-    const bool zero = a.reset && a.reset[b];
+    const bool zero = a.reset && a.reset[(s.flags & DN_RESET_PER_HEAD) ? b * s.Hv + hv : b];
 
     // ---- token vectors in one phase: warps 0..3 take k (every warp computes the norm for itself),
     //      the decay and beta = b * k_hat; warps 4..7 take q and w * v
@@ -495,6 +495,11 @@ static int launch_decode_t(const DecodeArgs& a, cudaStream_t st) {
   return DN_OK;
 }
 
+int launch_cap_state(float* state, int64_t n_states, int KV, float tau, cudaStream_t st) {
+  decode_cap_kernel<float><<<(unsigned)n_states, 256, 0, st>>>(state, KV, tau);
+  return cudaGetLastError() == cudaSuccess ? DN_OK : DN_ERR_CUDA_LAUNCH;
+}
+
 int launch_decode(const dn_decode_shape& s, const void* q, const void* k, const void* v,
                   const void* g, const void* b, const void* w, const void* state_in,
                   const uint8_t* reset, void* out, void* state_out, cudaStream_t st) {
@@ -503,7 +508,7 @@ int launch_decode(const dn_decode_shape& s, const void* q, const void* k, const 
     const int tiles = s.B * s.Hv;
     const bool sb16 = s.state_in_dtype == DN_BF16;
     const bool sc = s.g_cols == 1 || s.b_cols == 1 || s.w_cols == 1;
-    const int slots = (sb16 ? 2 : 1) * 148;
+    const int slots = (sb16 ? 2 : 1) * sm_count();
     const int grid = tiles < slots ? tiles : slots;
     const size_t smem = (size_t)bulk::STAGES * (sb16 ? bulk::Stage<2>::BYTES : bulk::Stage<4>::BYTES);
     auto go = [&](auto kern) {

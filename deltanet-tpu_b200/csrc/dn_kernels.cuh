@@ -35,6 +35,16 @@ struct StateArgs {
   // leaves it there; the backward pass uses it the other way round.  (B,H,K,Vw) fp32.
   int c_begin, c_end;
   float* carry;
+  int* err;                  // error word (bounded waits report here); set by the launchers
+  // Sequence-sharded use.  P_out (B,H,K,K): the forward launch carries K extra "value" columns per
+  // (batch, head) that start from the identity with U = 0 and end as the shard's transition matrix
+  // (grid.x grows by K / VS slices; those slices write neither outputs nor chunk states).
+  // until_independent: the chain stops at the first chunk whose results no longer depend on the
+  // state it was started from (a document boundary cuts the dependence); outputs, chunk states, dV
+  // and dH of the chunks before that point are (re)written, nothing else is, and neither the final
+  // state nor d_init is produced.
+  float* P_out;
+  bool until_independent;
 };
 
 struct PrepassBwdArgs {
@@ -71,8 +81,12 @@ int launch_state_fwd(const StateArgs& a, cudaStream_t st);
 bool state_tc_eligible(const Geo& g);
 int launch_state_fwd_tc(const StateArgs& a, cudaStream_t st);
 int launch_state_bwd_tc(const StateArgs& a, cudaStream_t st);
-int read_device_error();
+// The library's error word (dn_misc.cu): device address for the kernels; read without / with a
+// device synchronisation; clear.
 int* device_error_ptr();
+int peek_device_error();
+int read_device_error();
+void reset_device_error();
 int launch_state_bwd(const StateArgs& a, cudaStream_t st);
 int launch_prepass_bwd(PrepassBwdArgs& a, size_t scratch_floats, cudaStream_t st);
 int launch_prepass_bwd_tc(PrepassBwdArgs& a, size_t scratch_floats, cudaStream_t st);
@@ -80,12 +94,16 @@ bool prepass_bwd_tc_eligible(const Geo& g);
 size_t prepass_bwd_tc_scratch_per_cta(const Geo& g);
 int launch_canonical_segments(const int32_t* raw, const int32_t* first_is_new, int32_t* out,
                               int B, int L, cudaStream_t st);
+int launch_cu_seqlens_segments(const int32_t* cu, int n_cu, const int32_t* first_is_new, int32_t* out,
+                               int B, int L, cudaStream_t st);
 // sums `groups` consecutive heads: in (rows, heads_out*groups, cols) f32 -> out (rows, heads_out, cols)
 int launch_group_sum(const float* in, void* out, int out_dt, size_t rows, int heads_out, int groups,
                      int cols, cudaStream_t st);
 // S_out[b, h*G+g] = op(P[b,h]) S_in[b, h*G+g] (+ Q); op = transpose when asked.  P (B,H,K,K), states (B,H*G,K,V).
 int launch_sp_apply(const float* P, const float* S_in, const float* Q, float* S_out, int B, int H, int G,
                     int K, int V, int transpose, cudaStream_t st);
+// Frobenius cap of n_states fp32 (K,V) states in place: S <- S * min(1, tau / sqrt(|S|^2 + 1e-6))
+int launch_cap_state(float* state, int64_t n_states, int KV, float tau, cudaStream_t st);
 int launch_decode(const dn_decode_shape& s, const void* q, const void* k, const void* v,
                   const void* g, const void* b, const void* w, const void* state_in,
                   const uint8_t* reset, void* out, void* state_out, cudaStream_t st);

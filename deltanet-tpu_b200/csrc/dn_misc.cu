@@ -2,8 +2,64 @@
 #include "dn_kernels.cuh"
 
 #include <cstdlib>
+#include <mutex>
 
 namespace dn {
+
+int sm_count() {
+  static int table[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  int n = __atomic_load_n(&table[dev], __ATOMIC_RELAXED);
+  if (n == 0) {
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n < 1) { cudaGetLastError(); n = 148; }
+    __atomic_store_n(&table[dev], n, __ATOMIC_RELAXED);
+  }
+  return n;
+}
+
+// ---- the error word ------------------------------------------------------------------------------
+// Kernels whose bounded waits give up store 1 into one int.  The int lives in a page of this
+// library's own static host memory that is pinned and mapped into the device address space on first
+// use (registering existing memory allocates nothing), so the host can look at it WITHOUT
+// synchronising: every entry point checks it before it enqueues anything.  If the page cannot be
+// registered the word falls back to a __device__ variable, which only dn_device_error() (a
+// synchronising call) can read.
+namespace {
+alignas(4096) int g_err_page[1024];
+__device__ int g_err_fallback = 0;
+std::once_flag g_err_once;
+bool g_err_mapped = false;
+void err_setup() {
+  g_err_mapped = cudaHostRegister(g_err_page, sizeof(g_err_page), cudaHostRegisterPortable | cudaHostRegisterMapped) == cudaSuccess;
+  if (!g_err_mapped) cudaGetLastError();
+}
+}  // namespace
+
+int* device_error_ptr() {
+  std::call_once(g_err_once, err_setup);
+  int* p = nullptr;
+  if (g_err_mapped && cudaHostGetDevicePointer(reinterpret_cast<void**>(&p), g_err_page, 0) == cudaSuccess && p) return p;
+  cudaGetLastError();
+  p = nullptr;
+  cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_err_fallback);
+  return p;
+}
+
+int peek_device_error() { return g_err_mapped ? __atomic_load_n(&g_err_page[0], __ATOMIC_RELAXED) : 0; }
+
+int read_device_error() {
+  cudaDeviceSynchronize();
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_err_fallback, sizeof(int)) != cudaSuccess) { cudaGetLastError(); v = 0; }
+  return (v || peek_device_error()) ? 1 : 0;
+}
+
+void reset_device_error() {
+  __atomic_store_n(&g_err_page[0], 0, __ATOMIC_RELAXED);
+  const int zero = 0;
+  if (cudaMemcpyToSymbol(g_err_fallback, &zero, sizeof(int)) != cudaSuccess) cudaGetLastError();
+}
 
 bool force_simt() {
   static const bool v = [] { const char* e = std::getenv("DN_FORCE_SIMT"); return e && e[0] == '1'; }();
@@ -41,6 +97,31 @@ int launch_canonical_segments(const int32_t* raw, const int32_t* first_is_new, i
   return cudaGetLastError() == cudaSuccess ? DN_OK : DN_ERR_CUDA_LAUNCH;
 }
 
+// Canonical ids straight from cumulative sequence lengths: token t belongs to document d with
+// cu[d] <= t < cu[d+1] (binary search per token); the same ids for every batch row, plus
+// first_is_new[b].  Tokens at or past cu[n_cu-1] take the last document.
+__global__ void __launch_bounds__(256) cu_seqlens_segments_kernel(const int32_t* cu, int n_cu, const int32_t* first_is_new,
+                                                                  int32_t* out, int B, int L) {
+  const size_t total = (size_t)B * L;
+  for (size_t e = (size_t)blockIdx.x * 256 + threadIdx.x; e < total; e += (size_t)gridDim.x * 256) {
+    const int t = (int)(e % L), b = (int)(e / L);
+    int lo = 0, hi = n_cu - 1;                          // invariant: cu[lo] <= t, and t < cu[hi] or hi is the end
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (cu[mid] <= t) lo = mid; else hi = mid;
+    }
+    out[e] = lo + (first_is_new ? first_is_new[b] : 0);
+  }
+}
+
+int launch_cu_seqlens_segments(const int32_t* cu, int n_cu, const int32_t* first_is_new, int32_t* out,
+                               int B, int L, cudaStream_t st) {
+  size_t blocks = ((size_t)B * L + 255) / 256;
+  if (blocks > (size_t)sm_count() * 8) blocks = (size_t)sm_count() * 8;
+  cu_seqlens_segments_kernel<<<(unsigned)blocks, 256, 0, st>>>(cu, n_cu, first_is_new, out, B, L);
+  return cudaGetLastError() == cudaSuccess ? DN_OK : DN_ERR_CUDA_LAUNCH;
+}
+
 // out[row][ho][c] = sum over gi of in[row][ho*groups + gi][c], added in a fixed order.
 __global__ void __launch_bounds__(256) group_sum_kernel(const float* in, void* out, int out_dt, size_t total,
                                                         int heads_out, int groups, int cols) {
@@ -60,7 +141,7 @@ int launch_group_sum(const float* in, void* out, int out_dt, size_t rows, int he
                      int cols, cudaStream_t st) {
   const size_t total = rows * heads_out * cols;
   size_t blocks = (total + 255) / 256;
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks > (size_t)sm_count() * 16) blocks = (size_t)sm_count() * 16;
   group_sum_kernel<<<(unsigned)blocks, 256, 0, st>>>(in, out, out_dt, total, heads_out, groups, cols);
   return cudaGetLastError() == cudaSuccess ? DN_OK : DN_ERR_CUDA_LAUNCH;
 }

@@ -46,10 +46,11 @@ int dn_prepass_fwd_static(const dn_shape* s, const void* q, const void* k, const
   dn::Geo g;
   int rc = dn::make_geo(s, &g);
   if (rc) return rc;
+  if (dn::peek_device_error()) return DN_ERR_DEVICE_WAIT;
   if (!q || !k || !v || !g_ || !b || !w || !res) return DN_ERR_NULL_POINTER;
   if (!res->W || !res->U || !res->M || !res->qe || !res->ke || !res->lam_end) return DN_ERR_NULL_POINTER;
   // what the launcher will ask for: one scratch block per CTA, at most one CTA per SM
-  const size_t items = (size_t)g.B * g.H * g.NC, ctas = items < 148 ? items : 148;
+  const size_t items = (size_t)g.B * g.H * g.NC, ctas = items < (size_t)dn::sm_count() ? items : (size_t)dn::sm_count();
   const bool tc = dn::prepass_fwd_tc_eligible(g);
   const size_t per_cta = tc ? dn::prepass_fwd_tc_scratch_per_cta() : dn::prepass_fwd_scratch_per_cta(g);
   const size_t need = ctas * per_cta * sizeof(float);

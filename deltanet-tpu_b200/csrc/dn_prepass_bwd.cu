@@ -110,6 +110,7 @@ __global__ void __launch_bounds__(DN_THREADS, 1) prepass_bwd_kernel(PrepassBwdAr
           } else {
             ga = gr <= 0.f ? gr : 0.f;
             ba = br;
+            if (guard) { ga = fminf(ga, -1e-6f); ba = fmaxf(ba, 0.f); }      // gdn2.py:1972-1974
           }
         }
         QH[i * K + c] = qh;
@@ -275,7 +276,12 @@ __global__ void __launch_bounds__(DN_THREADS, 1) prepass_bwd_kernel(PrepassBwdAr
           const float ba = BA[i * K + c];
           dbv = dbv * (ba * (1.f - ba));
         } else {
-          dgv = gr <= 0.f ? dgv : 0.f;
+          dgv = (guard ? gr < -1e-6f : gr <= 0.f) ? dgv : 0.f;
+          if (guard) {                                             // through max(b, 0)
+            const size_t rowb = ((size_t)(b * (size_t)g.L + t) * g.bH + hb) * g.bC;
+            const float br = ldf(a.b, rowb + (g.bC == 1 ? 0 : c), g.gate_dt);
+            dbv *= br > 0.f ? 1.f : (br == 0.f ? 0.5f : 0.f);
+          }
         }
         if (g.gC == 1) sg += dgv; else stf(a.dg, outg + c, dgv, a.dg_dt);
         if (g.bC == 1) sb2 += dbv; else stf(a.db, outb + c, dbv, a.db_dt);
@@ -348,7 +354,7 @@ int launch_prepass_bwd(PrepassBwdArgs& a, size_t scratch_floats, cudaStream_t st
   const bool tc = prepass_bwd_tc_eligible(g);
   a.err = device_error_ptr();
   if (tc) return launch_prepass_bwd_tc(a, scratch_floats, st);
-  const int max_ctas = 296;
+  const int max_ctas = 2 * sm_count();
   int grid = a.items < max_ctas ? a.items : max_ctas;
   if (scratch_floats < (size_t)grid * a.scratch_per_cta) return DN_ERR_SCRATCH_TOO_SMALL;
   const size_t smem = (GEMM_SMEM_FLOATS + (size_t)4 * g.C + g.K) * sizeof(float);

@@ -29,7 +29,9 @@
 // pieces of 8 channels (row = 8 * warp + (lane & 7) is fixed per thread); phases that drain or use
 // tensor memory own one row per thread (row = the thread's lane of its warp's lane quarter) and use
 // the panel layout of the scratch (see the header).
+#ifdef DN_PHASE_TIMING
 #include <cstdio>
+#endif
 #include "dn_chunkprep.cuh"
 #include "dn_kernels.cuh"
 #include "dn_prepass_bwd_tc.cuh"
@@ -197,7 +199,7 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
           umma::bulk_load(VB + tid * VP, reinterpret_cast<const __nv_bfloat16*>(a.v) + (tok * g.Hv + hv) * 128, 256, &v_bar);
           umma::bulk_load(WB + tid * WP, reinterpret_cast<const float*>(a.w) + (tok * g.wH + g.w_head(hv)) * 128, 512, &v_bar);
         }
-        if (!umma::mbar_wait(&v_bar, v_phase) && a.err) atomicExch(a.err, 1);
+        if (!umma::mbar_wait(&v_bar, v_phase)) umma::report_timeout(a.err);
         v_phase ^= 1u;
 #pragma unroll
         for (int it = 0; it < 4; ++it) {
@@ -510,10 +512,11 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
 #pragma unroll 1
       for (int it = 0; it < 4; ++it) {
         const int p = it * 4 + lgrp;
-        float qr[8], kr[8], ba[8], dbp[8], dqp[8], dkp[8], dx[8], dqe[8], dke[8];
+        float qr[8], kr[8], ba[8], braw[8], dbp[8], dqp[8], dkp[8], dx[8], dqe[8], dke[8];
         raw_q8(r, x, p, qr);
         raw_k8(r, x, p, kr);
         bact8(r, x, p, ba);
+        if (!fuse && guard) raw_gate8(r.b, r.b_row0, r.b_pitch, r.bC, r.gate_dt, live ? x : 0, p, braw);
         ld2x4(DBP4 + p4v(x, 8 * p), dbp);
         ld2x4(DQP4 + p4v(x, 8 * p), dqp);
         ld2x4(DKP4 + p4v(x, 8 * p), dkp);
@@ -540,6 +543,7 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
           odk[i] = dke[i] * ke;
           float dbv = dbeta * kh;                               // d b_act
           if (fuse) dbv *= ba[i] * (1.f - ba[i]);               // through the sigmoid
+          else if (guard) dbv *= braw[i] > 0.f ? 1.f : (braw[i] == 0.f ? 0.5f : 0.f);   // through max(b, 0)
           odb[i] = dbv;
           sb2 += dbv;
           dqp[i] = dq * g.scale;                                // d q_n (before the l2norm adjoint)
@@ -661,7 +665,7 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
             const bool pass = gr[u] <= 5.f && (!guard || gexp < -1e-6f);
             dgv[u] = pass ? dgv[u] * gexp : 0.f;
           } else {
-            dgv[u] = gr[u] <= 0.f ? dgv[u] : 0.f;
+            dgv[u] = (guard ? gr[u] < -1e-6f : gr[u] <= 0.f) ? dgv[u] : 0.f;      // through min(min(g, 0), -1e-6)
           }
           sg += dgv[u];
         }
@@ -703,7 +707,7 @@ int launch_prepass_bwd_tc(PrepassBwdArgs& a, size_t scratch_floats, cudaStream_t
   if (a.items <= 0) return DN_OK;
   a.scratch_per_cta = prepass_bwd_tc_scratch_per_cta(g);
   a.err = device_error_ptr();
-  const int grid = a.items < 148 ? a.items : 148;
+  const int grid = a.items < sm_count() ? a.items : sm_count();
   if (scratch_floats < (size_t)grid * a.scratch_per_cta) return DN_ERR_SCRATCH_TOO_SMALL;
   const size_t lam_phase = (size_t)C * LP * 4 + 4 * 32768;
   size_t smem = bwd_tc_image_bytes(g.Vw);

@@ -75,7 +75,7 @@ struct ImgLoader {
     if (threadIdx.x == 0) umma::bulk_load(dst, src, bytes, bar);
   }
   __device__ __forceinline__ void wait() {
-    if (!umma::mbar_wait(bar, phase) && err) atomicExch(err, 1);
+    if (!umma::mbar_wait(bar, phase)) umma::report_timeout(err);
     phase ^= 1u;
   }
 };

@@ -98,6 +98,7 @@ __global__ void __launch_bounds__(DN_THREADS, 1) prepass_fwd_kernel(PrepassFwdAr
           } else {
             ga = gr <= 0.f ? gr : 0.f;
             ba = br;
+            if (guard) { ga = fminf(ga, -1e-6f); ba = fmaxf(ba, 0.f); }      // gdn2.py:1972-1974
           }
         }
         QH[i * K + c] = qh;
@@ -287,17 +288,13 @@ int launch_prepass_fwd(const Geo& g, const void* q, const void* k, const void* v
   a.g = g; a.q = q; a.k = k; a.v = v; a.gg = gg; a.b = b; a.w = w; a.seg = seg; a.res = res;
   a.items = g.B * g.H * g.NC;
   a.scratch_per_cta = prepass_fwd_scratch_per_cta(g);
-  int grid = a.items < 148 ? a.items : 148;
+  int grid = a.items < sm_count() ? a.items : sm_count();
   if (scratch_floats < (size_t)grid * a.scratch_per_cta) return DN_ERR_SCRATCH_TOO_SMALL;
   a.scratch = scratch;
   a.smem_tile_off = 3 * g.C * g.C;
   if (4 * g.C * 33 > 2 * g.C * g.C) a.smem_tile_off = g.C * g.C + 4 * g.C * 33;
   size_t smem = ((size_t)a.smem_tile_off + GEMM_SMEM_FLOATS + g.C) * sizeof(float);
-  static bool attr_done = false;
-  if (!attr_done) {
-    cudaFuncSetAttribute(prepass_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
-    attr_done = true;
-  }
+  cudaFuncSetAttribute(prepass_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   prepass_fwd_kernel<<<grid, DN_THREADS, smem, st>>>(a);
   return cudaGetLastError() == cudaSuccess ? DN_OK : DN_ERR_CUDA_LAUNCH;
 }

@@ -32,7 +32,9 @@
 // tensor memory own one row per thread, which the image layout of the outputs (and the panel
 // layout [col / 4][row][4] of the fp32 scratch that carries A to the inverse) turns into stores of
 // 512 contiguous bytes per warp.
+#ifdef DN_PHASE_TIMING
 #include <cstdio>
+#endif
 #include "dn_chunkprep.cuh"
 #include "dn_kernels.cuh"
 
@@ -522,7 +524,7 @@ int launch_prepass_fwd_tc(const Geo& g, const void* q, const void* k, const void
   if (a.items <= 0) return DN_OK;
   a.scratch_per_cta = prepass_fwd_tc_scratch_per_cta();
   a.smem_tile_off = 0;
-  const int grid = a.items < 148 ? a.items : 148;
+  const int grid = a.items < sm_count() ? a.items : sm_count();
   if (scratch_floats < (size_t)grid * a.scratch_per_cta) return DN_ERR_SCRATCH_TOO_SMALL;
   a.scratch = scratch;
   int* err = device_error_ptr();

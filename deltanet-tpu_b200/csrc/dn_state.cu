@@ -29,7 +29,10 @@ __global__ void __launch_bounds__(DN_THREADS) state_fwd_kernel(StateArgs a) {
   extern __shared__ __align__(16) float smem[];
   const Geo& g = a.g;
   const int C = g.C, K = g.K, Vw = g.Vw;
-  const int v0 = blockIdx.x * VS, h = blockIdx.y, b = blockIdx.z;
+  const int h = blockIdx.y, b = blockIdx.z;
+  // slices past the value width carry the transition columns (see StateArgs::P_out)
+  const bool trans = (int)blockIdx.x * VS >= Vw;
+  const int v0 = trans ? 0 : blockIdx.x * VS, p0 = trans ? blockIdx.x * VS - Vw : 0;
   const int tid = threadIdx.x;
   float* S = smem;               // K*VS
   float* Vn = S + K * VS;        // C*VS
@@ -43,14 +46,15 @@ __global__ void __launch_bounds__(DN_THREADS) state_fwd_kernel(StateArgs a) {
     if (c == 0 || is_new) {
       for (int e = tid; e < K * VS; e += DN_THREADS) {
         float s0 = 0.f;
-        if (c == 0 && !is_new && a.init_state)
+        if (c == 0 && !is_new && trans) s0 = (e / VS == p0 + e % VS) ? 1.f : 0.f;
+        else if (c == 0 && !is_new && a.init_state)
           s0 = a.init_state[native_state_index(g, b, h, e / VS, v0 + e % VS)];
         S[e] = s0;
       }
       __syncthreads();
     }
     const size_t item = ((size_t)b * g.H + h) * g.NC + c;
-    if (a.states)
+    if (a.states && !trans)
       for (int e = tid; e < K * VS; e += DN_THREADS)
         a.states[item * K * Vw + (size_t)(e / VS) * Vw + v0 + e % VS] = S[e];
 
@@ -60,11 +64,11 @@ __global__ void __launch_bounds__(DN_THREADS) state_fwd_kernel(StateArgs a) {
         [&](int i, int kk) { return ldf(a.res.W, bW + rix(g.img, i, kk, K), pre); },
         [&](int kk, int j) { float s = S[kk * VS + j]; return sbf ? bf16r(s) : s; },
         [&](int i, int j, float acc) {
-          const float u = a.res.U ? ldf(a.res.U, bU + rix(g.img, i, v0 + j, Vw), pre) : 0.f;   // U == NULL: transition pass
+          const float u = (a.res.U && !trans) ? ldf(a.res.U, bU + rix(g.img, i, v0 + j, Vw), pre) : 0.f;   // transition columns: U = 0
           Vn[i * VS + j] = u - acc;
         },
         tile);
-    if (WITH_OUT) {
+    if (WITH_OUT && !trans) {
       // O = [qe | M] [S ; V_new]
       cta_gemm<true, true>(C, VS, K + C,
           [&](int i, int kk) {
@@ -92,8 +96,18 @@ __global__ void __launch_bounds__(DN_THREADS) state_fwd_kernel(StateArgs a) {
           S[i * VS + j] = carried + acc;
         },
         tile);
+    if (a.until_independent && !all_same) break;       // (uniform over the CTA: the flags depend on the chunk only)
+    if (a.until_independent && c + 1 < g.NC) {
+      bool nn, na;
+      chunk_flags(a.seg, g, b, c + 1, nn, na);
+      if (nn) break;
+    }
   }
-  if (a.final_state)
+  if (a.until_independent) return;                     // the caller has the final state from the shard's affine summary
+  if (trans) {
+    for (int e = tid; e < K * VS; e += DN_THREADS)
+      if (p0 + e % VS < K) a.P_out[(((size_t)b * g.H + h) * K + e / VS) * K + p0 + e % VS] = S[e];
+  } else if (a.final_state)
     for (int e = tid; e < K * VS; e += DN_THREADS)
       a.final_state[native_state_index(g, b, h, e / VS, v0 + e % VS)] = S[e];
 }
@@ -159,7 +173,9 @@ __global__ void __launch_bounds__(DN_THREADS) state_bwd_kernel(StateArgs a) {
           dH[i * VS + j] = is_new ? 0.f : carried + acc;
         },
         tile);
+    if (a.until_independent && (is_new || !all_same)) break;
   }
+  if (a.until_independent) return;                     // the caller has d_init from the shard's affine summary
   if (a.d_init)
     for (int e = tid; e < K * VS; e += DN_THREADS)
       a.d_init[native_state_index(g, b, h, e / VS, v0 + e % VS)] = dH[e];
@@ -173,16 +189,16 @@ static size_t state_smem(const Geo& g, bool bwd) {
 int launch_state_fwd(const StateArgs& a, cudaStream_t st) {
   const Geo& g = a.g;
   if (state_tc_eligible(g) && !force_simt()) return launch_state_fwd_tc(a, st);
-  dim3 grid(g.Vw / VS, g.H, g.B);
+  dim3 grid(g.Vw / VS + (a.P_out ? (g.K + VS - 1) / VS : 0), g.H, g.B);
   size_t smem = state_smem(g, false);
-  static bool done = false;
-  if (!done) {
-    cudaFuncSetAttribute(state_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
-    cudaFuncSetAttribute(state_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
-    done = true;
+  // (the attribute is per device: set on every launch, like the tensor-core launchers do)
+  if (a.out) {
+    cudaFuncSetAttribute(state_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    state_fwd_kernel<true><<<grid, DN_THREADS, smem, st>>>(a);
+  } else {
+    cudaFuncSetAttribute(state_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    state_fwd_kernel<false><<<grid, DN_THREADS, smem, st>>>(a);
   }
-  if (a.out) state_fwd_kernel<true><<<grid, DN_THREADS, smem, st>>>(a);
-  else state_fwd_kernel<false><<<grid, DN_THREADS, smem, st>>>(a);
   return cudaGetLastError() == cudaSuccess ? DN_OK : DN_ERR_CUDA_LAUNCH;
 }
 
@@ -191,11 +207,7 @@ int launch_state_bwd(const StateArgs& a, cudaStream_t st) {
   if (state_tc_eligible(g) && !force_simt()) return launch_state_bwd_tc(a, st);
   dim3 grid(g.Vw / VS, g.H, g.B);
   size_t smem = state_smem(g, true);
-  static bool done = false;
-  if (!done) {
-    cudaFuncSetAttribute(state_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
-    done = true;
-  }
+  cudaFuncSetAttribute(state_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   state_bwd_kernel<<<grid, DN_THREADS, smem, st>>>(a);
   return cudaGetLastError() == cudaSuccess ? DN_OK : DN_ERR_CUDA_LAUNCH;
 }

@@ -13,25 +13,11 @@
 //     operand (K-major descriptor) and as its transpose (MN-major descriptor), so ke^T, M^T,
 //     qe^T and W^T need no data movement.
 // Every wait on the MMA barrier is bounded; on a timeout the CTA stops issuing tensor work,
-// raises the library's device error word and runs to its end.
+// raises the library's error word and runs to its end.
 #include "dn_kernels.cuh"
 #include "dn_umma.cuh"
 
 namespace dn {
-
-__device__ int g_device_error = 0;
-
-int read_device_error() {
-  int v = 0;
-  cudaMemcpyFromSymbol(&v, g_device_error, sizeof(int));
-  return v;
-}
-
-int* device_error_ptr() {
-  int* p = nullptr;
-  cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_device_error);
-  return p;
-}
 
 namespace {
 
@@ -98,7 +84,10 @@ __global__ void __launch_bounds__(128, 1) state_fwd_tc_kernel(StateArgs a) {
   __shared__ uint32_t tmem_base;
   const Geo& g = a.g;
   constexpr int C = 128, K = 128;
-  const int Vw = g.Vw, v0 = blockIdx.x * VS, h = blockIdx.y, b = blockIdx.z;
+  const int Vw = g.Vw, h = blockIdx.y, b = blockIdx.z;
+  // slices past the value width carry the transition columns (see StateArgs::P_out)
+  const bool trans = (int)blockIdx.x * VS >= Vw;
+  const int v0 = trans ? 0 : blockIdx.x * VS, p0 = trans ? blockIdx.x * VS - Vw : 0;
   const int row = threadIdx.x, warp = row >> 5;
   uint4* sW = reinterpret_cast<uint4*>(sm);
   uint4* sQE = sW + TILE_U4;
@@ -111,12 +100,12 @@ __global__ void __launch_bounds__(128, 1) state_fwd_tc_kernel(StateArgs a) {
   umma::tc_fence_before();
   __syncthreads();
   umma::tc_fence_after();
-  umma::Ctx cx{tmem_base, &bar, 0u, &g_device_error, false};
+  umma::Ctx cx{tmem_base, &bar, 0u, a.err, false};
   constexpr uint32_t colP = 0, colO = VS, colS = 2 * VS;
   const bool img = g.img;
   uint32_t tph[2] = {0u, 0u};
   auto tile_wait = [&](int i) {                         // bounded, like every wait here
-    if (!umma::mbar_wait(&tb[i], tph[i])) atomicExch(&g_device_error, 1);
+    if (!umma::mbar_wait(&tb[i], tph[i])) umma::report_timeout(a.err);
     tph[i] ^= 1u;
   };
 
@@ -124,7 +113,8 @@ __global__ void __launch_bounds__(128, 1) state_fwd_tc_kernel(StateArgs a) {
   const __nv_bfloat16* QEg = reinterpret_cast<const __nv_bfloat16*>(a.res.qe);
   const __nv_bfloat16* KEg = reinterpret_cast<const __nv_bfloat16*>(a.res.ke);
   const __nv_bfloat16* Mg = reinterpret_cast<const __nv_bfloat16*>(a.res.M);
-  const __nv_bfloat16* Ug = reinterpret_cast<const __nv_bfloat16*>(a.res.U);
+  const __nv_bfloat16* Ug = trans ? nullptr : reinterpret_cast<const __nv_bfloat16*>(a.res.U);
+  float* const states = trans ? nullptr : a.states;
   const size_t item0 = ((size_t)b * g.H + h) * g.NC;
 
   const int cb = a.c_begin, ce = a.c_end;               // chunk range of this launch
@@ -163,21 +153,24 @@ __global__ void __launch_bounds__(128, 1) state_fwd_tc_kernel(StateArgs a) {
   chunk_flags(a.seg, g, b, cb, is_new, all_same);
   for (int c = cb; c < ce; ++c) {
     const size_t item = item0 + c;
-    if (c == 0 && !is_new && a.init_state) {
+    if (c == 0 && !is_new && trans) {
+#pragma unroll
+      for (int j = 0; j < VS; ++j) S[j] = row == p0 + j ? 1.f : 0.f;
+    } else if (c == 0 && !is_new && a.init_state) {
 #pragma unroll
       for (int j = 0; j < VS; ++j) S[j] = a.init_state[native_state_index_tc(g, b, h, row, v0 + j)];
     } else if (is_new) {
 #pragma unroll
       for (int j = 0; j < VS; ++j) S[j] = 0.f;
     }
-    if (a.states) {
-      float4* dst = reinterpret_cast<float4*>(a.states + item * K * Vw + (size_t)row * Vw + v0);
+    if (states) {
+      float4* dst = reinterpret_cast<float4*>(states + item * K * Vw + (size_t)row * Vw + v0);
 #pragma unroll
       for (int j = 0; j < VS / 4; ++j) dst[j] = make_float4(S[4 * j], S[4 * j + 1], S[4 * j + 2], S[4 * j + 3]);
     }
     stage_rows<VS>(sS, row, S);
-    if (a.states && g.img) {                            // the same bf16 rows, as an operand image for the backward
-      uint4* simg = reinterpret_cast<uint4*>(const_cast<__nv_bfloat16*>(states_img(g, a.states)) + item * K * Vw) + (size_t)(v0 / 8) * 128 + row;
+    if (states && g.img) {                              // the same bf16 rows, as an operand image for the backward
+      uint4* simg = reinterpret_cast<uint4*>(const_cast<__nv_bfloat16*>(states_img(g, states)) + item * K * Vw) + (size_t)(v0 / 8) * 128 + row;
 #pragma unroll
       for (int p = 0; p < VS / 8; ++p) simg[p * 128] = sS[p * 128 + row];
     }
@@ -200,12 +193,16 @@ __global__ void __launch_bounds__(128, 1) state_fwd_tc_kernel(StateArgs a) {
     // the next chunk's document flags: their (dependent) global loads overlap this chunk's products
     bool nis_new = false, nall_same = false;
     if (c + 1 < ce) chunk_flags(a.seg, g, b, c + 1, nis_new, nall_same);
+    // the last chunk this CTA walks: the end of the range, or (until_independent) the point after which
+    // nothing depends on the state the chain started from.  Uniform over the CTA (the flags depend on the
+    // chunk only).  Nothing is prefetched past it, so no copy is in flight when the CTA leaves.
+    const bool last = c + 1 >= ce || (a.until_independent && (!all_same || nis_new));
 
     if (img) tile_wait(0); else umma::cp_async_wait<1>();      // this chunk's W has landed
     umma::pre_issue_sync();
     umma::issue<VS, false, true>(cx, sW, sS, K, colP, false);          // P = W S
     umma::commit_wait(cx);
-    if (c + 1 < ce) fetch_W(item + 1); else umma::cp_async_commit();
+    if (!last) fetch_W(item + 1); else umma::cp_async_commit();
 
     float vn[VS];
     read_acc<VS>(cx, colP, warp, vn);
@@ -220,15 +217,15 @@ __global__ void __launch_bounds__(128, 1) state_fwd_tc_kernel(StateArgs a) {
 
     if (img) tile_wait(1); else umma::cp_async_wait<1>();      // this chunk's qe, M, ke have landed
     umma::pre_issue_sync();
-    if (WITH_OUT) {
+    if (WITH_OUT && !trans) {
       umma::issue<VS, false, true>(cx, sQE, sS, K, colO, false);       // O  = qe S
       umma::issue<VS, false, true>(cx, sM, sVn, C, colO, true);        //    + M V_new
     }
     umma::issue<VS, true, true>(cx, sKE, sVn, C, colS, false);         // ke^T V_new
     umma::commit_wait(cx);
-    if (c + 1 < ce) fetch_QMK(item + 1); else umma::cp_async_commit();
+    if (!last) fetch_QMK(item + 1); else umma::cp_async_commit();
 
-    if (WITH_OUT) {
+    if (WITH_OUT && !trans) {
       float o[VS];
       read_acc<VS>(cx, colO, warp, o);
       const int t = c * C + row;
@@ -256,8 +253,15 @@ __global__ void __launch_bounds__(128, 1) state_fwd_tc_kernel(StateArgs a) {
     for (int j = 0; j < VS; ++j) S[j] = fmaf(dec, S[j], sn[j]);       // S <- decay * S + ke^T V_new
     umma::tc_fence_before();
     is_new = nis_new; all_same = nall_same;
+    if (last) break;
   }
-  if (ce < g.NC) {
+  if (a.until_independent) {
+    // nothing to hand on: the caller has the final state from the shard's affine summary
+  } else if (trans) {
+    float* dst = a.P_out + (((size_t)b * g.H + h) * K + row) * K + p0;
+#pragma unroll
+    for (int j = 0; j < VS; ++j) dst[j] = S[j];
+  } else if (ce < g.NC) {
 #pragma unroll
     for (int j = 0; j < VS; ++j) carry[j] = S[j];
   } else if (a.final_state) {
@@ -290,14 +294,14 @@ __global__ void __launch_bounds__(128, 1) state_bwd_tc_kernel(StateArgs a) {
   if (row == 0) { umma::mbar_init(&bar, 1); umma::mbar_init(&tb[0], 1); umma::mbar_init(&tb[1], 1); umma::fence_mbar_init(); }
   uint32_t tph[2] = {0u, 0u};
   auto tile_wait = [&](int i) {                         // bounded, like every wait here
-    if (!umma::mbar_wait(&tb[i], tph[i])) atomicExch(&g_device_error, 1);
+    if (!umma::mbar_wait(&tb[i], tph[i])) umma::report_timeout(a.err);
     tph[i] ^= 1u;
   };
   if (warp == 0) umma::tmem_alloc(&tmem_base, tmem_cols(VS));
   umma::tc_fence_before();
   __syncthreads();
   umma::tc_fence_after();
-  umma::Ctx cx{tmem_base, &bar, 0u, &g_device_error, false};
+  umma::Ctx cx{tmem_base, &bar, 0u, a.err, false};
   constexpr uint32_t colV = 0, colH = VS;
 
   const __nv_bfloat16* Wg = reinterpret_cast<const __nv_bfloat16*>(a.res.W);
@@ -395,9 +399,13 @@ __global__ void __launch_bounds__(128, 1) state_bwd_tc_kernel(StateArgs a) {
         dO[4 * p + 2] = __uint_as_float(raw[p].z); dO[4 * p + 3] = __uint_as_float(raw[p].w);
       }
     }
-    fetch_dO(c - 1);                                    // in flight during this chunk's products
+    // the last chunk this CTA walks: the start of the range, or (until_independent) the point below which
+    // nothing depends on the cotangent the chain started from.  Uniform over the CTA; nothing is
+    // prefetched past it.
+    const bool last = c <= cb || (a.until_independent && (is_new || !all_same));
+    fetch_dO(last ? cb - 1 : c - 1);                    // in flight during this chunk's products (zeros past the end)
     bool nis_new = false, nall_same = false;
-    if (c > cb) chunk_flags(a.seg, g, b, c - 1, nis_new, nall_same);
+    if (!last) chunk_flags(a.seg, g, b, c - 1, nis_new, nall_same);
     stage_rows<VS>(sdO, row, dO);
     stage_rows<VS>(sdH, row, dH);
     if (img) {                                           // dH as a bf16 operand image
@@ -426,7 +434,7 @@ __global__ void __launch_bounds__(128, 1) state_bwd_tc_kernel(StateArgs a) {
     umma::issue<VS, true, true>(cx, sM, sdO, C, colV, false);          // dV  = M^T dO
     umma::issue<VS, false, true>(cx, sKE, sdH, K, colV, true);         //     + ke dH
     umma::commit_wait(cx);
-    if (c > cb) fetch_MK(item - 1); else umma::cp_async_commit();
+    if (!last) fetch_MK(item - 1); else umma::cp_async_commit();
 
     float dv[VS];
     read_acc<VS>(cx, colV, warp, dv);
@@ -451,7 +459,7 @@ __global__ void __launch_bounds__(128, 1) state_bwd_tc_kernel(StateArgs a) {
     umma::issue<VS, true, true>(cx, sQE, sdO, C, colH, false);         // qe^T dO
     umma::issue<VS, true, true>(cx, sW, sdV, C, colH, true);           // - W^T dV
     umma::commit_wait(cx);
-    if (c > cb) fetch_QW(item - 1); else umma::cp_async_commit();
+    if (!last) fetch_QW(item - 1); else umma::cp_async_commit();
 
     float dn_[VS];
     read_acc<VS>(cx, colH, warp, dn_);
@@ -459,8 +467,11 @@ __global__ void __launch_bounds__(128, 1) state_bwd_tc_kernel(StateArgs a) {
     for (int j = 0; j < VS; ++j) dH[j] = is_new ? 0.f : fmaf(dec, dH[j], dn_[j]);
     umma::tc_fence_before();
     is_new = nis_new; all_same = nall_same;
+    if (last) break;
   }
-  if (cb > 0) {
+  if (a.until_independent) {
+    // nothing to hand on: the caller has d_init from the shard's affine summary
+  } else if (cb > 0) {
 #pragma unroll
     for (int j = 0; j < VS; ++j) carry[j] = dH[j];
   } else if (a.d_init) {
@@ -474,7 +485,7 @@ __global__ void __launch_bounds__(128, 1) state_bwd_tc_kernel(StateArgs a) {
 
 int pick_vs(const Geo& g) {
   const int chains = g.B * g.H;
-  if (g.Vw % 64 == 0 && chains * (g.Vw / 64) >= 148) return 64;
+  if (g.Vw % 64 == 0 && chains * (g.Vw / 64) >= sm_count()) return 64;
   return 32;
 }
 
@@ -485,7 +496,7 @@ size_t tc_smem(bool bwd) {
 
 template <int VS>
 int launch_fwd_vs(const StateArgs& a, cudaStream_t st) {
-  dim3 grid(a.g.Vw / VS, a.g.H, a.g.B);
+  dim3 grid((a.g.Vw + (a.P_out ? a.g.K : 0)) / VS, a.g.H, a.g.B);
   const size_t smem = tc_smem<VS>(false);
   if (a.out) {
     cudaFuncSetAttribute(state_fwd_tc_kernel<VS, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -515,12 +526,16 @@ bool state_tc_eligible(const Geo& g) {
 static StateArgs with_range(const StateArgs& in) {
   StateArgs a = in;
   if (a.c_end <= 0) { a.c_begin = 0; a.c_end = a.g.NC; }
+  a.err = device_error_ptr();
   return a;
 }
 
 int launch_state_fwd_tc(const StateArgs& in, cudaStream_t st) {
   const StateArgs a = with_range(in);
-  switch (pick_vs(a.g)) {
+  // with the transition columns aboard, 64-column slices keep one (batch, head)'s Vw + K columns in few
+  // enough CTAs to run in one wave; the chain's time is its per-chunk latency, not the slice width
+  const int vs = (a.P_out && a.g.Vw % 64 == 0) ? 64 : pick_vs(a.g);
+  switch (vs) {
     case 64: return launch_fwd_vs<64>(a, st);
     default: return launch_fwd_vs<32>(a, st);
   }

@@ -25,6 +25,12 @@ constexpr uint32_t SPIN_LIMIT = 1u << 22;   // bounded wait: ~tens of ms, then t
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
+// A bounded wait gave up: raise the library's error word (a plain store; the word may live in host
+// memory that the device reaches over the bus).
+__device__ __forceinline__ void report_timeout(int* err) {
+  if (err) { *reinterpret_cast<volatile int*>(err) = 1; __threadfence_system(); }
+}
+
 // ---- mbarrier ----------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
@@ -243,7 +249,7 @@ __device__ __forceinline__ void commit_wait(Ctx& cx) {
   if (threadIdx.x == 0 && !cx.dead) mma_commit(cx.bar);
   if (!cx.dead && !mbar_wait(cx.bar, cx.phase)) {
     cx.dead = true;
-    if (cx.err) atomicExch(cx.err, 1);
+    report_timeout(cx.err);
   }
   cx.phase ^= 1u;
   tc_fence_after();

@@ -20,6 +20,7 @@ DN_STABILITY_GUARD = 1 << 3
 DN_STATE_FP32_MM = 1 << 4
 DN_INFERENCE = 1 << 5
 DN_TRUNC_DT_BF16 = 1 << 6
+DN_RESET_PER_HEAD = 1 << 7
 
 
 class Shape(C.Structure):
@@ -30,7 +31,7 @@ class Shape(C.Structure):
 
 
 class Exec(C.Structure):
-    _fields_ = [(n, C.c_int32) for n in ("H", "Vw", "G", "NC", "pre_dtype")]
+    _fields_ = [(n, C.c_int32) for n in ("H", "Vw", "G", "NC", "pre_dtype", "chunk")]
 
 
 class Residuals(C.Structure):
@@ -48,12 +49,15 @@ _P = C.c_void_p
 _SIGNATURES = {
     "dn_version": (C.c_int, []),
     "dn_device_error": (C.c_int, []),
+    "dn_device_error_reset": (None, []),
+    "dn_cap_state": (C.c_int, [_P, C.c_int64, C.c_int32, C.c_int32, C.c_float, _P]),
     "dn_status_string": (C.c_char_p, [C.c_int]),
     "dn_exec_view": (C.c_int, [C.POINTER(Shape), C.POINTER(Exec)]),
     "dn_residual_bytes": (C.c_size_t, [C.POINTER(Shape)]),
     "dn_residual_carve": (C.c_int, [C.POINTER(Shape), _P, C.POINTER(Residuals)]),
     "dn_scratch_bytes": (C.c_size_t, [C.POINTER(Shape), C.c_int, C.c_int]),
     "dn_canonical_segments": (C.c_int, [_P, _P, _P, C.c_int32, C.c_int32, _P]),
+    "dn_cu_seqlens_segments": (C.c_int, [_P, C.c_int32, _P, _P, C.c_int32, C.c_int32, _P]),
     "dn_chunk_fwd": (C.c_int, [C.POINTER(Shape)] + [_P] * 10 + [C.POINTER(Residuals), _P, C.c_size_t, _P]),
     "dn_chunk_bwd": (C.c_int, [C.POINTER(Shape)] + [_P] * 8 + [C.POINTER(Residuals)] + [_P] * 9 + [_P, C.c_size_t, _P]),
     "dn_prepass_fwd": (C.c_int, [C.POINTER(Shape)] + [_P] * 7 + [C.POINTER(Residuals), _P, C.c_size_t, _P]),
@@ -63,6 +67,9 @@ _SIGNATURES = {
     "dn_prepass_bwd": (C.c_int, [C.POINTER(Shape)] + [_P] * 7 + [C.POINTER(Residuals)] + [_P] * 9 + [_P, C.c_size_t, _P]),
     "dn_decode_step": (C.c_int, [C.POINTER(DecodeShape)] + [_P] * 11),
     "dn_sp_transition": (C.c_int, [C.POINTER(Shape), C.POINTER(Residuals)] + [_P] * 4),
+    "dn_sp_summary": (C.c_int, [C.POINTER(Shape), C.POINTER(Residuals)] + [_P] * 5),
+    "dn_sp_correct_fwd": (C.c_int, [C.POINTER(Shape), C.POINTER(Residuals)] + [_P] * 4),
+    "dn_sp_correct_bwd": (C.c_int, [C.POINTER(Shape), C.POINTER(Residuals)] + [_P] * 6),
     "dn_sp_apply": (C.c_int, [_P] * 4 + [C.c_int32] * 6 + [_P]),
     "dn_static_scratch_bytes": (C.c_size_t, []),
     "dn_prepass_fwd_static": (C.c_int, [C.POINTER(Shape)] + [_P] * 7 + [C.POINTER(Residuals), _P]),

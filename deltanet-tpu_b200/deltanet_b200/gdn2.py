@@ -135,16 +135,17 @@ def _segments(segment_ids, cu_seqlens, B, Lq, device, first_is_new):
         raw = segment_ids if segment_ids.dim() == 2 else segment_ids[None].expand(B, Lq)
         raw = raw.to(device=device, dtype=torch.int32).contiguous()
     elif cu_seqlens is not None:
-        cu = np.asarray(cu_seqlens.detach().cpu() if isinstance(cu_seqlens, torch.Tensor) else cu_seqlens)
-        if len(cu) == 0 or int(cu[0]) != 0:
-            raise ValueError(f"cu_seqlens[0] must be 0, got {int(cu[0]) if len(cu) else 'empty'}.")
-        if int(cu[-1]) != Lq:
-            raise ValueError(f"cu_seqlens[-1] ({int(cu[-1])}) must equal sequence length ({Lq}).")
-        lens = np.diff(cu)
-        if len(lens) > 0 and np.any(lens <= 0):
-            raise ValueError(f"cu_seqlens must be strictly monotonically increasing, got {cu_seqlens}.")
-        ids = np.repeat(np.arange(len(lens), dtype=np.int32), lens)
-        raw = torch.from_numpy(ids).to(device)[None].expand(B, Lq).contiguous()
+        if isinstance(cu_seqlens, torch.Tensor) and cu_seqlens.is_cuda:
+            # values on the device are not brought back to the host (no synchronisation), hence not
+            # checked, as the reference does not check traced values (gdn2.py:2062-2077)
+            cu_dev = cu_seqlens.to(device=device, dtype=torch.int32).contiguous()
+        else:
+            cu = _validate_cu_seqlens(cu_seqlens, Lq)
+            cu_dev = torch.from_numpy(cu.astype(np.int32)).to(device)
+        out = torch.empty(B, Lq, dtype=torch.int32, device=device)
+        L.check(lib.dn_cu_seqlens_segments(cu_dev.data_ptr(), cu_dev.numel(), _ptr(first_is_new), out.data_ptr(),
+                                           B, Lq, _stream()), "dn_cu_seqlens_segments")
+        return out, None
     elif first_is_new is not None:
         raw = torch.zeros(B, Lq, dtype=torch.int32, device=device)
     else:
@@ -155,9 +156,25 @@ def _segments(segment_ids, cu_seqlens, B, Lq, device, first_is_new):
     return out, raw
 
 
+def _validate_cu_seqlens(cu_seqlens, Lq):
+    """Host-side cu_seqlens checks of the reference (gdn2.py:2041-2061); returns a numpy array."""
+    cu = np.asarray(cu_seqlens.detach().cpu() if isinstance(cu_seqlens, torch.Tensor) else cu_seqlens)
+    if len(cu) == 0 or int(cu[0]) != 0:
+        raise ValueError(f"cu_seqlens[0] must be 0, got {int(cu[0]) if len(cu) else 'empty'}.")
+    if int(cu[-1]) != Lq:
+        raise ValueError(f"cu_seqlens[-1] ({int(cu[-1])}) must equal sequence length ({Lq}).")
+    if len(cu) > 1 and np.any(np.diff(cu) <= 0):
+        raise ValueError(f"cu_seqlens must be strictly monotonically increasing, got {cu_seqlens}.")
+    return cu
+
+
 def _cap_state(state, tau):
-    nrm = torch.sqrt((state ** 2).sum(dim=(-2, -1), keepdim=True) + 1e-6)
-    return state * torch.clamp(tau / nrm, max=1.0)
+    """stability_guard's Frobenius cap (gdn2.py:2180-2188), in place on a fresh fp32 state."""
+    state = state.contiguous()
+    n = state.numel() // (state.shape[-2] * state.shape[-1])
+    L.check(L.lib().dn_cap_state(state.data_ptr(), n, state.shape[-2], state.shape[-1], float(tau), _stream()),
+            "dn_cap_state")
+    return state
 
 
 def chunk_gdn2(
@@ -236,6 +253,8 @@ def chunk_gdn2(
             raise ValueError(f"{name} last dimension ({x.shape[3]}) must be 1 or {wname} ({width}).")
     if segment_ids is not None and cu_seqlens is not None:
         raise ValueError("Cannot pass both segment_ids and cu_seqlens; specify at most one.")
+    if cu_seqlens is not None and not (isinstance(cu_seqlens, torch.Tensor) and cu_seqlens.is_cuda):
+        _validate_cu_seqlens(cu_seqlens, Lq)
     if segment_ids is not None:
         if segment_ids.dtype.is_floating_point or segment_ids.dtype == torch.bool:
             raise ValueError(f"segment_ids must have integer dtype, got {segment_ids.dtype}.")
@@ -262,9 +281,6 @@ def chunk_gdn2(
     _require_cuda(q, k, v, g, b, w, initial_state)
 
     out_dtype = v.dtype
-    if stability_guard and not fuse_prologue:
-        b = torch.clamp(b, min=0.0)
-        g = torch.clamp(g, max=-1e-6)
     qkv_dt = _common_dtype((q, k, v))
     gate_dt = _common_dtype((g, b, w))
     q, k, v = (t.to(qkv_dt).contiguous() for t in (q, k, v))
@@ -292,8 +308,8 @@ def chunk_gdn2(
         flags |= L.DN_QK_L2NORM
     if fuse_prologue:
         flags |= L.DN_FUSE_PROLOGUE
-        if stability_guard:
-            flags |= L.DN_STABILITY_GUARD
+    if stability_guard:              # the gate clamps (gdn2.py:1972-1974, 141) happen where the kernels load g, b
+        flags |= L.DN_STABILITY_GUARD
     if state_fp32_matmul:
         flags |= L.DN_STATE_FP32_MM
     if truncate_bwd_dT_bf16:
@@ -412,14 +428,27 @@ def gdn2_decode_step(
             raise ValueError(f"{name} shape {tuple(x.shape)} invalid for batch={B}, Hk={Hk}, Hv={Hv}, "
                              f"{'V' if name == 'w' else 'K'}={width}.")
     tgt = _torch_dtype(state_dtype)
-    reset_t = None
+    reset_t, reset_per_head = None, False
     if reset is not None:
         reset_t = torch.as_tensor(reset, device=q.device)
         if reset_t.dim() > 0 and reset_t.shape[0] != B:
             raise ValueError(f"reset batch dimension ({reset_t.shape[0]}) must match input batch dimension ({B}).")
         if reset_t.dim() > 4:
             raise ValueError(f"reset ndim ({reset_t.dim()}) cannot exceed 4.")
-        reset_t = reset_t.reshape(-1)[:B] if reset_t.dim() > 0 else reset_t.expand(B)
+        # the reference broadcasts reset over (B,Hv,K,V) (gdn2.py:2404-2410): one flag per sequence, or
+        # one per sequence and value head
+        if reset_t.dim() == 0:
+            reset_t = reset_t.expand(B)
+        else:
+            while reset_t.dim() > 2 and reset_t.shape[-1] == 1:
+                reset_t = reset_t[..., 0]
+            if reset_t.dim() == 2 and reset_t.shape[1] == 1:
+                reset_t = reset_t[:, 0]
+            if reset_t.dim() == 2 and reset_t.shape[1] == v.shape[-2]:
+                reset_per_head = True
+            elif reset_t.dim() != 1:
+                raise ValueError(f"reset shape {tuple(torch.as_tensor(reset).shape)} must broadcast over (B, Hv, 1, 1); "
+                                 "per-element resets inside a (K, V) state are not supported.")
         reset_t = reset_t.to(torch.uint8).contiguous()
     _require_cuda(q, k, v, g, b, w, state)
     if scale is None:
@@ -434,7 +463,8 @@ def gdn2_decode_step(
     state = state.contiguous()
     lay = lambda x: (x.shape[1], 1) if x.dim() == 2 else (x.shape[1], x.shape[2])
     (gh, gc), (bh, bc), (wh, wc) = lay(g), lay(b), lay(w)
-    flags = (L.DN_QK_L2NORM if qk_l2norm else 0) | (L.DN_STABILITY_GUARD if stability_guard else 0)
+    flags = (L.DN_QK_L2NORM if qk_l2norm else 0) | (L.DN_STABILITY_GUARD if stability_guard else 0) | \
+        (L.DN_RESET_PER_HEAD if reset_per_head else 0)
     if out_state is None:
         out_state = torch.empty(B, Hv, K, V, dtype=tgt, device=q.device)
     elif out_state.dtype != tgt or tuple(out_state.shape) != (B, Hv, K, V) or not out_state.is_contiguous():

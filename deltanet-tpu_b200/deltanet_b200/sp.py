@@ -3,22 +3,35 @@
 The reference has no sequence-parallel implementation; it provides the hooks
 (``initial_state`` / ``output_final_state`` / ``initial_state_segment_id``,
 ``src/deltanet_tpu/gdn2.py:2081-2085``).  Chaining those serially would make every rank wait for
-the whole state pass of its predecessor.  Instead the chain only carries small states:
+the whole state pass of its predecessor.  Two facts make the chain cheap instead:
 
-  forward   1. every rank: prepass + state pass from a zero state  -> Q (its final state) and
-               the transition matrix P (the state pass is affine: S_out = P S_in + Q);
-            2. chain: rank r receives S_in from r-1, sends P S_in + Q to r+1 (zeroed where the
-               next shard starts a new document);
-            3. every rank: state pass again from its true S_in (outputs, chunk states).
-  backward  the mirror image with the state cotangent: a reverse pass with zero incoming
-            cotangent gives d_init0, the chain carries d_S_in = P^T d_final + d_init0 from rank
-            r to r-1, and a second reverse pass with the true d_final feeds the chunk-parallel
-            backward.
+* the state pass of a shard is affine in the incoming state, ``S_out = P S_in + Q`` per (batch, exec
+  head), and P comes out of the SAME launch as Q: K extra columns that start from the identity with
+  U = 0 (the recurrence acts on every value column independently);
+* whatever a shard computes after its first document boundary does not depend on the incoming state
+  at all (and, going backwards, nothing before its last boundary depends on the incoming cotangent).
+
+  forward   1. every rank: prepass, then ONE state pass from a zero state that writes outputs and
+               chunk states for the whole shard (final after the first boundary, provisional
+               before it) and yields Q and P;
+            2. chain: rank r receives S_in from r-1 and sends P S_in + Q to r+1 (zeroed where the
+               next shard starts a new document); that value is also the shard's final state;
+            3. every rank: the state pass again from its true S_in, which stops at the first chunk
+               that no longer depends on it.
+  backward  the mirror image with the state cotangent: a reverse pass with zero incoming cotangent
+            writes dV / dH for the whole shard and d_init0, the chain carries
+            d_S_in = P^T d_final + d_init0 from rank r to r-1, a second reverse pass from the true
+            d_final stops where dH no longer depends on it, and the chunk-parallel backward runs
+            over the shard.
+
+With ``recompute_states`` nothing but the inputs, P and S_in survives the forward; the backward
+rebuilds the prepass outputs and the chunk states first (what ``gdn2.py:1545-1630`` does per call).
 
 The per-shard arithmetic is behind an ``ops`` object: ``CudaOps`` (the C-ABI kernels) on GPUs;
 tests substitute CPU ops to exercise the chain logic with the gloo backend.  Point-to-point
 transfers use ``torch.distributed`` (NCCL over NVLink on a B200 box); the received state always
-lands in a local buffer before any kernel reads it.
+lands in a local buffer before any kernel reads it.  Sends are not waited for: the correction pass
+of a rank runs while its state travels on.
 """
 from __future__ import annotations
 
@@ -39,29 +52,43 @@ class Chain:
         self.group = group
         self.rank = dist.get_rank(group)
         self.size = dist.get_world_size(group)
+        self._pending = []          # (work, tensor) of sends in flight: kept alive until the call ends
 
     def _peer(self, r):
         return dist.get_global_rank(self.group, r) if self.group is not None else r
 
+    def _send(self, y, r):
+        y = y.contiguous()
+        self._pending.append((dist.isend(y, dst=self._peer(r), group=self.group), y))
+
+    def _recv(self, like, r):
+        x = torch.empty_like(like)
+        dist.irecv(x, src=self._peer(r), group=self.group).wait()      # stream-ordered for NCCL, blocking for gloo
+        return x
+
+    def drain(self):
+        """Waits for this rank's sends (their buffers may be released afterwards)."""
+        for work, _ in self._pending:
+            work.wait()
+        self._pending.clear()
+
     def forward(self, first_value, step):
         """first_value on rank 0, else what rank-1 sent; returns (received, produced); sends produced on."""
-        x = first_value
-        if self.rank > 0:
-            x = torch.empty_like(first_value)
-            dist.recv(x, src=self._peer(self.rank - 1), group=self.group)
-        y = step(x)
+        x = first_value if self.rank == 0 else self._recv(first_value, self.rank - 1)
+        y, y_next = step(x)
         if self.rank < self.size - 1:
-            dist.send(y.contiguous(), dst=self._peer(self.rank + 1), group=self.group)
+            self._send(y_next, self.rank + 1)
         return x, y
 
     def backward(self, last_value, step):
+        """Cotangents flow r+1 -> r.  last_value is this rank's own d_final_state (zeros if none): it is
+        added to what rank+1 sends, so a loss on an intermediate rank's final_state is honoured too."""
         x = last_value
         if self.rank < self.size - 1:
-            x = torch.empty_like(last_value)
-            dist.recv(x, src=self._peer(self.rank + 1), group=self.group)
+            x = self._recv(last_value, self.rank + 1) + last_value
         y = step(x)
         if self.rank > 0:
-            dist.send(y.contiguous(), dst=self._peer(self.rank - 1), group=self.group)
+            self._send(y, self.rank - 1)
         return x, y
 
     def gather_edges(self, edges):
@@ -89,19 +116,28 @@ class LocalChain:
                       edges=[None] * n, barrier=threading.Barrier(n))
         return [LocalChain(r, n, shared) for r in range(n)]
 
+    @staticmethod
+    def _handoff(y):
+        return y.clone()            # (all threads of the process enqueue on the same stream: host order is device order)
+
     def forward(self, first_value, step):
         x = first_value if self.rank == 0 else self._s["fwd"][self.rank].get(timeout=120)
-        y = step(x)
+        y, y_next = step(x)
         if self.rank < self.size - 1:
-            self._s["fwd"][self.rank + 1].put(y.clone())
+            self._s["fwd"][self.rank + 1].put(self._handoff(y_next))
         return x, y
 
     def backward(self, last_value, step):
-        x = last_value if self.rank == self.size - 1 else self._s["bwd"][self.rank].get(timeout=120)
+        x = last_value
+        if self.rank < self.size - 1:
+            x = self._s["bwd"][self.rank].get(timeout=120) + last_value
         y = step(x)
         if self.rank > 0:
-            self._s["bwd"][self.rank - 1].put(y.clone())
+            self._s["bwd"][self.rank - 1].put(self._handoff(y))
         return x, y
+
+    def drain(self):
+        pass
 
     def gather_edges(self, edges):
         self._s["edges"][self.rank] = edges
@@ -116,11 +152,12 @@ def continues_from_previous(edges_prev, edges_mine):
 
 # --------------------------------------------------------------------------------- CUDA shard ops
 class CudaOps:
-    """Per-shard work through the C-ABI phase entry points (no torch arithmetic on the path)."""
+    """Per-shard work through the C-ABI entry points (no torch arithmetic on the path)."""
 
-    def __init__(self, *, chunk_size=128, precision="bf16", scale=None, qk_l2norm=False, fuse_prologue=False):
+    def __init__(self, *, chunk_size=128, precision="bf16", scale=None, qk_l2norm=False, fuse_prologue=False,
+                 recompute_states=False):
         self.chunk, self.precision, self.scale = chunk_size, precision, scale
-        self.l2, self.fuse = qk_l2norm, fuse_prologue
+        self.l2, self.fuse, self.recompute = qk_l2norm, fuse_prologue, recompute_states
 
     # -- forward
     def prepare(self, q, k, v, g, b, w, seg_raw):
@@ -143,81 +180,84 @@ class CudaOps:
         seg = torch.empty(B, Lq, dtype=torch.int32, device=q.device)
         raw = seg_raw.to(device=q.device, dtype=torch.int32).contiguous()
         L.check(lib.dn_canonical_segments(raw.data_ptr(), None, seg.data_ptr(), B, Lq, _g._stream()), "segments")
+        c = dict(shape=shape, ex=ex, seg=seg, ins=(q, k, v, g, b, w), dims=(B, Lq, Hk, Hv, K, V))
+        self._prepass(c)
+        return c
+
+    def _prepass(self, c):
+        """Runs the forward prepass into a fresh residual block (with T and room for the chunk states)."""
+        lib, shape = L.lib(), c["shape"]
+        q, k, v, g, b, w = c["ins"]
         block = torch.empty(lib.dn_residual_bytes(shape), dtype=torch.uint8, device=q.device)
         res = L.Residuals()
         L.check(lib.dn_residual_carve(shape, block.data_ptr(), res), "carve")
         n = max(lib.dn_scratch_bytes(shape, 0, 0), lib.dn_scratch_bytes(shape, 1, 0))
         scratch = torch.empty(n, dtype=torch.uint8, device=q.device)
         L.check(lib.dn_prepass_fwd(shape, q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), b.data_ptr(),
-                                   w.data_ptr(), seg.data_ptr(), res, scratch.data_ptr(), n, _g._stream()),
+                                   w.data_ptr(), c["seg"].data_ptr(), res, scratch.data_ptr(), n, _g._stream()),
                 "dn_prepass_fwd")
-        return dict(shape=shape, ex=ex, res=res, block=block, scratch=scratch, seg=seg, ins=(q, k, v, g, b, w),
-                    dims=(B, Lq, Hk, Hv, K, V))
+        c.update(res=res, block=block, scratch=scratch)
 
     def summary(self, c):
-        lib = L.lib()
         B, Lq, Hk, Hv, K, V = c["dims"]
-        dev = c["seg"].device
-        H = c["ex"].H
-        zero = torch.zeros(B, Hv, K, V, device=dev)
-        Q = torch.empty(B, Hv, K, V, device=dev)
-        states_ptr, c["res"].states = c["res"].states, None          # no chunk states from this pass
-        L.check(lib.dn_state_fwd(c["shape"], c["res"], c["seg"].data_ptr(), zero.data_ptr(), None, Q.data_ptr(),
-                                 _g._stream()), "dn_state_fwd (Q)")
-        eye = torch.eye(K, device=dev).expand(B, H, K, K).contiguous()
-        P = torch.empty(B, H, K, K, device=dev)
-        L.check(lib.dn_sp_transition(c["shape"], c["res"], c["seg"].data_ptr(), eye.data_ptr(), P.data_ptr(),
-                                     _g._stream()), "dn_sp_transition")
-        c["res"].states = states_ptr
+        q, v = c["ins"][0], c["ins"][2]
+        c["out"] = torch.empty(B, Lq, Hv, V, dtype=v.dtype, device=q.device)
+        Q = torch.empty(B, Hv, K, V, device=q.device)
+        P = torch.empty(B, c["ex"].H, K, K, device=q.device)
+        L.check(L.lib().dn_sp_summary(c["shape"], c["res"], c["seg"].data_ptr(), c["out"].data_ptr(), Q.data_ptr(),
+                                      P.data_ptr(), _g._stream()), "dn_sp_summary")
         return P, Q
 
     def apply(self, c, P, S_in, Q, transpose=False):
         B, Lq, Hk, Hv, K, V = c["dims"]
         H = c["ex"].H
+        S_in = S_in.contiguous()
         out = torch.empty_like(S_in)
-        L.check(L.lib().dn_sp_apply(P.data_ptr(), S_in.contiguous().data_ptr(), None if Q is None else Q.data_ptr(),
+        L.check(L.lib().dn_sp_apply(P.data_ptr(), S_in.data_ptr(), None if Q is None else Q.data_ptr(),
                                     out.data_ptr(), B, H, Hv // H, K, V, 1 if transpose else 0, _g._stream()),
                 "dn_sp_apply")
         return out
 
     def finish(self, c, S_in):
-        lib = L.lib()
-        B, Lq, Hk, Hv, K, V = c["dims"]
-        q = c["ins"][0]
-        out = torch.empty(B, Lq, Hv, V, dtype=c["ins"][2].dtype, device=q.device)
-        final = torch.empty(B, Hv, K, V, device=q.device)
         c["S_in"] = S_in.contiguous()
-        L.check(lib.dn_state_fwd(c["shape"], c["res"], c["seg"].data_ptr(), c["S_in"].data_ptr(), out.data_ptr(),
-                                 final.data_ptr(), _g._stream()), "dn_state_fwd")
-        return out, final
+        L.check(L.lib().dn_sp_correct_fwd(c["shape"], c["res"], c["seg"].data_ptr(), c["S_in"].data_ptr(),
+                                          c["out"].data_ptr(), _g._stream()), "dn_sp_correct_fwd")
+        out = c.pop("out")
+        if self.recompute:                                  # keep only what the backward cannot rebuild
+            for name in ("res", "block", "scratch"):
+                c.pop(name)
+        return out
 
     # -- backward
-    def _chain_bwd(self, c, d_out, d_final):
+    def bwd_summary(self, c, d_out):
         lib = L.lib()
         B, Lq, Hk, Hv, K, V = c["dims"]
+        if "res" not in c:                                  # recompute_states: prepass outputs and chunk states again
+            self._prepass(c)
+            L.check(lib.dn_recompute_states(c["shape"], c["res"], c["seg"].data_ptr(), c["S_in"].data_ptr(),
+                                            _g._stream()), "dn_recompute_states")
         ex, dev = c["ex"], d_out.device
         items = B * ex.H * ex.NC
-        dV = torch.empty(items * self.chunk * ex.Vw, device=dev)
-        dH = torch.empty(items * K * ex.Vw, device=dev)
-        d_init = torch.empty(B, Hv, K, V, device=dev)
-        L.check(lib.dn_state_bwd(c["shape"], c["res"], c["seg"].data_ptr(), d_out.data_ptr(),
-                                 None if d_final is None else d_final.contiguous().data_ptr(), dV.data_ptr(),
-                                 dH.data_ptr(), d_init.data_ptr(), _g._stream()), "dn_state_bwd")
-        return dV, dH, d_init
-
-    def bwd_summary(self, c, d_out):
         c["d_out"] = d_out.to(c["ins"][2].dtype).contiguous()
-        return self._chain_bwd(c, c["d_out"], None)[2]
+        c["dV"] = torch.empty(items * ex.chunk * ex.Vw, device=dev)
+        c["dH"] = torch.empty(items * K * ex.Vw, device=dev)
+        d_init0 = torch.empty(B, Hv, K, V, device=dev)
+        L.check(lib.dn_state_bwd(c["shape"], c["res"], c["seg"].data_ptr(), c["d_out"].data_ptr(), None,
+                                 c["dV"].data_ptr(), c["dH"].data_ptr(), d_init0.data_ptr(), _g._stream()), "dn_state_bwd")
+        return d_init0
 
     def bwd_finish(self, c, d_final):
         lib = L.lib()
         q, k, v, g, b, w = c["ins"]
-        dV, dH, d_init = self._chain_bwd(c, c["d_out"], d_final)
+        d_final = d_final.contiguous()
+        L.check(lib.dn_sp_correct_bwd(c["shape"], c["res"], c["seg"].data_ptr(), c["d_out"].data_ptr(),
+                                      d_final.data_ptr(), c["dV"].data_ptr(), c["dH"].data_ptr(), _g._stream()),
+                "dn_sp_correct_bwd")
         grads = [torch.empty_like(t) for t in (q, k, v, g, b, w)]
         sc = c["scratch"]
         L.check(lib.dn_prepass_bwd(c["shape"], q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), b.data_ptr(),
-                                   w.data_ptr(), c["seg"].data_ptr(), c["res"], c["d_out"].data_ptr(), dV.data_ptr(),
-                                   dH.data_ptr(), *[t.data_ptr() for t in grads], sc.data_ptr(), sc.numel(),
+                                   w.data_ptr(), c["seg"].data_ptr(), c["res"], c["d_out"].data_ptr(), c["dV"].data_ptr(),
+                                   c["dH"].data_ptr(), *[t.data_ptr() for t in grads], sc.data_ptr(), sc.numel(),
                                    _g._stream()), "dn_prepass_bwd")
         return grads
 
@@ -235,19 +275,20 @@ def sp_forward(ops, chain, tensors, seg_raw, initial_state):
     P, Q = ops.summary(c)
     edges = chain.gather_edges(shard_edges(seg_raw).to(q.device))
     r = chain.rank
-    cont_in = continues_from_previous(edges[r - 1], edges[r]) if r > 0 else torch.ones(B, dtype=torch.bool, device=q.device)
+    cont_in = continues_from_previous(edges[r - 1], edges[r]) if r > 0 else None
     cont_out = continues_from_previous(edges[r], edges[r + 1]) if r < chain.size - 1 else None
     first = initial_state if initial_state is not None else torch.zeros(B, Hv, K, V, device=q.device)
 
     def step(S_in):
-        S_out = ops.apply(c, P, S_in, Q)
-        if cont_out is not None:                      # what the next shard may keep of it
-            S_out = S_out * cont_out.view(B, 1, 1, 1).to(S_out.dtype)
-        return S_out
+        S_out = ops.apply(c, P, S_in, Q)                  # the state after this shard
+        if cont_out is None:
+            return S_out, None
+        # what the next shard may keep of it: nothing where it starts a new document
+        return S_out, S_out * cont_out.view(B, 1, 1, 1).to(S_out.dtype)
 
-    S_in, _ = chain.forward(first.float().contiguous(), step)
-    out, final = ops.finish(c, S_in)
-    c.update(P=P, cont_in=cont_in, cont_out=cont_out)
+    S_in, final = chain.forward(first.float().contiguous(), step)
+    out = ops.finish(c, S_in)
+    c.update(P=P, cont_in=cont_in)
     return out, final, c
 
 
@@ -259,7 +300,7 @@ def sp_backward(ops, chain, c, d_out, d_final_state):
 
     def step(d_final):
         d_in = ops.apply(c, c["P"], d_final, d_init0, transpose=True)      # P^T d_final + d_init0
-        if chain.rank > 0:                                                  # previous shard's state was dropped
+        if c["cont_in"] is not None:                                        # the previous shard's state was dropped
             d_in = d_in * c["cont_in"].view(B, 1, 1, 1).to(d_in.dtype)      # where this shard starts a document
         return d_in
 
@@ -272,6 +313,7 @@ class _SPFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, ops, chain, seg_raw, q, k, v, g, b, w, initial_state):
         out, final, c = sp_forward(ops, chain, (q, k, v, g, b, w), seg_raw, initial_state)
+        chain.drain()
         ctx.ops, ctx.chain, ctx.c = ops, chain, c
         ctx.has_init = initial_state is not None
         ctx.set_materialize_grads(False)
@@ -284,20 +326,24 @@ class _SPFunction(torch.autograd.Function):
             B, Lq, Hk, Hv, K, V = c["dims"]
             d_out = torch.zeros(B, Lq, Hv, V, device=c["seg"].device)
         (dq, dk, dv, dg, db, dw), d_in = sp_backward(ctx.ops, ctx.chain, c, d_out, d_final)
+        ctx.chain.drain()
         return None, None, None, dq, dk, dv, dg, db, dw, (d_in if ctx.has_init else None)
 
 
 def chunk_gdn2_sp(q, k, v, g, b, w, *, segment_ids: torch.Tensor, initial_state: Optional[torch.Tensor] = None,
                   group=None, chunk_size: int = 128, precision: str = "bf16", scale: Optional[float] = None,
-                  qk_l2norm: bool = False, fuse_prologue: bool = False, ops=None, chain=None):
+                  qk_l2norm: bool = False, fuse_prologue: bool = False, recompute_states: bool = False,
+                  ops=None, chain=None):
     """chunk_gdn2 on this rank's contiguous shard of a packed sequence split over the ranks of ``group``.
 
     ``segment_ids`` (B, L_shard) are the GLOBAL document ids of the shard's tokens (any change of id is
     a boundary, also across shards).  ``initial_state`` is used on the first rank only.  Returns
     ``(out, final_state)``; ``final_state`` is the state after this shard (the sequence's final state on
-    the last rank).  Differentiable: backward runs the reverse chain, so every rank must take part.
+    the last rank) and is differentiable on every rank.  ``recompute_states`` keeps no prepass output or
+    chunk state between forward and backward (``gdn2.py:1384-1386``).  Differentiable: backward runs the
+    reverse chain, so every rank must take part.
     """
     ops = ops or CudaOps(chunk_size=chunk_size, precision=precision, scale=scale, qk_l2norm=qk_l2norm,
-                         fuse_prologue=fuse_prologue)
+                         fuse_prologue=fuse_prologue, recompute_states=recompute_states)
     chain = chain or Chain(group)
     return _SPFunction.apply(ops, chain, segment_ids, q, k, v, g, b, w, initial_state)

@@ -20,8 +20,14 @@ def _check_scalar_beta(beta):
             f"channel-wise beta with shape {tuple(beta.shape)} is not supported.")
 
 
-def _forward(q, k, v, g, b, w, kw):
-    return chunk_gdn2(q, k, v, g, b, w, **kw)
+def _const_gate(like, value, dims, dtype=torch.float32):
+    """A gate that is one constant for all heads and channels: shape (B, L, 1) (or (B, 1) for decode).
+
+    The reference writes ``zeros_like(k)`` / ``ones_like(v)`` here (variants.py:206-207, 271) and
+    relies on its compiler to fold them; the kernels read a one-head scalar gate natively, so nothing
+    of the size of k or v is materialised.
+    """
+    return torch.full(tuple(like.shape[:dims]) + (1,), float(value), dtype=dtype if dtype in (torch.float32, torch.bfloat16) else torch.float32, device=like.device)
 
 
 def chunk_gdn(q, k, v, g, beta, *, segment_ids=None, cu_seqlens=None, initial_state=None,
@@ -56,8 +62,8 @@ def chunk_gla(q, k, v, g, *, segment_ids=None, cu_seqlens=None, initial_state=No
               output_final_state=False, chunk_size=128, precision="bf16", scale=None,
               qk_l2norm=False, fallback_scan=False, is_inference=False, recompute_states=False):
     """Gated Linear Attention: GDN-2 with erase gate 0 and write gate 1."""
-    b = torch.zeros_like(k)
-    w = torch.ones_like(v)
+    b = _const_gate(k, 0.0, 2, g.dtype)
+    w = _const_gate(v, 1.0, 2, g.dtype)
     return chunk_gdn2(q, k, v, g, b, w, segment_ids=segment_ids, cu_seqlens=cu_seqlens,
                       initial_state=initial_state, output_final_state=output_final_state,
                       chunk_size=chunk_size, precision=precision, scale=scale, qk_l2norm=qk_l2norm,
@@ -70,7 +76,7 @@ def chunk_delta_rule(q, k, v, beta, *, segment_ids=None, cu_seqlens=None, initia
                      qk_l2norm=False, fallback_scan=False, is_inference=False, recompute_states=False):
     """DeltaNet: no decay (g = 0) and b = w = beta."""
     _check_scalar_beta(beta)
-    g = torch.zeros_like(k)
+    g = _const_gate(k, 0.0, 2, beta.dtype)
     return chunk_gdn2(q, k, v, g, beta, beta, segment_ids=segment_ids, cu_seqlens=cu_seqlens,
                       initial_state=initial_state, output_final_state=output_final_state,
                       chunk_size=chunk_size, precision=precision, scale=scale, qk_l2norm=qk_l2norm,
@@ -110,12 +116,13 @@ def kda_decode_step(q, k, v, g, beta, state, *, reset=None, scale=None, qk_l2nor
 
 def gla_decode_step(q, k, v, g, state, *, reset=None, scale=None, qk_l2norm=False, state_dtype=None):
     """Single-token Gated Linear Attention step."""
-    return gdn2_decode_step(q, k, v, g, torch.zeros_like(k), torch.ones_like(v), state, reset=reset,
+    one_tok = k[:, 0] if k.dim() == 4 else k
+    return gdn2_decode_step(q, k, v, g, _const_gate(one_tok, 0.0, 1, g.dtype), _const_gate(one_tok, 1.0, 1, g.dtype), state, reset=reset,
                             scale=scale, qk_l2norm=qk_l2norm, state_dtype=state_dtype)
 
 
 def delta_rule_decode_step(q, k, v, beta, state, *, reset=None, scale=None, qk_l2norm=False, state_dtype=None):
     """Single-token DeltaNet step (no decay)."""
     beta = _validate_decode_beta(beta)
-    return gdn2_decode_step(q, k, v, torch.zeros_like(k), beta, beta, state, reset=reset, scale=scale,
+    return gdn2_decode_step(q, k, v, _const_gate(k[:, 0] if k.dim() == 4 else k, 0.0, 1, beta.dtype), beta, beta, state, reset=reset, scale=scale,
                             qk_l2norm=qk_l2norm, state_dtype=state_dtype)

@@ -51,10 +51,12 @@ enum {
   DN_QK_L2NORM      = 1u << 0, /* normalise q,k in the kernel prologue (gdn2.py:2113-2122 / 133-138) */
   DN_FUSE_PROLOGUE  = 1u << 1, /* g,b,w are pre-activations (gdn2.py:133-142, adjoints 558-575)   */
   DN_HAS_INIT       = 1u << 2, /* an initial state is given (gdn2.py:613-617)                      */
-  DN_STABILITY_GUARD= 1u << 3, /* with DN_FUSE_PROLOGUE: clamp the activated decay to <= -1e-6      */
+  DN_STABILITY_GUARD= 1u << 3, /* stability_guard: decay clamped to <= -1e-6 (activated, with DN_FUSE_PROLOGUE;
+                                  else the given g) and, without the fused prologue, b to >= 0 (gdn2.py:1972-1974) */
   DN_STATE_FP32_MM  = 1u << 4, /* state_fp32_matmul (gdn2.py:625)                                   */
   DN_INFERENCE      = 1u << 5, /* forward only: no T / chunk-state residuals (gdn2.py:1257,1322)    */
-  DN_TRUNC_DT_BF16  = 1u << 6  /* truncate_bwd_dT_bf16 (gdn2.py:327-330)                            */
+  DN_TRUNC_DT_BF16  = 1u << 6, /* truncate_bwd_dT_bf16 (gdn2.py:327-330)                            */
+  DN_RESET_PER_HEAD = 1u << 7  /* decode: reset is (B,Hv), one flag per sequence and value head      */
 };
 
 /* status codes */
@@ -66,12 +68,14 @@ enum {
   DN_ERR_SCRATCH_TOO_SMALL = 4,
   DN_ERR_CUDA_LAUNCH = 5,    /* cudaGetLastError() after a launch was not cudaSuccess  */
   DN_ERR_UNSUPPORTED = 6,
-  DN_ERR_STATIC_SCRATCH_EXCEEDED = 7  /* dn_prepass_fwd_static: the shape needs more scratch than the built-in array */
+  DN_ERR_STATIC_SCRATCH_EXCEEDED = 7, /* dn_prepass_fwd_static: the shape needs more scratch than the built-in array */
+  DN_ERR_DEVICE_WAIT = 8     /* an EARLIER kernel gave up a bounded wait: results since then are not to be
+                                trusted; nothing was enqueued by this call (see dn_device_error_reset)  */
 };
 
 typedef struct dn_shape {
   int32_t B, L, Hk, Hv, K, V;
-  int32_t chunk;               /* 64 or 128                                    */
+  int32_t chunk;               /* 64 or 128 (see dn_exec.chunk)                */
   int32_t g_heads, g_cols;     /* layout of g (see above)                      */
   int32_t b_heads, b_cols;
   int32_t w_heads, w_cols;
@@ -86,17 +90,23 @@ typedef struct dn_shape {
 typedef struct dn_exec {
   int32_t H, Vw, G, NC;        /* exec heads, value width, value heads per exec head, chunks */
   int32_t pre_dtype;           /* dtype of W,U,M,qe,ke: bf16 in bf16 precision else f32 (gdn2.py:1247) */
+  int32_t chunk;               /* rows per tile the kernels use, the C of every layout below.  Equal to
+                                  dn_shape.chunk except on the tensor-core path (bf16 precision, K = 128,
+                                  Vw in {128,256}): there tiles are 128 rows, the M of a tcgen05.mma, and a
+                                  request for 64 runs with pairs of requested chunks merged into one tile
+                                  (the chunked form regroups the token recurrence exactly; only the points
+                                  where the state is rounded to bf16 move).  NC = ceil(L / chunk).          */
 } dn_exec;
 int dn_exec_view(const dn_shape* s, dn_exec* out);
 
 /*
  * Residuals written by the forward and read by the backward: the reference's residual tuple
- * (gdn2.py:1384-1388).  All in exec-head layout; NC = ceil(L/chunk), C = chunk.
+ * (gdn2.py:1384-1388).  All in exec-head layout; C = dn_exec.chunk, NC = ceil(L / C).
  *
  * The five pre_dtype tiles are opaque to the caller: only the library's own entry points read
  * them.  Each (batch, head, chunk) tile holds rows x cols elements, row-major in general; for shapes
- * that take the tensor-core path (precision bf16, chunk = K = 128, Vw in {128,256}, DN_FORCE_SIMT
- * unset) a tile is stored as the tensor cores' operand image, [col / 8][row][8 elements], so that
+ * that take the tensor-core path (precision bf16 without DN_STATE_FP32_MM, K = 128, Vw in {128,256},
+ * DN_FORCE_SIMT unset) a tile is stored as the tensor cores' operand image, [col / 8][row][8 elements], so that
  * every kernel copies it into shared memory as it lies.  The sizes are the same in both layouts.
  * On that path T holds a bf16 image in the first half of its slot, and the chunk-entry states are
  * followed by a bf16 image copy of themselves (dn_residual_bytes accounts for it).  The dV / dH
@@ -125,6 +135,11 @@ size_t dn_scratch_bytes(const dn_shape* s, int for_backward, int recompute);
 /* (B,L) raw ids -> canonical ids; first_is_new (B) may be NULL (gdn2.py:2081-2094). */
 int dn_canonical_segments(const int32_t* raw, const int32_t* first_is_new, int32_t* out,
                           int32_t B, int32_t L, void* stream);
+
+/* The same ids from cumulative sequence lengths cu_seqlens (n_cu int32 values on the device, the
+ * first 0 and the last L, strictly increasing; applied to every batch row, gdn2.py:2037-2052). */
+int dn_cu_seqlens_segments(const int32_t* cu_seqlens, int32_t n_cu, const int32_t* first_is_new, int32_t* out,
+                           int32_t B, int32_t L, void* stream);
 
 /*
  * Forward of the chunked recurrence.  seg may be NULL (one document).  init_state
@@ -204,6 +219,29 @@ int dn_prepass_bwd(const dn_shape* s, const void* q, const void* k, const void* 
  */
 int dn_sp_transition(const dn_shape* s, const dn_residuals* res, const int32_t* seg,
                      const float* identity, float* P, void* stream);
+/*
+ * The cheaper schedule built on the same fact (what a shard computes after its first document boundary
+ * does not depend on the incoming state at all):
+ *
+ * dn_sp_summary: ONE launch that runs the state pass from a zero state over the whole shard -- writing
+ *   outputs (out may be NULL) and chunk-entry states (res->states may be NULL) as dn_state_fwd does, and
+ *   Q (B,Hv,K,V) -- while K extra columns per (batch, exec head) start from the identity with U = 0 and
+ *   end as P (B,H,K,K).  Everything it writes for chunks after the first boundary is final.
+ * dn_sp_correct_fwd: the forward chain again from the true incoming state S_in (B,Hv,K,V), stopping at
+ *   the first chunk whose results no longer depend on it; rewrites out and the chunk-entry states of the
+ *   chunks it walks.  The shard's final state is P S_in + Q (dn_sp_apply); this call does not produce it.
+ *   The shape must carry DN_HAS_INIT.
+ * dn_sp_correct_bwd: the mirror image for the reverse chain: after dn_state_bwd with a NULL
+ *   d_final_state (cotangent 0, which also gives d_init0), this walks back from the true d_final_state
+ *   and stops where dH no longer depends on it, rewriting dV and dH of the chunks it walks.  The shard's
+ *   d_init is P^T d_final_state + d_init0.
+ */
+int dn_sp_summary(const dn_shape* s, const dn_residuals* res, const int32_t* seg,
+                  void* out, float* Q, float* P, void* stream);
+int dn_sp_correct_fwd(const dn_shape* s, const dn_residuals* res, const int32_t* seg,
+                      const float* S_in, void* out, void* stream);
+int dn_sp_correct_bwd(const dn_shape* s, const dn_residuals* res, const int32_t* seg,
+                      const void* d_out, const float* d_final_state, float* dV, float* dH, void* stream);
 int dn_sp_apply(const float* P, const float* S_in, const float* Q, float* S_out, int32_t B, int32_t H,
                 int32_t G, int32_t K, int32_t V, int32_t transpose, void* stream);
 
@@ -238,13 +276,14 @@ typedef struct dn_decode_shape {
   int32_t g_heads, g_cols, b_heads, b_cols, w_heads, w_cols;
   int32_t qkv_dtype, gate_dtype;
   int32_t state_in_dtype, state_out_dtype;
-  uint32_t flags;              /* DN_QK_L2NORM, DN_STABILITY_GUARD */
+  uint32_t flags;              /* DN_QK_L2NORM, DN_STABILITY_GUARD, DN_RESET_PER_HEAD */
   float scale, stability_tau;
 } dn_decode_shape;
 
 /*
  * One token for B sequences.  state_in and state_out may be the same buffer when their
- * dtypes match (in-place update).  reset (B) uint8 may be NULL.  out is (B,Hv,V) in qkv_dtype.
+ * dtypes match (in-place update).  reset, (B) uint8 or (B,Hv) with DN_RESET_PER_HEAD, may be NULL
+ * (the reference broadcasts reset over (B,Hv,K,V), gdn2.py:2404-2410).  out is (B,Hv,V) in qkv_dtype.
  */
 int dn_decode_step(const dn_decode_shape* s,
                    const void* q, const void* k, const void* v,
@@ -263,16 +302,28 @@ int dn_selftest_umma(int32_t a_mn, int32_t b_mn, int32_t N, int32_t Kc, const vo
                      float* D, int32_t* err, void* stream);
 
 /*
- * Diagnostic (no reference counterpart): reads the library's device error word.  It is 0 unless a
- * bounded wait inside a tensor-core kernel gave up (the kernel then finished without the
- * affected products).  Synchronises with the device; meant for tests and debugging.
+ * The library's error word (no reference counterpart).  Every wait inside a kernel (on a tensor-core
+ * or copy barrier) is bounded; a kernel whose wait gives up finishes without the affected work and
+ * stores 1 into the word.  The word sits in pinned host memory the device writes directly, so the
+ * host sees it without synchronising: once it is set, every enqueueing entry point returns
+ * DN_ERR_DEVICE_WAIT instead of enqueueing (results produced since the failed wait are not to be
+ * trusted) until dn_device_error_reset() clears it.  dn_device_error() synchronises with the current
+ * device first and then returns the word (0 or 1): the check for "did everything I enqueued so far
+ * run to completion normally".
  */
 int dn_device_error(void);
+void dn_device_error_reset(void);
+
+/*
+ * stability_guard's cap of a recurrent state (gdn2.py:2180-2188, 2224-2238): each of the n_states
+ * consecutive fp32 (K,V) matrices is scaled in place by min(1, tau / sqrt(sum S^2 + 1e-6)).
+ */
+int dn_cap_state(float* state, int64_t n_states, int32_t K, int32_t V, float tau, void* stream);
 
 /*
  * Diagnostic (no reference counterpart): the number of kernels dn_chunk_fwd (backward = 0) or
  * dn_chunk_bwd (backward = 1; recompute = 1 adds the rebuilt prepass and states) enqueues for this
- * shape.  0 for an invalid shape.
+ * shape on the current device.  0 for an invalid shape.  A pure query: creates no stream or event.
  */
 int dn_launch_count(const dn_shape* s, int backward, int recompute);
 

@@ -40,9 +40,14 @@ def _run_sharded(n, ins, seg, init, do, dfs, **opts):
     return results
 
 
-@pytest.mark.parametrize("n,prec,C,K,V,tol", [(2, "fp32", 64, 64, 64, 2e-4), (4, "fp32", 64, 64, 64, 2e-4),
-                                                (2, "bf16", 128, 128, 128, 2e-2), (4, "bf16", 128, 128, 128, 2e-2)])
-def test_sharded_equals_unsharded(n, prec, C, K, V, tol):
+@pytest.mark.parametrize("n,prec,C,K,V,tol,recompute", [
+    (2, "fp32", 64, 64, 64, 2e-4, False), (4, "fp32", 64, 64, 64, 2e-4, True),
+    (2, "bf16", 128, 128, 128, 2e-2, False), (4, "bf16", 128, 128, 128, 2e-2, False),
+    (4, "bf16", 64, 128, 128, 2e-2, True)])                 # chunk 64 + recompute_states: the long-sequence configuration's settings
+def test_sharded_equals_unsharded(n, prec, C, K, V, tol, recompute):
+    """Shards with no boundary, with one, and with several, so that the correction passes stop at the
+    first / last boundary of a shard, run through a whole shard, and are skipped where a shard starts a
+    document."""
     import deltanet_b200 as dn
     B, L, Hk, Hv = 2, 1024, 2, 4
     q, k, v, g, b, w = O.make_inputs(91, B, L, Hk, Hv, K, V, qkv_scale=0.5)
@@ -55,7 +60,7 @@ def test_sharded_equals_unsharded(n, prec, C, K, V, tol):
     cu = lambda t: t.cuda()
     ins = [cu(t) for t in (q, k, v, g, b, w)]
     opts = dict(chunk_size=C, precision=prec, qk_l2norm=True)
-    res = _run_sharded(n, ins, cu(seg), cu(init), cu(do), cu(dfs), **opts)
+    res = _run_sharded(n, ins, cu(seg), cu(init), cu(do), cu(dfs), recompute_states=recompute, **opts)
 
     # the unsharded operator on the same device
     leaves = [t.clone().requires_grad_() for t in ins]
@@ -69,6 +74,11 @@ def test_sharded_equals_unsharded(n, prec, C, K, V, tol):
         got = torch.cat([r["grads"][i] for r in res], 1)
         assert O.rel_l2(got.cpu(), g1[i].cpu()) < tol, i
     assert O.rel_l2(res[0]["grads"][6].cpu(), g1[6].cpu()) < tol
+
+    # every rank's final_state is the state after its shard: rank 0's equals a call on the first shard alone
+    _, f_first = dn.chunk_gdn2(*(t[:, :L // n].contiguous() for t in ins), segment_ids=cu(seg)[:, :L // n].contiguous(),
+                               initial_state=cu(init), output_final_state=True, **opts)
+    assert O.rel_l2(res[0]["final"].cpu(), f_first.cpu()) < tol
 
     # and the CPU oracle on the unsplit sequence (fp32 only: the bf16 pair above shares its rounding)
     if prec == "fp32":

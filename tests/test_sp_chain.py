@@ -48,7 +48,7 @@ class OracleOps:
         c["S_in"] = S_in.detach().clone().requires_grad_()
         with torch.enable_grad():                      # called from inside an autograd.Function forward
             c["out"], c["final"] = self._run(c, c["S_in"])
-        return c["out"].detach(), c["final"].detach()
+        return c["out"].detach()                       # (the shard's final state is P S_in + Q, from apply)
 
     def bwd_summary(self, c, d_out):
         c["d_out"] = d_out
@@ -88,6 +88,8 @@ def _worker(rank, world, port, ret):
     loss = (out * do[:, lo:hi]).sum()
     if rank == world - 1:
         loss = loss + (final * dfs).sum()
+    if rank == 0:                                      # a loss on an intermediate rank's final_state
+        loss = loss + (final * dfs.flip(0) * 0.5).sum()
     grads = torch.autograd.grad(loss, shard + ([init_leaf] if rank == 0 else []))
     ret[rank] = dict(out=out.detach(), final=final.detach(), grads=[x.detach() for x in grads])
     dist.barrier()
@@ -107,7 +109,11 @@ def test_sp_chain_matches_unsplit_oracle(world):
     init_leaf = init.clone().requires_grad_()
     o_ref, f_ref = O.chunk_gdn2(*leaves, segment_ids=seg, initial_state=init_leaf, output_final_state=True,
                                 chunk_size=64, precision="fp32", qk_l2norm=True)
-    g_ref = torch.autograd.grad((o_ref * do).sum() + (f_ref * dfs).sum(), leaves + [init_leaf])
+    hi0 = ins[0].shape[1] // world                      # the state after the first rank's shard enters the loss too
+    _, f_mid = O.chunk_gdn2(*(t[:, :hi0] for t in leaves), segment_ids=seg[:, :hi0], initial_state=init_leaf,
+                            output_final_state=True, chunk_size=64, precision="fp32", qk_l2norm=True)
+    g_ref = torch.autograd.grad((o_ref * do).sum() + (f_ref * dfs).sum() + (f_mid * dfs.flip(0) * 0.5).sum(),
+                                leaves + [init_leaf])
     out = torch.cat([ret[r]["out"] for r in range(world)], 1)
     assert O.rel_l2(out, o_ref) < 1e-5
     assert O.rel_l2(ret[world - 1]["final"], f_ref) < 1e-5
