@@ -1,36 +1,39 @@
 #!/usr/bin/env python
 """Benchmark of the delta-rule hot path on B200.
 
-Workload (N=1): chunk_gdn2 training forward+backward at the headline shape
+Workload (per GPU): chunk_gdn2 training forward+backward at the headline shape
 B=1, L=2048, Hk=12, Hv=24, K=V=128, bf16 q/k/v, fp32 gates, precision='bf16',
-chunk 128, qk_l2norm, documents split at L/2, all six gradients -- plus the decode
-step on 256 sequences x 32 value heads x (128x128) bf16 state.  Inputs are seeded
-synthetic tensors with the reference benchmark's distributions.
+chunk 128, qk_l2norm, documents split at L/2, all six gradients.  Inputs are seeded
+synthetic tensors with the reference benchmark's distributions.  A "step" is one
+forward+backward; K steps are timed as one region between CUDA events, the region is
+repeated until about half a second has been measured and the median is reported.
 
 One JSON line is printed by rank 0:
-  value        tokens/s of fwd+bwd with inputs resident in HBM (all GPUs together),
+  value        tokens/s of fwd+bwd with inputs resident in HBM, summed over all GPUs
+               (every rank runs the workload on its own batch row: weak scaling),
   e2e          the same through the public Python operator with HOST buffers (pinned H2D of
                the inputs and D2H of out + all gradients of every timed step inside the timed
-               region; batches are double-buffered, so one step's copies overlap its neighbours'
-               compute; the unpipelined time per step is reported beside it),
-  roofline     the dominant kernel of the step against the measured peak,
-  decode       state-stream GB/s of the decode step with its own roofline,
+               region, double-buffered); `e2e.light_inputs` is the same work with the gates
+               uploaded as bf16 pre-activations (fuse_prologue), the lightest layout the operator takes,
+  roofline     the slowest kernel of the step against the measured peak, plus the whole step
+               against the user-visible bytes and FLOPs (`step_*` keys),
+  decode       state-stream GB/s of the decode step (value heads sharded over the GPUs),
+  sp           the long-sequence workload: KDA-style fwd+bwd on ONE packed sequence of 131072
+               tokens, chunk_size 64, recompute_states, split into contiguous shards over the
+               GPUs (strong scaling; the state chain crosses the ranks by NCCL point-to-point),
   cpu_baseline the CPU oracle (a port of the reference's chunked path) on the host cores.
 
-`--only sp` runs a different workload and prints its own line: KDA-style fwd+bwd on one packed
-sequence of 131072 tokens, split over the ranks (strong scaling; the state chain crosses the ranks
-by NCCL point-to-point).
-
-`--impl reference` times the CPU oracle instead (the reference itself needs an array
-library that is not installed on the box; the oracle restates its chunked algorithm).
-With N>1 GPUs every rank runs the same per-GPU workload on its own data (batch
-sharding: no collective on the data path), so scaling is weak.
+`--impl reference` times the CPU oracle on the same workload instead (the reference itself
+needs an array library that is not installed on the box; the oracle restates its chunked
+algorithm).  `--only chunk|decode|sp` run one leg (profiling aid).
 """
 from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
+import re
 import subprocess
 import sys
 import threading
@@ -44,7 +47,11 @@ for p in (ROOT, os.path.join(ROOT, "deltanet-tpu_b200")):
 import torch  # noqa: E402
 
 CFG = dict(B=1, L=2048, Hk=12, Hv=24, K=128, V=128, chunk=128)
-DEC = dict(B=256, Hk=16, Hv=32, K=128, V=128)
+DEC = dict(B=256, Hk=16, Hv=32, K=128, V=128, steps=1000)
+SPCFG = dict(L=131072, H=32, K=128, V=128, chunk=64)
+WORKLOAD = ("chunk_gdn2 fwd+bwd B=1 L=2048 Hk=12 Hv=24 K=V=128 chunk=128 precision=bf16 qk_l2norm, "
+            "bf16 q/k/v, fp32 channel-wise gates, documents split at L/2, all six gradients")
+METRIC = "chunk_gdn2 fwd+bwd tokens/s, all GPUs together (L=2048 Hk=12 Hv=24 K=V=128 bf16)"
 
 
 # ------------------------------------------------------------------------------------------ peaks
@@ -57,7 +64,7 @@ def measured_peaks():
     return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
 
 
-# ------------------------------------------------------------------------------------------ flops
+# ------------------------------------------------------------------------------------------ flops and bytes
 def alg_flops(c):
     """Algorithmic dense-matmul FLOPs per chunk-head of each kernel of this build.
 
@@ -79,37 +86,57 @@ def alg_flops(c):
 
 
 def alg_bytes(c):
-    """Algorithmic HBM bytes per (batch, exec head, chunk) item and kernel: every array the kernel must
-    read or write, once (bf16 q/k/v/out/dO and residual tiles, fp32 gates, T, states, dV, dH)."""
+    """HBM bytes per (batch, exec head, chunk) item and kernel: every array the kernel must read or
+    write, once (bf16 q/k/v/out/dO and residual tiles, fp32 gates, bf16 T / state / dV / dH images,
+    the fp32 chunk-entry state the reverse chain reads)."""
     C, K, Vw = c["chunk"], c["K"], (c["Hv"] // c["Hk"]) * c["V"]
     qk, gb, vv, ww = 2 * C * K * 2, 2 * C * K * 4, C * Vw * 2, C * Vw * 4
     tiles = 3 * C * K * 2 + C * C * 2 + C * Vw * 2              # W, qe, ke, M, U
-    pre_fwd = qk + gb + vv + ww + tiles + C * C * 4 + K * 4
-    st_fwd = tiles + C * Vw * 2 + K * Vw * 4                     # + out, chunk-entry state
-    chain_bwd = 3 * C * K * 2 + C * C * 2 + C * Vw * 2 + C * Vw * 4 + K * Vw * 4    # tiles, dO -> dV, dH
-    par_bwd = (C * K * 2 + C * Vw * 2 + K * Vw * 4 + C * C * 4 + C * Vw * 2 + C * Vw * 4 + K * Vw * 4
-               + qk + gb + vv + ww + qk + gb + vv + ww)          # W,U,S,T,dO,dV,dH, inputs, six gradients
+    pre_fwd = qk + gb + vv + ww + tiles + C * C * 2 + K * 4      # + T image, Lambda_end
+    st_fwd = tiles + C * Vw * 2 + K * Vw * (4 + 2)               # + out, chunk-entry state (fp32 + image)
+    chain_bwd = 3 * C * K * 2 + C * C * 2 + C * Vw * 2 + K * Vw * 4 + C * Vw * 2 + K * Vw * 2    # tiles, dO, S -> dV, dH images
+    par_bwd = (C * K * 2 + C * Vw * 2 + K * Vw * 2 + C * C * 2 + C * Vw * 2 + C * Vw * 2 + K * Vw * 2
+               + qk + gb + vv + ww + qk + gb + vv + ww)          # W,U,S,T,dO,dV,dH images, inputs, six gradients
     return dict(prepass_fwd=pre_fwd, state_fwd=st_fwd, state_bwd=chain_bwd, prepass_bwd=par_bwd)
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of a kernel's launches in one step of the headline workload
-# (both chunk ranges together), from the ncu capture summarised in profiles/chunk_step_kernels_headline.md
-NCU_DRAM_BYTES = {"prepass_bwd": 301.1e6, "prepass_fwd": 82.1e6, "state_fwd": 40.5e6, "state_bwd": 66.2e6}
+def step_alg(c):
+    """The whole step against what a user sees: every input read once in forward and once in backward
+    in its own shape and dtype, out written, dO read, six gradients written (intermediates that go
+    through HBM between the kernels are NOT counted, so they lower the fraction); dense-matmul FLOPs
+    of all four kernels."""
+    B, L, Hk, Hv, K, V = c["B"], c["L"], c["Hk"], c["Hv"], c["K"], c["V"]
+    ins = B * L * (2 * Hk * K * 2 + Hv * V * 2 + 2 * Hk * K * 4 + Hv * V * 4)
+    out = B * L * Hv * V * 2
+    items = B * Hk * math.ceil(L / c["chunk"])
+    return dict(bytes=3 * ins + 2 * out + 2 * B * L * 4, flops=sum(alg_flops(c).values()) * items)
+
+
+def ncu_traffic():
+    """dram__bytes_read.sum + dram__bytes_write.sum per kernel and step of the headline workload, taken
+    from the line `traffic_bytes_per_step: kernel=bytes ...` of the kept ncu summary; {} if absent."""
+    path = os.path.join(ROOT, "profiles", "chunk_step_kernels_headline.md")
+    try:
+        m = re.search(r"^traffic_bytes_per_step:(.*)$", open(path).read(), flags=re.M)
+        return {k_: float(v_) for k_, v_ in re.findall(r"(\w+)=([0-9.eE+]+)", m.group(1))} if m else {}
+    except OSError:
+        return {}
 
 
 # ------------------------------------------------------------------------------------------ inputs
-def make_training_inputs(seed, c, device=None, pin=False):
+def make_training_inputs(seed, c, device=None, pin=False, light=False):
+    """light: gates as bf16 PRE-activations for fuse_prologue (sigmoid / -exp are applied in the kernels)."""
     gen = torch.Generator().manual_seed(seed)
     B, L, Hk, Hv, K, V = c["B"], c["L"], c["Hk"], c["Hv"], c["K"], c["V"]
     rn = lambda *s: torch.randn(*s, generator=gen)
-    t = dict(
-        q=rn(B, L, Hk, K).to(torch.bfloat16), k=rn(B, L, Hk, K).to(torch.bfloat16),
-        v=rn(B, L, Hv, V).to(torch.bfloat16),
-        b=torch.sigmoid(rn(B, L, Hk, K) * 0.39), w=torch.sigmoid(rn(B, L, Hv, V) * 0.39),
-        g=-torch.exp(rn(B, L, Hk, K) * 0.39 - 1.0),
-        do=rn(B, L, Hv, V).to(torch.bfloat16),
-        seg=(torch.arange(L) >= L // 2).to(torch.int32)[None].expand(B, L).contiguous(),
-    )
+    t = dict(q=rn(B, L, Hk, K).to(torch.bfloat16), k=rn(B, L, Hk, K).to(torch.bfloat16), v=rn(B, L, Hv, V).to(torch.bfloat16))
+    nb, nw, ng = rn(B, L, Hk, K) * 0.39, rn(B, L, Hv, V) * 0.39, rn(B, L, Hk, K) * 0.39 - 1.0
+    if light:
+        t.update(b=nb.to(torch.bfloat16), w=nw.to(torch.bfloat16), g=ng.to(torch.bfloat16))
+    else:
+        t.update(b=torch.sigmoid(nb), w=torch.sigmoid(nw), g=-torch.exp(ng))
+    t.update(do=rn(B, L, Hv, V).to(torch.bfloat16),
+             seg=(torch.arange(L) >= L // 2).to(torch.int32)[None].expand(B, L).contiguous())
     if pin:
         t = {k_: v_.pin_memory() for k_, v_ in t.items()}
     if device is not None:
@@ -267,34 +294,56 @@ class ClockSampler:
                     reasons=sorted(reasons), samples=len(sm))
 
 
-def time_steps(fn, steps, warmup, dist=None):
-    """W warm-ups, then K steps between CUDA events on the current stream; max over ranks (ms)."""
+def time_steps(fn, steps, warmup, dist=None, min_seconds=0.0, max_repeats=64):
+    """W warm-ups, then regions of exactly K steps between CUDA events on the current stream, repeated
+    until min_seconds have been measured; returns (median region time in ms, max over ranks; repeats)."""
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
-    if dist is not None:
-        dist.barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda.synchronize()
-    e0.record()
-    for _ in range(steps):
-        fn()
-    e1.record()
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1)
-    if dist is not None:
-        t = torch.tensor([ms], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        dist.barrier()
-        ms = float(t.item())
-    return ms
+    times = []
+    while True:
+        if dist is not None:
+            dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        more = 1.0 if (sum(times) + ms) * 1e-3 < min_seconds and len(times) + 1 < max_repeats else 0.0
+        if dist is not None:
+            t = torch.tensor([ms, more], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dist.barrier()
+            ms, more = float(t[0].item()), float(t[1].item())
+        times.append(ms)
+        if not more:
+            break
+    times.sort()
+    return times[len(times) // 2], len(times)
+
+
+def bind_to_local_cores(local_rank, ranks_on_node):
+    """Pins this process to its share of the host's cores BEFORE it allocates and first-touches its pinned
+    buffers, so that they come from memory near those cores (a process setting only; no GPU or driver
+    setting is involved).  Returns the number of cores now allowed."""
+    try:
+        cores = sorted(os.sched_getaffinity(0))
+        if ranks_on_node > 1 and len(cores) >= ranks_on_node:
+            per = len(cores) // ranks_on_node
+            os.sched_setaffinity(0, cores[local_rank * per:(local_rank + 1) * per])
+        return len(os.sched_getaffinity(0))
+    except (AttributeError, OSError):
+        return os.cpu_count() or 1
 
 
 # ------------------------------------------------------------------------------------------ CPU oracle leg
-def cpu_oracle_step(c, heads_frac, seed=11):
-    """One fwd+bwd of the oracle's chunked path on a head-subset of the workload; returns seconds."""
+def cpu_oracle_step(c, heads_frac=1.0, seed=11):
+    """One fwd+bwd of the oracle's chunked path on the workload (or a head-subset of it); returns seconds."""
     from oracle import delta_oracle as O
-    Hk = max(1, int(c["Hk"] * heads_frac))
+    Hk = max(1, int(round(c["Hk"] * heads_frac)))
     Hv = Hk * (c["Hv"] // c["Hk"])
     cc = dict(c, Hk=Hk, Hv=Hv)
     t = make_training_inputs(seed, cc)
@@ -306,43 +355,39 @@ def cpu_oracle_step(c, heads_frac, seed=11):
 
 
 def run_reference(args):
+    """The CPU arm: the oracle port of the reference's chunked forward + backward on the SAME workload,
+    all 24 value heads per step, on all host threads."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
-    frac = 1.0 / 6.0                       # 2 key heads / 4 value heads of the 12 / 24
-    times, budget, t_start = [], 150.0, time.perf_counter()
-    for i in range(args.warmup + args.steps):
-        dt, f = cpu_oracle_step(CFG, frac)
-        if i >= args.warmup:
-            times.append(dt)
-        if time.perf_counter() - t_start > budget and times:
+    times, budget, t_start = [], 240.0, time.perf_counter()
+    cpu_oracle_step(CFG, 1.0 / 12.0)                           # first-call overheads
+    cpu_oracle_step(CFG)                                       # one full-size warm-up step is enough on a CPU
+    while len(times) < args.steps:
+        if times and time.perf_counter() - t_start > budget:
             break
-    sec = sum(times) / len(times)
-    tok = CFG["B"] * CFG["L"] * f / sec
+        times.append(cpu_oracle_step(CFG)[0])
+    sec = sorted(times)[len(times) // 2]
+    tok = CFG["B"] * CFG["L"] / sec
     sample = (f"oracle port of the reference's chunked path (gdn2.py:772-1173), torch CPU, {cores} threads; each step = "
-              f"fwd+bwd on {int(24 * f)} of 24 value heads at L=2048 (token count scaled by the head fraction); "
-              f"{len(times)} timed steps")
-    line = dict(metric="chunk_gdn2 fwd+bwd tokens/s/GPU (L=2048 Hk=12 Hv=24 K=V=128 bf16)", value=tok, unit="tokens/s",
+              f"fwd+bwd on the whole workload (24 of 24 value heads, L=2048); median of {len(times)} timed steps")
+    line = dict(metric=METRIC, value=tok, unit="tokens/s",
                 impl="reference", n_gpus=args.gpus, steps=len(times), warmup=args.warmup, ms_per_step=sec * 1e3,
                 higher_is_better=True, scaling="weak", vs_baseline=None, dtype="bf16", data="synthetic",
-                config=dict(workload="chunk_gdn2 fwd+bwd B=1 L=2048 Hk=12 Hv=24 K=V=128 chunk=128 bf16"),
+                config=dict(workload=WORKLOAD),
                 cpu_baseline=dict(value=tok, unit="tokens/s", cores=cores, kind="port", sample=sample),
                 e2e=dict(value=tok, unit="tokens/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0))
     print(json.dumps(line), flush=True)
 
 
-# ------------------------------------------------------------------------------------------ main arm
 # ------------------------------------------------------------------------------------------ long sequence
-SPCFG = dict(L=131072, H=32, K=128, V=128, chunk=128)
-
-
-def sp_leg(args, dn, dist, world, rank, dev):
+def sp_leg(dn, dist, world, rank, dev, steps=3):
     """KDA-style fwd+bwd on ONE packed sequence of 131072 tokens (channel-wise decay, per-head beta,
-    documents of 2048..32768 tokens), split into equal contiguous shards over the ranks: the state
-    chain crosses the ranks by NCCL point-to-point, everything else is local.  Total work is fixed, so
-    this is strong scaling.  chunk_size is 128, the only size the reference's operator accepts."""
+    documents of 2048..32768 tokens, chunk_size 64, recompute_states), split into equal contiguous
+    shards over the ranks: the state chain crosses the ranks by NCCL point-to-point, everything else is
+    local.  Total work is fixed, so this is strong scaling.  Returns the `sp` object (rank 0) or None."""
     from deltanet_b200 import sp
     c = SPCFG
     L, H, K, V = c["L"], c["H"], c["K"], c["V"]
@@ -353,137 +398,83 @@ def sp_leg(args, dn, dist, world, rank, dev):
         lens.append(min(n, L - tot))
         tot += lens[-1]
     seg = torch.repeat_interleave(torch.arange(len(lens), dtype=torch.int32), torch.tensor(lens))[None]
-    lo, hi = rank * L // world, (rank + 1) * L // world
-    n = hi - lo
-    g2 = torch.Generator(device=dev).manual_seed(4100 + rank)
-    rn = lambda *sh: torch.randn(*sh, generator=g2, device=dev)
-    q, k, v = (rn(1, n, H, K).bfloat16().requires_grad_(), rn(1, n, H, K).bfloat16().requires_grad_(),
-               rn(1, n, H, V).bfloat16().requires_grad_())
-    g = (-torch.exp(rn(1, n, H, K) * 0.39 - 1.0)).requires_grad_()
-    beta = torch.sigmoid(rn(1, n, H)).requires_grad_()
-    do = rn(1, n, H, V).bfloat16()
-    seg_d = seg[:, lo:hi].contiguous().to(dev)
 
-    def step():
-        if world == 1:
-            o = dn.chunk_kda(q, k, v, g, beta, segment_ids=seg_d, chunk_size=c["chunk"], qk_l2norm=True)
+    def make(lo, hi, seed):
+        g2 = torch.Generator(device=dev).manual_seed(seed)
+        rn = lambda *sh: torch.randn(*sh, generator=g2, device=dev)
+        n = hi - lo
+        return dict(q=rn(1, n, H, K).bfloat16().requires_grad_(), k=rn(1, n, H, K).bfloat16().requires_grad_(),
+                    v=rn(1, n, H, V).bfloat16().requires_grad_(), g=(-torch.exp(rn(1, n, H, K) * 0.39 - 1.0)).requires_grad_(),
+                    beta=torch.sigmoid(rn(1, n, H)).requires_grad_(), do=rn(1, n, H, V).bfloat16(),
+                    seg=seg[:, lo:hi].contiguous().to(dev))
+
+    def run(t, sharded):
+        if sharded:
+            o, _ = sp.chunk_gdn2_sp(t["q"], t["k"], t["v"], t["g"], t["beta"], t["beta"], segment_ids=t["seg"],
+                                    chunk_size=c["chunk"], precision="bf16", qk_l2norm=True, recompute_states=True)
         else:
-            o, _ = sp.chunk_gdn2_sp(q, k, v, g, beta, beta, segment_ids=seg_d, chunk_size=c["chunk"],
-                                    precision="bf16", qk_l2norm=True)
-        torch.autograd.grad(o, [q, k, v, g, beta], grad_outputs=do)
+            o = dn.chunk_kda(t["q"], t["k"], t["v"], t["g"], t["beta"], segment_ids=t["seg"], chunk_size=c["chunk"],
+                             qk_l2norm=True, recompute_states=True)
+        torch.autograd.grad(o, [t["q"], t["k"], t["v"], t["g"], t["beta"]], grad_outputs=t["do"])
 
-    steps = max(2, min(args.steps, 5))
-    ms = time_steps(step, steps, 3, dist) / steps
-    if rank == 0:
-        print(json.dumps(dict(only="sp", metric="kda fwd+bwd tokens/s, one sequence split over the GPUs",
-                              value=L / (ms * 1e-3), unit="tokens/s", n_gpus=world, steps=steps, warmup=3,
-                              ms_per_step=ms, scaling="strong", dtype="bf16", data="synthetic",
-                              config=dict(workload="chunk_kda fwd+bwd B=1 L=131072 H=32 K=V=128 chunk=128 bf16 "
-                                                   "qk_l2norm, documents of 2048..32768 tokens",
-                                          parallelism=f"sequence-sharded x{world}, state chain by NCCL send/recv"))),
-              flush=True)
+    lib = dn._lib.lib()
+    mine = make(rank * L // world, (rank + 1) * L // world, 4100 + rank)
+    n0 = lib.dn_launches_total()
+    ms, reps = time_steps(lambda: run(mine, world > 1), steps, 3, dist)
+    launches = (lib.dn_launches_total() - n0) // (reps * steps + 3)
+    ms /= steps
+    del mine
+    single_ms = None
+    if world > 1:                                               # the same sequence on ONE GPU of this box, for the ratio
+        if rank == 0:
+            torch.cuda.empty_cache()
+            whole = make(0, L, 4100)
+            single_ms = time_steps(lambda: run(whole, False), steps, 2)[0] / steps
+            del whole
+            torch.cuda.empty_cache()
+        dist.barrier()
+    if rank != 0:
+        return None
+    out = dict(workload="chunk_kda fwd+bwd B=1 L=131072 H=32 K=V=128 chunk_size=64 bf16 qk_l2norm recompute_states, "
+                        "documents of 2048..32768 tokens (seeded), one sequence",
+               parallelism=(f"sequence-sharded x{world}: per-shard affine summary, state chain by NCCL send/recv, "
+                            "partial correction pass") if world > 1 else "one GPU",
+               scaling="strong", ms_per_step=ms, tokens_per_s=L / (ms * 1e-3), steps=steps, warmup=3,
+               kernels_per_step_per_rank=int(launches))
+    if single_ms is not None:
+        out.update(single_gpu_ms_per_step=single_ms, speedup_vs_single_gpu=single_ms / ms,
+                   efficiency_vs_single_gpu=single_ms / ms / world)
+    return out
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--only", default="all", choices=["all", "chunk", "decode", "sp"],
-                    help="profiling aid: run only the chunked fwd+bwd device loop, or only the decode loop")
-    args = ap.parse_args()
-    args.warmup = max(args.warmup, 3)
-    if args.impl == "reference":
-        return run_reference(args)
-
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    dist = None
-    if world > 1:
-        import torch.distributed as dist_mod
-        dist_mod.init_process_group("nccl", device_id=dev)
-        dist = dist_mod
-    import deltanet_b200 as dn
-    peaks = measured_peaks()
+# ------------------------------------------------------------------------------------------ end to end
+def e2e_leg(dn, dev, dist, world, rank, steps, light):
+    """fwd+bwd through the public operator from pinned HOST buffers, every step's uploads and read-backs
+    inside the timed region: serial, and double-buffered over a copy-in stream, the compute stream and a
+    copy-out stream as a training loop prefetches."""
     tokens = CFG["B"] * CFG["L"]
-
-    if args.only == "sp":
-        sp_leg(args, dn, dist, world, rank, dev)
-        return
-    if args.only == "decode":
-        dj = DecodeJob(DEC, dev, seed=3000 + rank, heads=DEC["Hv"] // world)
-        ms_dec = time_steps(dj.step, args.steps, args.warmup, dist) / args.steps
-        if rank == 0:
-            print(json.dumps(dict(only="decode", us_per_step=ms_dec * 1e3,
-                                  state_gbs=world * dj.state_bytes / (ms_dec * 1e-3) / 1e9)), flush=True)
-        return
-    # ---- device-resident throughput through the C ABI
-    job = DeviceJob(CFG, dev, seed=1000 + rank)
-    with ClockSampler(local) as clk:
-        ms = time_steps(job.step, args.steps, args.warmup, dist)
-    clocks = clk.summary()
-    ms_step = ms / args.steps
-    value = world * tokens / (ms_step * 1e-3)
-
-    if args.only == "chunk":
-        if rank == 0:
-            print(json.dumps(dict(only="chunk", ms_per_step=ms_step, tokens_per_s=value)), flush=True)
-        return
-    # ---- per-kernel timing (each kernel alone, CUDA events on its stream) and the roofline of the slowest
-    fl = alg_flops(CFG)
-    items = CFG["B"] * job.ex.H * job.ex.NC
-    job.step()
-    per = {}
-    for name in ("prepass_fwd", "state_fwd", "state_bwd", "prepass_bwd"):
-        per[name] = time_steps(lambda: job.phase(name), 10, 3) / 10
-    dom = max(per, key=per.get)
-    by = alg_bytes(CFG)
-    t_hbm = by[dom] * items / (peaks["hbm_gbs"] * 1e9)          # seconds at the measured copy bandwidth
-    t_tc = fl[dom] * items / (peaks["bf16_tflops"] * 1e12)      # seconds at the measured dense bf16 rate
-    sec = per[dom] * 1e-3
-    if t_hbm >= t_tc:
-        ach = by[dom] * items / sec / 1e9
-        roofline = dict(kernel=dom, bound="hbm", achieved=ach, peak=peaks["hbm_gbs"], unit="GB/s", frac=ach / peaks["hbm_gbs"])
-    else:
-        ach = fl[dom] * items / sec / 1e12
-        roofline = dict(kernel=dom, bound="tensor", achieved=ach, peak=peaks["bf16_tflops"], unit="TFLOP/s",
-                        frac=ach / peaks["bf16_tflops"])
-    roofline.update(traffic=NCU_DRAM_BYTES.get(dom), peak_source=peaks["source"],
-                    tensor_frac=fl[dom] * items / sec / 1e12 / peaks["bf16_tflops"],
-                    hbm_frac=by[dom] * items / sec / 1e9 / peaks["hbm_gbs"],
-                    kernel_ms={k_: round(v_, 4) for k_, v_ in per.items()},
-                    alg_gflop={k_: round(v_ * items / 1e9, 3) for k_, v_ in fl.items()},
-                    alg_mbytes={k_: round(v_ * items / 1e6, 1) for k_, v_ in by.items()})
-
-    # ---- end to end through the public operator with host buffers
-    host = make_training_inputs(2000 + rank, CFG, pin=True)
+    host = make_training_inputs(2000 + rank, CFG, pin=True, light=light)
     names = "qkvgbw"
-    h2d = sum(host[n].numel() * host[n].element_size() for n in list(names) + ["do", "seg"])
-    out_host = {n: torch.empty_like(host[n]).pin_memory() for n in list(names) + ["v"]}
+    in_names = list(names) + ["do", "seg"]
+    h2d = sum(host[n].numel() * host[n].element_size() for n in in_names)
+    out_host = {n: torch.empty_like(host[n]).pin_memory() for n in names}
     o_host = torch.empty_like(host["v"]).pin_memory()
+    for t in list(out_host.values()) + [o_host]:
+        t.zero_()                                              # first touch from this process's cores
     d2h = sum(host[n].numel() * host[n].element_size() for n in names) + o_host.numel() * o_host.element_size()
+    kw = dict(chunk_size=CFG["chunk"], precision="bf16", qk_l2norm=True, fuse_prologue=light)
 
-    def e2e_step():
-        d = {n: host[n].to(dev, non_blocking=True) for n in list(names) + ["do", "seg"]}
+    def serial_step():
+        d = {n: host[n].to(dev, non_blocking=True) for n in in_names}
         ins = [d[n].requires_grad_() for n in names]
-        o = dn.chunk_gdn2(*ins, segment_ids=d["seg"], chunk_size=CFG["chunk"], precision="bf16", qk_l2norm=True)
+        o = dn.chunk_gdn2(*ins, segment_ids=d["seg"], **kw)
         grads = torch.autograd.grad(o, ins, grad_outputs=d["do"])
         o_host.copy_(o.detach(), non_blocking=True)
         for n, gr in zip(names, grads):
             out_host[n].copy_(gr, non_blocking=True)
 
-    e2e_steps = max(3, min(args.steps, 40))
-    ms_serial = time_steps(e2e_step, e2e_steps, 3, dist) / e2e_steps
+    ms_serial = time_steps(serial_step, steps, 3, dist)[0] / steps
 
-    # The same work as a training loop would run it: batch i+1 is uploaded on a copy stream while
-    # batch i computes and batch i-1's results are read back.  Every upload and read-back of the K
-    # timed steps lies inside the timed region (run() starts and ends with all three streams joined).
-    in_names = list(names) + ["do", "seg"]
     main = torch.cuda.current_stream()
     s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
     slots = [{n: torch.empty_like(host[n], device=dev) for n in in_names} for _ in range(2)]
@@ -508,7 +499,7 @@ def main():
             d = slots[i % 2]
             main.wait_event(loaded[i % 2])
             ins = [d[n].detach().requires_grad_() for n in names]
-            o = dn.chunk_gdn2(*ins, segment_ids=d["seg"], chunk_size=CFG["chunk"], precision="bf16", qk_l2norm=True)
+            o = dn.chunk_gdn2(*ins, segment_ids=d["seg"], **kw)
             grads = torch.autograd.grad(o, ins, grad_outputs=d["do"])
             freed[i % 2].record(main)
             s_out.wait_stream(main)
@@ -521,22 +512,128 @@ def main():
         main.wait_stream(s_in)
         main.wait_stream(s_out)
 
-    ms_e2e = time_steps(lambda: run_pipeline(e2e_steps), 1, 1, dist) / e2e_steps
-    e2e = dict(value=world * tokens / (ms_e2e * 1e-3), unit="tokens/s", ms_per_step=ms_e2e,
-               h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h,
-               schedule="double-buffered: upload of batch i+1 and read-back of batch i-1 overlap batch i",
-               unpipelined_ms_per_step=ms_serial)
+    ms = time_steps(lambda: run_pipeline(steps), 1, 1, dist, min_seconds=0.3, max_repeats=8)[0] / steps
+    return dict(value=world * tokens / (ms * 1e-3), unit="tokens/s", ms_per_step=ms, h2d_bytes_per_step=h2d,
+                d2h_bytes_per_step=d2h, unpipelined_ms_per_step=ms_serial,
+                host_gbs_per_rank=(h2d + d2h) / (ms * 1e-3) / 1e9)
+
+
+# ------------------------------------------------------------------------------------------ main arm
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--only", default="all", choices=["all", "chunk", "decode", "sp"],
+                    help="profiling aid: run only the chunked fwd+bwd device loop, only the decode loop, or only the long-sequence leg")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        return run_reference(args)
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    host_cores = bind_to_local_cores(local, int(os.environ.get("LOCAL_WORLD_SIZE", str(world))))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist_mod.init_process_group("nccl", device_id=dev)
+        dist = dist_mod
+    import deltanet_b200 as dn
+    lib = dn._lib.lib()
+    peaks = measured_peaks()
+    tokens = CFG["B"] * CFG["L"]
+
+    if args.only == "sp":
+        r = sp_leg(dn, dist, world, rank, dev, steps=max(2, min(args.steps, 5)))
+        if rank == 0:
+            print(json.dumps(dict(only="sp", n_gpus=world, **r)), flush=True)
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+    if args.only == "decode":
+        dj = DecodeJob(DEC, dev, seed=3000 + rank, heads=DEC["Hv"] // world)
+        ms_dec = time_steps(dj.step, args.steps, args.warmup, dist)[0] / args.steps
+        if rank == 0:
+            print(json.dumps(dict(only="decode", us_per_step=ms_dec * 1e3,
+                                  state_gbs=world * dj.state_bytes / (ms_dec * 1e-3) / 1e9)), flush=True)
+        return
+    # ---- device-resident throughput through the C ABI
+    job = DeviceJob(CFG, dev, seed=1000 + rank)
+    n0 = lib.dn_launches_total()
+    with ClockSampler(local) as clk:
+        ms, repeats = time_steps(job.step, args.steps, args.warmup, dist, min_seconds=0.5)
+    launches_per_region = (lib.dn_launches_total() - n0) * args.steps // (args.warmup + repeats * args.steps)
+    clocks = clk.summary()
+    ms_step = ms / args.steps
+    value = world * tokens / (ms_step * 1e-3)
+
+    if args.only == "chunk":
+        if rank == 0:
+            print(json.dumps(dict(only="chunk", ms_per_step=ms_step, tokens_per_s=value, repeats=repeats)), flush=True)
+        return
+    # ---- per-kernel timing (each kernel alone, CUDA events on its stream) and the roofline of the slowest
+    fl = alg_flops(CFG)
+    items = CFG["B"] * job.ex.H * job.ex.NC
+    job.step()
+    per = {}
+    for name in ("prepass_fwd", "state_fwd", "state_bwd", "prepass_bwd"):
+        per[name] = time_steps(lambda: job.phase(name), 20, 3, min_seconds=0.05)[0] / 20
+    dom = max(per, key=per.get)
+    by = alg_bytes(CFG)
+    t_hbm = by[dom] * items / (peaks["hbm_gbs"] * 1e9)          # seconds at the measured copy bandwidth
+    t_tc = fl[dom] * items / (peaks["bf16_tflops"] * 1e12)      # seconds at the measured dense bf16 rate
+    sec = per[dom] * 1e-3
+    if t_hbm >= t_tc:
+        ach = by[dom] * items / sec / 1e9
+        roofline = dict(kernel=dom, bound="hbm", achieved=ach, peak=peaks["hbm_gbs"], unit="GB/s", frac=ach / peaks["hbm_gbs"])
+    else:
+        ach = fl[dom] * items / sec / 1e12
+        roofline = dict(kernel=dom, bound="tensor", achieved=ach, peak=peaks["bf16_tflops"], unit="TFLOP/s",
+                        frac=ach / peaks["bf16_tflops"])
+    st = step_alg(CFG)
+    st_hbm, st_tc = st["bytes"] / (peaks["hbm_gbs"] * 1e9), st["flops"] / (peaks["bf16_tflops"] * 1e12)
+    traffic = ncu_traffic()
+    roofline.update(traffic=traffic.get(dom), peak_source=peaks["source"],
+                    tensor_frac=fl[dom] * items / sec / 1e12 / peaks["bf16_tflops"],
+                    hbm_frac=by[dom] * items / sec / 1e9 / peaks["hbm_gbs"],
+                    kernel_ms={k_: round(v_, 4) for k_, v_ in per.items()},
+                    alg_gflop={k_: round(v_ * items / 1e9, 3) for k_, v_ in fl.items()},
+                    alg_mbytes={k_: round(v_ * items / 1e6, 1) for k_, v_ in by.items()},
+                    step_alg_mbytes=round(st["bytes"] / 1e6, 1), step_alg_gflop=round(st["flops"] / 1e9, 2),
+                    step_bound="hbm" if st_hbm >= st_tc else "tensor",
+                    step_frac=max(st_hbm, st_tc) / (ms_step * 1e-3),
+                    step_traffic=sum(traffic.values()) or None)
+
+    # ---- end to end through the public operator with host buffers
+    e2e_steps = max(3, min(args.steps, 40))
+    e2e = e2e_leg(dn, dev, dist, world, rank, e2e_steps, light=False)
+    e2e.update(schedule="double-buffered: upload of batch i+1 and read-back of batch i-1 overlap batch i",
+               host_cores_per_rank=host_cores,
+               light_inputs=dict(layout="gates as bf16 pre-activations, fuse_prologue=True (sigmoid / -exp in the kernels)",
+                                 **e2e_leg(dn, dev, dist, world, rank, e2e_steps, light=True)))
 
     # ---- decode: value heads sharded over the ranks, no collective
     dj = DecodeJob(DEC, dev, seed=3000 + rank, heads=DEC["Hv"] // world)
-    dsteps = 200
-    ms_dec = time_steps(dj.step, dsteps, 20, dist) / dsteps
+    dsteps = DEC["steps"]
+    ms_dec = time_steps(dj.step, dsteps, 20, dist)[0] / dsteps
     st_gbs = world * dj.state_bytes / (ms_dec * 1e-3) / 1e9
     decode = dict(workload=f"gdn2 decode step, 256 sequences, Hk=16 Hv=32 K=V=128, bf16 state, {DEC['Hv'] // world} value heads per GPU",
                   us_per_step=ms_dec * 1e3, state_gbs=st_gbs,
                   total_gbs=world * (dj.state_bytes + dj.vec_bytes) / (ms_dec * 1e-3) / 1e9, steps=dsteps,
                   roofline=dict(bound="hbm", achieved=st_gbs / world, peak=peaks["hbm_gbs"], unit="GB/s",
                                 frac=st_gbs / world / peaks["hbm_gbs"], traffic=None, peak_source=peaks["source"]))
+    touched_mb = job.bytes / 1e6
+    del dj, job
+    torch.cuda.empty_cache()
+
+    # ---- the long-sequence workload, sharded over the ranks
+    spr = sp_leg(dn, dist, world, rank, dev)
 
     if rank != 0:
         if dist is not None:
@@ -547,20 +644,19 @@ def main():
         cores = os.cpu_count() or 1
         torch.set_num_threads(cores)
         cpu_oracle_step(CFG, 1.0 / 12.0)                       # warm-up on a small slice
-        sec, f = cpu_oracle_step(CFG, 0.5)
-        cpu = dict(value=tokens * f / sec, unit="tokens/s", cores=cores, kind="port",
-                   sample=f"CPU oracle (port of the reference's chunked fwd+bwd), one step on {int(24 * f)} of 24 value "
-                          f"heads at L=2048, {sec:.1f} s, token count scaled by the head fraction")
+        sec, _ = cpu_oracle_step(CFG)
+        cpu = dict(value=tokens / sec, unit="tokens/s", cores=cores, kind="port",
+                   sample=f"CPU oracle (port of the reference's chunked fwd+bwd, gdn2.py:772-1173), one step on the whole "
+                          f"workload (24 of 24 value heads, L=2048), {sec:.1f} s")
     line = dict(
-        metric="chunk_gdn2 fwd+bwd tokens/s/GPU (L=2048 Hk=12 Hv=24 K=V=128 bf16)", value=value, unit="tokens/s",
+        metric=METRIC, value=value, unit="tokens/s",
         n_gpus=world, steps=args.steps, warmup=args.warmup, ms_per_step=ms_step, higher_is_better=True,
         scaling="weak", vs_baseline=None, dtype="bf16", data="synthetic",
-        config=dict(workload="chunk_gdn2 fwd+bwd B=1 L=2048 Hk=12 Hv=24 K=V=128 chunk=128 precision=bf16 qk_l2norm "
-                             "docs split at L/2 (per GPU)", global_batch=world, parallelism=f"batch-sharded x{world}, no collective",
-                    l2=f"no flush: the step touches {job.bytes / 1e6:.0f} MB (inputs, residuals, scratch, grads) > 126 MB L2"),
-        roofline=roofline, e2e=e2e, decode=decode, cpu_baseline=cpu,
-        gpu_launches=(job.lib.dn_launch_count(job.shape, 0, 0) + job.lib.dn_launch_count(job.shape, 1, 0)) * args.steps,
-        clocks=clocks)
+        config=dict(workload=WORKLOAD, global_batch=world, parallelism=f"batch-sharded x{world}, no collective",
+                    timing=f"median of {repeats} regions of {args.steps} steps",
+                    l2=f"no flush: the step touches {touched_mb:.0f} MB (inputs, residuals, scratch, grads) > 126 MB L2"),
+        roofline=roofline, e2e=e2e, decode=decode, sp=spr, cpu_baseline=cpu,
+        gpu_launches=int(launches_per_region), clocks=clocks)
     print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()

@@ -68,6 +68,7 @@ int dn_version(void) { return 1; }
 
 int dn_device_error(void) { return read_device_error(); }
 void dn_device_error_reset(void) { reset_device_error(); }
+int64_t dn_launches_total(void) { return launches_total(); }
 
 const char* dn_status_string(int st) {
   switch (st) {

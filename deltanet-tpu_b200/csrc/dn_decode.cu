@@ -487,17 +487,17 @@ static int launch_decode_t(const DecodeArgs& a, cudaStream_t st) {
   const int grid = s.B * s.Hv * (s.V / DV);
   if (s.K == 128) decode_kernel<SI, SO, 128><<<grid, DEC_THREADS, 0, st>>>(a);
   else decode_kernel<SI, SO, 64><<<grid, DEC_THREADS, 0, st>>>(a);
-  if (cudaGetLastError() != cudaSuccess) return DN_ERR_CUDA_LAUNCH;
+  if (launch_status()) return DN_ERR_CUDA_LAUNCH;
   if (s.flags & DN_STABILITY_GUARD) {
     decode_cap_kernel<SO><<<s.B * s.Hv, 256, 0, st>>>(reinterpret_cast<SO*>(a.state_out), s.K * s.V, s.stability_tau);
-    if (cudaGetLastError() != cudaSuccess) return DN_ERR_CUDA_LAUNCH;
+    if (launch_status()) return DN_ERR_CUDA_LAUNCH;
   }
   return DN_OK;
 }
 
 int launch_cap_state(float* state, int64_t n_states, int KV, float tau, cudaStream_t st) {
   decode_cap_kernel<float><<<(unsigned)n_states, 256, 0, st>>>(state, KV, tau);
-  return cudaGetLastError() == cudaSuccess ? DN_OK : DN_ERR_CUDA_LAUNCH;
+  return launch_status();
 }
 
 int launch_decode(const dn_decode_shape& s, const void* q, const void* k, const void* v,
@@ -517,11 +517,11 @@ int launch_decode(const dn_decode_shape& s, const void* q, const void* k, const 
     };
     if (sb16) { if (sc) go(bulk::decode_bulk_kernel<2, true>); else go(bulk::decode_bulk_kernel<2, false>); }
     else      { if (sc) go(bulk::decode_bulk_kernel<4, true>); else go(bulk::decode_bulk_kernel<4, false>); }
-    if (cudaGetLastError() != cudaSuccess) return DN_ERR_CUDA_LAUNCH;
+    if (launch_status()) return DN_ERR_CUDA_LAUNCH;
     if (s.flags & DN_STABILITY_GUARD) {
       if (sb16) decode_cap_kernel<__nv_bfloat16><<<s.B * s.Hv, 256, 0, st>>>(reinterpret_cast<__nv_bfloat16*>(a.state_out), s.K * s.V, s.stability_tau);
       else decode_cap_kernel<float><<<s.B * s.Hv, 256, 0, st>>>(reinterpret_cast<float*>(a.state_out), s.K * s.V, s.stability_tau);
-      if (cudaGetLastError() != cudaSuccess) return DN_ERR_CUDA_LAUNCH;
+      if (launch_status()) return DN_ERR_CUDA_LAUNCH;
     }
     return DN_OK;
   }

@@ -65,6 +65,11 @@ struct PrepassBwdArgs {
   bool bulk_v;                     // v, w, dv, dw move by bulk copies (set by the launcher)
 };
 
+// Called right after every kernel launch of the library: DN_OK or DN_ERR_CUDA_LAUNCH from
+// cudaGetLastError(), and one more in the library's count of kernels it has launched.
+int launch_status();
+long long launches_total();
+
 size_t prepass_fwd_scratch_per_cta(const Geo& g);
 size_t prepass_bwd_scratch_per_cta(const Geo& g);
 

@@ -18,6 +18,14 @@ int sm_count() {
   return n;
 }
 
+namespace { long long g_launches = 0; }
+int launch_status() {
+  if (cudaGetLastError() != cudaSuccess) return DN_ERR_CUDA_LAUNCH;
+  __atomic_fetch_add(&g_launches, 1, __ATOMIC_RELAXED);
+  return DN_OK;
+}
+long long launches_total() { return __atomic_load_n(&g_launches, __ATOMIC_RELAXED); }
+
 // ---- the error word ------------------------------------------------------------------------------
 // Kernels whose bounded waits give up store 1 into one int.  The int lives in a page of this
 // library's own static host memory that is pinned and mapped into the device address space on first
@@ -94,7 +102,7 @@ __global__ void __launch_bounds__(256) canonical_segments_kernel(const int32_t* 
 int launch_canonical_segments(const int32_t* raw, const int32_t* first_is_new, int32_t* out,
                               int B, int L, cudaStream_t st) {
   canonical_segments_kernel<<<B, 256, 0, st>>>(raw, first_is_new, out, L);
-  return cudaGetLastError() == cudaSuccess ? DN_OK : DN_ERR_CUDA_LAUNCH;
+  return launch_status();
 }
 
 // Canonical ids straight from cumulative sequence lengths: token t belongs to document d with
@@ -119,7 +127,7 @@ int launch_cu_seqlens_segments(const int32_t* cu, int n_cu, const int32_t* first
   size_t blocks = ((size_t)B * L + 255) / 256;
   if (blocks > (size_t)sm_count() * 8) blocks = (size_t)sm_count() * 8;
   cu_seqlens_segments_kernel<<<(unsigned)blocks, 256, 0, st>>>(cu, n_cu, first_is_new, out, B, L);
-  return cudaGetLastError() == cudaSuccess ? DN_OK : DN_ERR_CUDA_LAUNCH;
+  return launch_status();
 }
 
 // out[row][ho][c] = sum over gi of in[row][ho*groups + gi][c], added in a fixed order.
@@ -143,7 +151,7 @@ int launch_group_sum(const float* in, void* out, int out_dt, size_t rows, int he
   size_t blocks = (total + 255) / 256;
   if (blocks > (size_t)sm_count() * 16) blocks = (size_t)sm_count() * 16;
   group_sum_kernel<<<(unsigned)blocks, 256, 0, st>>>(in, out, out_dt, total, heads_out, groups, cols);
-  return cudaGetLastError() == cudaSuccess ? DN_OK : DN_ERR_CUDA_LAUNCH;
+  return launch_status();
 }
 
 // One CTA per (batch, value head): S_out = op(P) S_in + Q with the CTA-wide fp32 GEMM.
@@ -167,7 +175,7 @@ __global__ void __launch_bounds__(DN_THREADS) sp_apply_kernel(const float* P, co
 int launch_sp_apply(const float* P, const float* S_in, const float* Q, float* S_out, int B, int H, int G,
                     int K, int V, int transpose, cudaStream_t st) {
   sp_apply_kernel<<<B * H * G, DN_THREADS, 0, st>>>(P, S_in, Q, S_out, H, G, K, V, transpose);
-  return cudaGetLastError() == cudaSuccess ? DN_OK : DN_ERR_CUDA_LAUNCH;
+  return launch_status();
 }
 
 }  // namespace dn

@@ -359,7 +359,7 @@ int launch_prepass_bwd(PrepassBwdArgs& a, size_t scratch_floats, cudaStream_t st
   if (scratch_floats < (size_t)grid * a.scratch_per_cta) return DN_ERR_SCRATCH_TOO_SMALL;
   const size_t smem = (GEMM_SMEM_FLOATS + (size_t)4 * g.C + g.K) * sizeof(float);
   prepass_bwd_kernel<<<grid, DN_THREADS, smem, st>>>(a);
-  return cudaGetLastError() == cudaSuccess ? DN_OK : DN_ERR_CUDA_LAUNCH;
+  return launch_status();
 }
 
 }  // namespace dn

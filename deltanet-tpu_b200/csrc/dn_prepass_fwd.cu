@@ -296,7 +296,7 @@ int launch_prepass_fwd(const Geo& g, const void* q, const void* k, const void* v
   size_t smem = ((size_t)a.smem_tile_off + GEMM_SMEM_FLOATS + g.C) * sizeof(float);
   cudaFuncSetAttribute(prepass_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   prepass_fwd_kernel<<<grid, DN_THREADS, smem, st>>>(a);
-  return cudaGetLastError() == cudaSuccess ? DN_OK : DN_ERR_CUDA_LAUNCH;
+  return launch_status();
 }
 
 }  // namespace dn

@@ -538,7 +538,7 @@ int launch_prepass_fwd_tc(const Geo& g, const void* q, const void* k, const void
   } else {
     if (mode == 0) go(prepass_fwd_tc_kernel<128, 0>); else if (mode == 1) go(prepass_fwd_tc_kernel<128, 1>); else if (mode == 3) go(prepass_fwd_tc_kernel<128, 3>); else go(prepass_fwd_tc_kernel<128, 2>);
   }
-  return cudaGetLastError() == cudaSuccess ? DN_OK : DN_ERR_CUDA_LAUNCH;
+  return launch_status();
 }
 
 }  // namespace dn

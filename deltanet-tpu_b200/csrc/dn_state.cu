@@ -199,7 +199,7 @@ int launch_state_fwd(const StateArgs& a, cudaStream_t st) {
     cudaFuncSetAttribute(state_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     state_fwd_kernel<false><<<grid, DN_THREADS, smem, st>>>(a);
   }
-  return cudaGetLastError() == cudaSuccess ? DN_OK : DN_ERR_CUDA_LAUNCH;
+  return launch_status();
 }
 
 int launch_state_bwd(const StateArgs& a, cudaStream_t st) {
@@ -209,7 +209,7 @@ int launch_state_bwd(const StateArgs& a, cudaStream_t st) {
   size_t smem = state_smem(g, true);
   cudaFuncSetAttribute(state_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   state_bwd_kernel<<<grid, DN_THREADS, smem, st>>>(a);
-  return cudaGetLastError() == cudaSuccess ? DN_OK : DN_ERR_CUDA_LAUNCH;
+  return launch_status();
 }
 
 }  // namespace dn

@@ -505,7 +505,7 @@ int launch_fwd_vs(const StateArgs& a, cudaStream_t st) {
     cudaFuncSetAttribute(state_fwd_tc_kernel<VS, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     state_fwd_tc_kernel<VS, false><<<grid, 128, smem, st>>>(a);
   }
-  return cudaGetLastError() == cudaSuccess ? DN_OK : DN_ERR_CUDA_LAUNCH;
+  return launch_status();
 }
 
 template <int VS>
@@ -514,7 +514,7 @@ int launch_bwd_vs(const StateArgs& a, cudaStream_t st) {
   const size_t smem = tc_smem<VS>(true);
   cudaFuncSetAttribute(state_bwd_tc_kernel<VS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   state_bwd_tc_kernel<VS><<<grid, 128, smem, st>>>(a);
-  return cudaGetLastError() == cudaSuccess ? DN_OK : DN_ERR_CUDA_LAUNCH;
+  return launch_status();
 }
 
 }  // namespace

@@ -45,7 +45,7 @@ static int launch_selftest(int a_mn, int b_mn, int Kc, const void* A, const void
   else if (!a_mn && b_mn) go(umma_selftest_kernel<N, false, true>);
   else if (a_mn && !b_mn) go(umma_selftest_kernel<N, true, false>);
   else go(umma_selftest_kernel<N, true, true>);
-  return cudaGetLastError() == cudaSuccess ? DN_OK : DN_ERR_CUDA_LAUNCH;
+  return launch_status();
 }
 
 }  // namespace dn

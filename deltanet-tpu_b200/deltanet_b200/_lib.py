@@ -74,6 +74,7 @@ _SIGNATURES = {
     "dn_static_scratch_bytes": (C.c_size_t, []),
     "dn_prepass_fwd_static": (C.c_int, [C.POINTER(Shape)] + [_P] * 7 + [C.POINTER(Residuals), _P]),
     "dn_selftest_umma": (C.c_int, [C.c_int32] * 4 + [_P] * 5),
+    "dn_launches_total": (C.c_int64, []),
     "dn_launch_count": (C.c_int, [C.POINTER(Shape), C.c_int, C.c_int]),
 }
 EXPORTED = tuple(_SIGNATURES)

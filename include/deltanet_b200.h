@@ -326,6 +326,9 @@ int dn_cap_state(float* state, int64_t n_states, int32_t K, int32_t V, float tau
  * shape on the current device.  0 for an invalid shape.  A pure query: creates no stream or event.
  */
 int dn_launch_count(const dn_shape* s, int backward, int recompute);
+/* Diagnostic (no reference counterpart): kernels this library has launched in this process so far
+ * (every successful launch of one of its own kernels counts one), for callers that report launch counts. */
+int64_t dn_launches_total(void);
 
 const char* dn_status_string(int status);
 int dn_version(void);

@@ -426,7 +426,7 @@ def test_adversarial_alternating_keys(dn, prec, chunk):
     o = dn.chunk_gdn2(*gpu, chunk_size=chunk, precision=prec, **okw)
     gr = torch.autograd.grad((o * do.cuda()).sum(), gpu)
     assert bool(torch.isfinite(o).all()) and all(bool(torch.isfinite(x).all()) for x in gr)
-    tol = 1e-4 if prec == "fp32" else BF16_TOL
+    tol = 1e-4 if prec == "fp32" else 0.05          # (bf16 is not in the reference's version of this case; its bf16 bars for this suite are 0.05-0.10)
     assert O.rel_l2(o.cpu(), o_ref.detach()) < tol
     for i, (a, r) in enumerate(zip(gr, g_ref)):
         if float(r.norm()) > 1e-6:
@@ -458,7 +458,7 @@ def test_error_word_reset_and_status(dn):
     assert lib.dn_device_error() == 0
     assert lib.dn_status_string(8).startswith(b"an earlier kernel gave up")
     ins = [x.cuda() for x in O.make_inputs(3300, 1, 128, 1, 1, 128, 128, qkv_dtype=torch.bfloat16)]
-    o = dn.chunk_gdn2(*ins, precision="bf16")
+    o = dn.chunk_gdn2(*ins, precision="bf16", qk_l2norm=True)
     assert bool(torch.isfinite(o.float()).all())
 
 
