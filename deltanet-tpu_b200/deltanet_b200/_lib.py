@@ -71,6 +71,14 @@ _SIGNATURES = {
     "dn_sp_correct_fwd": (C.c_int, [C.POINTER(Shape), C.POINTER(Residuals)] + [_P] * 4),
     "dn_sp_correct_bwd": (C.c_int, [C.POINTER(Shape), C.POINTER(Residuals)] + [_P] * 6),
     "dn_sp_apply": (C.c_int, [_P] * 4 + [C.c_int32] * 6 + [_P]),
+    "dn_gdn_producer_scratch_bytes": (C.c_size_t, [C.c_int32] * 4),
+    "dn_gdn_producer_fwd": (C.c_int, [_P] * 4 + [C.c_int32] * 8 + [_P] * 4),
+    "dn_gdn_producer_bwd": (C.c_int, [_P] * 4 + [C.c_int32] * 8 + [_P] * 7 + [C.c_size_t, _P]),
+    "dn_gdn_gates_fwd": (C.c_int, [_P] * 4 + [C.c_int32] * 4 + [_P] * 3),
+    "dn_gdn_gates_bwd": (C.c_int, [_P] * 6 + [C.c_int32] * 4 + [_P] * 5),
+    "dn_gated_rmsnorm_scratch_bytes": (C.c_size_t, [C.c_int64, C.c_int32]),
+    "dn_gated_rmsnorm_fwd": (C.c_int, [_P] * 3 + [C.c_int64, C.c_int32, C.c_int32, C.c_float, _P, _P]),
+    "dn_gated_rmsnorm_bwd": (C.c_int, [_P] * 3 + [C.c_int64, C.c_int32, C.c_int32, C.c_float] + [_P] * 5 + [C.c_size_t, _P]),
     "dn_static_scratch_bytes": (C.c_size_t, []),
     "dn_prepass_fwd_static": (C.c_int, [C.POINTER(Shape)] + [_P] * 7 + [C.POINTER(Residuals), _P]),
     "dn_selftest_umma": (C.c_int, [C.c_int32] * 4 + [_P] * 5),

@@ -270,6 +270,43 @@ int dn_prepass_fwd_static(const dn_shape* s, const void* q, const void* k, const
                           const void* g, const void* b, const void* w, const int32_t* seg,
                           const dn_residuals* res, void* stream);
 
+/* ---- the steps either side of the recurrence in a Gated DeltaNet layer -------------------------------
+ * The reference shows them in its layer example (examples/qwen3_5_layer_parity.py:144-159): the projected
+ * activations go through a short depthwise causal convolution and SiLU and are split into q, k, v; the
+ * gate pre-activations become g = -exp(A_log) * softplus(a + dt_bias) and beta = sigmoid(b); the
+ * recurrence's output is normalised per value head and gated, y = weight * rmsnorm(o) * silu(z).  All are
+ * bound by HBM bytes: each kernel reads its inputs once and writes its outputs once.
+ *
+ * producer: mixed (B,L,D), D = 2*Hk*K + Hv*V, channel order q | k | v; conv_w (D,W) fp32 with tap W-1 on the
+ *   current token, W in {2,3,4}; conv_b (D) fp32 or NULL; seg (B,L) canonical ids (>= 0) or NULL -- taps that
+ *   would reach into another document (or before token 0) read zero.  q,k (B,L,Hk,K), v (B,L,Hv,V), in `dtype`.
+ *   backward: dq,dk,dv -> d_mixed (B,L,D), d_conv_w (D,W), d_conv_b (D, may be NULL); scratch of
+ *   dn_gdn_producer_scratch_bytes holds per-tile partial sums (added in a fixed order).
+ * gates: a, b (B,L,Hv) in `dtype`; A_log, dt_bias (Hv) fp32; g, beta (B,L,Hv) fp32 -- the per-head scalar
+ *   gates chunk_gdn takes.  backward: dg, dbeta fp32 -> da, db in `dtype`, dA_log, d_dt_bias (Hv) fp32.
+ * gated rmsnorm: o, z, y (rows, V) in `dtype`, rows = B*L*Hv, V in {64,128}; weight (V) fp32; the normalised
+ *   value is rounded to `dtype` before the weight is applied.  backward: dy -> d_o, d_z, d_weight (V) fp32.
+ */
+size_t dn_gdn_producer_scratch_bytes(int32_t B, int32_t L, int32_t D, int32_t W);
+int dn_gdn_producer_fwd(const void* mixed, const float* conv_w, const float* conv_b, const int32_t* seg,
+                        int32_t B, int32_t L, int32_t Hk, int32_t Hv, int32_t K, int32_t V, int32_t W, int32_t dtype,
+                        void* q, void* k, void* v, void* stream);
+int dn_gdn_producer_bwd(const void* mixed, const float* conv_w, const float* conv_b, const int32_t* seg,
+                        int32_t B, int32_t L, int32_t Hk, int32_t Hv, int32_t K, int32_t V, int32_t W, int32_t dtype,
+                        const void* dq, const void* dk, const void* dv, void* d_mixed, float* d_conv_w, float* d_conv_b,
+                        void* scratch, size_t scratch_bytes, void* stream);
+int dn_gdn_gates_fwd(const void* a, const void* b, const float* A_log, const float* dt_bias, int32_t B, int32_t L,
+                     int32_t Hv, int32_t dtype, float* g, float* beta, void* stream);
+int dn_gdn_gates_bwd(const void* a, const void* b, const float* A_log, const float* dt_bias, const float* dg,
+                     const float* dbeta, int32_t B, int32_t L, int32_t Hv, int32_t dtype, void* da, void* db,
+                     float* dA_log, float* d_dt_bias, void* stream);
+size_t dn_gated_rmsnorm_scratch_bytes(int64_t rows, int32_t V);
+int dn_gated_rmsnorm_fwd(const void* o, const void* z, const float* weight, int64_t rows, int32_t V, int32_t dtype,
+                         float eps, void* y, void* stream);
+int dn_gated_rmsnorm_bwd(const void* o, const void* z, const float* weight, int64_t rows, int32_t V, int32_t dtype,
+                         float eps, const void* dy, void* d_o, void* d_z, float* d_weight, void* scratch,
+                         size_t scratch_bytes, void* stream);
+
 /* ---- decode ------------------------------------------------------------------------------ */
 typedef struct dn_decode_shape {
   int32_t B, Hk, Hv, K, V;

@@ -466,10 +466,15 @@ def test_error_word_reset_and_status(dn):
 def test_second_device_in_one_process(dn):
     """Per-device launch attributes: an fp32 call on cuda:1 after one on cuda:0 in the same process."""
     q, k, v, g, b, w = O.make_inputs(3400, 1, 256, 2, 4, 128, 128, qkv_scale=0.5)
-    ref = O.chunk_gdn2(q, k, v, g, b, w, chunk_size=128, precision="fp32")
+    ref = O.chunk_gdn2(q, k, v, g, b, w, chunk_size=128, precision="fp32", qk_l2norm=True)
+    qb, kb, vb = q.bfloat16(), k.bfloat16(), v.bfloat16()
+    ref_b = O.chunk_gdn2(qb, kb, vb, g, b, w, chunk_size=128, precision="bf16", qk_l2norm=True)
+    outs = []
     for d in (0, 1):
         with torch.cuda.device(d):
-            o = dn.chunk_gdn2(*(t.to(f"cuda:{d}") for t in (q, k, v, g, b, w)), chunk_size=128, precision="fp32")
+            o = dn.chunk_gdn2(*(t.to(f"cuda:{d}") for t in (q, k, v, g, b, w)), chunk_size=128, precision="fp32", qk_l2norm=True)
             assert O.rel_l2(o.cpu(), ref) < FP32_TOL
-            ob = dn.chunk_gdn2(*(t.to(f"cuda:{d}") for t in (q.bfloat16(), k.bfloat16(), v.bfloat16(), g, b, w)), chunk_size=128)
-            assert O.rel_l2(ob.float().cpu(), ref) < 3e-2
+            ob = dn.chunk_gdn2(*(t.to(f"cuda:{d}") for t in (qb, kb, vb, g, b, w)), chunk_size=128, qk_l2norm=True)
+            assert O.rel_l2(ob.float().cpu(), ref_b.float()) < BF16_TOL
+            outs.append(ob.cpu())
+    assert torch.equal(outs[0], outs[1])
