@@ -18,6 +18,7 @@ One JSON line is printed by rank 0:
   roofline     the slowest kernel of the step against the measured peak, plus the whole step
                against the user-visible bytes and FLOPs (`step_*` keys),
   decode       state-stream GB/s of the decode step (value heads sharded over the GPUs),
+  layer_steps  the steps either side of the recurrence in a layer (conv+SiLU+split, gated RMSNorm), GB/s each,
   sp           the long-sequence workload: KDA-style fwd+bwd on ONE packed sequence of 131072
                tokens, chunk_size 64, recompute_states, split into contiguous shards over the
                GPUs (strong scaling; the state chain crosses the ranks by NCCL point-to-point),
@@ -447,6 +448,51 @@ def sp_leg(dn, dist, world, rank, dev, steps=3):
     return out
 
 
+# ------------------------------------------------------------------------------------------ layer steps
+def layer_steps_leg(dn, dev, peaks):
+    """The steps either side of the recurrence at the packed-prefill layer shape (B=4, L=8192, Hk=16, Hv=32,
+    K=V=128, bf16, conv width 4): each kernel alone, achieved HBM GB/s on the bytes it must move (inputs read
+    once, outputs written once) against the measured copy bandwidth.  Device-resident buffers, C ABI."""
+    from deltanet_b200 import _lib as L
+    lib = L.lib()
+    B, Lq, Hk, Hv, K, V, W = 4, 8192, 16, 32, 128, 128, 4
+    D = 2 * Hk * K + Hv * V
+    rows = B * Lq * Hv
+    gen = torch.Generator(device=dev).manual_seed(5000)
+    rn = lambda *sh: torch.randn(*sh, generator=gen, device=dev)
+    mixed, d_mixed = rn(B, Lq, D).bfloat16(), torch.empty(B, Lq, D, dtype=torch.bfloat16, device=dev)
+    w, dw, db = rn(D, W) * 0.5, torch.empty(D, W, device=dev), torch.empty(D, device=dev)
+    q, k = (torch.empty(B, Lq, Hk, K, dtype=torch.bfloat16, device=dev) for _ in range(2))
+    v = torch.empty(B, Lq, Hv, V, dtype=torch.bfloat16, device=dev)
+    z, y = rn(B, Lq, Hv, V).bfloat16(), torch.empty(B, Lq, Hv, V, dtype=torch.bfloat16, device=dev)
+    d_o, d_z = torch.empty_like(y), torch.empty_like(y)
+    nw, dnw = 1 + 0.2 * rn(V), torch.empty(V, device=dev)
+    seg = (torch.arange(Lq, device=dev) // 1024).to(torch.int32)[None].expand(B, Lq).contiguous()
+    sc1 = torch.empty(lib.dn_gdn_producer_scratch_bytes(B, Lq, D, W), dtype=torch.uint8, device=dev)
+    sc2 = torch.empty(lib.dn_gated_rmsnorm_scratch_bytes(rows, V), dtype=torch.uint8, device=dev)
+    st = torch.cuda.current_stream().cuda_stream
+    P = lambda t: t.data_ptr()
+    calls = dict(
+        producer_fwd=(lambda: L.check(lib.dn_gdn_producer_fwd(P(mixed), P(w), None, P(seg), B, Lq, Hk, Hv, K, V, W, L.DN_BF16,
+                                                            P(q), P(k), P(v), st), "producer_fwd"), 2 * mixed.numel() * 2),
+        producer_bwd=(lambda: L.check(lib.dn_gdn_producer_bwd(P(mixed), P(w), None, P(seg), B, Lq, Hk, Hv, K, V, W, L.DN_BF16,
+                                                            P(q), P(k), P(v), P(d_mixed), P(dw), None, P(sc1), sc1.numel(), st),
+                                      "producer_bwd"), 3 * mixed.numel() * 2),
+        gated_rmsnorm_fwd=(lambda: L.check(lib.dn_gated_rmsnorm_fwd(P(v), P(z), P(nw), rows, V, L.DN_BF16, 1e-6, P(y), st),
+                                           "norm_fwd"), 3 * y.numel() * 2),
+        gated_rmsnorm_bwd=(lambda: L.check(lib.dn_gated_rmsnorm_bwd(P(v), P(z), P(nw), rows, V, L.DN_BF16, 1e-6, P(y), P(d_o),
+                                                                  P(d_z), P(dnw), P(sc2), sc2.numel(), st), "norm_bwd"),
+                           5 * y.numel() * 2),
+    )
+    out = dict(workload="GDN layer steps at B=4 L=8192 Hk=16 Hv=32 K=V=128 bf16, conv width 4, documents of 1024 tokens", kernels={})
+    for name, (fn, nbytes) in calls.items():
+        ms = time_steps(fn, 10, 3, min_seconds=0.05)[0] / 10
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        out["kernels"][name] = dict(ms=round(ms, 4), alg_mbytes=round(nbytes / 1e6, 1), gbs=round(gbs, 1),
+                                    frac=round(gbs / peaks["hbm_gbs"], 3))
+    return out
+
+
 # ------------------------------------------------------------------------------------------ end to end
 def e2e_leg(dn, dev, dist, world, rank, steps, light):
     """fwd+bwd through the public operator from pinned HOST buffers, every step's uploads and read-backs
@@ -632,6 +678,10 @@ def main():
     del dj, job
     torch.cuda.empty_cache()
 
+    # ---- the layer steps either side of the path (one GPU's worth; rank 0 reports)
+    layer = layer_steps_leg(dn, dev, peaks) if rank == 0 else None
+    torch.cuda.empty_cache()
+
     # ---- the long-sequence workload, sharded over the ranks
     spr = sp_leg(dn, dist, world, rank, dev)
 
@@ -655,7 +705,7 @@ def main():
         config=dict(workload=WORKLOAD, global_batch=world, parallelism=f"batch-sharded x{world}, no collective",
                     timing=f"median of {repeats} regions of {args.steps} steps",
                     l2=f"no flush: the step touches {touched_mb:.0f} MB (inputs, residuals, scratch, grads) > 126 MB L2"),
-        roofline=roofline, e2e=e2e, decode=decode, sp=spr, cpu_baseline=cpu,
+        roofline=roofline, e2e=e2e, decode=decode, sp=spr, layer_steps=layer, cpu_baseline=cpu,
         gpu_launches=int(launches_per_region), clocks=clocks)
     print(json.dumps(line), flush=True)
     if dist is not None:

@@ -9,7 +9,8 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libdeltanet_b200.so")
+# DELTANET_B200_LIB points at another build of the same library (a debug or instrumented one)
+LIB_PATH = os.environ.get("DELTANET_B200_LIB") or os.path.join(_HERE, "libdeltanet_b200.so")
 
 DN_F32, DN_BF16 = 0, 1
 DN_PREC_FP32, DN_PREC_BF16 = 0, 1
