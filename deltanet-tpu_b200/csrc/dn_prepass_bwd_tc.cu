@@ -88,7 +88,7 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
   __shared__ uint32_t tmem_base;
   __shared__ int seg_s[C];
   __shared__ int reset_s[8];                 // per 32-row quarter: a document starts inside it
-  __shared__ float rq_s[C], rk_s[C], dlend_s[K];
+  __shared__ float rq_s[C], rk_s[C], dlend_s[K], dlend_b_s[C];     // dlend_b_s: the activated scalar erase gate per row (scalar-gate path)
   const Geo& g = a.g;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int myrow = warp * 8 + (lane & 7), lgrp = lane >> 3;      // the 8 rows x 4 pieces mapping
@@ -282,6 +282,101 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
       __syncthreads();
     }
 
+    if constexpr (CF::scalar_gates) {
+      // ---- D + H for one scalar decay and one scalar beta per (token, head).  With f_ij = e^{lam_i - lam_j}
+      //      (exact, <= 1 on the entries that survive the masks) and b_i the activated erase gate,
+      //        dbeta'_i = sum_j (dA_ij f_ij) k_j            dq'_i = sum_{j<i} (dM_ij f_ij) k_j
+      //        dk'_j    = sum_i (dA_ij f_ij b_i) k_i + sum_{i>j} (dM_ij f_ij) q_i
+      //      i.e. four products on the plain bf16 images of k_hat and q_hat: no levels, no diagonal pass.
+      //      The image of dA f is used twice, the second time with its rows scaled by b_i.
+      DN_MARK(8);
+      {
+        const int x = myrow;
+        const bool live = x < r.rows_valid;
+        if (lgrp == 0) dlend_b_s[x] = live ? ldf_ro(r.b, r.b_row0 + (size_t)x * r.b_pitch, DN_F32) : 0.f;
+#pragma unroll 2
+        for (int it = 0; it < 4; ++it) {
+          const int p = it * 4 + lgrp;
+          float qh[8], kh[8];
+          qhat8(r, x, p, qh);
+          khat8(r, x, p, kh);
+          I_KR[p * 128 + x] = umma::pack8(kh);
+          I_QK[p * 128 + x] = umma::pack8(qh);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {                    // images of dA f and dM f (strictly lower; the diagonal of dM goes through E)
+        const int e = u * NT + tid, p = e >> 7, x = e & 127;
+        const bool any = 8 * p < x;                    // the piece has entries below the diagonal
+        const float4 a0 = umma::ldcg_pred(DA4 + p4v(x, 8 * p), any), a1 = umma::ldcg_pred(DA4 + p4v(x, 8 * p + 4), any);
+        const float4 m0 = umma::ldcg_pred(DM4 + p4v(x, 8 * p), any), m1 = umma::ldcg_pred(DM4 + p4v(x, 8 * p + 4), any);
+        const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w}, mv[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+        const float lx = LAM[x * LP] * DN_LOG2E;
+        float oa[8], om[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int j = 8 * p + i;
+          const float f = umma::ex2_fast(fminf(lx - LAM[j * LP] * DN_LOG2E, 0.f));
+          oa[i] = av[i] * f;                           // (dA is zero on and above the diagonal and across documents)
+          om[i] = j < x ? mv[i] * f : 0.f;
+        }
+        I_DA[e] = umma::pack8(oa);
+        I_DM[e] = umma::pack8(om);
+      }
+      umma::pre_issue_sync();
+      umma::issue<128, false, true>(cx, I_DA, I_KR, C, 0, false);          // (dA f)   k_hat
+      umma::issue<128, false, true>(cx, I_DM, I_KR, C, 128, false);        // (dM f)   k_hat
+      umma::commit_wait(cx);
+      DN_MARK(9);
+      const int dq_quarter = warp & 3, dq_group = warp >> 2, dq_row = dq_quarter * 32 + lane;
+      const uint32_t dq_tbase = cx.tmem + ((uint32_t)(dq_quarter * 32) << 16);
+#pragma unroll 1
+      for (int cc = 0; cc < 32; cc += 16) {
+        const int col = dq_group * 32 + cc;
+        float t1[16], t2[16];
+        if (!cx.dead) { umma::tmem_ld16(dq_tbase + col, t1); umma::tmem_ld16(dq_tbase + 128 + col, t2); }
+        else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) t1[i] = t2[i] = 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          __stcg(DBP4 + p4v(dq_row, col + 4 * i), make_float4(t1[4 * i], t1[4 * i + 1], t1[4 * i + 2], t1[4 * i + 3]));
+          __stcg(DQP4 + p4v(dq_row, col + 4 * i), make_float4(t2[4 * i], t2[4 * i + 1], t2[4 * i + 2], t2[4 * i + 3]));
+        }
+      }
+      umma::tc_fence_before();
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {                    // rows of the dA f image scaled by b_i
+        const int e = u * NT + tid, x = e & 127;
+        float v8[8];
+        umma::unpack8(I_DA[e], v8);
+        const float bx = dlend_b_s[x];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v8[i] *= bx;
+        I_DA[e] = umma::pack8(v8);
+      }
+      umma::pre_issue_sync();
+      umma::issue<128, true, true>(cx, I_DA, I_KR, C, 0, false);           // (dA f b)^T k_hat
+      umma::issue<128, true, true>(cx, I_DM, I_QK, C, 0, true);            // + (dM f)^T q_hat
+      umma::commit_wait(cx);
+      DN_MARK(10);
+#pragma unroll 1
+      for (int cc = 0; cc < 32; cc += 16) {
+        const int col = dq_group * 32 + cc;
+        float t3[16];
+        if (!cx.dead) umma::tmem_ld16(dq_tbase + col, t3);
+        else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) t3[i] = 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          __stcg(DKP4 + p4v(dq_row, col + 4 * i), make_float4(t3[4 * i], t3[4 * i + 1], t3[4 * i + 2], t3[4 * i + 3]));
+      }
+      umma::tc_fence_before();
+      __syncthreads();
+    } else {
     DN_MARK(8);
     // ---- D. diagonal 16x16 blocks, exact.  The blocks of dA and dM are staged in shared memory
     //         (all lanes of a warp read the same entry), and so are k_hat, q_hat and beta of 64 rows
@@ -488,6 +583,7 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
       }
     }
     __syncthreads();
+    }
 
     DN_MARK(13);
     // ---- E. combination (8 rows x 4 pieces per warp step; a thread keeps row `myrow`):

@@ -104,7 +104,7 @@ __global__ void __launch_bounds__(NT, 1) prepass_fwd_tc_kernel(PrepassFwdArgs a,
   __shared__ uint32_t tmem_base;
   __shared__ int seg_s[C];
   __shared__ int reset_s[4];
-  __shared__ float rq_s[C], rk_s[C];
+  __shared__ float rq_s[C], rk_s[C], bsc_s[C];
   const Geo& g = a.g;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int myrow = warp * 8 + (lane & 7), lgrp = lane >> 3;
@@ -331,6 +331,81 @@ __global__ void __launch_bounds__(NT, 1) prepass_fwd_tc_kernel(PrepassFwdArgs a,
       if (tid < K) a.res.lam_end[ibase * K + tid] = LAM[(C - 1) * LP + tid];
     };
 
+    if constexpr (CF::scalar_gates) {
+      // ---- one scalar decay and one scalar beta per (token, head): the decay leaves the channel sum,
+      //      A_ij = beta_i e^{lam_i - lam_j} (k_i . k_j),  M_ij = e^{lam_i - lam_j} (q_i . k_j),
+      //      so A and M are two Gram products on the plain bf16 images of k_hat and q_hat, and the decay
+      //      (exact, <= 1) is applied per entry by the drain.  No levels, no diagonal pass.
+      DN_MARK(1);
+      {
+        const int x = myrow;
+        const bool first = seg_s[x] == seg0, last = seg_s[x] == segL;
+        const bool live = x < r.rows_valid;
+        const float lam = LAM[x * LP], lend = LAM[(C - 1) * LP];
+        const float el = umma::exp_neg(fminf(lam, 0.f)), eke = umma::exp_neg(fminf(lend - lam, 0.f));
+        const float bx = live ? ldf_ro(r.b, r.b_row0 + (size_t)x * r.b_pitch, DN_F32) : 0.f;
+#pragma unroll 2
+        for (int it = 0; it < 4; ++it) {
+          const int p = it * 4 + lgrp;
+          float qh[8], kh[8], o[8];
+          qhat8(r, x, p, qh);
+          khat8(r, x, p, kh);
+          KR[p * 128 + x] = umma::pack8(kh);
+          QK[p * 128 + x] = umma::pack8(qh);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] = first ? qh[i] * el : 0.f;
+          QEimg[p * 128 + x] = umma::pack8(o);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] = last ? kh[i] * eke : 0.f;
+          KEimg[p * 128 + x] = umma::pack8(o);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] = first ? (bx * kh[i]) * el : 0.f;
+          XI[p * 128 + x] = umma::pack8(o);
+        }
+        if (lgrp == 0) bsc_s[x] = bx;
+        if (tid < K) a.res.lam_end[ibase * K + tid] = lend;
+      }
+      DN_MARK(2);
+      umma::pre_issue_sync();
+      umma::issue<128, false, false>(cx, KR, KR, K, 0, false);             // k_hat k_hat^T
+      umma::issue<128, false, false>(cx, QK, KR, K, 128, false);           // q_hat k_hat^T
+      umma::commit_wait(cx);
+      DN_MARK(3);
+      {
+        const int quarter = warp & 3, group = warp >> 2;
+        const int row = quarter * 32 + lane;
+        const uint32_t tbase = cx.tmem + ((uint32_t)(quarter * 32) << 16);
+        const float lrow = LAM[row * LP] * DN_LOG2E, brow = bsc_s[row];
+        const int srow = seg_s[row];
+#pragma unroll 1
+        for (int cc = 0; cc < 32; cc += 16) {
+          const int col = group * 32 + cc;
+          float va[16], vm[16];
+          if (!cx.dead && col <= quarter * 32 + 31) {    // warp-uniform: a piece wholly above the warp's rows is zeros
+            umma::tmem_ld16(tbase + col, va);
+            umma::tmem_ld16(tbase + 128 + col, vm);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) va[i] = vm[i] = 0.f;
+          }
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const int j = col + i;
+            const bool same = srow == seg_s[j];
+            const float f = umma::ex2_fast(fminf(lrow - LAM[j * LP] * DN_LOG2E, 0.f));
+            va[i] = (same && j < row) ? brow * f * va[i] : 0.f;
+            vm[i] = (same && j <= row) ? f * vm[i] : 0.f;
+          }
+#pragma unroll
+          for (int i = 0; i < 4; ++i) __stcg(Ag4 + p4v(row, col + 4 * i), make_float4(va[4 * i], va[4 * i + 1], va[4 * i + 2], va[4 * i + 3]));
+          Mimg[(col / 8) * 128 + row] = umma::pack8p(vm);
+          Mimg[(col / 8 + 1) * 128 + row] = umma::pack8p(vm + 8);
+        }
+        umma::tc_fence_before();
+      }
+      __syncthreads();
+      DN_MARK(6);
+    } else {
     DN_MARK(1);
     if (tm_cache) diag_pass();                 // first: it also fills the tensor-memory operand cache
     xi_pass();
@@ -402,6 +477,7 @@ __global__ void __launch_bounds__(NT, 1) prepass_fwd_tc_kernel(PrepassFwdArgs a,
 
     DN_MARK(6);
     if (!tm_cache) diag_pass();
+    }
 
     DN_MARK(7);
     // ---- T = (I + A)^-1 in fp32: substitution on the diagonal blocks, then block merges
