@@ -88,14 +88,13 @@ def alg_flops(c):
 
 def alg_bytes(c):
     """HBM bytes per (batch, exec head, chunk) item and kernel: every array the kernel must read or
-    write, once (bf16 q/k/v/out/dO and residual tiles, fp32 gates, bf16 T / state / dV / dH images,
-    the fp32 chunk-entry state the reverse chain reads)."""
+    write, once (bf16 q/k/v/out/dO and residual tiles, fp32 gates, bf16 T / state / dV / dH images)."""
     C, K, Vw = c["chunk"], c["K"], (c["Hv"] // c["Hk"]) * c["V"]
     qk, gb, vv, ww = 2 * C * K * 2, 2 * C * K * 4, C * Vw * 2, C * Vw * 4
     tiles = 3 * C * K * 2 + C * C * 2 + C * Vw * 2              # W, qe, ke, M, U
     pre_fwd = qk + gb + vv + ww + tiles + C * C * 2 + K * 4      # + T image, Lambda_end
-    st_fwd = tiles + C * Vw * 2 + K * Vw * (4 + 2)               # + out, chunk-entry state (fp32 + image)
-    chain_bwd = 3 * C * K * 2 + C * C * 2 + C * Vw * 2 + K * Vw * 4 + C * Vw * 2 + K * Vw * 2    # tiles, dO, S -> dV, dH images
+    st_fwd = tiles + C * Vw * 2 + K * Vw * 2                     # + out, chunk-entry state image
+    chain_bwd = 3 * C * K * 2 + C * C * 2 + C * Vw * 2 + K * Vw * 2 + C * Vw * 2 + K * Vw * 2    # tiles, dO, S -> dV, dH images
     par_bwd = (C * K * 2 + C * Vw * 2 + K * Vw * 2 + C * C * 2 + C * Vw * 2 + C * Vw * 2 + K * Vw * 2
                + qk + gb + vv + ww + qk + gb + vv + ww)          # W,U,S,T,dO,dV,dH images, inputs, six gradients
     return dict(prepass_fwd=pre_fwd, state_fwd=st_fwd, state_bwd=chain_bwd, prepass_bwd=par_bwd)

@@ -105,7 +105,7 @@ static void residual_sizes(const Geo& g, size_t sz[8]) {
   sz[4] = sz[0];
   sz[5] = n * g.K * sizeof(float);
   sz[6] = keep ? n * g.C * g.C * sizeof(float) : 0;
-  sz[7] = keep ? n * g.K * g.Vw * (sizeof(float) + (g.img ? 2 : 0)) : 0;      // + the bf16 image copy (states_img)
+  sz[7] = keep ? n * g.K * g.Vw * (g.img ? 2 : sizeof(float)) : 0;            // image path: a bf16 operand image (states_img)
 }
 
 size_t dn_residual_bytes(const dn_shape* s) {

@@ -84,13 +84,13 @@ inline int make_geo(const dn_shape* s, Geo* g) {
 }
 
 // On the image path three more arrays are kept as bf16 operand images, [col / 8][128 rows][8]:
-//   * the chunk-entry states a second time, behind the fp32 copy (which the reverse chain still
-//     reads): states_img();
+//   * the chunk-entry states (the only copy on this path: the `states` slot holds the image): states_img();
 //   * T, in the first half of its fp32-sized slot;
 //   * dV and dH, in the first half of their fp32-sized buffers; the second half of the dH buffer
 //     carries the partial sums of dLambda_end, (item, column slice of 32, K) fp32: dlend_part().
 __host__ __device__ __forceinline__ const __nv_bfloat16* states_img(const Geo& g, const float* states) {
-  return reinterpret_cast<const __nv_bfloat16*>(states + (size_t)g.B * g.H * g.NC * g.K * g.Vw);
+  (void)g;
+  return reinterpret_cast<const __nv_bfloat16*>(states);
 }
 __host__ __device__ __forceinline__ float* dlend_part(const Geo& g, float* dH) {
   return dH + (size_t)g.B * g.H * g.NC * g.K * g.Vw / 2;

@@ -163,7 +163,7 @@ __global__ void __launch_bounds__(128, 1) state_fwd_tc_kernel(StateArgs a) {
 #pragma unroll
       for (int j = 0; j < VS; ++j) S[j] = 0.f;
     }
-    if (states) {
+    if (states && !g.img) {
       float4* dst = reinterpret_cast<float4*>(states + item * K * Vw + (size_t)row * Vw + v0);
 #pragma unroll
       for (int j = 0; j < VS / 4; ++j) dst[j] = make_float4(S[4 * j], S[4 * j + 1], S[4 * j + 2], S[4 * j + 3]);
@@ -289,7 +289,7 @@ __global__ void __launch_bounds__(128, 1) state_bwd_tc_kernel(StateArgs a) {
   uint4* sdO = sW + TILE_U4;
   uint4* sdH = sdO + (VS / 8) * 128;
   uint4* sdV = sdH + (VS / 8) * 128;
-  float4* sSl = reinterpret_cast<float4*>(sdV + (VS / 8) * 128) + row;   // this thread's row of S (image path): piece j at sSl[j * 128]
+  uint4* sSl = sdV + (VS / 8) * 128 + row;              // this thread's row of S (image path, bf16): piece j at sSl[j * 128]
   const bool img = g.img;
   if (row == 0) { umma::mbar_init(&bar, 1); umma::mbar_init(&tb[0], 1); umma::mbar_init(&tb[1], 1); umma::fence_mbar_init(); }
   uint32_t tph[2] = {0u, 0u};
@@ -313,12 +313,13 @@ __global__ void __launch_bounds__(128, 1) state_bwd_tc_kernel(StateArgs a) {
   float* carry = a.carry ? a.carry + (((size_t)b * g.H + h) * K + row) * Vw + v0 : nullptr;
   const size_t last = item0 + ce - 1;
 
-  // image path: the thread's own row of the chunk-entry state (fp32) travels with M and ke, one chunk
-  // ahead, into a private strip of shared memory; it is needed for dLambda_end = sum_v dH * S
+  // image path: the thread's own row of the chunk-entry state (its bf16 image, the only copy kept)
+  // travels with M and ke, one chunk ahead, into a private strip of shared memory; it is needed for
+  // dLambda_end = sum_v dH * S
   auto copy_S_row = [&](size_t it_) {
-    const float4* src = reinterpret_cast<const float4*>(a.res.states + it_ * K * Vw + (size_t)row * Vw + v0);
+    const uint4* src = reinterpret_cast<const uint4*>(states_img(g, a.res.states) + it_ * K * Vw) + (size_t)(v0 / 8) * 128 + row;
 #pragma unroll
-    for (int j = 0; j < VS / 4; ++j) umma::cp_async16(sSl + j * 128, src + j);
+    for (int j = 0; j < VS / 8; ++j) umma::cp_async16(sSl + j * 128, src + j * 128);
   };
   // image path: whole tiles by bulk copies on tb[], the S row by this thread's own cp.async group;
   // otherwise everything by cp.async groups (two per chunk)
@@ -424,9 +425,11 @@ __global__ void __launch_bounds__(128, 1) state_bwd_tc_kernel(StateArgs a) {
     if (img) {                                          // partial sum of dLambda_end over this CTA's columns
       float part = 0.f;
 #pragma unroll
-      for (int j = 0; j < VS / 4; ++j) {
-        const float4 sv = sSl[j * 128];
-        part += dH[4 * j] * sv.x + dH[4 * j + 1] * sv.y + dH[4 * j + 2] * sv.z + dH[4 * j + 3] * sv.w;
+      for (int j = 0; j < VS / 8; ++j) {
+        float sv[8];
+        umma::unpack8(sSl[j * 128], sv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) part = fmaf(dH[8 * j + i], sv[i], part);
       }
       dlend_part(g, a.dH)[(item * gridDim.x + blockIdx.x) * K + row] = part;
     }
@@ -491,7 +494,7 @@ int pick_vs(const Geo& g) {
 
 template <int VS>
 size_t tc_smem(bool bwd) {
-  return (size_t)4 * TILE_U4 * 16 + (size_t)(bwd ? 3 : 2) * (VS / 8) * 128 * 16 + (bwd ? (size_t)128 * VS * 4 : 0);
+  return (size_t)4 * TILE_U4 * 16 + (size_t)(bwd ? 3 : 2) * (VS / 8) * 128 * 16 + (bwd ? (size_t)128 * VS * 2 : 0);
 }
 
 template <int VS>

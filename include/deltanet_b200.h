@@ -108,8 +108,8 @@ int dn_exec_view(const dn_shape* s, dn_exec* out);
  * that take the tensor-core path (precision bf16 without DN_STATE_FP32_MM, K = 128, Vw in {128,256},
  * DN_FORCE_SIMT unset) a tile is stored as the tensor cores' operand image, [col / 8][row][8 elements], so that
  * every kernel copies it into shared memory as it lies.  The sizes are the same in both layouts.
- * On that path T holds a bf16 image in the first half of its slot, and the chunk-entry states are
- * followed by a bf16 image copy of themselves (dn_residual_bytes accounts for it).  The dV / dH
+ * On that path T holds a bf16 image in the first half of its slot, and the chunk-entry states are kept
+ * as a bf16 operand image only (half the bytes; dn_residual_bytes accounts for it).  The dV / dH
  * buffers that dn_state_bwd hands to dn_prepass_bwd are opaque in the same way (bf16 images plus the
  * partial sums of the decay cotangent); a caller only sizes them (fp32 element counts) and passes
  * them on.
@@ -122,7 +122,7 @@ typedef struct dn_residuals {
   void*  ke;       /* (B,H,NC) tiles of C x K    pre_dtype */
   float* lam_end;  /* (B,H,NC,K)     */
   float* T;        /* (B,H,NC,C,C)   or NULL (inference); opaque */
-  float* states;   /* (B,H,NC,K,Vw)  chunk-entry states (+ image copy), or NULL (inference) */
+  float* states;   /* (B,H,NC,K,Vw)  chunk-entry states (fp32; a bf16 image on the tensor-core path), or NULL (inference) */
 } dn_residuals;
 
 /* Bytes of one packed residual block, and a helper that carves the block into the struct. */
