@@ -60,19 +60,41 @@ __device__ __forceinline__ void stage_rows(uint4* dst, int row, const float (&x)
   }
 }
 
+// issue the loads of one accumulator row (VS columns) without waiting; read_wait() before use
+template <int VS>
+__device__ __forceinline__ void read_acc_nowait(const umma::Ctx& cx, uint32_t col, int warp, float (&x)[VS]) {
+  if (!cx.dead) {
+#pragma unroll
+    for (int c = 0; c < VS; c += 32) umma::tmem_ld32_nowait(cx.tmem + ((uint32_t)(warp * 32) << 16) + col + c, x + c);
+  } else {
+#pragma unroll
+    for (int i = 0; i < VS; ++i) x[i] = 0.f;
+  }
+}
+__device__ __forceinline__ void read_wait(const umma::Ctx& cx) { if (!cx.dead) umma::tmem_wait_ld(); }
 template <int VS>
 __device__ __forceinline__ void read_acc(const umma::Ctx& cx, uint32_t col, int warp, float (&x)[VS]) {
-#pragma unroll
-  for (int c = 0; c < VS; c += 16) {
-    float v[16];
-    if (!cx.dead) umma::tmem_ld16(cx.tmem + ((uint32_t)(warp * 32) << 16) + col + c, v);
-    else {
-#pragma unroll
-      for (int i = 0; i < 16; ++i) v[i] = 0.f;
+  read_acc_nowait<VS>(cx, col, warp, x);
+  read_wait(cx);
+}
+
+// Document flags of the chunks a chain walks, kept in shared memory 128 chunks at a time (plus one of
+// look-ahead) so that no step of the chain waits for the segment ids: thread i fills entry i.
+// dir = +1: entry i is chunk top + i; dir = -1: chunk top - i.  Bit 0: the chunk starts a document; bit 1:
+// the chunk is one document.  Ends with a __syncthreads().
+__device__ __forceinline__ void fill_flags(uint8_t* fl, const int32_t* seg, const Geo& g, int b, int top, int dir,
+                                           int lo, int hi) {
+  for (int i = threadIdx.x; i < 129; i += blockDim.x) {
+    const int c = top + dir * i;
+    uint8_t f = 0;
+    if (c >= lo && c < hi) {
+      bool n, s;
+      chunk_flags(seg, g, b, c, n, s);
+      f = (n ? 1 : 0) | (s ? 2 : 0);
     }
-#pragma unroll
-    for (int i = 0; i < 16; ++i) x[c + i] = v[i];
+    fl[i] = f;
   }
+  __syncthreads();
 }
 
 __host__ __device__ constexpr uint32_t tmem_cols(int vs) { return 3 * vs <= 128 ? 128u : (3 * vs <= 256 ? 256u : 512u); }
@@ -82,6 +104,7 @@ __global__ void __launch_bounds__(128, 1) state_fwd_tc_kernel(StateArgs a) {
   extern __shared__ __align__(128) uint8_t sm[];
   __shared__ uint64_t bar, tb[2];                       // MMA completion; tile arrival: W | qe, M, ke
   __shared__ uint32_t tmem_base;
+  __shared__ uint8_t fl_s[132];
   const Geo& g = a.g;
   constexpr int C = 128, K = 128;
   const int Vw = g.Vw, h = blockIdx.y, b = blockIdx.z;
@@ -127,17 +150,24 @@ __global__ void __launch_bounds__(128, 1) state_fwd_tc_kernel(StateArgs a) {
     }
     umma::cp_async_commit();
   };
+  // (a pass without outputs needs neither qe nor M: half the bytes a chunk step pulls through L2, which
+  // is what bounds the step)
+  const bool need_out_tiles = WITH_OUT && !trans;
   auto fetch_QMK = [&](size_t it_) {
     if (img) {
       if (row == 0) {
-        umma::mbar_expect_tx(&tb[1], 3 * TILE_U4 * 16);
-        bulk_tile(sQE, QEg + it_ * C * K, &tb[1]);
-        bulk_tile(sM, Mg + it_ * C * C, &tb[1]);
+        umma::mbar_expect_tx(&tb[1], (need_out_tiles ? 3 : 1) * TILE_U4 * 16);
+        if (need_out_tiles) {
+          bulk_tile(sQE, QEg + it_ * C * K, &tb[1]);
+          bulk_tile(sM, Mg + it_ * C * C, &tb[1]);
+        }
         bulk_tile(sKE, KEg + it_ * C * K, &tb[1]);
       }
     } else {
-      copy_tile_async(sQE, QEg + it_ * C * K, row, false);
-      copy_tile_async(sM, Mg + it_ * C * C, row, false);
+      if (need_out_tiles) {
+        copy_tile_async(sQE, QEg + it_ * C * K, row, false);
+        copy_tile_async(sM, Mg + it_ * C * C, row, false);
+      }
       copy_tile_async(sKE, KEg + it_ * C * K, row, false);
     }
     umma::cp_async_commit();
@@ -149,10 +179,35 @@ __global__ void __launch_bounds__(128, 1) state_fwd_tc_kernel(StateArgs a) {
 #pragma unroll
   for (int j = 0; j < VS; ++j) S[j] = cb > 0 ? carry[j] : 0.f;
 
-  bool is_new, all_same;
-  chunk_flags(a.seg, g, b, cb, is_new, all_same);
+  // This thread's row of U (VS columns) and of Lambda_end for one chunk, fetched one chunk ahead of use
+  // (right after the previous chunk's copy has been consumed), so the chain never waits for them.
+  uint4 ureg[VS / 8];
+  float lam_cur;
+  auto fetch_row = [&](size_t it_) {
+    if (Ug) {
+      if (g.img) {
+        const uint4* up = reinterpret_cast<const uint4*>(Ug + it_ * C * Vw) + (size_t)(v0 / 8) * 128 + row;
+#pragma unroll
+        for (int p = 0; p < VS / 8; ++p) ureg[p] = __ldg(up + p * 128);
+      } else {
+        const uint4* up = reinterpret_cast<const uint4*>(Ug + it_ * C * Vw + (size_t)row * Vw + v0);
+#pragma unroll
+        for (int p = 0; p < VS / 8; ++p) ureg[p] = __ldg(up + p);
+      }
+    } else {                                            // transition columns / U == NULL: U = 0
+#pragma unroll
+      for (int p = 0; p < VS / 8; ++p) ureg[p] = make_uint4(0, 0, 0, 0);
+    }
+    lam_cur = __ldg(a.res.lam_end + it_ * K + row);
+  };
+  fetch_row(item0 + cb);
+
   for (int c = cb; c < ce; ++c) {
     const size_t item = item0 + c;
+    const int fo = (c - cb) & 127;
+    if (fo == 0) fill_flags(fl_s, a.seg, g, b, c, 1, cb, ce);
+    const bool is_new = fl_s[fo] & 1, all_same = fl_s[fo] & 2;
+    const bool nis_new = fl_s[fo + 1] & 1;              // (zero past the end of the range)
     if (c == 0 && !is_new && trans) {
 #pragma unroll
       for (int j = 0; j < VS; ++j) S[j] = row == p0 + j ? 1.f : 0.f;
@@ -174,25 +229,7 @@ __global__ void __launch_bounds__(128, 1) state_fwd_tc_kernel(StateArgs a) {
 #pragma unroll
       for (int p = 0; p < VS / 8; ++p) simg[p * 128] = sS[p * 128 + row];
     }
-    uint4 ureg[VS / 8];
-    if (Ug) {
-      if (g.img) {
-        const uint4* up = reinterpret_cast<const uint4*>(Ug + item * C * Vw) + (size_t)(v0 / 8) * 128 + row;
-#pragma unroll
-        for (int p = 0; p < VS / 8; ++p) ureg[p] = up[p * 128];
-      } else {
-        const uint4* up = reinterpret_cast<const uint4*>(Ug + item * C * Vw + (size_t)row * Vw + v0);
-#pragma unroll
-        for (int p = 0; p < VS / 8; ++p) ureg[p] = up[p];
-      }
-    } else {                                            // U == NULL: transition pass (U = 0)
-#pragma unroll
-      for (int p = 0; p < VS / 8; ++p) ureg[p] = make_uint4(0, 0, 0, 0);
-    }
-    const float dec = all_same ? expf(fminf(__ldg(a.res.lam_end + item * K + row), 0.f)) : 0.f;
-    // the next chunk's document flags: their (dependent) global loads overlap this chunk's products
-    bool nis_new = false, nall_same = false;
-    if (c + 1 < ce) chunk_flags(a.seg, g, b, c + 1, nis_new, nall_same);
+    const float dec = all_same ? expf(fminf(lam_cur, 0.f)) : 0.f;
     // the last chunk this CTA walks: the end of the range, or (until_independent) the point after which
     // nothing depends on the state the chain started from.  Uniform over the CTA (the flags depend on the
     // chunk only).  Nothing is prefetched past it, so no copy is in flight when the CTA leaves.
@@ -213,6 +250,7 @@ __global__ void __launch_bounds__(128, 1) state_fwd_tc_kernel(StateArgs a) {
 #pragma unroll
       for (int i = 0; i < 8; ++i) vn[p * 8 + i] = u[i] - vn[p * 8 + i];      // V_new = U - W S
     }
+    if (!last) fetch_row(item + 1);
     stage_rows<VS>(sVn, row, vn);
 
     if (img) tile_wait(1); else umma::cp_async_wait<1>();      // this chunk's qe, M, ke have landed
@@ -225,9 +263,12 @@ __global__ void __launch_bounds__(128, 1) state_fwd_tc_kernel(StateArgs a) {
     umma::commit_wait(cx);
     if (!last) fetch_QMK(item + 1); else umma::cp_async_commit();
 
+    float sn[VS];
     if (WITH_OUT && !trans) {
       float o[VS];
-      read_acc<VS>(cx, colO, warp, o);
+      read_acc_nowait<VS>(cx, colO, warp, o);
+      read_acc_nowait<VS>(cx, colS, warp, sn);
+      read_wait(cx);
       const int t = c * C + row;
       if (t < g.L) {
         const size_t off = ((size_t)b * g.L + t) * g.Hv * g.V + (size_t)h * Vw + v0;
@@ -247,12 +288,10 @@ __global__ void __launch_bounds__(128, 1) state_fwd_tc_kernel(StateArgs a) {
         }
       }
     }
-    float sn[VS];
-    read_acc<VS>(cx, colS, warp, sn);
+    if (!(WITH_OUT && !trans)) read_acc<VS>(cx, colS, warp, sn);
 #pragma unroll
     for (int j = 0; j < VS; ++j) S[j] = fmaf(dec, S[j], sn[j]);       // S <- decay * S + ke^T V_new
     umma::tc_fence_before();
-    is_new = nis_new; all_same = nall_same;
     if (last) break;
   }
   if (a.until_independent) {
@@ -278,6 +317,7 @@ __global__ void __launch_bounds__(128, 1) state_bwd_tc_kernel(StateArgs a) {
   extern __shared__ __align__(128) uint8_t sm[];
   __shared__ uint64_t bar, tb[2];                       // MMA completion; tile arrival: M, ke | qe, W
   __shared__ uint32_t tmem_base;
+  __shared__ uint8_t fl_s[132];
   const Geo& g = a.g;
   constexpr int C = 128, K = 128;
   const int Vw = g.Vw, v0 = blockIdx.x * VS, h = blockIdx.y, b = blockIdx.z;
@@ -378,11 +418,12 @@ __global__ void __launch_bounds__(128, 1) state_bwd_tc_kernel(StateArgs a) {
     }
   };
   fetch_dO(ce - 1);
-  bool is_new, all_same;
-  chunk_flags(a.seg, g, b, ce - 1, is_new, all_same);
 
   for (int c = ce - 1; c >= cb; --c) {
     const size_t item = item0 + c;
+    const int fo = (ce - 1 - c) & 127;
+    if (fo == 0) fill_flags(fl_s, a.seg, g, b, c, -1, cb, ce);
+    const bool is_new = fl_s[fo] & 1, all_same = fl_s[fo] & 2;
     // dO of this chunk, rounded to bf16 as the reference does (gdn2.py:731)
     float dO[VS];
     if (dobf) {
@@ -405,8 +446,6 @@ __global__ void __launch_bounds__(128, 1) state_bwd_tc_kernel(StateArgs a) {
     // prefetched past it.
     const bool last = c <= cb || (a.until_independent && (is_new || !all_same));
     fetch_dO(last ? cb - 1 : c - 1);                    // in flight during this chunk's products (zeros past the end)
-    bool nis_new = false, nall_same = false;
-    if (!last) chunk_flags(a.seg, g, b, c - 1, nis_new, nall_same);
     stage_rows<VS>(sdO, row, dO);
     stage_rows<VS>(sdH, row, dH);
     if (img) {                                           // dH as a bf16 operand image
@@ -469,7 +508,6 @@ __global__ void __launch_bounds__(128, 1) state_bwd_tc_kernel(StateArgs a) {
 #pragma unroll
     for (int j = 0; j < VS; ++j) dH[j] = is_new ? 0.f : fmaf(dec, dH[j], dn_[j]);
     umma::tc_fence_before();
-    is_new = nis_new; all_same = nall_same;
     if (last) break;
   }
   if (a.until_independent) {
