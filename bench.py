@@ -571,6 +571,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--min-seconds", type=float, default=0.5,
+                    help="repeat the timed region of K steps until this much time has been measured (0: one region)")
     ap.add_argument("--only", default="all", choices=["all", "chunk", "decode", "sp"],
                     help="profiling aid: run only the chunked fwd+bwd device loop, only the decode loop, or only the long-sequence leg")
     args = ap.parse_args()
@@ -612,7 +614,7 @@ def main():
     job = DeviceJob(CFG, dev, seed=1000 + rank)
     n0 = lib.dn_launches_total()
     with ClockSampler(local) as clk:
-        ms, repeats = time_steps(job.step, args.steps, args.warmup, dist, min_seconds=0.5)
+        ms, repeats = time_steps(job.step, args.steps, args.warmup, dist, min_seconds=args.min_seconds)
     launches_per_region = (lib.dn_launches_total() - n0) * args.steps // (args.warmup + repeats * args.steps)
     clocks = clk.summary()
     ms_step = ms / args.steps
