@@ -43,7 +43,7 @@ using namespace prep;
 constexpr int NT = 512;
 
 __device__ __forceinline__ void ld2x4(const float4* p, float (&o)[8]) {      // scratch written by this CTA
-  const float4 a = __ldcg(p), b = __ldcg(p + 128);
+  const float4 a = umma::ld_keep4(p), b = umma::ld_keep4(p + 128);
   o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
 }
 __device__ __forceinline__ void out8(void* base, size_t off, int dt, const float (&v)[8]) {
@@ -308,8 +308,8 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
       for (int u = 0; u < 4; ++u) {                    // images of dA f and dM f (strictly lower; the diagonal of dM goes through E)
         const int e = u * NT + tid, p = e >> 7, x = e & 127;
         const bool any = 8 * p < x;                    // the piece has entries below the diagonal
-        const float4 a0 = umma::ldcg_pred(DA4 + p4v(x, 8 * p), any), a1 = umma::ldcg_pred(DA4 + p4v(x, 8 * p + 4), any);
-        const float4 m0 = umma::ldcg_pred(DM4 + p4v(x, 8 * p), any), m1 = umma::ldcg_pred(DM4 + p4v(x, 8 * p + 4), any);
+        const float4 a0 = umma::ld_keep4_pred(DA4 + p4v(x, 8 * p), any), a1 = umma::ld_keep4_pred(DA4 + p4v(x, 8 * p + 4), any);
+        const float4 m0 = umma::ld_keep4_pred(DM4 + p4v(x, 8 * p), any), m1 = umma::ld_keep4_pred(DM4 + p4v(x, 8 * p + 4), any);
         const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w}, mv[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
         const float lx = LAM[x * LP] * DN_LOG2E;
         float oa[8], om[8];
@@ -341,8 +341,8 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
         }
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          __stcg(DBP4 + p4v(dq_row, col + 4 * i), make_float4(t1[4 * i], t1[4 * i + 1], t1[4 * i + 2], t1[4 * i + 3]));
-          __stcg(DQP4 + p4v(dq_row, col + 4 * i), make_float4(t2[4 * i], t2[4 * i + 1], t2[4 * i + 2], t2[4 * i + 3]));
+          umma::st_keep4(DBP4 + p4v(dq_row, col + 4 * i), make_float4(t1[4 * i], t1[4 * i + 1], t1[4 * i + 2], t1[4 * i + 3]));
+          umma::st_keep4(DQP4 + p4v(dq_row, col + 4 * i), make_float4(t2[4 * i], t2[4 * i + 1], t2[4 * i + 2], t2[4 * i + 3]));
         }
       }
       umma::tc_fence_before();
@@ -372,7 +372,7 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
         }
 #pragma unroll
         for (int i = 0; i < 4; ++i)
-          __stcg(DKP4 + p4v(dq_row, col + 4 * i), make_float4(t3[4 * i], t3[4 * i + 1], t3[4 * i + 2], t3[4 * i + 3]));
+          umma::st_keep4(DKP4 + p4v(dq_row, col + 4 * i), make_float4(t3[4 * i], t3[4 * i + 1], t3[4 * i + 2], t3[4 * i + 3]));
       }
       umma::tc_fence_before();
       __syncthreads();
@@ -392,8 +392,8 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
       float4* DG4 = reinterpret_cast<float4*>(BC + 64 * CP);         // [2][8 blocks][16 rows][4]
       for (int e = tid; e < 512; e += NT) {
         const int blk = e >> 6, q4 = (e >> 4) & 3, row = e & 15;
-        DG4[(blk * 16 + row) * 4 + q4] = __ldcg(DA4 + p4v(blk * 16 + row, blk * 16 + 4 * q4));
-        DG4[512 + (blk * 16 + row) * 4 + q4] = __ldcg(DM4 + p4v(blk * 16 + row, blk * 16 + 4 * q4));
+        DG4[(blk * 16 + row) * 4 + q4] = umma::ld_keep4(DA4 + p4v(blk * 16 + row, blk * 16 + 4 * q4));
+        DG4[512 + (blk * 16 + row) * 4 + q4] = umma::ld_keep4(DM4 + p4v(blk * 16 + row, blk * 16 + 4 * q4));
       }
 #pragma unroll 1
       for (int half = 0; half < 2; ++half) {
@@ -449,8 +449,8 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
             kh[i] = kc[i * CP];
             sk[i] = 0.f;
           }
-          DBP[p4f(r0, c)] = 0.f;
-          DQP[p4f(r0, c)] = 0.f;
+          umma::st_keep1(DBP + p4f(r0, c), 0.f);
+          umma::st_keep1(DQP + p4f(r0, c), 0.f);
           // rolled over the rows (the body is executed 15 times, which keeps the code small enough
           // to stay in the instruction cache): rows 1..7 see columns j < i <= 7, rows 8..15 see
           // columns 0..7 unconditionally and columns 8..14 while j < i
@@ -458,18 +458,18 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
           for (int i = 1; i < 8; ++i) {
             float sb, sq;
             diag_row<0, 7>(i, LAM[(r0 + i) * LP + c] * DN_LOG2E, lam, kh, sk, DG4 + (r0 + i) * 4, DG4 + 512 + (r0 + i) * 4, bc[i * CP], qc[i * CP], sb, sq);
-            DBP[p4f(r0 + i, c)] = sb;
-            DQP[p4f(r0 + i, c)] = sq;
+            umma::st_keep1(DBP + p4f(r0 + i, c), sb);
+            umma::st_keep1(DQP + p4f(r0 + i, c), sq);
           }
 #pragma unroll 1
           for (int i = 8; i < 16; ++i) {
             float sb, sq;
             diag_row<8, 7>(i, LAM[(r0 + i) * LP + c] * DN_LOG2E, lam, kh, sk, DG4 + (r0 + i) * 4, DG4 + 512 + (r0 + i) * 4, bc[i * CP], qc[i * CP], sb, sq);
-            DBP[p4f(r0 + i, c)] = sb;
-            DQP[p4f(r0 + i, c)] = sq;
+            umma::st_keep1(DBP + p4f(r0 + i, c), sb);
+            umma::st_keep1(DQP + p4f(r0 + i, c), sq);
           }
 #pragma unroll
-          for (int j = 0; j < 16; ++j) DKP[p4f(r0 + j, c)] = sk[j];
+          for (int j = 0; j < 16; ++j) umma::st_keep1(DKP + p4f(r0 + j, c), sk[j]);
         }
         DN_MARK(21 + 3 * half);
         __syncthreads();
@@ -491,8 +491,8 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
           const int e = (2 * half + u) * NT + tid, p = e >> 7, x = e & 127;
           const int bi = x >> 4, bj = p >> 1;
           own[u] = bj < bi && owner_level(bi, bj) == lv;
-          a0[u] = umma::ldcg_pred(DA4 + p4v(x, 8 * p), own[u]); a1[u] = umma::ldcg_pred(DA4 + p4v(x, 8 * p + 4), own[u]);
-          m0[u] = umma::ldcg_pred(DM4 + p4v(x, 8 * p), own[u]); m1[u] = umma::ldcg_pred(DM4 + p4v(x, 8 * p + 4), own[u]);
+          a0[u] = umma::ld_keep4_pred(DA4 + p4v(x, 8 * p), own[u]); a1[u] = umma::ld_keep4_pred(DA4 + p4v(x, 8 * p + 4), own[u]);
+          m0[u] = umma::ld_keep4_pred(DM4 + p4v(x, 8 * p), own[u]); m1[u] = umma::ld_keep4_pred(DM4 + p4v(x, 8 * p + 4), own[u]);
         }
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
@@ -540,7 +540,7 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
         const int col = group * 32 + cc;
         float4 ob[4], oq[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) { ob[i] = __ldcg(pb + p4v(x, col + 4 * i)); oq[i] = umma::ldcg_pred(DQP4 + p4v(x, col + 4 * i), lower); }
+        for (int i = 0; i < 4; ++i) { ob[i] = umma::ld_keep4(pb + p4v(x, col + 4 * i)); oq[i] = umma::ld_keep4_pred(DQP4 + p4v(x, col + 4 * i), lower); }
         float t1[16], t2[16];
         if (!cx.dead) {
           umma::tmem_ld16(tbase + col, t1);
@@ -560,8 +560,8 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
           ob[i].z = fmaf(t1[4 * i + 2], f[4 * i + 2], ob[i].z); ob[i].w = fmaf(t1[4 * i + 3], f[4 * i + 3], ob[i].w);
           oq[i].x = fmaf(t2[4 * i], f[4 * i], oq[i].x); oq[i].y = fmaf(t2[4 * i + 1], f[4 * i + 1], oq[i].y);
           oq[i].z = fmaf(t2[4 * i + 2], f[4 * i + 2], oq[i].z); oq[i].w = fmaf(t2[4 * i + 3], f[4 * i + 3], oq[i].w);
-          __stcg(pb + p4v(x, col + 4 * i), ob[i]);
-          if (lower) __stcg(DQP4 + p4v(x, col + 4 * i), oq[i]);
+          umma::st_keep4(pb + p4v(x, col + 4 * i), ob[i]);
+          if (lower) umma::st_keep4(DQP4 + p4v(x, col + 4 * i), oq[i]);
         }
       }
       umma::tc_fence_before();
@@ -598,7 +598,7 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
       const int x = myrow, t = t0 + x;
       const bool live = x < r.rows_valid;
       const bool first = seg_s[x] == seg0, last = seg_s[x] == segL;
-      const float dmii = __ldcg(DM + p4f(x, x));
+      const float dmii = umma::ld_keep1(DM + p4f(x, x));
       const float rq = rq_s[x], rk = rk_s[x];
       const size_t tok = (size_t)b * g.L + t;
       const size_t outb = (tok * g.H + h) * r.bC;

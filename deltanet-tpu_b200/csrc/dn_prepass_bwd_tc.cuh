@@ -159,14 +159,14 @@ __device__ __forceinline__ void bwd_gemms_tc(umma::Ctx& cx, uint8_t* img, const 
   ld.load(Z, io.dV, B_KV);                           // dO has been consumed: dV for step 3 travels during the drains
   umma::drain<NT, 128>(cx, 256, [&](int row, int col, const float (&v)[16]) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) DQE4[p4v(row, col + 4 * i)] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+    for (int i = 0; i < 4; ++i) umma::st_keep4(DQE4 + p4v(row, col + 4 * i), make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]));
   });
   umma::drain<NT, 128>(cx, 384, [&](int row, int col, const float (&v)[16]) {
     float m[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) m[i] = (row >= col + i && seg_s[row] == seg_s[col + i]) ? v[i] : 0.f;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) DM4[p4v(row, col + 4 * i)] = make_float4(m[4 * i], m[4 * i + 1], m[4 * i + 2], m[4 * i + 3]);
+    for (int i = 0; i < 4; ++i) umma::st_keep4(DM4 + p4v(row, col + 4 * i), make_float4(m[4 * i], m[4 * i + 1], m[4 * i + 2], m[4 * i + 3]));
   });
 
   DN_MARK(3);
@@ -195,7 +195,7 @@ __device__ __forceinline__ void bwd_gemms_tc(umma::Ctx& cx, uint8_t* img, const 
   ld.load(Y, io.T, B_KK);                             // V_new has been consumed: T for step 5
   umma::drain<NT, 128>(cx, 128, [&](int row, int col, const float (&v)[16]) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) DKE4[p4v(row, col + 4 * i)] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+    for (int i = 0; i < 4; ++i) umma::st_keep4(DKE4 + p4v(row, col + 4 * i), make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]));
   });
 
   DN_MARK(5);
@@ -213,7 +213,7 @@ __device__ __forceinline__ void bwd_gemms_tc(umma::Ctx& cx, uint8_t* img, const 
 #pragma unroll
     for (int i = 0; i < 16; ++i) r[i] = io.trunc ? bf16r(v[i]) : v[i];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) DX4[p4v(row, col + 4 * i)] = make_float4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
+    for (int i = 0; i < 4; ++i) umma::st_keep4(DX4 + p4v(row, col + 4 * i), make_float4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]));
     Y2[(col / 8) * 128 + row] = umma::pack8p(r);
     Y2[(col / 8 + 1) * 128 + row] = umma::pack8p(r + 8);
   });
@@ -235,7 +235,7 @@ __device__ __forceinline__ void bwd_gemms_tc(umma::Ctx& cx, uint8_t* img, const 
 #pragma unroll
     for (int i = 0; i < 16; ++i) m[i] = (row > col + i && seg_s[row] == seg_s[col + i]) ? -v[i] : 0.f;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) DA4[p4v(row, col + 4 * i)] = make_float4(m[4 * i], m[4 * i + 1], m[4 * i + 2], m[4 * i + 3]);
+    for (int i = 0; i < 4; ++i) umma::st_keep4(DA4 + p4v(row, col + 4 * i), make_float4(m[4 * i], m[4 * i + 1], m[4 * i + 2], m[4 * i + 3]));
   });
   __syncthreads();
 }

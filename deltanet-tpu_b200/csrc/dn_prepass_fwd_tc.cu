@@ -262,7 +262,7 @@ __global__ void __launch_bounds__(NT, 1) prepass_fwd_tc_kernel(PrepassFwdArgs a,
           }
         }
         if (lane < 16) {
-          Ag[p4f(ri, r0 + lane)] = arow;
+          umma::st_keep1(Ag + p4f(ri, r0 + lane), arow);
           Mel[rix(true, ri, r0 + lane, C)] = __float2bfloat16_rn(mrow);
         }
       }
@@ -397,7 +397,7 @@ __global__ void __launch_bounds__(NT, 1) prepass_fwd_tc_kernel(PrepassFwdArgs a,
             vm[i] = (same && j <= row) ? f * vm[i] : 0.f;
           }
 #pragma unroll
-          for (int i = 0; i < 4; ++i) __stcg(Ag4 + p4v(row, col + 4 * i), make_float4(va[4 * i], va[4 * i + 1], va[4 * i + 2], va[4 * i + 3]));
+          for (int i = 0; i < 4; ++i) umma::st_keep4(Ag4 + p4v(row, col + 4 * i), make_float4(va[4 * i], va[4 * i + 1], va[4 * i + 2], va[4 * i + 3]));
           Mimg[(col / 8) * 128 + row] = umma::pack8p(vm);
           Mimg[(col / 8 + 1) * 128 + row] = umma::pack8p(vm + 8);
         }
@@ -456,7 +456,7 @@ __global__ void __launch_bounds__(NT, 1) prepass_fwd_tc_kernel(PrepassFwdArgs a,
           vm[i] = keep ? vm[i] : 0.f;
         }
 #pragma unroll
-        for (int i = 0; i < 4; ++i) __stcg(Ag4 + p4v(row, col + 4 * i), make_float4(va[4 * i], va[4 * i + 1], va[4 * i + 2], va[4 * i + 3]));
+        for (int i = 0; i < 4; ++i) umma::st_keep4(Ag4 + p4v(row, col + 4 * i), make_float4(va[4 * i], va[4 * i + 1], va[4 * i + 2], va[4 * i + 3]));
         Mimg[(col / 8) * 128 + row] = umma::pack8p(vm);
         Mimg[(col / 8 + 1) * 128 + row] = umma::pack8p(vm + 8);
       }
@@ -487,7 +487,7 @@ __global__ void __launch_bounds__(NT, 1) prepass_fwd_tc_kernel(PrepassFwdArgs a,
 #pragma unroll 4
       for (int e = tid; e < 32 * C; e += NT) {
         const int q = e >> 7, i = e & 127;
-        As4[i * (AP / 4) + q] = __ldcg(Ag4 + e);
+        As4[i * (AP / 4) + q] = umma::ld_keep4(Ag4 + e);
       }
       for (int e = tid; e < C * AP / 4; e += NT) Ts4[e] = make_float4(0.f, 0.f, 0.f, 0.f);
     }

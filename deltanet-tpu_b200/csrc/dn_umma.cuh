@@ -168,6 +168,44 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int PENDING>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(PENDING) : "memory"); }
 
+// ---- per-CTA scratch that should stay in L2 -----------------------------------------------------
+// Loads and stores of the fp32 scratch a CTA writes and reads back within one work item: through L2 only
+// (no L1), with an evict-last L2 policy, so that the streaming inputs and outputs of the kernel, which
+// are touched once, do not push the scratch out to HBM between its write and its read.
+__device__ __forceinline__ uint64_t keep_policy() {
+  uint64_t p;
+  asm("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ void st_keep4(float4* p, float4 v) {
+  asm volatile("st.global.cg.L2::cache_hint.v4.f32 [%0], {%1,%2,%3,%4}, %5;"
+               ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w), "l"(keep_policy()) : "memory");
+}
+__device__ __forceinline__ void st_keep1(float* p, float v) {
+  asm volatile("st.global.cg.L2::cache_hint.f32 [%0], %1, %2;" ::"l"(p), "f"(v), "l"(keep_policy()) : "memory");
+}
+__device__ __forceinline__ float4 ld_keep4(const float4* p) {
+  float4 v;
+  asm volatile("ld.global.cg.L2::cache_hint.v4.f32 {%0,%1,%2,%3}, [%4], %5;"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p), "l"(keep_policy()) : "memory");
+  return v;
+}
+__device__ __forceinline__ float ld_keep1(const float* p) {
+  float v;
+  asm volatile("ld.global.cg.L2::cache_hint.f32 %0, [%1], %2;" : "=f"(v) : "l"(p), "l"(keep_policy()) : "memory");
+  return v;
+}
+// the same 16-byte load skipped (zeros returned) when `pred` is false: no branch
+__device__ __forceinline__ float4 ld_keep4_pred(const float4* p, bool pred) {
+  float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+  asm volatile(
+      "{\n\t.reg .pred q;\n\t"
+      "setp.ne.b32 q, %5, 0;\n\t"
+      "@q ld.global.cg.L2::cache_hint.v4.f32 {%0, %1, %2, %3}, [%4], %6;\n\t}"
+      : "+f"(v.x), "+f"(v.y), "+f"(v.z), "+f"(v.w) : "l"(p), "r"((int)pred), "l"(keep_policy()) : "memory");
+  return v;
+}
+
 // ---- predicated loads ------------------------------------------------------------------------
 // 16-byte global load through L2 only, skipped (zeros returned) when `pred` is false: no branch, so
 // the loads of an unrolled group stay back to back
