@@ -88,6 +88,7 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
   __shared__ uint32_t tmem_base;
   __shared__ int seg_s[C];
   __shared__ int reset_s[8];                 // per 32-row quarter: a document starts inside it
+  __shared__ uint8_t ds_s[C], de_s[C];       // first / last row of each row's document inside the chunk
   __shared__ float rq_s[C], rk_s[C], dlend_s[K], dlend_b_s[C];     // dlend_b_s: the activated scalar erase gate per row (scalar-gate path)
   const Geo& g = a.g;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -377,6 +378,141 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
       umma::tc_fence_before();
       __syncthreads();
     } else {
+    // ---- Channel-wise decay, moderate in every channel of every document of the chunk (the same test as
+    //      in the forward prepass): D + H collapse to four products as in the scalar case.  With m_c the
+    //      midpoint of a document's cumulative decay and f_ic = e^{Lam_ic - m_c}, all within
+    //      e^{+-FAST_HALF_RANGE},
+    //        dbeta'_i = f_i * sum_j dA_ij (k_j / f_j)          dq'_i = f_i * sum_{j<i} dM_ij (k_j / f_j)
+    //        dk'_j    = (1 / f_j) * sum_i (dA_ij (beta_i f_i) + [i>j] dM_ij (q_i f_i))
+    constexpr float FAST_HALF_RANGE = 32.f;
+    if (tid < C) {                              // first and last row of each row's document inside the chunk
+      const int sx = seg_s[tid];
+      int lo = 0, hi = tid;                     // seg_s is non-decreasing: binary searches
+      while (lo < hi) { const int mid = (lo + hi) >> 1; if (seg_s[mid] < sx) lo = mid + 1; else hi = mid; }
+      ds_s[tid] = (uint8_t)lo;
+      lo = tid; hi = C - 1;
+      while (lo < hi) { const int mid = (lo + hi + 1) >> 1; if (seg_s[mid] > sx) hi = mid - 1; else lo = mid; }
+      de_s[tid] = (uint8_t)lo;
+    }
+    __syncthreads();
+    bool strong = false;
+    if (tid < K) {
+      for (int x = 0; x < C; ++x) {
+        if (de_s[x] != x) continue;             // one test per document: at its last row
+        strong |= 0.5f * (LAM[ds_s[x] * LP + tid] - LAM[x * LP + tid]) > FAST_HALF_RANGE;
+      }
+    }
+    const bool fast = !__syncthreads_or(strong);
+    if (fast) {
+      DN_MARK(8);
+      // log2 of f for (row x, channels 8p..8p+7)
+      auto log2f8 = [&](int x, int p, float (&d)[8]) {
+        const float* lx = LAM + x * LP + 8 * p;
+        const float* ls = LAM + ds_s[x] * LP + 8 * p;
+        const float* le = LAM + de_s[x] * LP + 8 * p;
+        const float4 a0 = *reinterpret_cast<const float4*>(lx), a1 = *reinterpret_cast<const float4*>(lx + 4);
+        const float4 s0 = *reinterpret_cast<const float4*>(ls), s1 = *reinterpret_cast<const float4*>(ls + 4);
+        const float4 e0 = *reinterpret_cast<const float4*>(le), e1 = *reinterpret_cast<const float4*>(le + 4);
+        const float l8[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+        const float m8[8] = {s0.x + e0.x, s0.y + e0.y, s0.z + e0.z, s0.w + e0.w, s1.x + e1.x, s1.y + e1.y, s1.z + e1.z, s1.w + e1.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) d[i] = (l8[i] - 0.5f * m8[i]) * DN_LOG2E;
+      };
+      {
+        const int x = myrow;
+#pragma unroll 2
+        for (int it = 0; it < 4; ++it) {               // images of k / f (slot KR) and q f (slot QK)
+          const int p = it * 4 + lgrp;
+          float qh[8], kh[8], d[8];
+          qhat8(r, x, p, qh);
+          khat8(r, x, p, kh);
+          log2f8(x, p, d);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) { kh[i] *= umma::ex2_fast(-d[i]); qh[i] *= umma::ex2_fast(d[i]); }
+          I_KR[p * 128 + x] = umma::pack8(kh);
+          I_QK[p * 128 + x] = umma::pack8(qh);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {                    // images of dA and of the strictly lower part of dM
+        const int e = u * NT + tid, p = e >> 7, x = e & 127;
+        const bool any = 8 * p < x;
+        const float4 a0 = umma::ld_keep4_pred(DA4 + p4v(x, 8 * p), any), a1 = umma::ld_keep4_pred(DA4 + p4v(x, 8 * p + 4), any);
+        const float4 m0 = umma::ld_keep4_pred(DM4 + p4v(x, 8 * p), any), m1 = umma::ld_keep4_pred(DM4 + p4v(x, 8 * p + 4), any);
+        const float mv[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+        float om[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) om[i] = 8 * p + i < x ? mv[i] : 0.f;
+        I_DA[e] = make_uint4(umma::pack2(a0.x, a0.y), umma::pack2(a0.z, a0.w), umma::pack2(a1.x, a1.y), umma::pack2(a1.z, a1.w));
+        I_DM[e] = umma::pack8(om);
+      }
+      umma::pre_issue_sync();
+      umma::issue<128, false, true>(cx, I_DA, I_KR, C, 0, false);          // dA (k / f)
+      umma::issue<128, false, true>(cx, I_DM, I_KR, C, 128, false);        // dM (k / f)
+      umma::commit_wait(cx);
+      DN_MARK(9);
+      const int fq = warp & 3, fg = warp >> 2, frow = fq * 32 + lane;
+      const uint32_t ftb = cx.tmem + ((uint32_t)(fq * 32) << 16);
+      {
+        // the k / f image has been consumed: beta f takes its slot for the second pair of products
+        const int x = myrow;
+#pragma unroll 2
+        for (int it = 0; it < 4; ++it) {
+          const int p = it * 4 + lgrp;
+          float kh[8], ba[8], d[8];
+          khat8(r, x, p, kh);
+          bact8(r, x, p, ba);
+          log2f8(x, p, d);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) ba[i] = (ba[i] * kh[i]) * umma::ex2_fast(d[i]);
+          I_KR[p * 128 + x] = umma::pack8(ba);
+        }
+      }
+#pragma unroll 1
+      for (int cc = 0; cc < 32; cc += 16) {
+        const int col = fg * 32 + cc;
+        float t1[16], t2[16], d[16];
+        if (!cx.dead) { umma::tmem_ld16(ftb + col, t1); umma::tmem_ld16(ftb + 128 + col, t2); }
+        else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) t1[i] = t2[i] = 0.f;
+        }
+        log2f8(frow, col / 8, *reinterpret_cast<float(*)[8]>(d));
+        log2f8(frow, col / 8 + 1, *reinterpret_cast<float(*)[8]>(d + 8));
+#pragma unroll
+        for (int i = 0; i < 16; ++i) { const float f = umma::ex2_fast(d[i]); t1[i] *= f; t2[i] *= f; }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          umma::st_keep4(DBP4 + p4v(frow, col + 4 * i), make_float4(t1[4 * i], t1[4 * i + 1], t1[4 * i + 2], t1[4 * i + 3]));
+          umma::st_keep4(DQP4 + p4v(frow, col + 4 * i), make_float4(t2[4 * i], t2[4 * i + 1], t2[4 * i + 2], t2[4 * i + 3]));
+        }
+      }
+      umma::tc_fence_before();
+      umma::pre_issue_sync();
+      umma::issue<128, true, true>(cx, I_DA, I_KR, C, 0, false);           // dA^T (beta f)
+      umma::issue<128, true, true>(cx, I_DM, I_QK, C, 0, true);            // + dM^T (q f)
+      umma::commit_wait(cx);
+      DN_MARK(10);
+#pragma unroll 1
+      for (int cc = 0; cc < 32; cc += 16) {
+        const int col = fg * 32 + cc;
+        float t3[16], d[16];
+        if (!cx.dead) umma::tmem_ld16(ftb + col, t3);
+        else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) t3[i] = 0.f;
+        }
+        log2f8(frow, col / 8, *reinterpret_cast<float(*)[8]>(d));
+        log2f8(frow, col / 8 + 1, *reinterpret_cast<float(*)[8]>(d + 8));
+#pragma unroll
+        for (int i = 0; i < 16; ++i) t3[i] *= umma::ex2_fast(-d[i]);
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          umma::st_keep4(DKP4 + p4v(frow, col + 4 * i), make_float4(t3[4 * i], t3[4 * i + 1], t3[4 * i + 2], t3[4 * i + 3]));
+      }
+      umma::tc_fence_before();
+      __syncthreads();
+    } else {
     DN_MARK(8);
     // ---- D. diagonal 16x16 blocks, exact.  The blocks of dA and dM are staged in shared memory
     //         (all lanes of a warp read the same entry), and so are k_hat, q_hat and beta of 64 rows
@@ -583,6 +719,7 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
       }
     }
     __syncthreads();
+    }
     }
 
     DN_MARK(13);

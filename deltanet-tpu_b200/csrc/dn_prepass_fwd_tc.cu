@@ -105,6 +105,7 @@ __global__ void __launch_bounds__(NT, 1) prepass_fwd_tc_kernel(PrepassFwdArgs a,
   __shared__ int seg_s[C];
   __shared__ int reset_s[4];
   __shared__ float rq_s[C], rk_s[C], bsc_s[C];
+  __shared__ uint8_t ds_s[C], de_s[C];                  // first / last row of each row's document inside the chunk
   const Geo& g = a.g;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int myrow = warp * 8 + (lane & 7), lgrp = lane >> 3;
@@ -406,6 +407,120 @@ __global__ void __launch_bounds__(NT, 1) prepass_fwd_tc_kernel(PrepassFwdArgs a,
       __syncthreads();
       DN_MARK(6);
     } else {
+    // ---- Channel-wise decay.  When the decay of every document inside the chunk is moderate in every
+    //      channel, A and M are single Gram products as well: with m_c the midpoint of a document's
+    //      cumulative decay in channel c and f_ic = e^{Lam_ic - m_c},
+    //        A_ij = sum_c (beta_ic f_ic) (k_jc / f_jc),   M_ij = sum_c (q_ic f_ic) (k_jc / f_jc)
+    //      for i, j in one document, and every factor stays within e^{+-FAST_HALF_RANGE}: nothing can
+    //      overflow, and bf16 keeps its relative precision at any magnitude.  Chunks with a stronger decay
+    //      (half range above the bound in some channel of some document) take the hierarchical
+    //      factorisation below, whose factors never exceed 1 whatever the decay.
+    constexpr float FAST_HALF_RANGE = 32.f;
+    if (tid < C) {                              // first and last row of each row's document inside the chunk
+      const int sx = seg_s[tid];
+      int lo = 0, hi = tid;                     // seg_s is non-decreasing: binary searches
+      while (lo < hi) { const int mid = (lo + hi) >> 1; if (seg_s[mid] < sx) lo = mid + 1; else hi = mid; }
+      ds_s[tid] = (uint8_t)lo;
+      lo = tid; hi = C - 1;
+      while (lo < hi) { const int mid = (lo + hi + 1) >> 1; if (seg_s[mid] > sx) hi = mid - 1; else lo = mid; }
+      de_s[tid] = (uint8_t)lo;
+    }
+    __syncthreads();
+    bool strong = false;
+    if (tid < K) {
+      for (int x = 0; x < C; ++x) {
+        if (de_s[x] != x) continue;             // one test per document: at its last row
+        strong |= 0.5f * (LAM[ds_s[x] * LP + tid] - LAM[x * LP + tid]) > FAST_HALF_RANGE;
+      }
+    }
+    const bool fast = !__syncthreads_or(strong);
+    if (fast) {
+      DN_MARK(1);
+      uint4* BT = reinterpret_cast<uint4*>(smraw + OFF_TI);      // third image (beta f); the T image is built later
+      {
+        const int x = myrow;
+        const bool first = seg_s[x] == seg0, last = seg_s[x] == segL;
+        const float* lam_s = LAM + ds_s[x] * LP;
+        const float* lam_e = LAM + de_s[x] * LP;
+#pragma unroll 2
+        for (int it = 0; it < 4; ++it) {
+          const int p = it * 4 + lgrp;
+          float qh[8], kh[8], be[8], lam[8], ls[8], le[8], lend[8], o1[8], o2[8], o3[8];
+          qhat8(r, x, p, qh);
+          khat8(r, x, p, kh);
+          bact8(r, x, p, be);
+          *reinterpret_cast<float4*>(lam) = *reinterpret_cast<const float4*>(LAM + x * LP + 8 * p);
+          *reinterpret_cast<float4*>(lam + 4) = *reinterpret_cast<const float4*>(LAM + x * LP + 8 * p + 4);
+          *reinterpret_cast<float4*>(ls) = *reinterpret_cast<const float4*>(lam_s + 8 * p);
+          *reinterpret_cast<float4*>(ls + 4) = *reinterpret_cast<const float4*>(lam_s + 8 * p + 4);
+          *reinterpret_cast<float4*>(le) = *reinterpret_cast<const float4*>(lam_e + 8 * p);
+          *reinterpret_cast<float4*>(le + 4) = *reinterpret_cast<const float4*>(lam_e + 8 * p + 4);
+          *reinterpret_cast<float4*>(lend) = *reinterpret_cast<const float4*>(LAM + (C - 1) * LP + 8 * p);
+          *reinterpret_cast<float4*>(lend + 4) = *reinterpret_cast<const float4*>(LAM + (C - 1) * LP + 8 * p + 4);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            be[i] *= kh[i];                                             // beta = b_act * k_hat
+            const float d = (lam[i] - 0.5f * (ls[i] + le[i])) * DN_LOG2E;      // log2 f, |d| <= FAST_HALF_RANGE * log2 e
+            const float f = umma::ex2_fast(d), fi = umma::ex2_fast(-d);
+            o1[i] = kh[i] * fi;
+            o2[i] = qh[i] * f;
+            o3[i] = be[i] * f;
+          }
+          KR[p * 128 + x] = umma::pack8(o1);
+          QK[p * 128 + x] = umma::pack8(o2);
+          BT[p * 128 + x] = umma::pack8(o3);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float el = umma::exp_neg(fminf(lam[i], 0.f));
+            o1[i] = first ? qh[i] * el : 0.f;
+            o2[i] = last ? kh[i] * umma::exp_neg(fminf(lend[i] - lam[i], 0.f)) : 0.f;
+            o3[i] = first ? be[i] * el : 0.f;
+          }
+          QEimg[p * 128 + x] = umma::pack8(o1);
+          KEimg[p * 128 + x] = umma::pack8(o2);
+          XI[p * 128 + x] = umma::pack8(o3);
+        }
+        if (tid < K) a.res.lam_end[ibase * K + tid] = LAM[(C - 1) * LP + tid];
+      }
+      DN_MARK(2);
+      umma::pre_issue_sync();
+      umma::issue<128, false, false>(cx, BT, KR, K, 0, false);             // A = (beta f) (k / f)^T
+      umma::issue<128, false, false>(cx, QK, KR, K, 128, false);           // M = (q f) (k / f)^T
+      umma::commit_wait(cx);
+      DN_MARK(3);
+      {
+        const int quarter = warp & 3, group = warp >> 2;
+        const int row = quarter * 32 + lane;
+        const uint32_t tbase = cx.tmem + ((uint32_t)(quarter * 32) << 16);
+        const int srow = seg_s[row];
+#pragma unroll 1
+        for (int cc = 0; cc < 32; cc += 16) {
+          const int col = group * 32 + cc;
+          float va[16], vm[16];
+          if (!cx.dead && col <= quarter * 32 + 31) {    // warp-uniform: a piece wholly above the warp's rows is zeros
+            umma::tmem_ld16(tbase + col, va);
+            umma::tmem_ld16(tbase + 128 + col, vm);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) va[i] = vm[i] = 0.f;
+          }
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const int j = col + i;
+            const bool same = srow == seg_s[j];
+            va[i] = (same && j < row) ? va[i] : 0.f;
+            vm[i] = (same && j <= row) ? vm[i] : 0.f;
+          }
+#pragma unroll
+          for (int i = 0; i < 4; ++i) umma::st_keep4(Ag4 + p4v(row, col + 4 * i), make_float4(va[4 * i], va[4 * i + 1], va[4 * i + 2], va[4 * i + 3]));
+          Mimg[(col / 8) * 128 + row] = umma::pack8p(vm);
+          Mimg[(col / 8 + 1) * 128 + row] = umma::pack8p(vm + 8);
+        }
+        umma::tc_fence_before();
+      }
+      __syncthreads();
+      DN_MARK(6);
+    } else {
     DN_MARK(1);
     if (tm_cache) diag_pass();                 // first: it also fills the tensor-memory operand cache
     xi_pass();
@@ -477,6 +592,7 @@ __global__ void __launch_bounds__(NT, 1) prepass_fwd_tc_kernel(PrepassFwdArgs a,
 
     DN_MARK(6);
     if (!tm_cache) diag_pass();
+    }
     }
 
     DN_MARK(7);

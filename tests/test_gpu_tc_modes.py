@@ -152,6 +152,31 @@ def test_chunk64_uses_tensor_core_tiles(dn):
     assert L.lib().dn_exec_view(s, e) == 0 and (e.chunk, e.NC) == (64, 16)
 
 
+@pytest.mark.parametrize("strength", ["mild", "strong", "mixed", "one_strong_channel"])
+def test_channelwise_decay_strength_paths(dn, strength):
+    """Channel-wise decay on the tensor-core kernels takes one of two routes per chunk: single Gram
+    products around the midpoint of each document's cumulative decay when that decay is moderate in every
+    channel, the hierarchical factorisation otherwise.  Mild decay, strong decay (hundreds of nats per
+    chunk), a sequence whose chunks differ, and a single strongly decaying channel must all match the
+    oracle; documents start inside chunks so that the per-document midpoints are exercised."""
+    B, L, Hk, Hv = 1, 768, 2, 4
+    q, k, v, g, b, w = O.make_inputs(2250, B, L, Hk, Hv, 128, 128, qkv_dtype=torch.bfloat16)
+    if strength == "strong":
+        g = g * 6.0
+    elif strength == "mixed":
+        g = torch.cat([g[:, :384] * 6.0, g[:, 384:] * 0.5], 1)
+    elif strength == "one_strong_channel":
+        g = g.clone()
+        g[..., 17] = g[..., 17] * 8.0 - 1.0
+    seg = torch.zeros(B, L, dtype=torch.int32)
+    seg[0, 100:] = 1
+    seg[0, 130:] = 2
+    seg[0, 600:] = 3
+    kw = dict(chunk_size=128, precision="bf16", qk_l2norm=True, output_final_state=True)
+    compare(lambda t, i: dn.chunk_gdn2(*t, segment_ids=seg.cuda(), **kw),
+            lambda t, i: O.chunk_gdn2(*t, segment_ids=seg, **kw), [q, k, v, g, b, w], tol=BF16_TOL)
+
+
 # ------------------------------------------------------------------ fused prologue, bf16 gates, flags (mode 2)
 def test_fused_prologue_bf16_unaligned(dn):
     """fuse_prologue=True on bf16 q/k/v with an unaligned length (L = 300): pre-activation gates."""
