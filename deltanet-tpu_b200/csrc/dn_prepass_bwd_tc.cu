@@ -395,11 +395,15 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
       de_s[tid] = (uint8_t)lo;
     }
     __syncthreads();
+    // one test per document and channel, at the document's last row: threads (row x, channel quarter)
     bool strong = false;
-    if (tid < K) {
-      for (int x = 0; x < C; ++x) {
-        if (de_s[x] != x) continue;             // one test per document: at its last row
-        strong |= 0.5f * (LAM[ds_s[x] * LP + tid] - LAM[x * LP + tid]) > FAST_HALF_RANGE;
+    {
+      const int x = tid & 127;
+      if (de_s[x] == x) {
+        const float* ls = LAM + ds_s[x] * LP + (tid >> 7) * 32;
+        const float* le = LAM + x * LP + (tid >> 7) * 32;
+#pragma unroll 8
+        for (int c = 0; c < 32; ++c) strong |= 0.5f * (ls[c] - le[c]) > FAST_HALF_RANGE;
       }
     }
     const bool fast = !__syncthreads_or(strong);

@@ -426,11 +426,15 @@ __global__ void __launch_bounds__(NT, 1) prepass_fwd_tc_kernel(PrepassFwdArgs a,
       de_s[tid] = (uint8_t)lo;
     }
     __syncthreads();
+    // one test per document and channel, at the document's last row: threads (row x, channel quarter)
     bool strong = false;
-    if (tid < K) {
-      for (int x = 0; x < C; ++x) {
-        if (de_s[x] != x) continue;             // one test per document: at its last row
-        strong |= 0.5f * (LAM[ds_s[x] * LP + tid] - LAM[x * LP + tid]) > FAST_HALF_RANGE;
+    {
+      const int x = tid & 127;
+      if (de_s[x] == x) {
+        const float* ls = LAM + ds_s[x] * LP + (tid >> 7) * 32;
+        const float* le = LAM + x * LP + (tid >> 7) * 32;
+#pragma unroll 8
+        for (int c = 0; c < 32; ++c) strong |= 0.5f * (ls[c] - le[c]) > FAST_HALF_RANGE;
       }
     }
     const bool fast = !__syncthreads_or(strong);
@@ -596,6 +600,15 @@ __global__ void __launch_bounds__(NT, 1) prepass_fwd_tc_kernel(PrepassFwdArgs a,
     }
 
     DN_MARK(7);
+    // The inverse below works out of shared memory for a while: ask for this item's rows of v and w (read
+    // right after it, for the first time) to be brought into L2 meanwhile.
+    if (tid < r.rows_valid) {
+      const size_t tok = (size_t)b * g.L + t0 + tid;
+      const uint32_t qe = (uint32_t)dt_size(qdt), ge = (uint32_t)dt_size(gdt);
+      umma::prefetch_l2(reinterpret_cast<const uint8_t*>(a.v) + (tok * g.Hv * g.V + (size_t)h * VW) * qe, VW * qe);
+      if (wC == g.V && g.wH == g.Hv)
+        umma::prefetch_l2(reinterpret_cast<const uint8_t*>(a.w) + (tok * g.Hv * g.V + (size_t)h * VW) * ge, VW * ge);
+    }
     // ---- T = (I + A)^-1 in fp32: substitution on the diagonal blocks, then block merges
     {
       float4* As4 = reinterpret_cast<float4*>(As);

@@ -69,6 +69,13 @@ __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.comm
 template <int N>
 __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
 
+// Asks the memory system to bring a contiguous global range into L2 (no destination, nothing to wait
+// for).  Skipped unless address and size are multiples of 16 bytes.
+__device__ __forceinline__ void prefetch_l2(const void* p, uint32_t bytes) {
+  if (((reinterpret_cast<uintptr_t>(p) | bytes) & 15u) == 0 && bytes)
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
+
 // ---- fences ------------------------------------------------------------------------------
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
