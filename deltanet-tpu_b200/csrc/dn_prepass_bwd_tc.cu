@@ -422,19 +422,27 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
 #pragma unroll
         for (int i = 0; i < 8; ++i) d[i] = (l8[i] - 0.5f * m8[i]) * DN_LOG2E;
       };
+      uint4 bt[4];                                     // this thread's pieces of the beta f image, for the second round
       {
         const int x = myrow;
-#pragma unroll 2
+#pragma unroll
         for (int it = 0; it < 4; ++it) {               // images of k / f (slot KR) and q f (slot QK)
           const int p = it * 4 + lgrp;
-          float qh[8], kh[8], d[8];
+          float qh[8], kh[8], ba[8], d[8];
           qhat8(r, x, p, qh);
           khat8(r, x, p, kh);
+          bact8(r, x, p, ba);
           log2f8(x, p, d);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) { kh[i] *= umma::ex2_fast(-d[i]); qh[i] *= umma::ex2_fast(d[i]); }
+          for (int i = 0; i < 8; ++i) {
+            const float f = umma::ex2_fast(d[i]);
+            ba[i] = (ba[i] * kh[i]) * f;
+            kh[i] *= umma::ex2_fast(-d[i]);
+            qh[i] *= f;
+          }
           I_KR[p * 128 + x] = umma::pack8(kh);
           I_QK[p * 128 + x] = umma::pack8(qh);
+          bt[it] = umma::pack8(ba);
         }
       }
 #pragma unroll
@@ -457,21 +465,9 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
       DN_MARK(9);
       const int fq = warp & 3, fg = warp >> 2, frow = fq * 32 + lane;
       const uint32_t ftb = cx.tmem + ((uint32_t)(fq * 32) << 16);
-      {
-        // the k / f image has been consumed: beta f takes its slot for the second pair of products
-        const int x = myrow;
-#pragma unroll 2
-        for (int it = 0; it < 4; ++it) {
-          const int p = it * 4 + lgrp;
-          float kh[8], ba[8], d[8];
-          khat8(r, x, p, kh);
-          bact8(r, x, p, ba);
-          log2f8(x, p, d);
+      // the k / f image has been consumed: beta f takes its slot for the second pair of products
 #pragma unroll
-          for (int i = 0; i < 8; ++i) ba[i] = (ba[i] * kh[i]) * umma::ex2_fast(d[i]);
-          I_KR[p * 128 + x] = umma::pack8(ba);
-        }
-      }
+      for (int it = 0; it < 4; ++it) I_KR[(it * 4 + lgrp) * 128 + myrow] = bt[it];
 #pragma unroll 1
       for (int cc = 0; cc < 32; cc += 16) {
         const int col = fg * 32 + cc;
