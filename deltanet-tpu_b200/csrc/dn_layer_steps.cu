@@ -29,14 +29,6 @@ __device__ __forceinline__ float dsilu(float x) {
   return s * (1.f + x * (1.f - s));
 }
 
-__device__ __forceinline__ void ld8(const void* base, size_t off, int dt, float (&x)[8]) {
-  if (dt == DN_BF16) umma::unpack8(__ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(base) + off)), x);
-  else {
-    const float4 a = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + off));
-    const float4 b = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + off + 4));
-    x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
-  }
-}
 __device__ __forceinline__ void st8(void* base, size_t off, int dt, const float (&v)[8]) {
   if (dt == DN_BF16) *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(base) + off) = umma::pack8(v);
   else {
@@ -58,16 +50,33 @@ struct ProducerArgs {
   float* part;                   // backward: (tiles, D, W+1) partial sums of d w | d bias
 };
 
-// where channel group c0 of token (b,t) goes: pointer and element offset
-__device__ __forceinline__ void route(const ProducerArgs& a, size_t tok, int c0, void*& base, size_t& off) {
-  const int HkK = a.Hk_K, Dv = a.D - 2 * HkK;
-  if (c0 < HkK) { base = a.q; off = tok * HkK + c0; }
-  else if (c0 < 2 * HkK) { base = a.k; off = tok * HkK + (c0 - HkK); }
-  else { base = a.v; off = tok * Dv + (c0 - 2 * HkK); }
-}
+// One row of 8 channels as it was loaded (conversion to fp32 happens when the row is used, so a batch
+// of loads can be issued back to back without holding 8 floats per row).
+template <bool BF16> struct Raw;
+template <> struct Raw<true> {
+  uint4 r;
+  __device__ __forceinline__ void load(const void* base, size_t off) {
+    r = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(base) + off));
+  }
+  __device__ __forceinline__ void get(float (&x)[8]) const { umma::unpack8(r, x); }
+};
+template <> struct Raw<false> {
+  float4 a, b;
+  __device__ __forceinline__ void load(const void* base, size_t off) {
+    const float4* p = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + off);
+    a = __ldg(p); b = __ldg(p + 1);
+  }
+  __device__ __forceinline__ void get(float (&x)[8]) const {
+    x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+  }
+};
 
-template <int W>
+// The token loops below work in batches: all rows (and document ids) of a batch are requested first,
+// then the batch is walked with the stencil window in registers.  A thread therefore has NB (forward:
+// 8) or 2*NB (backward: 4 + 4) 16-byte loads in flight instead of one.
+template <int W, bool BF16>
 __global__ void __launch_bounds__(PT) producer_fwd_kernel(ProducerArgs a) {
+  constexpr int NB = BF16 ? 8 : 4;
   const int c0 = (blockIdx.y * PT + threadIdx.x) * CG;
   if (c0 >= a.D) return;
   const int tiles_per_row = (a.L + TT_FWD - 1) / TT_FWD;
@@ -93,36 +102,54 @@ __global__ void __launch_bounds__(PT) producer_fwd_kernel(ProducerArgs a) {
   for (int h = W - 1; h >= 1; --h) {                 // halo rows t0-h
     const int t = t0 - h, j = W - 1 - h;
     if (t >= 0) {
-      ld8(a.mixed, (row0 + t) * a.D + c0, a.dt, xw[j]);
+      Raw<BF16> r;
+      r.load(a.mixed, (row0 + t) * a.D + c0);
+      r.get(xw[j]);
       sw[j] = a.seg ? __ldg(a.seg + row0 + t) : 0;
     }
   }
   const int t_end = min(t0 + TT_FWD, a.L);
-  for (int t = t0; t < t_end; ++t) {
-    ld8(a.mixed, (row0 + t) * a.D + c0, a.dt, xw[W - 1]);
-    const int s = a.seg ? __ldg(a.seg + row0 + t) : 0;
-    sw[W - 1] = s;
-    float y[CG];
+  const int HkK = a.Hk_K, Dv = a.D - 2 * HkK;
+  // where this thread's channels go: q, k or v, each token-major
+  char* obase; size_t ostride, ooff;
+  if (c0 < HkK) { obase = (char*)a.q; ostride = HkK; ooff = c0; }
+  else if (c0 < 2 * HkK) { obase = (char*)a.k; ostride = HkK; ooff = c0 - HkK; }
+  else { obase = (char*)a.v; ostride = Dv; ooff = c0 - 2 * HkK; }
+  for (int tb = t0; tb < t_end; tb += NB) {
+    Raw<BF16> raw[NB];
+    int sg[NB];
 #pragma unroll
-    for (int i = 0; i < CG; ++i) y[i] = bs[i];
-#pragma unroll
-    for (int j = 0; j < MAXW; ++j) {
-      if (j < W && sw[j] == s) {
-#pragma unroll
-        for (int i = 0; i < CG; ++i) y[i] = fmaf(wt[j][i], xw[j][i], y[i]);
-      }
+    for (int n = 0; n < NB; ++n) {                   // rows past the end read the last row and are not stored
+      const int t = min(tb + n, a.L - 1);
+      raw[n].load(a.mixed, (row0 + t) * a.D + c0);
+      sg[n] = a.seg ? __ldg(a.seg + row0 + t) : 0;
     }
 #pragma unroll
-    for (int i = 0; i < CG; ++i) y[i] = silu(y[i]);
-    void* base; size_t off;
-    route(a, row0 + t, c0, base, off);
-    st8(base, off, a.dt, y);
+    for (int n = 0; n < NB; ++n) {
+      const int t = tb + n;
+      raw[n].get(xw[W - 1]);
+      const int s = sg[n];
+      sw[W - 1] = s;
+      float y[CG];
 #pragma unroll
-    for (int j = 0; j + 1 < MAXW; ++j) {
-      if (j + 1 < W) {
-        sw[j] = sw[j + 1];
+      for (int i = 0; i < CG; ++i) y[i] = bs[i];
 #pragma unroll
-        for (int i = 0; i < CG; ++i) xw[j][i] = xw[j + 1][i];
+      for (int j = 0; j < MAXW; ++j) {
+        if (j < W && sw[j] == s) {
+#pragma unroll
+          for (int i = 0; i < CG; ++i) y[i] = fmaf(wt[j][i], xw[j][i], y[i]);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < CG; ++i) y[i] = silu(y[i]);
+      if (t < t_end) st8(obase, (row0 + t) * ostride + ooff, BF16 ? DN_BF16 : DN_F32, y);
+#pragma unroll
+      for (int j = 0; j + 1 < MAXW; ++j) {
+        if (j + 1 < W) {
+          sw[j] = sw[j + 1];
+#pragma unroll
+          for (int i = 0; i < CG; ++i) xw[j][i] = xw[j + 1][i];
+        }
       }
     }
   }
@@ -133,8 +160,9 @@ __global__ void __launch_bounds__(PT) producer_fwd_kernel(ProducerArgs a) {
 //   d x[s]    = sum_j w[j] * dpre[s + (W-1-j)]      (taps inside the same document)
 //   d w[j]   += dpre[u] * x[u - (W-1) + j],   d bias += dpre[u]    (u inside this run)
 // The loop walks u over the run plus W-1 rows of look-ahead and emits d x with a lag of W-1.
-template <int W>
+template <int W, bool BF16>
 __global__ void __launch_bounds__(PT) producer_bwd_kernel(ProducerArgs a) {
+  constexpr int NB = 4;
   const int c0 = (blockIdx.y * PT + threadIdx.x) * CG;
   if (c0 >= a.D) return;
   const int tiles_per_row = (a.L + TT_BWD - 1) / TT_BWD;
@@ -159,71 +187,84 @@ __global__ void __launch_bounds__(PT) producer_bwd_kernel(ProducerArgs a) {
   for (int h = W - 1; h >= 1; --h) {
     const int t = t0 - h, j = W - 1 - h;
     if (t >= 0) {
-      ld8(a.mixed, (row0 + t) * a.D + c0, a.dt, xw[j]);
+      Raw<BF16> r;
+      r.load(a.mixed, (row0 + t) * a.D + c0);
+      r.get(xw[j]);
       sw[j] = a.seg ? __ldg(a.seg + row0 + t) : 0;
     }
   }
   const int t_end = min(t0 + TT_BWD, a.L);
   const int u_end = t_end + W - 1;                   // look-ahead rows; rows >= L contribute nothing
-  for (int u = t0; u < u_end; ++u) {
-    const bool live = u < a.L;
-    int s = -2;
-    float dy[CG];
+  const int HkK = a.Hk_K, Dv = a.D - 2 * HkK;
+  const char* gbase; size_t gstride, goff;           // this thread's channels of the cotangent of q, k or v
+  if (c0 < HkK) { gbase = (const char*)a.q; gstride = HkK; goff = c0; }
+  else if (c0 < 2 * HkK) { gbase = (const char*)a.k; gstride = HkK; goff = c0 - HkK; }
+  else { gbase = (const char*)a.v; gstride = Dv; goff = c0 - 2 * HkK; }
+  for (int ub = t0; ub < u_end; ub += NB) {
+    Raw<BF16> rx[NB], rg[NB];
+    int sg[NB];
 #pragma unroll
-    for (int i = 0; i < CG; ++i) { xw[W - 1][i] = 0.f; dy[i] = 0.f; }
-    if (live) {
-      ld8(a.mixed, (row0 + u) * a.D + c0, a.dt, xw[W - 1]);
-      s = a.seg ? __ldg(a.seg + row0 + u) : 0;
-      void* base; size_t off;
-      route(a, row0 + u, c0, base, off);
-      ld8(base, off, a.dt, dy);
-    }
-    sw[W - 1] = s;
-    float pre[CG];
-#pragma unroll
-    for (int i = 0; i < CG; ++i) pre[i] = bs[i];
-#pragma unroll
-    for (int j = 0; j < MAXW; ++j) {
-      if (j < W && sw[j] == s) {
-#pragma unroll
-        for (int i = 0; i < CG; ++i) pre[i] = fmaf(wt[j][i], xw[j][i], pre[i]);
-      }
+    for (int n = 0; n < NB; ++n) {                   // rows past the end read the last row and count as not live
+      const int u = min(ub + n, a.L - 1);
+      rx[n].load(a.mixed, (row0 + u) * a.D + c0);
+      rg[n].load(gbase, (row0 + u) * gstride + goff);
+      sg[n] = a.seg ? __ldg(a.seg + row0 + u) : 0;
     }
 #pragma unroll
-    for (int i = 0; i < CG; ++i) dp[W - 1][i] = live ? dy[i] * dsilu(pre[i]) : 0.f;
-    if (u < t_end) {                                 // parameter gradients of the rows this run owns
+    for (int n = 0; n < NB; ++n) {
+      const int u = ub + n;
+      const bool live = u < a.L;
+      float dy[CG];
+      rx[n].get(xw[W - 1]);
+      rg[n].get(dy);
+      const int s = live ? sg[n] : -2;
+      sw[W - 1] = s;
+      float pre[CG];
+#pragma unroll
+      for (int i = 0; i < CG; ++i) pre[i] = bs[i];
 #pragma unroll
       for (int j = 0; j < MAXW; ++j) {
         if (j < W && sw[j] == s) {
 #pragma unroll
-          for (int i = 0; i < CG; ++i) dwt[j][i] = fmaf(dp[W - 1][i], xw[j][i], dwt[j][i]);
+          for (int i = 0; i < CG; ++i) pre[i] = fmaf(wt[j][i], xw[j][i], pre[i]);
         }
       }
 #pragma unroll
-      for (int i = 0; i < CG; ++i) dbs[i] += dp[W - 1][i];
-    }
-    // d x of token sx = u - (W-1): output token sx + (W-1-j) used it through tap j; that token sits at window slot W-1-j
-    const int sx = u - (W - 1);
-    if (sx >= t0 && sx < t_end) {
-      float dx[CG];
+      for (int i = 0; i < CG; ++i) dp[W - 1][i] = live ? dy[i] * dsilu(pre[i]) : 0.f;
+      if (u < t_end) {                               // parameter gradients of the rows this run owns
 #pragma unroll
-      for (int i = 0; i < CG; ++i) dx[i] = 0.f;
-      const int s0 = sw[0];                          // document of token sx (slot 0 of the window)
+        for (int j = 0; j < MAXW; ++j) {
+          if (j < W && sw[j] == s) {
 #pragma unroll
-      for (int j = 0; j < MAXW; ++j) {
-        if (j < W && sw[W - 1 - j] == s0) {
-#pragma unroll
-          for (int i = 0; i < CG; ++i) dx[i] = fmaf(wt[j][i], dp[W - 1 - j][i], dx[i]);
+            for (int i = 0; i < CG; ++i) dwt[j][i] = fmaf(dp[W - 1][i], xw[j][i], dwt[j][i]);
+          }
         }
+#pragma unroll
+        for (int i = 0; i < CG; ++i) dbs[i] += dp[W - 1][i];
       }
-      st8(a.d_mixed, (row0 + sx) * a.D + c0, a.dt, dx);
-    }
+      // d x of token sx = u - (W-1): output token sx + (W-1-j) used it through tap j; that token sits at window slot W-1-j
+      const int sx = u - (W - 1);
+      if (sx >= t0 && sx < t_end) {
+        float dx[CG];
 #pragma unroll
-    for (int j = 0; j + 1 < MAXW; ++j) {
-      if (j + 1 < W) {
-        sw[j] = sw[j + 1];
+        for (int i = 0; i < CG; ++i) dx[i] = 0.f;
+        const int s0 = sw[0];                        // document of token sx (slot 0 of the window)
 #pragma unroll
-        for (int i = 0; i < CG; ++i) { xw[j][i] = xw[j + 1][i]; dp[j][i] = dp[j + 1][i]; }
+        for (int j = 0; j < MAXW; ++j) {
+          if (j < W && sw[W - 1 - j] == s0) {
+#pragma unroll
+            for (int i = 0; i < CG; ++i) dx[i] = fmaf(wt[j][i], dp[W - 1 - j][i], dx[i]);
+          }
+        }
+        st8(a.d_mixed, (row0 + sx) * a.D + c0, BF16 ? DN_BF16 : DN_F32, dx);
+      }
+#pragma unroll
+      for (int j = 0; j + 1 < MAXW; ++j) {
+        if (j + 1 < W) {
+          sw[j] = sw[j + 1];
+#pragma unroll
+          for (int i = 0; i < CG; ++i) { xw[j][i] = xw[j + 1][i]; dp[j][i] = dp[j + 1][i]; }
+        }
       }
     }
   }
@@ -327,79 +368,103 @@ __device__ __forceinline__ void st_row(void* base, size_t off, int dt, const flo
   }
 }
 
-template <int EPL>
-__global__ void __launch_bounds__(256) gated_rmsnorm_fwd_kernel(const void* o, const void* z, const float* weight, int dt,
+// A warp takes NR rows per iteration, all loads of the batch first (rows past the end read the last
+// row and are not stored), so NR * 2 (forward) or NR * 3 (backward) loads per lane are in flight.
+template <int EPL, bool BF16>
+__global__ void __launch_bounds__(256) gated_rmsnorm_fwd_kernel(const void* o, const void* z, const float* weight,
                                                                 size_t rows, float eps, void* y, float* rstd) {
-  constexpr int V = EPL * 32;
+  constexpr int V = EPL * 32, NR = 4, dt = BF16 ? DN_BF16 : DN_F32;
   const int lane = threadIdx.x & 31;
   float w[EPL];
 #pragma unroll
   for (int i = 0; i < EPL; ++i) w[i] = __ldg(weight + lane * EPL + i);
-  for (size_t r = (size_t)blockIdx.x * 8 + (threadIdx.x >> 5); r < rows; r += (size_t)gridDim.x * 8) {
-    float x[EPL], zz[EPL], out[EPL];
-    ld_row<EPL>(o, r * V + lane * EPL, dt, x);
-    ld_row<EPL>(z, r * V + lane * EPL, dt, zz);
-    float ss = 0.f;
+  const size_t stride = (size_t)gridDim.x * 8;
+  for (size_t r0 = (size_t)blockIdx.x * 8 + (threadIdx.x >> 5); r0 < rows; r0 += stride * NR) {
+    float x[NR][EPL], zz[NR][EPL];
 #pragma unroll
-    for (int i = 0; i < EPL; ++i) ss = fmaf(x[i], x[i], ss);
-    ss = warp_sum(ss);
-    const float rs = rsqrtf(ss * (1.f / V) + eps);
-#pragma unroll
-    for (int i = 0; i < EPL; ++i) {
-      float n = x[i] * rs;
-      if (dt == DN_BF16) n = bf16r(n);
-      out[i] = w[i] * n * silu(zz[i]);
+    for (int u = 0; u < NR; ++u) {
+      const size_t r = min(r0 + u * stride, rows - 1);
+      ld_row<EPL>(o, r * V + lane * EPL, dt, x[u]);
+      ld_row<EPL>(z, r * V + lane * EPL, dt, zz[u]);
     }
-    st_row<EPL>(y, r * V + lane * EPL, dt, out);
-    if (rstd && lane == 0) rstd[r] = rs;
+#pragma unroll
+    for (int u = 0; u < NR; ++u) {
+      const size_t r = r0 + u * stride;
+      float ss = 0.f, out[EPL];
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) ss = fmaf(x[u][i], x[u][i], ss);
+      ss = warp_sum(ss);
+      const float rs = rsqrtf(ss * (1.f / V) + eps);
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) {
+        float n = x[u][i] * rs;
+        if (BF16) n = bf16r(n);
+        out[i] = w[i] * n * silu(zz[u][i]);
+      }
+      if (r < rows) {
+        st_row<EPL>(y, r * V + lane * EPL, dt, out);
+        if (rstd && lane == 0) rstd[r] = rs;
+      }
+    }
   }
 }
 
-template <int EPL>
-__global__ void __launch_bounds__(256) gated_rmsnorm_bwd_kernel(const void* o, const void* z, const float* weight, int dt,
+template <int EPL, bool BF16>
+__global__ void __launch_bounds__(256) gated_rmsnorm_bwd_kernel(const void* o, const void* z, const float* weight,
                                                                 size_t rows, float eps, const void* dy, void* d_o, void* d_z,
                                                                 float* part) {
-  constexpr int V = EPL * 32;
+  constexpr int V = EPL * 32, NR = 2, dt = BF16 ? DN_BF16 : DN_F32;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   float w[EPL], dwp[EPL];
 #pragma unroll
   for (int i = 0; i < EPL; ++i) { w[i] = __ldg(weight + lane * EPL + i); dwp[i] = 0.f; }
-  for (size_t r = (size_t)blockIdx.x * 8 + warp; r < rows; r += (size_t)gridDim.x * 8) {
-    float x[EPL], zz[EPL], g[EPL], dn_[EPL], n[EPL], dzo[EPL], dxo[EPL];
-    ld_row<EPL>(o, r * V + lane * EPL, dt, x);
-    ld_row<EPL>(z, r * V + lane * EPL, dt, zz);
-    ld_row<EPL>(dy, r * V + lane * EPL, dt, g);
-    float ss = 0.f;
+  const size_t stride = (size_t)gridDim.x * 8;
+  for (size_t r0 = (size_t)blockIdx.x * 8 + warp; r0 < rows; r0 += stride * NR) {
+    float x[NR][EPL], zz[NR][EPL], g[NR][EPL];
 #pragma unroll
-    for (int i = 0; i < EPL; ++i) ss = fmaf(x[i], x[i], ss);
-    ss = warp_sum(ss);
-    const float rs = rsqrtf(ss * (1.f / V) + eps);
-    float dot = 0.f;
-#pragma unroll
-    for (int i = 0; i < EPL; ++i) {
-      n[i] = x[i] * rs;
-      const float nr = dt == DN_BF16 ? bf16r(n[i]) : n[i];
-      const float s = silu(zz[i]);
-      dzo[i] = g[i] * w[i] * nr * dsilu(zz[i]);
-      dn_[i] = g[i] * w[i] * s;
-      dwp[i] = fmaf(g[i] * nr, s, dwp[i]);
-      dot = fmaf(dn_[i], n[i], dot);
+    for (int u = 0; u < NR; ++u) {
+      const size_t r = min(r0 + u * stride, rows - 1);
+      ld_row<EPL>(o, r * V + lane * EPL, dt, x[u]);
+      ld_row<EPL>(z, r * V + lane * EPL, dt, zz[u]);
+      ld_row<EPL>(dy, r * V + lane * EPL, dt, g[u]);
     }
-    dot = warp_sum(dot) * (1.f / V);
 #pragma unroll
-    for (int i = 0; i < EPL; ++i) dxo[i] = rs * (dn_[i] - n[i] * dot);
-    st_row<EPL>(d_o, r * V + lane * EPL, dt, dxo);
-    st_row<EPL>(d_z, r * V + lane * EPL, dt, dzo);
+    for (int u = 0; u < NR; ++u) {                   // rows in ascending order: the weight gradient's order of addition is fixed
+      const size_t r = r0 + u * stride;
+      if (r >= rows) break;
+      float dn_[EPL], n[EPL], dzo[EPL], dxo[EPL];
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) ss = fmaf(x[u][i], x[u][i], ss);
+      ss = warp_sum(ss);
+      const float rs = rsqrtf(ss * (1.f / V) + eps);
+      float dot = 0.f;
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) {
+        n[i] = x[u][i] * rs;
+        const float nr = BF16 ? bf16r(n[i]) : n[i];
+        const float sl = silu(zz[u][i]);
+        dzo[i] = g[u][i] * w[i] * nr * dsilu(zz[u][i]);
+        dn_[i] = g[u][i] * w[i] * sl;
+        dwp[i] = fmaf(g[u][i] * nr, sl, dwp[i]);
+        dot = fmaf(dn_[i], n[i], dot);
+      }
+      dot = warp_sum(dot) * (1.f / V);
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) dxo[i] = rs * (dn_[i] - n[i] * dot);
+      st_row<EPL>(d_o, r * V + lane * EPL, dt, dxo);
+      st_row<EPL>(d_z, r * V + lane * EPL, dt, dzo);
+    }
   }
   __shared__ float red[8][V];
 #pragma unroll
   for (int i = 0; i < EPL; ++i) red[warp][lane * EPL + i] = dwp[i];
   __syncthreads();
   for (int c = threadIdx.x; c < V; c += 256) {
-    float s = 0.f;
+    float sacc = 0.f;
 #pragma unroll
-    for (int k = 0; k < 8; ++k) s += red[k][c];
-    part[(size_t)blockIdx.x * V + c] = s;
+    for (int k = 0; k < 8; ++k) sacc += red[k][c];
+    part[(size_t)blockIdx.x * V + c] = sacc;
   }
 }
 
@@ -441,9 +506,10 @@ int dn_gdn_producer_fwd(const void* mixed, const float* conv_w, const float* con
   a.q = q; a.k = k; a.v = v;
   dim3 grid(B * ((L + TT_FWD - 1) / TT_FWD), (a.D / CG + PT - 1) / PT);
   cudaStream_t st = (cudaStream_t)stream;
-  if (W == 4) producer_fwd_kernel<4><<<grid, PT, 0, st>>>(a);
-  else if (W == 3) producer_fwd_kernel<3><<<grid, PT, 0, st>>>(a);
-  else producer_fwd_kernel<2><<<grid, PT, 0, st>>>(a);
+  const bool bf = dtype == DN_BF16;
+#define DN_GO(WW) (bf ? producer_fwd_kernel<WW, true><<<grid, PT, 0, st>>>(a) : producer_fwd_kernel<WW, false><<<grid, PT, 0, st>>>(a))
+  if (W == 4) DN_GO(4); else if (W == 3) DN_GO(3); else DN_GO(2);
+#undef DN_GO
   return launch_status();
 }
 
@@ -461,9 +527,10 @@ int dn_gdn_producer_bwd(const void* mixed, const float* conv_w, const float* con
   const int tiles = B * ((L + TT_BWD - 1) / TT_BWD);
   dim3 grid(tiles, (a.D / CG + PT - 1) / PT);
   cudaStream_t st = (cudaStream_t)stream;
-  if (W == 4) producer_bwd_kernel<4><<<grid, PT, 0, st>>>(a);
-  else if (W == 3) producer_bwd_kernel<3><<<grid, PT, 0, st>>>(a);
-  else producer_bwd_kernel<2><<<grid, PT, 0, st>>>(a);
+  const bool bf = dtype == DN_BF16;
+#define DN_GO(WW) (bf ? producer_bwd_kernel<WW, true><<<grid, PT, 0, st>>>(a) : producer_bwd_kernel<WW, false><<<grid, PT, 0, st>>>(a))
+  if (W == 4) DN_GO(4); else if (W == 3) DN_GO(3); else DN_GO(2);
+#undef DN_GO
   if ((rc = launch_status())) return rc;
   const size_t n = (size_t)a.D * (W + 1);
   tile_sum_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(a.part, tiles, n, d_conv_w, d_conv_b, W);
@@ -502,8 +569,12 @@ int dn_gated_rmsnorm_fwd(const void* o, const void* z, const float* weight, int6
   if (rows < 1 || (V != 64 && V != 128)) return DN_ERR_BAD_SHAPE;
   if (dtype != DN_F32 && dtype != DN_BF16) return DN_ERR_BAD_DTYPE;
   const int grid = norm_grid((size_t)rows);
-  if (V == 128) gated_rmsnorm_fwd_kernel<4><<<grid, 256, 0, (cudaStream_t)stream>>>(o, z, weight, dtype, (size_t)rows, eps, y, nullptr);
-  else gated_rmsnorm_fwd_kernel<2><<<grid, 256, 0, (cudaStream_t)stream>>>(o, z, weight, dtype, (size_t)rows, eps, y, nullptr);
+  cudaStream_t st = (cudaStream_t)stream;
+  const bool bf = dtype == DN_BF16;
+#define DN_GO(E) (bf ? gated_rmsnorm_fwd_kernel<E, true><<<grid, 256, 0, st>>>(o, z, weight, (size_t)rows, eps, y, nullptr) \
+                     : gated_rmsnorm_fwd_kernel<E, false><<<grid, 256, 0, st>>>(o, z, weight, (size_t)rows, eps, y, nullptr))
+  if (V == 128) DN_GO(4); else DN_GO(2);
+#undef DN_GO
   return launch_status();
 }
 
@@ -517,8 +588,11 @@ int dn_gated_rmsnorm_bwd(const void* o, const void* z, const float* weight, int6
   const int grid = norm_grid((size_t)rows);
   cudaStream_t st = (cudaStream_t)stream;
   float* part = reinterpret_cast<float*>(scratch);
-  if (V == 128) gated_rmsnorm_bwd_kernel<4><<<grid, 256, 0, st>>>(o, z, weight, dtype, (size_t)rows, eps, dy, d_o, d_z, part);
-  else gated_rmsnorm_bwd_kernel<2><<<grid, 256, 0, st>>>(o, z, weight, dtype, (size_t)rows, eps, dy, d_o, d_z, part);
+  const bool bf = dtype == DN_BF16;
+#define DN_GO(E) (bf ? gated_rmsnorm_bwd_kernel<E, true><<<grid, 256, 0, st>>>(o, z, weight, (size_t)rows, eps, dy, d_o, d_z, part) \
+                     : gated_rmsnorm_bwd_kernel<E, false><<<grid, 256, 0, st>>>(o, z, weight, (size_t)rows, eps, dy, d_o, d_z, part))
+  if (V == 128) DN_GO(4); else DN_GO(2);
+#undef DN_GO
   int rc = launch_status();
   if (rc) return rc;
   tile_sum_kernel<<<1, 256, 0, st>>>(part, grid, (size_t)V, d_weight, nullptr, -1);
