@@ -19,6 +19,7 @@ One JSON line is printed by rank 0:
                against the user-visible bytes and FLOPs (`step_*` keys),
   decode       state-stream GB/s of the decode step (value heads sharded over the GPUs),
   layer_steps  the steps either side of the recurrence in a layer (conv+SiLU+split, gated RMSNorm), GB/s each,
+  prefill      Gated DeltaNet packed-document forward prefill (scalar gates, B=4 L=8192, inference mode),
   sp           the long-sequence workload: KDA-style fwd+bwd on ONE packed sequence of 131072
                tokens, chunk_size 64, recompute_states, split into contiguous shards over the
                GPUs (strong scaling; the state chain crosses the ranks by NCCL point-to-point),
@@ -447,6 +448,41 @@ def sp_leg(dn, dist, world, rank, dev, steps=3):
     return out
 
 
+# ------------------------------------------------------------------------------------------ packed prefill
+def prefill_leg(dn, dev):
+    """Gated DeltaNet packed-document forward prefill through the public operator (`chunk_gdn`, is_inference,
+    final state returned): B=4, L=8192, Hk=16, Hv=32, K=V=128, bf16 q/k/v, one fp32 decay and beta per (token,
+    value head), document lengths geometric with mean 1024 clipped to >= 32 (seeded).  Device-resident inputs."""
+    B, L, Hk, Hv, K, V = 4, 8192, 16, 32, 128, 128
+    gen = torch.Generator().manual_seed(6000)
+    seg = torch.empty(B, L, dtype=torch.int32)
+    for b in range(B):
+        t, d = 0, 0
+        while t < L:
+            n = max(32, int(torch.empty(1).geometric_(1.0 / 1024.0, generator=gen)))
+            seg[b, t:t + n] = d
+            t, d = t + n, d + 1
+    g2 = torch.Generator(device=dev).manual_seed(6001)
+    rn = lambda *sh: torch.randn(*sh, generator=g2, device=dev)
+    q, k, v = rn(B, L, Hk, K).bfloat16(), rn(B, L, Hk, K).bfloat16(), rn(B, L, Hv, V).bfloat16()
+    A = 1 + 15 * torch.rand(Hv, generator=g2, device=dev)
+    g = -A * torch.nn.functional.softplus(rn(B, L, Hv) + 0.5 * rn(Hv))
+    beta = torch.sigmoid(rn(B, L, Hv))
+    seg = seg.to(dev)
+    lib = dn._lib.lib()
+    fn = lambda: dn.chunk_gdn(q, k, v, g, beta, segment_ids=seg, is_inference=True, output_final_state=True, qk_l2norm=True)
+    n0 = lib.dn_launches_total()
+    ms, reps = time_steps(fn, 5, 3, min_seconds=0.1)
+    launches = (lib.dn_launches_total() - n0) // (reps * 5 + 3)
+    ms /= 5
+    in_bytes = (q.numel() + k.numel() + v.numel()) * 2 + (g.numel() + beta.numel()) * 4 + seg.numel() * 4
+    out_bytes = v.numel() * 2 + B * Hv * K * V * 4
+    return dict(workload="chunk_gdn forward prefill, is_inference, B=4 L=8192 Hk=16 Hv=32 K=V=128 bf16 qk_l2norm, scalar gates per "
+                         "(token, value head), documents geometric(mean 1024) >= 32 tokens, final state returned",
+                ms_per_step=ms, tokens_per_s=B * L / (ms * 1e-3), user_mbytes=round((in_bytes + out_bytes) / 1e6, 1),
+                user_gbs=(in_bytes + out_bytes) / (ms * 1e-3) / 1e9, kernels_per_step=int(launches))
+
+
 # ------------------------------------------------------------------------------------------ layer steps
 def layer_steps_leg(dn, dev, peaks):
     """The steps either side of the recurrence at the packed-prefill layer shape (B=4, L=8192, Hk=16, Hv=32,
@@ -682,6 +718,8 @@ def main():
     # ---- the layer steps either side of the path (one GPU's worth; rank 0 reports)
     layer = layer_steps_leg(dn, dev, peaks) if rank == 0 else None
     torch.cuda.empty_cache()
+    prefill = prefill_leg(dn, dev) if rank == 0 else None
+    torch.cuda.empty_cache()
 
     # ---- the long-sequence workload, sharded over the ranks
     spr = sp_leg(dn, dist, world, rank, dev)
@@ -706,7 +744,7 @@ def main():
         config=dict(workload=WORKLOAD, global_batch=world, parallelism=f"batch-sharded x{world}, no collective",
                     timing=f"median of {repeats} regions of {args.steps} steps",
                     l2=f"no flush: the step touches {touched_mb:.0f} MB (inputs, residuals, scratch, grads) > 126 MB L2"),
-        roofline=roofline, e2e=e2e, decode=decode, sp=spr, layer_steps=layer, cpu_baseline=cpu,
+        roofline=roofline, e2e=e2e, decode=decode, sp=spr, prefill=prefill, layer_steps=layer, cpu_baseline=cpu,
         gpu_launches=int(launches_per_region), clocks=clocks)
     print(json.dumps(line), flush=True)
     if dist is not None:

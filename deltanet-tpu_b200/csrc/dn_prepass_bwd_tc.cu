@@ -101,7 +101,7 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
   uint4* I_QK = I_KR + IMG;
   float* DLs = reinterpret_cast<float*>(smraw + OFF_IMG);          // dLambda (pitch LP), over the images
   float* DKs = DLs + C * LP;                                        // dke*ke   (pitch LP)
-  float* TOT = reinterpret_cast<float*>(smraw + 3 * C * LP * 4);   // 2 x 4 x 128 partial sums of phase R
+  float* TOT = reinterpret_cast<float*>(smraw + 3 * C * LP * 4);   // 3 x 4 x 128 partial sums of phases E and R
   float* TOTL = reinterpret_cast<float*>(smraw + OFF_IMG);         // 4 x 128 partial sums of phase L
 
   const size_t CK = (size_t)C * K, CV = (size_t)C * VW, CC = (size_t)C * C;
@@ -283,6 +283,9 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
       __syncthreads();
     }
 
+    // where phase E finds dbeta', dq', dk': 0 = fp32 panels in the scratch; 1 = the accumulators T1 | T2 | T3 in tensor
+    // memory, still to be scaled by f, f, 1/f; 2 = the same unscaled
+    int tm_src = 0;
     if constexpr (CF::scalar_gates) {
       // ---- D + H for one scalar decay and one scalar beta per (token, head).  With f_ij = e^{lam_i - lam_j}
       //      (exact, <= 1 on the entries that survive the masks) and b_i the activated erase gate,
@@ -329,23 +332,7 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
       umma::issue<128, false, true>(cx, I_DM, I_KR, C, 128, false);        // (dM f)   k_hat
       umma::commit_wait(cx);
       DN_MARK(9);
-      const int dq_quarter = warp & 3, dq_group = warp >> 2, dq_row = dq_quarter * 32 + lane;
-      const uint32_t dq_tbase = cx.tmem + ((uint32_t)(dq_quarter * 32) << 16);
-#pragma unroll 1
-      for (int cc = 0; cc < 32; cc += 16) {
-        const int col = dq_group * 32 + cc;
-        float t1[16], t2[16];
-        if (!cx.dead) { umma::tmem_ld16(dq_tbase + col, t1); umma::tmem_ld16(dq_tbase + 128 + col, t2); }
-        else {
-#pragma unroll
-          for (int i = 0; i < 16; ++i) t1[i] = t2[i] = 0.f;
-        }
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          umma::st_keep4(DBP4 + p4v(dq_row, col + 4 * i), make_float4(t1[4 * i], t1[4 * i + 1], t1[4 * i + 2], t1[4 * i + 3]));
-          umma::st_keep4(DQP4 + p4v(dq_row, col + 4 * i), make_float4(t2[4 * i], t2[4 * i + 1], t2[4 * i + 2], t2[4 * i + 3]));
-        }
-      }
+      // T1, T2 stay in tensor memory (columns [0, 256)): phase E reads them there
       umma::tc_fence_before();
 #pragma unroll
       for (int u = 0; u < 4; ++u) {                    // rows of the dA f image scaled by b_i
@@ -358,23 +345,11 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
         I_DA[e] = umma::pack8(v8);
       }
       umma::pre_issue_sync();
-      umma::issue<128, true, true>(cx, I_DA, I_KR, C, 0, false);           // (dA f b)^T k_hat
-      umma::issue<128, true, true>(cx, I_DM, I_QK, C, 0, true);            // + (dM f)^T q_hat
+      umma::issue<128, true, true>(cx, I_DA, I_KR, C, 256, false);         // (dA f b)^T k_hat
+      umma::issue<128, true, true>(cx, I_DM, I_QK, C, 256, true);          // + (dM f)^T q_hat
       umma::commit_wait(cx);
       DN_MARK(10);
-#pragma unroll 1
-      for (int cc = 0; cc < 32; cc += 16) {
-        const int col = dq_group * 32 + cc;
-        float t3[16];
-        if (!cx.dead) umma::tmem_ld16(dq_tbase + col, t3);
-        else {
-#pragma unroll
-          for (int i = 0; i < 16; ++i) t3[i] = 0.f;
-        }
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-          umma::st_keep4(DKP4 + p4v(dq_row, col + 4 * i), make_float4(t3[4 * i], t3[4 * i + 1], t3[4 * i + 2], t3[4 * i + 3]));
-      }
+      tm_src = 2;                                      // T3 at columns [256, 384), no scaling
       umma::tc_fence_before();
       __syncthreads();
     } else {
@@ -463,53 +438,17 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
       umma::issue<128, false, true>(cx, I_DM, I_KR, C, 128, false);        // dM (k / f)
       umma::commit_wait(cx);
       DN_MARK(9);
-      const int fq = warp & 3, fg = warp >> 2, frow = fq * 32 + lane;
-      const uint32_t ftb = cx.tmem + ((uint32_t)(fq * 32) << 16);
       // the k / f image has been consumed: beta f takes its slot for the second pair of products
 #pragma unroll
       for (int it = 0; it < 4; ++it) I_KR[(it * 4 + lgrp) * 128 + myrow] = bt[it];
-#pragma unroll 1
-      for (int cc = 0; cc < 32; cc += 16) {
-        const int col = fg * 32 + cc;
-        float t1[16], t2[16], d[16];
-        if (!cx.dead) { umma::tmem_ld16(ftb + col, t1); umma::tmem_ld16(ftb + 128 + col, t2); }
-        else {
-#pragma unroll
-          for (int i = 0; i < 16; ++i) t1[i] = t2[i] = 0.f;
-        }
-        log2f8(frow, col / 8, *reinterpret_cast<float(*)[8]>(d));
-        log2f8(frow, col / 8 + 1, *reinterpret_cast<float(*)[8]>(d + 8));
-#pragma unroll
-        for (int i = 0; i < 16; ++i) { const float f = umma::ex2_fast(d[i]); t1[i] *= f; t2[i] *= f; }
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          umma::st_keep4(DBP4 + p4v(frow, col + 4 * i), make_float4(t1[4 * i], t1[4 * i + 1], t1[4 * i + 2], t1[4 * i + 3]));
-          umma::st_keep4(DQP4 + p4v(frow, col + 4 * i), make_float4(t2[4 * i], t2[4 * i + 1], t2[4 * i + 2], t2[4 * i + 3]));
-        }
-      }
+      // f T1 = dbeta', f T2 = dq' are read from tensor memory by phase E (columns [0, 256))
       umma::tc_fence_before();
       umma::pre_issue_sync();
-      umma::issue<128, true, true>(cx, I_DA, I_KR, C, 0, false);           // dA^T (beta f)
-      umma::issue<128, true, true>(cx, I_DM, I_QK, C, 0, true);            // + dM^T (q f)
+      umma::issue<128, true, true>(cx, I_DA, I_KR, C, 256, false);         // dA^T (beta f)
+      umma::issue<128, true, true>(cx, I_DM, I_QK, C, 256, true);          // + dM^T (q f)
       umma::commit_wait(cx);
       DN_MARK(10);
-#pragma unroll 1
-      for (int cc = 0; cc < 32; cc += 16) {
-        const int col = fg * 32 + cc;
-        float t3[16], d[16];
-        if (!cx.dead) umma::tmem_ld16(ftb + col, t3);
-        else {
-#pragma unroll
-          for (int i = 0; i < 16; ++i) t3[i] = 0.f;
-        }
-        log2f8(frow, col / 8, *reinterpret_cast<float(*)[8]>(d));
-        log2f8(frow, col / 8 + 1, *reinterpret_cast<float(*)[8]>(d + 8));
-#pragma unroll
-        for (int i = 0; i < 16; ++i) t3[i] *= umma::ex2_fast(-d[i]);
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-          umma::st_keep4(DKP4 + p4v(frow, col + 4 * i), make_float4(t3[4 * i], t3[4 * i + 1], t3[4 * i + 2], t3[4 * i + 3]));
-      }
+      tm_src = 1;                                      // T3 / f = dk' at columns [256, 384)
       umma::tc_fence_before();
       __syncthreads();
     } else {
@@ -723,36 +662,50 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
     }
 
     DN_MARK(13);
-    // ---- E. combination (8 rows x 4 pieces per warp step; a thread keeps row `myrow`):
-    //         dLambda and dke*ke to shared memory, d b written.  The l2norm adjoint needs each row's
-    //         <q_n, dq_n> and <k_n, dk_n> (partial sums per thread, the four threads of a row sit 8
-    //         lanes apart) before dq, dk can be written: until then a thread parks its d q_n, d k_n,
-    //         q_n, k_n in tensor memory, which is idle in this phase (128 columns per group of four
-    //         warps, the thread's own lane), so nothing goes through global memory twice.
+    // ---- E. combination.  Thread mapping of a tensor-memory drain: warp w owns rows 32 (w % 4) + lane
+    //         and the 32 channels [32 (w / 4), +32), walked in four pieces of 8.  dbeta', dq', dk' come
+    //         straight from the accumulators of the two product rounds when the chunk took a single-Gram
+    //         route (tm_src != 0), else from the scratch panels.  dLambda and dke*ke go to shared memory,
+    //         d b is written.  The l2norm adjoint needs each row's <q_n, dq_n> and <k_n, dk_n>, whose
+    //         four partial sums sit in four warps: they meet in shared memory; until then a thread
+    //         parks its d q_n, d k_n, q_n, k_n in the tensor-memory columns it has just read (and in
+    //         [384, 512)), so nothing goes through global memory twice.
     {
       umma::tc_fence_after();
-      const uint32_t stash = cx.tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)((warp >> 2) * 128);
-      const int x = myrow, t = t0 + x;
+      const int fq = warp & 3, fg = warp >> 2;
+      const uint32_t tb = cx.tmem + ((uint32_t)(fq * 32) << 16) + (uint32_t)(fg * 32);
+      const int x = fq * 32 + lane, t = t0 + x;
       const bool live = x < r.rows_valid;
       const bool first = seg_s[x] == seg0, last = seg_s[x] == segL;
       const float dmii = umma::ld_keep1(DM + p4f(x, x));
       const float rq = rq_s[x], rk = rk_s[x];
       const size_t tok = (size_t)b * g.L + t;
       const size_t outb = (tok * g.H + h) * r.bC;
-      const size_t rowqk = (tok * g.Hk + h / g.qk_div) * K;
       const size_t outqk = (tok * g.H + h) * K;
+      const bool tm_live = tm_src != 0 && !cx.dead;
       float dq_dot = 0.f, dk_dot = 0.f, sb2 = 0.f;
 #pragma unroll 1
       for (int it = 0; it < 4; ++it) {
-        const int p = it * 4 + lgrp;
+        const int p = fg * 4 + it;
         float qr[8], kr[8], ba[8], braw[8], dbp[8], dqp[8], dkp[8], dx[8], dqe[8], dke[8];
         raw_q8(r, x, p, qr);
         raw_k8(r, x, p, kr);
         bact8(r, x, p, ba);
         if (!fuse && guard) raw_gate8(r.b, r.b_row0, r.b_pitch, r.bC, r.gate_dt, live ? x : 0, p, braw);
-        ld2x4(DBP4 + p4v(x, 8 * p), dbp);
-        ld2x4(DQP4 + p4v(x, 8 * p), dqp);
-        ld2x4(DKP4 + p4v(x, 8 * p), dkp);
+        if (tm_src != 0) {
+          if (tm_live) {
+            umma::tmem_ld8(tb + it * 8, dbp);
+            umma::tmem_ld8(tb + 128 + it * 8, dqp);
+            umma::tmem_ld8(tb + 256 + it * 8, dkp);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) dbp[i] = dqp[i] = dkp[i] = 0.f;
+          }
+        } else {
+          ld2x4(DBP4 + p4v(x, 8 * p), dbp);
+          ld2x4(DQP4 + p4v(x, 8 * p), dqp);
+          ld2x4(DKP4 + p4v(x, 8 * p), dkp);
+        }
         ld2x4(DX4 + p4v(x, 8 * p), dx);
         ld2x4(DQE4 + p4v(x, 8 * p), dqe);
         ld2x4(DKE4 + p4v(x, 8 * p), dke);
@@ -761,6 +714,19 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
         *reinterpret_cast<float4*>(lam + 4) = *reinterpret_cast<const float4*>(LAM + x * LP + 8 * p + 4);
         *reinterpret_cast<float4*>(lend) = *reinterpret_cast<const float4*>(LAM + (C - 1) * LP + 8 * p);
         *reinterpret_cast<float4*>(lend + 4) = *reinterpret_cast<const float4*>(LAM + (C - 1) * LP + 8 * p + 4);
+        if (tm_src == 1) {                                       // f = e^{Lambda - the document's midpoint}
+          const float* ls = LAM + ds_s[x] * LP + 8 * p;
+          const float* le = LAM + de_s[x] * LP + 8 * p;
+          const float4 s0 = *reinterpret_cast<const float4*>(ls), s1 = *reinterpret_cast<const float4*>(ls + 4);
+          const float4 e0 = *reinterpret_cast<const float4*>(le), e1 = *reinterpret_cast<const float4*>(le + 4);
+          const float m8[8] = {s0.x + e0.x, s0.y + e0.y, s0.z + e0.z, s0.w + e0.w, s1.x + e1.x, s1.y + e1.y, s1.z + e1.z, s1.w + e1.w};
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float d = (lam[i] - 0.5f * m8[i]) * DN_LOG2E;
+            const float f = umma::ex2_fast(d);
+            dbp[i] *= f; dqp[i] *= f; dkp[i] *= umma::ex2_fast(-d);
+          }
+        }
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           float qh = (qr[i] * rq) * r.scale, kh = kr[i];
@@ -786,32 +752,34 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
           dq_dot = fmaf(qr[i], dqp[i], dq_dot);
           dk_dot = fmaf(kr[i], dkp[i], dk_dot);
         }
-        umma::tmem_st8(stash + it * 32, dqp);
-        umma::tmem_st8(stash + it * 32 + 8, dkp);
-        umma::tmem_st8(stash + it * 32 + 16, qr);
-        umma::tmem_st8(stash + it * 32 + 24, kr);
+        umma::tmem_st8(tb + 128 + it * 8, dqp);
+        umma::tmem_st8(tb + 256 + it * 8, dkp);
+        umma::tmem_st8(tb + it * 8, qr);
+        umma::tmem_st8(tb + 384 + it * 8, kr);
         *reinterpret_cast<float4*>(DLs + x * LP + 8 * p) = make_float4(odl[0], odl[1], odl[2], odl[3]);
         *reinterpret_cast<float4*>(DLs + x * LP + 8 * p + 4) = make_float4(odl[4], odl[5], odl[6], odl[7]);
         *reinterpret_cast<float4*>(DKs + x * LP + 8 * p) = make_float4(odk[0], odk[1], odk[2], odk[3]);
         *reinterpret_cast<float4*>(DKs + x * LP + 8 * p + 4) = make_float4(odk[4], odk[5], odk[6], odk[7]);
         if (live && r.bC != 1) out8(a.db, outb + 8 * p, a.db_dt, odb);
       }
-      dq_dot += __shfl_xor_sync(0xffffffffu, dq_dot, 8);  dk_dot += __shfl_xor_sync(0xffffffffu, dk_dot, 8);
-      dq_dot += __shfl_xor_sync(0xffffffffu, dq_dot, 16); dk_dot += __shfl_xor_sync(0xffffffffu, dk_dot, 16);
-      if (r.bC == 1) {
-        sb2 += __shfl_xor_sync(0xffffffffu, sb2, 8);
-        sb2 += __shfl_xor_sync(0xffffffffu, sb2, 16);
-        if (live && lgrp == 0) stf(a.db, outb, sb2, a.db_dt);
-      }
+      // the four channel groups of a row meet here (added in a fixed order)
+      TOT[fg * 128 + x] = dq_dot;
+      TOT[512 + fg * 128 + x] = dk_dot;
+      TOT[1024 + fg * 128 + x] = sb2;
       umma::tmem_wait_st();
+      __syncthreads();
+      dq_dot = (TOT[x] + TOT[128 + x]) + (TOT[256 + x] + TOT[384 + x]);
+      dk_dot = (TOT[512 + x] + TOT[640 + x]) + (TOT[768 + x] + TOT[896 + x]);
+      if (r.bC == 1 && fg == 0 && live)
+        stf(a.db, outb, (TOT[1024 + x] + TOT[1152 + x]) + (TOT[1280 + x] + TOT[1408 + x]), a.db_dt);
 #pragma unroll 2
-      for (int it = 0; it < 4; ++it) {                        // every thread takes part: the loads are warp-wide
-        const int p = it * 4 + lgrp;
+      for (int it = 0; it < 4; ++it) {
+        const int p = fg * 4 + it;
         float qn[8], kn[8], dqn[8], dkn[8];
-        umma::tmem_ld8(stash + it * 32, dqn);
-        umma::tmem_ld8(stash + it * 32 + 8, dkn);
-        umma::tmem_ld8(stash + it * 32 + 16, qn);
-        umma::tmem_ld8(stash + it * 32 + 24, kn);
+        umma::tmem_ld8(tb + 128 + it * 8, dqn);
+        umma::tmem_ld8(tb + 256 + it * 8, dkn);
+        umma::tmem_ld8(tb + it * 8, qn);
+        umma::tmem_ld8(tb + 384 + it * 8, kn);
         if (l2) {
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
@@ -825,7 +793,6 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
         }
       }
       umma::tc_fence_before();
-      (void)rowqk;
     }
     __syncthreads();
 
@@ -945,7 +912,7 @@ int launch_prepass_bwd_tc(PrepassBwdArgs& a, size_t scratch_floats, cudaStream_t
   const size_t lam_phase = (size_t)C * LP * 4 + 4 * 32768;
   size_t smem = bwd_tc_image_bytes(g.Vw);
   if (smem < lam_phase) smem = lam_phase;
-  if (smem < (size_t)3 * C * LP * 4 + 4096) smem = (size_t)3 * C * LP * 4 + 4096;
+  if (smem < (size_t)3 * C * LP * 4 + 6144) smem = (size_t)3 * C * LP * 4 + 6144;
   auto go = [&](auto kernel) {
     cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     kernel<<<grid, NT, smem, st>>>(a);
