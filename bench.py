@@ -27,7 +27,7 @@ One JSON line is printed by rank 0:
 
 `--impl reference` times the CPU oracle on the same workload instead (the reference itself
 needs an array library that is not installed on the box; the oracle restates its chunked
-algorithm).  `--only chunk|decode|sp` run one leg (profiling aid).
+algorithm).  `--only chunk|decode|sp|layer` run one leg (profiling aid).
 """
 from __future__ import annotations
 
@@ -609,8 +609,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--min-seconds", type=float, default=0.5,
                     help="repeat the timed region of K steps until this much time has been measured (0: one region)")
-    ap.add_argument("--only", default="all", choices=["all", "chunk", "decode", "sp"],
-                    help="profiling aid: run only the chunked fwd+bwd device loop, only the decode loop, or only the long-sequence leg")
+    ap.add_argument("--only", default="all", choices=["all", "chunk", "decode", "sp", "layer"],
+                    help="profiling aid: run only the chunked fwd+bwd device loop, only the decode loop, only the long-sequence leg, or only the layer steps")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
@@ -638,6 +638,10 @@ def main():
             print(json.dumps(dict(only="sp", n_gpus=world, **r)), flush=True)
         if dist is not None:
             dist.destroy_process_group()
+        return
+    if args.only == "layer":
+        if rank == 0:
+            print(json.dumps(dict(only="layer", **layer_steps_leg(dn, dev, peaks))), flush=True)
         return
     if args.only == "decode":
         dj = DecodeJob(DEC, dev, seed=3000 + rank, heads=DEC["Hv"] // world)

@@ -50,17 +50,32 @@ struct ProducerArgs {
   float* part;                   // backward: (tiles, D, W+1) partial sums of d w | d bias
 };
 
-// One row of 8 channels as it was loaded (conversion to fp32 happens when the row is used, so a batch
-// of loads can be issued back to back without holding 8 floats per row).
-template <bool BF16> struct Raw;
-template <> struct Raw<true> {
+// sigmoid by one MUFU op (tanh.approx, relative error ~2^-11): used where the result is rounded to bf16 anyway
+__device__ __forceinline__ float sigmoid_fast(float x) {
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * x));
+  return fmaf(0.5f, t, 0.5f);
+}
+template <bool FAST> __device__ __forceinline__ float silu_t(float x) {
+  if (FAST) return x * sigmoid_fast(x);
+  return silu(x);
+}
+template <bool FAST> __device__ __forceinline__ float dsilu_t(float x) {
+  if (FAST) { const float sg = sigmoid_fast(x); return sg * (1.f + x * (1.f - sg)); }
+  return dsilu(x);
+}
+
+// One row of CG (4 or 8) channels as it was loaded (conversion to fp32 happens when the row is used, so a
+// batch of loads can be issued back to back without holding CG floats per row).
+template <bool BF16, int CG_> struct Raw;
+template <> struct Raw<true, 8> {
   uint4 r;
   __device__ __forceinline__ void load(const void* base, size_t off) {
     r = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(base) + off));
   }
   __device__ __forceinline__ void get(float (&x)[8]) const { umma::unpack8(r, x); }
 };
-template <> struct Raw<false> {
+template <> struct Raw<false, 8> {
   float4 a, b;
   __device__ __forceinline__ void load(const void* base, size_t off) {
     const float4* p = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + off);
@@ -70,13 +85,48 @@ template <> struct Raw<false> {
     x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
   }
 };
+template <> struct Raw<true, 4> {
+  uint2 r;
+  __device__ __forceinline__ void load(const void* base, size_t off) {
+    r = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(base) + off));
+  }
+  __device__ __forceinline__ void get(float (&x)[4]) const {
+    x[0] = __uint_as_float(r.x << 16); x[1] = __uint_as_float(r.x & 0xffff0000u);
+    x[2] = __uint_as_float(r.y << 16); x[3] = __uint_as_float(r.y & 0xffff0000u);
+  }
+};
+template <> struct Raw<false, 4> {
+  float4 a;
+  __device__ __forceinline__ void load(const void* base, size_t off) {
+    a = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + off));
+  }
+  __device__ __forceinline__ void get(float (&x)[4]) const { x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; }
+};
+template <> struct Raw<true, 2> {
+  uint32_t r;
+  __device__ __forceinline__ void load(const void* base, size_t off) {
+    r = __ldg(reinterpret_cast<const uint32_t*>(reinterpret_cast<const __nv_bfloat16*>(base) + off));
+  }
+  __device__ __forceinline__ void get(float (&x)[2]) const { x[0] = __uint_as_float(r << 16); x[1] = __uint_as_float(r & 0xffff0000u); }
+};
+template <> struct Raw<false, 2> {
+  float2 a;
+  __device__ __forceinline__ void load(const void* base, size_t off) {
+    a = __ldg(reinterpret_cast<const float2*>(reinterpret_cast<const float*>(base) + off));
+  }
+  __device__ __forceinline__ void get(float (&x)[2]) const { x[0] = a.x; x[1] = a.y; }
+};
+template <bool BF16> __device__ __forceinline__ void st4(void* base, size_t off, const float (&v)[4]) {
+  if (BF16) *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(base) + off) = make_uint2(umma::pack2(v[0], v[1]), umma::pack2(v[2], v[3]));
+  else *reinterpret_cast<float4*>(reinterpret_cast<float*>(base) + off) = make_float4(v[0], v[1], v[2], v[3]);
+}
 
-// The token loops below work in batches: all rows (and document ids) of a batch are requested first,
-// then the batch is walked with the stencil window in registers.  A thread therefore has NB (forward:
-// 8) or 2*NB (backward: 4 + 4) 16-byte loads in flight instead of one.
+// The token loops below work in batches of NB rows with two sets of registers: while batch i is walked
+// with the stencil window in registers, the rows (and document ids) of batch i + 1 are already on
+// their way, so a thread always has NB (forward) or 2 NB (backward) loads in flight.
 template <int W, bool BF16>
-__global__ void __launch_bounds__(PT) producer_fwd_kernel(ProducerArgs a) {
-  constexpr int NB = BF16 ? 8 : 4;
+__global__ void __launch_bounds__(PT, 4) producer_fwd_kernel(ProducerArgs a) {
+  constexpr int NB = 4, NBATCH = TT_FWD / NB;
   const int c0 = (blockIdx.y * PT + threadIdx.x) * CG;
   if (c0 >= a.D) return;
   const int tiles_per_row = (a.L + TT_FWD - 1) / TT_FWD;
@@ -98,37 +148,44 @@ __global__ void __launch_bounds__(PT) producer_fwd_kernel(ProducerArgs a) {
     for (int i = 0; i < CG; ++i) xw[j][i] = 0.f;
   }
   const size_t row0 = (size_t)b * a.L;
+  const int t_end = min(t0 + TT_FWD, a.L);
+  Raw<BF16, CG> raw[2][NB];
+  int sg[2][NB];
+  auto fetch = [&](int tb, int slot) {                 // rows past the end read the last row and are not stored
+#pragma unroll
+    for (int n = 0; n < NB; ++n) {
+      const int t = min(tb + n, a.L - 1);
+      raw[slot][n].load(a.mixed, (row0 + t) * a.D + c0);
+      sg[slot][n] = a.seg ? __ldg(a.seg + row0 + t) : 0;
+    }
+  };
+  fetch(t0, 0);
 #pragma unroll
   for (int h = W - 1; h >= 1; --h) {                 // halo rows t0-h
     const int t = t0 - h, j = W - 1 - h;
     if (t >= 0) {
-      Raw<BF16> r;
+      Raw<BF16, CG> r;
       r.load(a.mixed, (row0 + t) * a.D + c0);
       r.get(xw[j]);
       sw[j] = a.seg ? __ldg(a.seg + row0 + t) : 0;
     }
   }
-  const int t_end = min(t0 + TT_FWD, a.L);
   const int HkK = a.Hk_K, Dv = a.D - 2 * HkK;
   // where this thread's channels go: q, k or v, each token-major
   char* obase; size_t ostride, ooff;
   if (c0 < HkK) { obase = (char*)a.q; ostride = HkK; ooff = c0; }
   else if (c0 < 2 * HkK) { obase = (char*)a.k; ostride = HkK; ooff = c0 - HkK; }
   else { obase = (char*)a.v; ostride = Dv; ooff = c0 - 2 * HkK; }
-  for (int tb = t0; tb < t_end; tb += NB) {
-    Raw<BF16> raw[NB];
-    int sg[NB];
-#pragma unroll
-    for (int n = 0; n < NB; ++n) {                   // rows past the end read the last row and are not stored
-      const int t = min(tb + n, a.L - 1);
-      raw[n].load(a.mixed, (row0 + t) * a.D + c0);
-      sg[n] = a.seg ? __ldg(a.seg + row0 + t) : 0;
-    }
+#pragma unroll 2
+  for (int bi = 0; bi < NBATCH; ++bi) {
+    const int tb = t0 + bi * NB, slot = bi & 1;
+    if (tb >= t_end) break;
+    if (tb + NB < t_end) fetch(tb + NB, slot ^ 1);
 #pragma unroll
     for (int n = 0; n < NB; ++n) {
       const int t = tb + n;
-      raw[n].get(xw[W - 1]);
-      const int s = sg[n];
+      raw[slot][n].get(xw[W - 1]);
+      const int s = sg[slot][n];
       sw[W - 1] = s;
       float y[CG];
 #pragma unroll
@@ -141,7 +198,7 @@ __global__ void __launch_bounds__(PT) producer_fwd_kernel(ProducerArgs a) {
         }
       }
 #pragma unroll
-      for (int i = 0; i < CG; ++i) y[i] = silu(y[i]);
+      for (int i = 0; i < CG; ++i) y[i] = silu_t<BF16>(y[i]);
       if (t < t_end) st8(obase, (row0 + t) * ostride + ooff, BF16 ? DN_BF16 : DN_F32, y);
 #pragma unroll
       for (int j = 0; j + 1 < MAXW; ++j) {
@@ -159,40 +216,33 @@ __global__ void __launch_bounds__(PT) producer_fwd_kernel(ProducerArgs a) {
 // dpre[u] = dy[u] * silu'(pre[u]),
 //   d x[s]    = sum_j w[j] * dpre[s + (W-1-j)]      (taps inside the same document)
 //   d w[j]   += dpre[u] * x[u - (W-1) + j],   d bias += dpre[u]    (u inside this run)
-// The loop walks u over the run plus W-1 rows of look-ahead and emits d x with a lag of W-1.
+// The loop walks u over the run plus W-1 rows of look-ahead and emits d x with a lag of W-1.  A thread
+// owns CB = 4 channels here (the windows of x and dpre and the parameter-gradient accumulators are
+// 10 CB + registers), so that twice as many threads are resident as with 8.
+constexpr int CB = 4;
 template <int W, bool BF16>
-__global__ void __launch_bounds__(PT) producer_bwd_kernel(ProducerArgs a) {
+__global__ void __launch_bounds__(PT, 4) producer_bwd_kernel(ProducerArgs a) {
   constexpr int NB = 4;
-  const int c0 = (blockIdx.y * PT + threadIdx.x) * CG;
+  const int c0 = (blockIdx.y * PT + threadIdx.x) * CB;
   if (c0 >= a.D) return;
   const int tiles_per_row = (a.L + TT_BWD - 1) / TT_BWD;
   const int b = blockIdx.x / tiles_per_row, t0 = (blockIdx.x % tiles_per_row) * TT_BWD;
-  float wt[MAXW][CG], bs[CG], dwt[MAXW][CG], dbs[CG];
+  float wt[MAXW][CB], bs[CB], dwt[MAXW][CB], dbs[CB];
 #pragma unroll
   for (int j = 0; j < MAXW; ++j)
 #pragma unroll
-    for (int i = 0; i < CG; ++i) { wt[j][i] = j < W ? __ldg(a.w + (size_t)(c0 + i) * W + j) : 0.f; dwt[j][i] = 0.f; }
+    for (int i = 0; i < CB; ++i) { wt[j][i] = j < W ? __ldg(a.w + (size_t)(c0 + i) * W + j) : 0.f; dwt[j][i] = 0.f; }
 #pragma unroll
-  for (int i = 0; i < CG; ++i) { bs[i] = a.bias ? __ldg(a.bias + c0 + i) : 0.f; dbs[i] = 0.f; }
-  float xw[MAXW][CG], dp[MAXW][CG];      // xw[j] = x[u-(W-1)+j]; dp[j] = dpre[u-(W-1)+j]
+  for (int i = 0; i < CB; ++i) { bs[i] = a.bias ? __ldg(a.bias + c0 + i) : 0.f; dbs[i] = 0.f; }
+  float xw[MAXW][CB], dp[MAXW][CB];      // xw[j] = x[u-(W-1)+j]; dp[j] = dpre[u-(W-1)+j]
   int sw[MAXW];
 #pragma unroll
   for (int j = 0; j < MAXW; ++j) {
     sw[j] = -1;
 #pragma unroll
-    for (int i = 0; i < CG; ++i) { xw[j][i] = 0.f; dp[j][i] = 0.f; }
+    for (int i = 0; i < CB; ++i) { xw[j][i] = 0.f; dp[j][i] = 0.f; }
   }
   const size_t row0 = (size_t)b * a.L;
-#pragma unroll
-  for (int h = W - 1; h >= 1; --h) {
-    const int t = t0 - h, j = W - 1 - h;
-    if (t >= 0) {
-      Raw<BF16> r;
-      r.load(a.mixed, (row0 + t) * a.D + c0);
-      r.get(xw[j]);
-      sw[j] = a.seg ? __ldg(a.seg + row0 + t) : 0;
-    }
-  }
   const int t_end = min(t0 + TT_BWD, a.L);
   const int u_end = t_end + W - 1;                   // look-ahead rows; rows >= L contribute nothing
   const int HkK = a.Hk_K, Dv = a.D - 2 * HkK;
@@ -200,77 +250,94 @@ __global__ void __launch_bounds__(PT) producer_bwd_kernel(ProducerArgs a) {
   if (c0 < HkK) { gbase = (const char*)a.q; gstride = HkK; goff = c0; }
   else if (c0 < 2 * HkK) { gbase = (const char*)a.k; gstride = HkK; goff = c0 - HkK; }
   else { gbase = (const char*)a.v; gstride = Dv; goff = c0 - 2 * HkK; }
-  for (int ub = t0; ub < u_end; ub += NB) {
-    Raw<BF16> rx[NB], rg[NB];
-    int sg[NB];
+  Raw<BF16, CB> rx[2][NB], rg[2][NB];
+  int sg[2][NB];
+  auto fetch = [&](int ub, int slot) {               // rows past the end read the last row and count as not live
 #pragma unroll
-    for (int n = 0; n < NB; ++n) {                   // rows past the end read the last row and count as not live
+    for (int n = 0; n < NB; ++n) {
       const int u = min(ub + n, a.L - 1);
-      rx[n].load(a.mixed, (row0 + u) * a.D + c0);
-      rg[n].load(gbase, (row0 + u) * gstride + goff);
-      sg[n] = a.seg ? __ldg(a.seg + row0 + u) : 0;
+      rx[slot][n].load(a.mixed, (row0 + u) * a.D + c0);
+      rg[slot][n].load(gbase, (row0 + u) * gstride + goff);
+      sg[slot][n] = a.seg ? __ldg(a.seg + row0 + u) : 0;
     }
+  };
+  fetch(t0, 0);
+#pragma unroll
+  for (int h = W - 1; h >= 1; --h) {
+    const int t = t0 - h, j = W - 1 - h;
+    if (t >= 0) {
+      Raw<BF16, CB> r;
+      r.load(a.mixed, (row0 + t) * a.D + c0);
+      r.get(xw[j]);
+      sw[j] = a.seg ? __ldg(a.seg + row0 + t) : 0;
+    }
+  }
+#pragma unroll 2
+  for (int bi = 0; bi < (TT_BWD + MAXW - 1 + NB - 1) / NB; ++bi) {
+    const int ub = t0 + bi * NB, slot = bi & 1;
+    if (ub >= u_end) break;
+    if (ub + NB < u_end) fetch(ub + NB, slot ^ 1);
 #pragma unroll
     for (int n = 0; n < NB; ++n) {
       const int u = ub + n;
       const bool live = u < a.L;
-      float dy[CG];
-      rx[n].get(xw[W - 1]);
-      rg[n].get(dy);
-      const int s = live ? sg[n] : -2;
+      float dy[CB];
+      rx[slot][n].get(xw[W - 1]);
+      rg[slot][n].get(dy);
+      const int s = live ? sg[slot][n] : -2;
       sw[W - 1] = s;
-      float pre[CG];
+      float pre[CB];
 #pragma unroll
-      for (int i = 0; i < CG; ++i) pre[i] = bs[i];
+      for (int i = 0; i < CB; ++i) pre[i] = bs[i];
 #pragma unroll
       for (int j = 0; j < MAXW; ++j) {
         if (j < W && sw[j] == s) {
 #pragma unroll
-          for (int i = 0; i < CG; ++i) pre[i] = fmaf(wt[j][i], xw[j][i], pre[i]);
+          for (int i = 0; i < CB; ++i) pre[i] = fmaf(wt[j][i], xw[j][i], pre[i]);
         }
       }
 #pragma unroll
-      for (int i = 0; i < CG; ++i) dp[W - 1][i] = live ? dy[i] * dsilu(pre[i]) : 0.f;
+      for (int i = 0; i < CB; ++i) dp[W - 1][i] = live ? dy[i] * dsilu_t<BF16>(pre[i]) : 0.f;
       if (u < t_end) {                               // parameter gradients of the rows this run owns
 #pragma unroll
         for (int j = 0; j < MAXW; ++j) {
           if (j < W && sw[j] == s) {
 #pragma unroll
-            for (int i = 0; i < CG; ++i) dwt[j][i] = fmaf(dp[W - 1][i], xw[j][i], dwt[j][i]);
+            for (int i = 0; i < CB; ++i) dwt[j][i] = fmaf(dp[W - 1][i], xw[j][i], dwt[j][i]);
           }
         }
 #pragma unroll
-        for (int i = 0; i < CG; ++i) dbs[i] += dp[W - 1][i];
+        for (int i = 0; i < CB; ++i) dbs[i] += dp[W - 1][i];
       }
       // d x of token sx = u - (W-1): output token sx + (W-1-j) used it through tap j; that token sits at window slot W-1-j
       const int sx = u - (W - 1);
       if (sx >= t0 && sx < t_end) {
-        float dx[CG];
+        float dx[CB];
 #pragma unroll
-        for (int i = 0; i < CG; ++i) dx[i] = 0.f;
+        for (int i = 0; i < CB; ++i) dx[i] = 0.f;
         const int s0 = sw[0];                        // document of token sx (slot 0 of the window)
 #pragma unroll
         for (int j = 0; j < MAXW; ++j) {
           if (j < W && sw[W - 1 - j] == s0) {
 #pragma unroll
-            for (int i = 0; i < CG; ++i) dx[i] = fmaf(wt[j][i], dp[W - 1 - j][i], dx[i]);
+            for (int i = 0; i < CB; ++i) dx[i] = fmaf(wt[j][i], dp[W - 1 - j][i], dx[i]);
           }
         }
-        st8(a.d_mixed, (row0 + sx) * a.D + c0, BF16 ? DN_BF16 : DN_F32, dx);
+        st4<BF16>(a.d_mixed, (row0 + sx) * a.D + c0, dx);
       }
 #pragma unroll
       for (int j = 0; j + 1 < MAXW; ++j) {
         if (j + 1 < W) {
           sw[j] = sw[j + 1];
 #pragma unroll
-          for (int i = 0; i < CG; ++i) { xw[j][i] = xw[j + 1][i]; dp[j][i] = dp[j + 1][i]; }
+          for (int i = 0; i < CB; ++i) { xw[j][i] = xw[j + 1][i]; dp[j][i] = dp[j + 1][i]; }
         }
       }
     }
   }
   float* p = a.part + ((size_t)blockIdx.x * a.D + c0) * (W + 1);
 #pragma unroll
-  for (int i = 0; i < CG; ++i) {
+  for (int i = 0; i < CB; ++i) {
 #pragma unroll
     for (int j = 0; j < MAXW; ++j)
       if (j < W) p[i * (W + 1) + j] = dwt[j][i];
@@ -368,8 +435,9 @@ __device__ __forceinline__ void st_row(void* base, size_t off, int dt, const flo
   }
 }
 
-// A warp takes NR rows per iteration, all loads of the batch first (rows past the end read the last
-// row and are not stored), so NR * 2 (forward) or NR * 3 (backward) loads per lane are in flight.
+// A warp takes NR rows per batch with two sets of registers: the rows of batch i + 1 are requested
+// before batch i is worked on (rows past the end read the last row and are not stored), so 2 NR
+// (forward) or 3 NR (backward) loads per lane are always in flight.
 template <int EPL, bool BF16>
 __global__ void __launch_bounds__(256) gated_rmsnorm_fwd_kernel(const void* o, const void* z, const float* weight,
                                                                 size_t rows, float eps, void* y, float* rstd) {
@@ -379,27 +447,37 @@ __global__ void __launch_bounds__(256) gated_rmsnorm_fwd_kernel(const void* o, c
 #pragma unroll
   for (int i = 0; i < EPL; ++i) w[i] = __ldg(weight + lane * EPL + i);
   const size_t stride = (size_t)gridDim.x * 8;
-  for (size_t r0 = (size_t)blockIdx.x * 8 + (threadIdx.x >> 5); r0 < rows; r0 += stride * NR) {
-    float x[NR][EPL], zz[NR][EPL];
+  const size_t rbeg = (size_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  Raw<BF16, EPL> rx[2][NR], rz[2][NR];
+  auto fetch = [&](size_t r0, int slot) {
 #pragma unroll
     for (int u = 0; u < NR; ++u) {
       const size_t r = min(r0 + u * stride, rows - 1);
-      ld_row<EPL>(o, r * V + lane * EPL, dt, x[u]);
-      ld_row<EPL>(z, r * V + lane * EPL, dt, zz[u]);
+      rx[slot][u].load(o, r * V + lane * EPL);
+      rz[slot][u].load(z, r * V + lane * EPL);
     }
+  };
+  if (rbeg < rows) fetch(rbeg, 0);
+  int slot = 0;
+#pragma unroll 2
+  for (size_t r0 = rbeg; r0 < rows; r0 += stride * NR, slot ^= 1) {
+    if (r0 + stride * NR < rows) fetch(r0 + stride * NR, slot ^ 1);
 #pragma unroll
     for (int u = 0; u < NR; ++u) {
       const size_t r = r0 + u * stride;
-      float ss = 0.f, out[EPL];
+      float x[EPL], zz[EPL], out[EPL];
+      rx[slot][u].get(x);
+      rz[slot][u].get(zz);
+      float ss = 0.f;
 #pragma unroll
-      for (int i = 0; i < EPL; ++i) ss = fmaf(x[u][i], x[u][i], ss);
+      for (int i = 0; i < EPL; ++i) ss = fmaf(x[i], x[i], ss);
       ss = warp_sum(ss);
       const float rs = rsqrtf(ss * (1.f / V) + eps);
 #pragma unroll
       for (int i = 0; i < EPL; ++i) {
-        float n = x[u][i] * rs;
+        float n = x[i] * rs;
         if (BF16) n = bf16r(n);
-        out[i] = w[i] * n * silu(zz[u][i]);
+        out[i] = w[i] * n * silu_t<BF16>(zz[i]);
       }
       if (r < rows) {
         st_row<EPL>(y, r * V + lane * EPL, dt, out);
@@ -419,34 +497,45 @@ __global__ void __launch_bounds__(256) gated_rmsnorm_bwd_kernel(const void* o, c
 #pragma unroll
   for (int i = 0; i < EPL; ++i) { w[i] = __ldg(weight + lane * EPL + i); dwp[i] = 0.f; }
   const size_t stride = (size_t)gridDim.x * 8;
-  for (size_t r0 = (size_t)blockIdx.x * 8 + warp; r0 < rows; r0 += stride * NR) {
-    float x[NR][EPL], zz[NR][EPL], g[NR][EPL];
+  const size_t rbeg = (size_t)blockIdx.x * 8 + warp;
+  Raw<BF16, EPL> rx[2][NR], rz[2][NR], rg[2][NR];
+  auto fetch = [&](size_t r0, int slot) {
 #pragma unroll
     for (int u = 0; u < NR; ++u) {
       const size_t r = min(r0 + u * stride, rows - 1);
-      ld_row<EPL>(o, r * V + lane * EPL, dt, x[u]);
-      ld_row<EPL>(z, r * V + lane * EPL, dt, zz[u]);
-      ld_row<EPL>(dy, r * V + lane * EPL, dt, g[u]);
+      rx[slot][u].load(o, r * V + lane * EPL);
+      rz[slot][u].load(z, r * V + lane * EPL);
+      rg[slot][u].load(dy, r * V + lane * EPL);
     }
+  };
+  if (rbeg < rows) fetch(rbeg, 0);
+  int slot = 0;
+#pragma unroll 2
+  for (size_t r0 = rbeg; r0 < rows; r0 += stride * NR, slot ^= 1) {
+    if (r0 + stride * NR < rows) fetch(r0 + stride * NR, slot ^ 1);
 #pragma unroll
     for (int u = 0; u < NR; ++u) {                   // rows in ascending order: the weight gradient's order of addition is fixed
       const size_t r = r0 + u * stride;
       if (r >= rows) break;
-      float dn_[EPL], n[EPL], dzo[EPL], dxo[EPL];
+      float x[EPL], zz[EPL], g[EPL], dn_[EPL], n[EPL], dzo[EPL], dxo[EPL];
+      rx[slot][u].get(x);
+      rz[slot][u].get(zz);
+      rg[slot][u].get(g);
       float ss = 0.f;
 #pragma unroll
-      for (int i = 0; i < EPL; ++i) ss = fmaf(x[u][i], x[u][i], ss);
+      for (int i = 0; i < EPL; ++i) ss = fmaf(x[i], x[i], ss);
       ss = warp_sum(ss);
       const float rs = rsqrtf(ss * (1.f / V) + eps);
       float dot = 0.f;
 #pragma unroll
       for (int i = 0; i < EPL; ++i) {
-        n[i] = x[u][i] * rs;
+        n[i] = x[i] * rs;
         const float nr = BF16 ? bf16r(n[i]) : n[i];
-        const float sl = silu(zz[u][i]);
-        dzo[i] = g[u][i] * w[i] * nr * dsilu(zz[u][i]);
-        dn_[i] = g[u][i] * w[i] * sl;
-        dwp[i] = fmaf(g[u][i] * nr, sl, dwp[i]);
+        const float sg = BF16 ? sigmoid_fast(zz[i]) : __frcp_rn(1.f + __expf(-zz[i]));
+        const float sl = zz[i] * sg;
+        dzo[i] = g[i] * w[i] * nr * (sg * (1.f + zz[i] * (1.f - sg)));
+        dn_[i] = g[i] * w[i] * sl;
+        dwp[i] = fmaf(g[i] * nr, sl, dwp[i]);
         dot = fmaf(dn_[i], n[i], dot);
       }
       dot = warp_sum(dot) * (1.f / V);
@@ -468,9 +557,16 @@ __global__ void __launch_bounds__(256) gated_rmsnorm_bwd_kernel(const void* o, c
   }
 }
 
-int norm_grid(size_t rows) {
-  const size_t want = (rows + 7) / 8, cap = (size_t)sm_count() * 8;
+// CTAs of 8 warps that walk the rows with a grid stride: as many as are resident at once (per_sm per SM,
+// from the occupancy of the kernel instance; 8 is the upper bound the scratch is sized for)
+int norm_grid(size_t rows, int per_sm = 8) {
+  const size_t want = (rows + 7) / 8, cap = (size_t)sm_count() * (per_sm < 1 ? 1 : (per_sm > 8 ? 8 : per_sm));
   return (int)(want < cap ? (want ? want : 1) : cap);
+}
+template <typename KernelT> int resident_ctas(KernelT kernel) {
+  int n = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, 256, 0) != cudaSuccess) { cudaGetLastError(); n = 4; }
+  return n;
 }
 
 }  // namespace
@@ -525,7 +621,7 @@ int dn_gdn_producer_bwd(const void* mixed, const float* conv_w, const float* con
   a.q = const_cast<void*>(dq); a.k = const_cast<void*>(dk); a.v = const_cast<void*>(dv);
   a.d_mixed = d_mixed; a.part = reinterpret_cast<float*>(scratch);
   const int tiles = B * ((L + TT_BWD - 1) / TT_BWD);
-  dim3 grid(tiles, (a.D / CG + PT - 1) / PT);
+  dim3 grid(tiles, (a.D / CB + PT - 1) / PT);
   cudaStream_t st = (cudaStream_t)stream;
   const bool bf = dtype == DN_BF16;
 #define DN_GO(WW) (bf ? producer_bwd_kernel<WW, true><<<grid, PT, 0, st>>>(a) : producer_bwd_kernel<WW, false><<<grid, PT, 0, st>>>(a))
@@ -568,13 +664,13 @@ int dn_gated_rmsnorm_fwd(const void* o, const void* z, const float* weight, int6
   if (!o || !z || !weight || !y) return DN_ERR_NULL_POINTER;
   if (rows < 1 || (V != 64 && V != 128)) return DN_ERR_BAD_SHAPE;
   if (dtype != DN_F32 && dtype != DN_BF16) return DN_ERR_BAD_DTYPE;
-  const int grid = norm_grid((size_t)rows);
   cudaStream_t st = (cudaStream_t)stream;
-  const bool bf = dtype == DN_BF16;
-#define DN_GO(E) (bf ? gated_rmsnorm_fwd_kernel<E, true><<<grid, 256, 0, st>>>(o, z, weight, (size_t)rows, eps, y, nullptr) \
-                     : gated_rmsnorm_fwd_kernel<E, false><<<grid, 256, 0, st>>>(o, z, weight, (size_t)rows, eps, y, nullptr))
-  if (V == 128) DN_GO(4); else DN_GO(2);
-#undef DN_GO
+  auto go = [&](auto kernel) {
+    const int grid = norm_grid((size_t)rows, resident_ctas(kernel));
+    kernel<<<grid, 256, 0, st>>>(o, z, weight, (size_t)rows, eps, y, nullptr);
+  };
+  if (dtype == DN_BF16) { if (V == 128) go(gated_rmsnorm_fwd_kernel<4, true>); else go(gated_rmsnorm_fwd_kernel<2, true>); }
+  else { if (V == 128) go(gated_rmsnorm_fwd_kernel<4, false>); else go(gated_rmsnorm_fwd_kernel<2, false>); }
   return launch_status();
 }
 
@@ -585,14 +681,15 @@ int dn_gated_rmsnorm_bwd(const void* o, const void* z, const float* weight, int6
   if (rows < 1 || (V != 64 && V != 128)) return DN_ERR_BAD_SHAPE;
   if (dtype != DN_F32 && dtype != DN_BF16) return DN_ERR_BAD_DTYPE;
   if (scratch_bytes < dn_gated_rmsnorm_scratch_bytes(rows, V)) return DN_ERR_SCRATCH_TOO_SMALL;
-  const int grid = norm_grid((size_t)rows);
   cudaStream_t st = (cudaStream_t)stream;
   float* part = reinterpret_cast<float*>(scratch);
-  const bool bf = dtype == DN_BF16;
-#define DN_GO(E) (bf ? gated_rmsnorm_bwd_kernel<E, true><<<grid, 256, 0, st>>>(o, z, weight, (size_t)rows, eps, dy, d_o, d_z, part) \
-                     : gated_rmsnorm_bwd_kernel<E, false><<<grid, 256, 0, st>>>(o, z, weight, (size_t)rows, eps, dy, d_o, d_z, part))
-  if (V == 128) DN_GO(4); else DN_GO(2);
-#undef DN_GO
+  int grid = 0;
+  auto go = [&](auto kernel) {
+    grid = norm_grid((size_t)rows, resident_ctas(kernel));
+    kernel<<<grid, 256, 0, st>>>(o, z, weight, (size_t)rows, eps, dy, d_o, d_z, part);
+  };
+  if (dtype == DN_BF16) { if (V == 128) go(gated_rmsnorm_bwd_kernel<4, true>); else go(gated_rmsnorm_bwd_kernel<2, true>); }
+  else { if (V == 128) go(gated_rmsnorm_bwd_kernel<4, false>); else go(gated_rmsnorm_bwd_kernel<2, false>); }
   int rc = launch_status();
   if (rc) return rc;
   tile_sum_kernel<<<1, 256, 0, st>>>(part, grid, (size_t)V, d_weight, nullptr, -1);
