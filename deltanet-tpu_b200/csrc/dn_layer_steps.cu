@@ -18,8 +18,8 @@ namespace {
 
 constexpr int CG = 8;            // channels per thread (one 16-byte bf16 vector)
 constexpr int PT = 128;          // threads per CTA of the producer kernels (= 1024 channels)
-constexpr int TT_FWD = 32;       // tokens per thread run, forward
-constexpr int TT_BWD = 128;      // tokens per thread run, backward (also the tile of the weight-gradient partials)
+constexpr int TT_FWD = 64;       // tokens per thread run, forward
+constexpr int TT_BWD = 256;      // tokens per thread run, backward (also the tile of the weight-gradient partials)
 constexpr int MAXW = 4;
 
 __device__ __forceinline__ float silu(float x) { return x * __frcp_rn(1.f + __expf(-x)); }
@@ -121,16 +121,68 @@ template <bool BF16> __device__ __forceinline__ void st4(void* base, size_t off,
   else *reinterpret_cast<float4*>(reinterpret_cast<float*>(base) + off) = make_float4(v[0], v[1], v[2], v[3]);
 }
 
-// The token loops below work in batches of NB rows with two sets of registers: while batch i is walked
-// with the stencil window in registers, the rows (and document ids) of batch i + 1 are already on
-// their way, so a thread always has NB (forward) or 2 NB (backward) loads in flight.
+// The token loops below keep a ring of NS batches of NB rows in shared memory, filled by asynchronous
+// copies (cp.async) that cost no registers: while batch i is walked with the stencil window in registers,
+// the rows of batches i+1 .. i+NS-1 are on their way (12 rows of 16 or 32 bytes per thread).  A thread
+// reads back only the slots it filled itself, so the ring needs no block-wide synchronisation.
+template <int BYTES> __device__ __forceinline__ void cp_async_row(void* dst, const void* src);
+template <> __device__ __forceinline__ void cp_async_row<16>(void* dst, const void* src) { umma::cp_async16(dst, src); }
+template <> __device__ __forceinline__ void cp_async_row<8>(void* dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(umma::smem_u32(dst)), "l"(src) : "memory");
+}
+// CGN channels of one row from the ring: PIECE bytes per copy, pieces of one row PT * PIECE bytes apart
+template <bool BF16, int CGN> __device__ __forceinline__ void ring_get(const uint8_t* slot, float (&x)[CGN]);
+template <> __device__ __forceinline__ void ring_get<true, 8>(const uint8_t* slot, float (&x)[8]) {
+  umma::unpack8(*reinterpret_cast<const uint4*>(slot), x);
+}
+template <> __device__ __forceinline__ void ring_get<false, 8>(const uint8_t* slot, float (&x)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(slot), b = *reinterpret_cast<const float4*>(slot + PT * 16);
+  x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+}
+template <> __device__ __forceinline__ void ring_get<true, 4>(const uint8_t* slot, float (&x)[4]) {
+  const uint2 r = *reinterpret_cast<const uint2*>(slot);
+  x[0] = __uint_as_float(r.x << 16); x[1] = __uint_as_float(r.x & 0xffff0000u);
+  x[2] = __uint_as_float(r.y << 16); x[3] = __uint_as_float(r.y & 0xffff0000u);
+}
+template <> __device__ __forceinline__ void ring_get<false, 4>(const uint8_t* slot, float (&x)[4]) {
+  const float4 a = *reinterpret_cast<const float4*>(slot);
+  x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w;
+}
+
 template <int W, bool BF16>
 __global__ void __launch_bounds__(PT, 4) producer_fwd_kernel(ProducerArgs a) {
-  constexpr int NB = 4, NBATCH = TT_FWD / NB;
-  const int c0 = (blockIdx.y * PT + threadIdx.x) * CG;
-  if (c0 >= a.D) return;
+  constexpr int NB = 4, NS = BF16 ? 4 : 2;           // rows per batch, batches in the ring (32 KB either way)
+  constexpr int ES = BF16 ? 2 : 4, NP = CG * ES / 16;  // element size; 16-byte copies per row and thread
+  __shared__ __align__(16) uint8_t ring[NS * NB * NP * PT * 16];
+  __shared__ int seg_sm[TT_FWD + MAXW];              // document ids of rows t0-(W-1) .. t_end-1 (-1 before the sequence)
+  const int tid = threadIdx.x;
+  const bool active = (blockIdx.y * PT + tid) * CG < a.D;
+  const int c0 = active ? (blockIdx.y * PT + tid) * CG : 0;
   const int tiles_per_row = (a.L + TT_FWD - 1) / TT_FWD;
   const int b = blockIdx.x / tiles_per_row, t0 = (blockIdx.x % tiles_per_row) * TT_FWD;
+  const size_t row0 = (size_t)b * a.L;
+  const int t_end = min(t0 + TT_FWD, a.L);
+  const int nbatch = (t_end - t0 + NB - 1) / NB;
+  const char* src = reinterpret_cast<const char*>(a.mixed);
+  auto fetch = [&](int bi) {                           // rows past the end read the last row and are not stored
+    if (bi < nbatch) {
+#pragma unroll
+      for (int n = 0; n < NB; ++n) {
+        const int t = min(t0 + bi * NB + n, a.L - 1);
+        const char* g = src + ((row0 + t) * a.D + c0) * ES;
+        uint8_t* d = ring + ((size_t)(((bi % NS) * NB + n) * NP) * PT + tid) * 16;
+#pragma unroll
+        for (int h = 0; h < NP; ++h) umma::cp_async16(d + h * PT * 16, g + h * 16);
+      }
+    }
+    umma::cp_async_commit();
+  };
+#pragma unroll
+  for (int bi = 0; bi < NS - 1; ++bi) fetch(bi);
+  for (int i = tid; i < TT_FWD + W - 1; i += PT) {
+    const int t = t0 - (W - 1) + i;
+    seg_sm[i] = t < 0 ? -1 : (a.seg ? __ldg(a.seg + row0 + min(t, a.L - 1)) : 0);
+  }
   float wt[MAXW][CG], bs[CG];
 #pragma unroll
   for (int j = 0; j < MAXW; ++j)
@@ -147,19 +199,7 @@ __global__ void __launch_bounds__(PT, 4) producer_fwd_kernel(ProducerArgs a) {
 #pragma unroll
     for (int i = 0; i < CG; ++i) xw[j][i] = 0.f;
   }
-  const size_t row0 = (size_t)b * a.L;
-  const int t_end = min(t0 + TT_FWD, a.L);
-  Raw<BF16, CG> raw[2][NB];
-  int sg[2][NB];
-  auto fetch = [&](int tb, int slot) {                 // rows past the end read the last row and are not stored
-#pragma unroll
-    for (int n = 0; n < NB; ++n) {
-      const int t = min(tb + n, a.L - 1);
-      raw[slot][n].load(a.mixed, (row0 + t) * a.D + c0);
-      sg[slot][n] = a.seg ? __ldg(a.seg + row0 + t) : 0;
-    }
-  };
-  fetch(t0, 0);
+  __syncthreads();
 #pragma unroll
   for (int h = W - 1; h >= 1; --h) {                 // halo rows t0-h
     const int t = t0 - h, j = W - 1 - h;
@@ -167,7 +207,7 @@ __global__ void __launch_bounds__(PT, 4) producer_fwd_kernel(ProducerArgs a) {
       Raw<BF16, CG> r;
       r.load(a.mixed, (row0 + t) * a.D + c0);
       r.get(xw[j]);
-      sw[j] = a.seg ? __ldg(a.seg + row0 + t) : 0;
+      sw[j] = seg_sm[j];
     }
   }
   const int HkK = a.Hk_K, Dv = a.D - 2 * HkK;
@@ -176,16 +216,15 @@ __global__ void __launch_bounds__(PT, 4) producer_fwd_kernel(ProducerArgs a) {
   if (c0 < HkK) { obase = (char*)a.q; ostride = HkK; ooff = c0; }
   else if (c0 < 2 * HkK) { obase = (char*)a.k; ostride = HkK; ooff = c0 - HkK; }
   else { obase = (char*)a.v; ostride = Dv; ooff = c0 - 2 * HkK; }
-#pragma unroll 2
-  for (int bi = 0; bi < NBATCH; ++bi) {
-    const int tb = t0 + bi * NB, slot = bi & 1;
-    if (tb >= t_end) break;
-    if (tb + NB < t_end) fetch(tb + NB, slot ^ 1);
+#pragma unroll 1
+  for (int bi = 0; bi < nbatch; ++bi) {
+    fetch(bi + NS - 1);
+    umma::cp_async_wait<NS - 1>();
 #pragma unroll
     for (int n = 0; n < NB; ++n) {
-      const int t = tb + n;
-      raw[slot][n].get(xw[W - 1]);
-      const int s = sg[slot][n];
+      const int t = t0 + bi * NB + n;
+      ring_get<BF16, CG>(ring + ((size_t)(((bi % NS) * NB + n) * NP) * PT + tid) * 16, xw[W - 1]);
+      const int s = seg_sm[bi * NB + n + W - 1];
       sw[W - 1] = s;
       float y[CG];
 #pragma unroll
@@ -199,7 +238,7 @@ __global__ void __launch_bounds__(PT, 4) producer_fwd_kernel(ProducerArgs a) {
       }
 #pragma unroll
       for (int i = 0; i < CG; ++i) y[i] = silu_t<BF16>(y[i]);
-      if (t < t_end) st8(obase, (row0 + t) * ostride + ooff, BF16 ? DN_BF16 : DN_F32, y);
+      if (active && t < t_end) st8(obase, (row0 + t) * ostride + ooff, BF16 ? DN_BF16 : DN_F32, y);
 #pragma unroll
       for (int j = 0; j + 1 < MAXW; ++j) {
         if (j + 1 < W) {
@@ -210,6 +249,7 @@ __global__ void __launch_bounds__(PT, 4) producer_fwd_kernel(ProducerArgs a) {
       }
     }
   }
+  umma::cp_async_wait<0>();
 }
 
 // Backward of the producer over one run of TT_BWD tokens: with pre[u] the conv output of token u and
@@ -222,11 +262,43 @@ __global__ void __launch_bounds__(PT, 4) producer_fwd_kernel(ProducerArgs a) {
 constexpr int CB = 4;
 template <int W, bool BF16>
 __global__ void __launch_bounds__(PT, 4) producer_bwd_kernel(ProducerArgs a) {
-  constexpr int NB = 4;
-  const int c0 = (blockIdx.y * PT + threadIdx.x) * CB;
-  if (c0 >= a.D) return;
+  constexpr int NB = 4, NS = BF16 ? 4 : 2;
+  constexpr int ES = BF16 ? 2 : 4, RB = CB * ES;     // bytes per row, thread and tensor: 8 or 16
+  __shared__ __align__(16) uint8_t ring[NS * NB * 2 * PT * RB];       // x rows | cotangent rows
+  __shared__ int seg_sm[TT_BWD + 2 * MAXW];          // document ids of rows t0-(W-1) .. u_end-1 (-1 / -2 outside the sequence)
+  const int tid = threadIdx.x;
+  const bool active = (blockIdx.y * PT + tid) * CB < a.D;
+  const int c0 = active ? (blockIdx.y * PT + tid) * CB : 0;
   const int tiles_per_row = (a.L + TT_BWD - 1) / TT_BWD;
   const int b = blockIdx.x / tiles_per_row, t0 = (blockIdx.x % tiles_per_row) * TT_BWD;
+  const size_t row0 = (size_t)b * a.L;
+  const int t_end = min(t0 + TT_BWD, a.L);
+  const int u_end = t_end + W - 1;                   // look-ahead rows; rows >= L contribute nothing
+  const int nbatch = (u_end - t0 + NB - 1) / NB;
+  const int HkK = a.Hk_K, Dv = a.D - 2 * HkK;
+  const char* gbase; size_t gstride, goff;           // this thread's channels of the cotangent of q, k or v
+  if (c0 < HkK) { gbase = (const char*)a.q; gstride = HkK; goff = c0; }
+  else if (c0 < 2 * HkK) { gbase = (const char*)a.k; gstride = HkK; goff = c0 - HkK; }
+  else { gbase = (const char*)a.v; gstride = Dv; goff = c0 - 2 * HkK; }
+  const char* xsrc = reinterpret_cast<const char*>(a.mixed);
+  auto fetch = [&](int bi) {                         // rows past the end read the last row and count as not live
+    if (bi < nbatch) {
+#pragma unroll
+      for (int n = 0; n < NB; ++n) {
+        const int u = min(t0 + bi * NB + n, a.L - 1);
+        uint8_t* d = ring + ((size_t)(((bi % NS) * NB + n) * 2) * PT + tid) * RB;
+        cp_async_row<RB>(d, xsrc + ((row0 + u) * a.D + c0) * ES);
+        cp_async_row<RB>(d + PT * RB, gbase + ((row0 + u) * gstride + goff) * ES);
+      }
+    }
+    umma::cp_async_commit();
+  };
+#pragma unroll
+  for (int bi = 0; bi < NS - 1; ++bi) fetch(bi);
+  for (int i = tid; i < TT_BWD + 2 * MAXW; i += PT) {
+    const int t = t0 - (W - 1) + i;
+    seg_sm[i] = t < 0 ? -1 : (t >= a.L ? -2 : (a.seg ? __ldg(a.seg + row0 + t) : 0));
+  }
   float wt[MAXW][CB], bs[CB], dwt[MAXW][CB], dbs[CB];
 #pragma unroll
   for (int j = 0; j < MAXW; ++j)
@@ -242,26 +314,7 @@ __global__ void __launch_bounds__(PT, 4) producer_bwd_kernel(ProducerArgs a) {
 #pragma unroll
     for (int i = 0; i < CB; ++i) { xw[j][i] = 0.f; dp[j][i] = 0.f; }
   }
-  const size_t row0 = (size_t)b * a.L;
-  const int t_end = min(t0 + TT_BWD, a.L);
-  const int u_end = t_end + W - 1;                   // look-ahead rows; rows >= L contribute nothing
-  const int HkK = a.Hk_K, Dv = a.D - 2 * HkK;
-  const char* gbase; size_t gstride, goff;           // this thread's channels of the cotangent of q, k or v
-  if (c0 < HkK) { gbase = (const char*)a.q; gstride = HkK; goff = c0; }
-  else if (c0 < 2 * HkK) { gbase = (const char*)a.k; gstride = HkK; goff = c0 - HkK; }
-  else { gbase = (const char*)a.v; gstride = Dv; goff = c0 - 2 * HkK; }
-  Raw<BF16, CB> rx[2][NB], rg[2][NB];
-  int sg[2][NB];
-  auto fetch = [&](int ub, int slot) {               // rows past the end read the last row and count as not live
-#pragma unroll
-    for (int n = 0; n < NB; ++n) {
-      const int u = min(ub + n, a.L - 1);
-      rx[slot][n].load(a.mixed, (row0 + u) * a.D + c0);
-      rg[slot][n].load(gbase, (row0 + u) * gstride + goff);
-      sg[slot][n] = a.seg ? __ldg(a.seg + row0 + u) : 0;
-    }
-  };
-  fetch(t0, 0);
+  __syncthreads();
 #pragma unroll
   for (int h = W - 1; h >= 1; --h) {
     const int t = t0 - h, j = W - 1 - h;
@@ -269,22 +322,22 @@ __global__ void __launch_bounds__(PT, 4) producer_bwd_kernel(ProducerArgs a) {
       Raw<BF16, CB> r;
       r.load(a.mixed, (row0 + t) * a.D + c0);
       r.get(xw[j]);
-      sw[j] = a.seg ? __ldg(a.seg + row0 + t) : 0;
+      sw[j] = seg_sm[j];
     }
   }
-#pragma unroll 2
-  for (int bi = 0; bi < (TT_BWD + MAXW - 1 + NB - 1) / NB; ++bi) {
-    const int ub = t0 + bi * NB, slot = bi & 1;
-    if (ub >= u_end) break;
-    if (ub + NB < u_end) fetch(ub + NB, slot ^ 1);
+#pragma unroll 1
+  for (int bi = 0; bi < nbatch; ++bi) {
+    fetch(bi + NS - 1);
+    umma::cp_async_wait<NS - 1>();
 #pragma unroll
     for (int n = 0; n < NB; ++n) {
-      const int u = ub + n;
+      const int u = t0 + bi * NB + n;
       const bool live = u < a.L;
       float dy[CB];
-      rx[slot][n].get(xw[W - 1]);
-      rg[slot][n].get(dy);
-      const int s = live ? sg[slot][n] : -2;
+      const uint8_t* slot = ring + ((size_t)(((bi % NS) * NB + n) * 2) * PT + tid) * RB;
+      ring_get<BF16, CB>(slot, xw[W - 1]);
+      ring_get<BF16, CB>(slot + PT * RB, dy);
+      const int s = seg_sm[bi * NB + n + W - 1];     // -2 past the end of the sequence: matches no tap
       sw[W - 1] = s;
       float pre[CB];
 #pragma unroll
@@ -323,7 +376,7 @@ __global__ void __launch_bounds__(PT, 4) producer_bwd_kernel(ProducerArgs a) {
             for (int i = 0; i < CB; ++i) dx[i] = fmaf(wt[j][i], dp[W - 1 - j][i], dx[i]);
           }
         }
-        st4<BF16>(a.d_mixed, (row0 + sx) * a.D + c0, dx);
+        if (active) st4<BF16>(a.d_mixed, (row0 + sx) * a.D + c0, dx);
       }
 #pragma unroll
       for (int j = 0; j + 1 < MAXW; ++j) {
@@ -335,6 +388,8 @@ __global__ void __launch_bounds__(PT, 4) producer_bwd_kernel(ProducerArgs a) {
       }
     }
   }
+  umma::cp_async_wait<0>();
+  if (!active) return;
   float* p = a.part + ((size_t)blockIdx.x * a.D + c0) * (W + 1);
 #pragma unroll
   for (int i = 0; i < CB; ++i) {
@@ -345,13 +400,33 @@ __global__ void __launch_bounds__(PT, 4) producer_bwd_kernel(ProducerArgs a) {
   }
 }
 
-// out[e] = sum over tiles of part[tile][e], tiles added in order
+// out[e] = sum over tiles of part[tile][e] in a fixed order: a CTA takes 32 elements; each of its 8 warps
+// adds one eighth of the tiles in ascending order (independent loads, several in flight), and the eight
+// partial sums are added in ascending order.
 __global__ void __launch_bounds__(256) tile_sum_kernel(const float* part, int tiles, size_t n, float* out_a, float* out_b,
                                                        int W) {
-  const size_t e = (size_t)blockIdx.x * 256 + threadIdx.x;
-  if (e >= n) return;
+  __shared__ float red[8][32];
+  const int lane = threadIdx.x & 31, grp = threadIdx.x >> 5;
+  const size_t e = (size_t)blockIdx.x * 32 + lane;
+  const int per = (tiles + 7) / 8, tb = grp * per, te = min(tb + per, tiles);
   float s = 0.f;
-  for (int t = 0; t < tiles; ++t) s += part[(size_t)t * n + e];
+  if (e < n) {
+    int t = tb;
+    for (; t + 8 <= te; t += 8) {
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = __ldg(part + (size_t)(t + u) * n + e);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) s += v[u];
+    }
+    for (; t < te; ++t) s += __ldg(part + (size_t)t * n + e);
+  }
+  red[grp][lane] = s;
+  __syncthreads();
+  if (grp != 0 || e >= n) return;
+  s = red[0][lane];
+#pragma unroll
+  for (int k = 1; k < 8; ++k) s += red[k][lane];
   if (W < 0) { out_a[e] = s; return; }
   const size_t c = e / (W + 1);
   const int j = (int)(e - c * (W + 1));
@@ -629,7 +704,7 @@ int dn_gdn_producer_bwd(const void* mixed, const float* conv_w, const float* con
 #undef DN_GO
   if ((rc = launch_status())) return rc;
   const size_t n = (size_t)a.D * (W + 1);
-  tile_sum_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(a.part, tiles, n, d_conv_w, d_conv_b, W);
+  tile_sum_kernel<<<(unsigned)((n + 31) / 32), 256, 0, st>>>(a.part, tiles, n, d_conv_w, d_conv_b, W);
   return launch_status();
 }
 
@@ -692,7 +767,7 @@ int dn_gated_rmsnorm_bwd(const void* o, const void* z, const float* weight, int6
   else { if (V == 128) go(gated_rmsnorm_bwd_kernel<4, false>); else go(gated_rmsnorm_bwd_kernel<2, false>); }
   int rc = launch_status();
   if (rc) return rc;
-  tile_sum_kernel<<<1, 256, 0, st>>>(part, grid, (size_t)V, d_weight, nullptr, -1);
+  tile_sum_kernel<<<(unsigned)((V + 31) / 32), 256, 0, st>>>(part, grid, (size_t)V, d_weight, nullptr, -1);
   return launch_status();
 }
 
