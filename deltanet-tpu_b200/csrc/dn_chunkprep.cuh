@@ -18,17 +18,21 @@ constexpr int LP = 132;                // row pitch (floats) of the shared-memor
 // in fp32 and already activated (no fused prologue), every gate with one value per channel; MODE 1:
 // the same with q/k/v in fp32; MODE 2: nothing (dtypes, gate widths and the prologue are run-time
 // properties, every load sits behind a branch and both activation paths are compiled in); MODE 3:
-// bf16 q/k/v, fp32 activated gates with ONE value per head (Gated DeltaNet's scalar decay and beta).
+// bf16 q/k/v, fp32 activated gates with ONE value per head (Gated DeltaNet's scalar decay and beta);
+// MODE 4: bf16 q/k/v, fp32 activated gates, the decay per channel and ONE erase / write gate value per head
+// (the KDA layout).
 template <int MODE>
 struct InCfg {
   static constexpr bool fixed = MODE != 2;
-  static constexpr bool scalar_gates = MODE == 3;
+  static constexpr bool scalar_gates = MODE == 3;                 // the decay is one scalar per (token, head)
+  static constexpr bool scalar_bw = MODE == 3 || MODE == 4;       // b and w are
   static constexpr int qkv_dt = MODE == 1 ? DN_F32 : DN_BF16;
 };
 inline int input_mode(const Geo& g) {
   if (g.gate_dt != DN_F32 || (g.flags & (DN_FUSE_PROLOGUE | DN_STABILITY_GUARD))) return 2;
   if (g.gC == g.K && g.bC == g.K && g.wC == g.V) return g.qkv_dt == DN_BF16 ? 0 : 1;
   if (g.gC == 1 && g.bC == 1 && g.wC == 1 && g.qkv_dt == DN_BF16) return 3;
+  if (g.gC == g.K && g.bC == 1 && g.wC == 1 && g.qkv_dt == DN_BF16) return 4;
   return 2;
 }
 
@@ -268,7 +272,7 @@ __device__ __forceinline__ Rows make_rows(const Geo& g, const void* q, const voi
   r.qk_pitch = (size_t)g.Hk * K;
   r.qk_row0 = tok0 * r.qk_pitch + (size_t)(h / g.qk_div) * K;
   r.gC = CF::fixed ? (CF::scalar_gates ? 1 : K) : g.gC;
-  r.bC = CF::fixed ? (CF::scalar_gates ? 1 : K) : g.bC;
+  r.bC = CF::fixed ? (CF::scalar_bw ? 1 : K) : g.bC;
   r.g_pitch = (size_t)g.gH * g.gC;
   r.g_row0 = tok0 * r.g_pitch + (size_t)g.gate_head(h, g.gH) * g.gC;
   r.b_pitch = (size_t)g.bH * g.bC;

@@ -151,7 +151,7 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
     const int seg0 = seg_s[0], segL = seg_s[C - 1];
     const Rows r = make_rows<CF>(g, a.q, a.k, a.gg, a.b, b, h, t0, rq_s, rk_s);
     const int qdt = r.qkv_dt, gdt = r.gate_dt;           // compile-time constants in the fixed modes
-    const int wC = CF::fixed ? (CF::scalar_gates ? 1 : g.V) : g.wC;
+    const int wC = CF::fixed ? (CF::scalar_bw ? 1 : g.V) : g.wC;
     const bool tm_cache = r.round_in;                    // k_hat, q_hat exactly bf16: they can be packed two per column
 
     // ---- G. the matrix products (and dLambda_end from the carried state)
@@ -921,9 +921,9 @@ int launch_prepass_bwd_tc(PrepassBwdArgs& a, size_t scratch_floats, cudaStream_t
   auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
   a.bulk_v = mode == 0 && g.V == 128 && a.dw_dt == DN_F32 && al16(a.v) && al16(a.w) && al16(a.dv) && al16(a.dw);
   if (g.Vw == 256) {
-    if (mode == 0) go(prepass_bwd_tc_kernel<256, 0>); else if (mode == 1) go(prepass_bwd_tc_kernel<256, 1>); else if (mode == 3) go(prepass_bwd_tc_kernel<256, 3>); else go(prepass_bwd_tc_kernel<256, 2>);
+    if (mode == 0) go(prepass_bwd_tc_kernel<256, 0>); else if (mode == 1) go(prepass_bwd_tc_kernel<256, 1>); else if (mode == 3) go(prepass_bwd_tc_kernel<256, 3>); else if (mode == 4) go(prepass_bwd_tc_kernel<256, 4>); else go(prepass_bwd_tc_kernel<256, 2>);
   } else {
-    if (mode == 0) go(prepass_bwd_tc_kernel<128, 0>); else if (mode == 1) go(prepass_bwd_tc_kernel<128, 1>); else if (mode == 3) go(prepass_bwd_tc_kernel<128, 3>); else go(prepass_bwd_tc_kernel<128, 2>);
+    if (mode == 0) go(prepass_bwd_tc_kernel<128, 0>); else if (mode == 1) go(prepass_bwd_tc_kernel<128, 1>); else if (mode == 3) go(prepass_bwd_tc_kernel<128, 3>); else if (mode == 4) go(prepass_bwd_tc_kernel<128, 4>); else go(prepass_bwd_tc_kernel<128, 2>);
   }
   return launch_status();
 }

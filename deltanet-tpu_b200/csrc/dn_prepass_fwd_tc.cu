@@ -154,7 +154,7 @@ __global__ void __launch_bounds__(NT, 1) prepass_fwd_tc_kernel(PrepassFwdArgs a,
     for (int i = tid; i < C; i += NT) seg_s[i] = seg_at(a.seg, b, t0 + i, g.L);
     const Rows r = make_rows<CF>(g, a.q, a.k, a.gg, a.b, b, h, t0, rq_s, rk_s);
     const int qdt = r.qkv_dt, gdt = r.gate_dt;           // compile-time constants in the fixed modes
-    const int wC = CF::fixed ? (CF::scalar_gates ? 1 : g.V) : g.wC;
+    const int wC = CF::fixed ? (CF::scalar_bw ? 1 : g.V) : g.wC;
     const bool tm_cache = r.round_in;                    // k_hat, q_hat exactly bf16: they can be packed two per column
     __syncthreads();
     const int seg0 = seg_s[0], segL = seg_s[C - 1];
@@ -739,9 +739,9 @@ int launch_prepass_fwd_tc(const Geo& g, const void* q, const void* k, const void
   };
   const int mode = input_mode(g);
   if (g.Vw == 256) {
-    if (mode == 0) go(prepass_fwd_tc_kernel<256, 0>); else if (mode == 1) go(prepass_fwd_tc_kernel<256, 1>); else if (mode == 3) go(prepass_fwd_tc_kernel<256, 3>); else go(prepass_fwd_tc_kernel<256, 2>);
+    if (mode == 0) go(prepass_fwd_tc_kernel<256, 0>); else if (mode == 1) go(prepass_fwd_tc_kernel<256, 1>); else if (mode == 3) go(prepass_fwd_tc_kernel<256, 3>); else if (mode == 4) go(prepass_fwd_tc_kernel<256, 4>); else go(prepass_fwd_tc_kernel<256, 2>);
   } else {
-    if (mode == 0) go(prepass_fwd_tc_kernel<128, 0>); else if (mode == 1) go(prepass_fwd_tc_kernel<128, 1>); else if (mode == 3) go(prepass_fwd_tc_kernel<128, 3>); else go(prepass_fwd_tc_kernel<128, 2>);
+    if (mode == 0) go(prepass_fwd_tc_kernel<128, 0>); else if (mode == 1) go(prepass_fwd_tc_kernel<128, 1>); else if (mode == 3) go(prepass_fwd_tc_kernel<128, 3>); else if (mode == 4) go(prepass_fwd_tc_kernel<128, 4>); else go(prepass_fwd_tc_kernel<128, 2>);
   }
   return launch_status();
 }
