@@ -218,10 +218,13 @@ class CudaOps:
                 "dn_sp_apply")
         return out
 
-    def finish(self, c, S_in):
+    def finish(self, c, S_in, exact=False):
+        """``exact``: the summary pass already started from the true incoming state (the first shard without
+        an initial state), so there is nothing to correct."""
         c["S_in"] = S_in.contiguous()
-        L.check(L.lib().dn_sp_correct_fwd(c["shape"], c["res"], c["seg"].data_ptr(), c["S_in"].data_ptr(),
-                                          c["out"].data_ptr(), _g._stream()), "dn_sp_correct_fwd")
+        if not exact:
+            L.check(L.lib().dn_sp_correct_fwd(c["shape"], c["res"], c["seg"].data_ptr(), c["S_in"].data_ptr(),
+                                              c["out"].data_ptr(), _g._stream()), "dn_sp_correct_fwd")
         out = c.pop("out")
         if self.recompute:                                  # keep only what the backward cannot rebuild
             for name in ("res", "block", "scratch"):
@@ -246,13 +249,16 @@ class CudaOps:
                                  c["dV"].data_ptr(), c["dH"].data_ptr(), d_init0.data_ptr(), _g._stream()), "dn_state_bwd")
         return d_init0
 
-    def bwd_finish(self, c, d_final):
+    def bwd_finish(self, c, d_final, exact=False):
+        """``exact``: the incoming cotangent is zero (the last shard without a loss on its final state), which
+        is what the zero-cotangent pass assumed."""
         lib = L.lib()
         q, k, v, g, b, w = c["ins"]
         d_final = d_final.contiguous()
-        L.check(lib.dn_sp_correct_bwd(c["shape"], c["res"], c["seg"].data_ptr(), c["d_out"].data_ptr(),
-                                      d_final.data_ptr(), c["dV"].data_ptr(), c["dH"].data_ptr(), _g._stream()),
-                "dn_sp_correct_bwd")
+        if not exact:
+            L.check(lib.dn_sp_correct_bwd(c["shape"], c["res"], c["seg"].data_ptr(), c["d_out"].data_ptr(),
+                                          d_final.data_ptr(), c["dV"].data_ptr(), c["dH"].data_ptr(), _g._stream()),
+                    "dn_sp_correct_bwd")
         grads = [torch.empty_like(t) for t in (q, k, v, g, b, w)]
         sc = c["scratch"]
         L.check(lib.dn_prepass_bwd(c["shape"], q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), b.data_ptr(),
@@ -287,7 +293,11 @@ def sp_forward(ops, chain, tensors, seg_raw, initial_state):
         return S_out, S_out * cont_out.view(B, 1, 1, 1).to(S_out.dtype)
 
     S_in, final = chain.forward(first.float().contiguous(), step)
-    out = ops.finish(c, S_in)
+    # The send must have left before a kernel that fills every SM is enqueued behind it: the transfer's own
+    # kernel needs room on an SM to start, and a persistent one-CTA-per-SM kernel (the chunk-parallel passes)
+    # would hold it back until it ends - and the next rank with it.  The stream waits here, not the host.
+    chain.drain()
+    out = ops.finish(c, S_in, exact=(r == 0 and initial_state is None))
     c.update(P=P, cont_in=cont_in)
     return out, final, c
 
@@ -305,7 +315,8 @@ def sp_backward(ops, chain, c, d_out, d_final_state):
         return d_in
 
     d_final, d_in = chain.backward(last.float().contiguous(), step)
-    grads = ops.bwd_finish(c, d_final)
+    chain.drain()                                                           # (as in sp_forward)
+    grads = ops.bwd_finish(c, d_final, exact=(chain.rank == chain.size - 1 and d_final_state is None))
     return grads, d_in
 
 

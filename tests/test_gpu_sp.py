@@ -84,3 +84,25 @@ def test_sharded_equals_unsharded(n, prec, C, K, V, tol, recompute):
     if prec == "fp32":
         o_ref, f_ref = O.chunk_gdn2(q, k, v, g, b, w, segment_ids=seg, initial_state=init, output_final_state=True, **opts)
         assert O.rel_l2(out.cpu(), o_ref) < tol and O.rel_l2(res[-1]["final"].cpu(), f_ref) < tol
+
+
+@pytest.mark.parametrize("n,prec,C,K,V,tol", [(2, "fp32", 64, 64, 64, 2e-4), (4, "bf16", 128, 128, 128, 2e-2)])
+def test_sharded_without_initial_state_or_final_state_loss(n, prec, C, K, V, tol):
+    """No initial state and no loss on the last final state: the first shard's forward correction and the
+    last shard's backward correction are exact by construction and are skipped."""
+    import deltanet_b200 as dn
+    B, L, Hk, Hv = 1, 1024, 2, 4
+    q, k, v, g, b, w = O.make_inputs(93, B, L, Hk, Hv, K, V, qkv_scale=0.5)
+    seg = torch.repeat_interleave(torch.tensor([0, 1, 2], dtype=torch.int32), torch.tensor([200, 500, 324]))[None]
+    do = torch.randn(B, L, Hv, V, generator=torch.Generator().manual_seed(6))
+    cu = lambda t: t.cuda()
+    ins = [cu(t) for t in (q, k, v, g, b, w)]
+    opts = dict(chunk_size=C, precision=prec, qk_l2norm=True)
+    res = _run_sharded(n, ins, cu(seg), None, cu(do), None, **opts)
+    leaves = [t.clone().requires_grad_() for t in ins]
+    o1, f1 = dn.chunk_gdn2(*leaves, segment_ids=cu(seg), output_final_state=True, **opts)
+    g1 = torch.autograd.grad((o1.float() * cu(do)).sum(), leaves)
+    assert O.rel_l2(torch.cat([r["out"] for r in res], 1).cpu(), o1.detach().cpu()) < tol
+    assert O.rel_l2(res[-1]["final"].cpu(), f1.detach().cpu()) < tol
+    for i in range(6):
+        assert O.rel_l2(torch.cat([r["grads"][i] for r in res], 1).cpu(), g1[i].cpu()) < tol, i
