@@ -62,6 +62,12 @@ inline int make_geo(const dn_shape* s, Geo* g) {
   if (s->precision != DN_PREC_FP32 && s->precision != DN_PREC_BF16) return DN_ERR_BAD_DTYPE;
   g->B = s->B; g->L = s->L; g->Hk = s->Hk; g->Hv = s->Hv; g->K = s->K; g->V = s->V;
   bool at_hv = (s->Hk < s->Hv) && (s->g_heads == s->Hv || s->b_heads == s->Hv);
+  // More than two value heads per key head would make a tile wider than the tensor-core kernels take
+  // (G V > 256): such calls use the per-value-head view too (the key-side work is repeated per value head,
+  // the key-side gradients are summed over the group as for gates given per value head).
+  if (s->Hk < s->Hv && s->precision == DN_PREC_BF16 && !(s->flags & DN_STATE_FP32_MM) && s->K == 128 && s->V == 128 &&
+      (s->Hv / s->Hk) * s->V > 256 && !force_simt())
+    at_hv = true;
   if (at_hv) { g->H = s->Hv; g->Vw = s->V; g->G = 1; g->qk_div = s->Hv / s->Hk; }
   else       { g->H = s->Hk; g->G = s->Hv / s->Hk; g->Vw = g->G * s->V; g->qk_div = 1; }
   if (g->Vw > 1024) return DN_ERR_BAD_SHAPE;

@@ -177,6 +177,24 @@ def test_channelwise_decay_strength_paths(dn, strength):
             lambda t, i: O.chunk_gdn2(*t, segment_ids=seg, **kw), [q, k, v, g, b, w], tol=BF16_TOL)
 
 
+def test_four_value_heads_per_key_head_runs_on_tensor_cores(dn):
+    """Hk = 1, Hv = 4 with gates per key head (a 512-column group): such calls are run per value head on the
+    tensor-core kernels, the key-side gradients summed over the group."""
+    from deltanet_b200 import _lib as L
+    B, Lq, Hk, Hv = 1, 384, 1, 4
+    q, k, v, g, b, w = O.make_inputs(2260, B, Lq, Hk, Hv, 128, 128, qkv_dtype=torch.bfloat16)
+    seg = torch.zeros(B, Lq, dtype=torch.int32)
+    seg[0, 200:] = 1
+    kw = dict(chunk_size=128, precision="bf16", qk_l2norm=True, output_final_state=True)
+    compare(lambda t, i: dn.chunk_gdn2(*t, segment_ids=seg.cuda(), **kw),
+            lambda t, i: O.chunk_gdn2(*t, segment_ids=seg, **kw), [q, k, v, g, b, w], tol=BF16_TOL)
+    shape = L.Shape(B=B, L=Lq, Hk=Hk, Hv=Hv, K=128, V=128, chunk=128, g_heads=Hk, g_cols=128, b_heads=Hk, b_cols=128,
+                    w_heads=Hv, w_cols=128, qkv_dtype=L.DN_BF16, gate_dtype=L.DN_F32, precision=L.DN_PREC_BF16, flags=0, scale=1.0)
+    ex = L.Exec()
+    L.check(L.lib().dn_exec_view(shape, ex), "dn_exec_view")
+    assert ex.H == Hv and ex.Vw == 128
+
+
 # ------------------------------------------------------------------ fused prologue, bf16 gates, flags (mode 2)
 def test_fused_prologue_bf16_unaligned(dn):
     """fuse_prologue=True on bf16 q/k/v with an unaligned length (L = 300): pre-activation gates."""
