@@ -22,7 +22,7 @@ One JSON line is printed by rank 0:
   prefill      Gated DeltaNet packed-document forward prefill (scalar gates, B=4 L=8192, inference mode),
   sp           the long-sequence workload: KDA-style fwd+bwd on ONE packed sequence of 131072
                tokens, chunk_size 64, recompute_states, split into contiguous shards over the
-               GPUs (strong scaling; the state chain crosses the ranks by NCCL point-to-point),
+               GPUs (strong scaling; the shards' affine state maps cross the ranks by one NCCL all-gather per direction),
   cpu_baseline the CPU oracle (a port of the reference's chunked path) on the host cores.
 
 `--impl reference` times the CPU oracle on the same workload instead (the reference itself
@@ -387,7 +387,7 @@ def run_reference(args):
 def sp_leg(dn, dist, world, rank, dev, steps=3):
     """KDA-style fwd+bwd on ONE packed sequence of 131072 tokens (channel-wise decay, per-head beta,
     documents of 2048..32768 tokens, chunk_size 64, recompute_states), split into equal contiguous
-    shards over the ranks: the state chain crosses the ranks by NCCL point-to-point, everything else is
+    shards over the ranks: the shards' affine state maps cross the ranks in one NCCL all-gather per direction, everything else is
     local.  Total work is fixed, so this is strong scaling.  Returns the `sp` object (rank 0) or None."""
     from deltanet_b200 import sp
     c = SPCFG
@@ -438,8 +438,9 @@ def sp_leg(dn, dist, world, rank, dev, steps=3):
         return None
     out = dict(workload="chunk_kda fwd+bwd B=1 L=131072 H=32 K=V=128 chunk_size=64 bf16 qk_l2norm recompute_states, "
                         "documents of 2048..32768 tokens (seeded), one sequence",
-               parallelism=(f"sequence-sharded x{world}: per-shard affine summary, state chain by NCCL send/recv, "
-                            "partial correction pass") if world > 1 else "one GPU",
+               parallelism=(f"sequence-sharded x{world}: per-shard affine summary, ONE NCCL all-gather of the shards' "
+                            "affine maps per direction (each rank composes its predecessors' maps), partial correction pass")
+               if world > 1 else "one GPU",
                scaling="strong", ms_per_step=ms, tokens_per_s=L / (ms * 1e-3), steps=steps, warmup=3,
                kernels_per_step_per_rank=int(launches))
     if single_ms is not None:

@@ -97,6 +97,17 @@ class Chain:
         dist.all_gather(out, edges, group=self.group)
         return out
 
+    def all_gather(self, tensors):
+        """Every rank's list of tensors (4-byte elements, same shapes on all ranks) in ONE collective:
+        returns a list indexed by rank of lists of tensors (views of one receive buffer)."""
+        flat = torch.cat([t.contiguous().reshape(-1).view(torch.float32) for t in tensors])
+        n = flat.numel()
+        buf = torch.empty(self.size * n, dtype=torch.float32, device=flat.device)
+        dist.all_gather_into_tensor(buf, flat, group=self.group)
+        sizes = [t.numel() for t in tensors]
+        return [[part.view(t.dtype).view(t.shape) for part, t in zip(torch.split(buf[r * n:(r + 1) * n], sizes), tensors)]
+                for r in range(self.size)]
+
 
 class LocalChain:
     """The same neighbour transfers between threads of ONE process (tests on a single device).
@@ -107,6 +118,7 @@ class LocalChain:
 
     def __init__(self, rank, size, shared):
         self.rank, self.size, self._s = rank, size, shared
+        self._calls = 0
 
     @staticmethod
     def make(n):
@@ -143,6 +155,14 @@ class LocalChain:
         self._s["edges"][self.rank] = edges
         self._s["barrier"].wait(timeout=120)
         return list(self._s["edges"])
+
+    def all_gather(self, tensors):
+        key = ("all_gather", self._calls)
+        self._calls += 1
+        slot = self._s.setdefault(key, [None] * self.size)
+        slot[self.rank] = [self._handoff(t) for t in tensors]
+        self._s["barrier"].wait(timeout=120)
+        return [list(x) for x in slot]
 
 
 def continues_from_previous(edges_prev, edges_mine):
@@ -273,12 +293,14 @@ def shard_edges(seg_raw):
     return torch.stack([seg_raw[:, 0], seg_raw[:, -1]], dim=1).to(torch.int32).contiguous()
 
 
-def sp_forward(ops, chain, tensors, seg_raw, initial_state):
+def sp_forward(ops, chain, tensors, seg_raw, initial_state, exchange="gather"):
     """Runs the three forward steps on this rank.  Returns (out, final_state, saved context)."""
     q, k, v, g, b, w = tensors
     B, Hv, K, V = q.shape[0], v.shape[2], q.shape[3], v.shape[3]
     c = ops.prepare(q, k, v, g, b, w, seg_raw)
     P, Q = ops.summary(c)
+    if exchange == "gather":
+        return _forward_gathered(ops, chain, c, P, Q, seg_raw, initial_state)
     edges = chain.gather_edges(shard_edges(seg_raw).to(q.device))
     r = chain.rank
     cont_in = continues_from_previous(edges[r - 1], edges[r]) if r > 0 else None
@@ -298,12 +320,71 @@ def sp_forward(ops, chain, tensors, seg_raw, initial_state):
     # would hold it back until it ends - and the next rank with it.  The stream waits here, not the host.
     chain.drain()
     out = ops.finish(c, S_in, exact=(r == 0 and initial_state is None))
-    c.update(P=P, cont_in=cont_in)
+    c.update(P=P, cont_in=cont_in, exchange="p2p")
     return out, final, c
+
+
+def _forward_gathered(ops, chain, c, P, Q, seg_raw, initial_state):
+    """Step 2 of the forward as ONE collective: every rank learns every shard's affine map (P, Q) and edge ids and
+    composes its predecessors' maps itself (r small launches on rank r) instead of waiting for r hops.  The
+    first rank publishes its own final state P S_0 + Q in place of Q, so the others start from zero and the
+    initial state does not travel.  It is the arithmetic of the hop-by-hop chain in the same order."""
+    r, n = chain.rank, chain.size
+    dev = P.device
+    B = P.shape[0]
+    S_in = None
+    if r == 0:
+        S_in = (initial_state if initial_state is not None else torch.zeros_like(Q)).float().contiguous()
+        Q_pub = ops.apply(c, P, S_in, Q) if initial_state is not None else Q      # = this shard's final state
+    else:
+        Q_pub = Q
+    got = chain.all_gather([P.contiguous(), Q_pub.contiguous(), shard_edges(seg_raw).to(dev)])
+    edges = [x[2] for x in got]
+    conts = [None] + [continues_from_previous(edges[j - 1], edges[j]) for j in range(1, n)]    # conts[j]: shard j continues j-1's document
+    if r == 0:
+        final = Q_pub
+    else:
+        S = got[0][1] * conts[1].view(B, 1, 1, 1).to(Q.dtype)                      # after shard 0; nothing of it where shard 1 starts a document
+        for j in range(1, r):
+            S = ops.apply(c, got[j][0], S, got[j][1])                              # the state after shard j ...
+            S = S * conts[j + 1].view(B, 1, 1, 1).to(S.dtype)                      # ... masked the same way for shard j+1
+        S_in = S
+        final = ops.apply(c, P, S_in, Q)
+    out = ops.finish(c, S_in, exact=(r == 0 and initial_state is None))
+    c.update(P=P, cont_in=conts[r], exchange="gather", P_all=[x[0] for x in got], conts=conts)
+    return out, final, c
+
+
+def _backward_gathered(ops, chain, c, d_out, d_final_state):
+    """The mirror image: rank j publishes e_j = P_j^T (its own final-state cotangent) + d_init0_j; the cotangent of
+    shard j's incoming state is then d_in_j = cont_j * (P_j^T d_in_{j+1} + e_j), which rank r evaluates for its
+    successors j = n-1 .. r+1 itself."""
+    r, n = chain.rank, chain.size
+    B = d_out.shape[0]
+    d_init0 = ops.bwd_summary(c, d_out)
+    e_mine = d_init0 if d_final_state is None else ops.apply(c, c["P"], d_final_state.float().contiguous(), d_init0, transpose=True)
+    got = chain.all_gather([e_mine.contiguous()])
+    d_next = None                                                                  # d_in of the successor (None: zero)
+    for j in range(n - 1, r, -1):
+        d = got[j][0] if d_next is None else ops.apply(c, c["P_all"][j], d_next, got[j][0], transpose=True)
+        d_next = d * c["conts"][j].view(B, 1, 1, 1).to(d.dtype)
+    own = d_final_state.float() if d_final_state is not None else None
+    x = d_next if own is None else (own if d_next is None else d_next + own)       # cotangent of this shard's final state
+    if x is None:
+        x = torch.zeros_like(d_init0)
+        d_in = d_init0
+    else:
+        d_in = ops.apply(c, c["P"], x.contiguous(), d_init0, transpose=True)
+    if c["cont_in"] is not None:
+        d_in = d_in * c["cont_in"].view(B, 1, 1, 1).to(d_in.dtype)
+    grads = ops.bwd_finish(c, x, exact=(r == n - 1 and d_final_state is None))
+    return grads, d_in
 
 
 def sp_backward(ops, chain, c, d_out, d_final_state):
     """Mirror of sp_forward for the cotangents; returns (grads of q,k,v,g,b,w, d_initial_state)."""
+    if c.get("exchange") == "gather":
+        return _backward_gathered(ops, chain, c, d_out, d_final_state)
     B = d_out.shape[0]
     d_init0 = ops.bwd_summary(c, d_out)
     last = d_final_state if d_final_state is not None else torch.zeros_like(d_init0)
@@ -322,8 +403,8 @@ def sp_backward(ops, chain, c, d_out, d_final_state):
 
 class _SPFunction(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, ops, chain, seg_raw, q, k, v, g, b, w, initial_state):
-        out, final, c = sp_forward(ops, chain, (q, k, v, g, b, w), seg_raw, initial_state)
+    def forward(ctx, ops, chain, exchange, seg_raw, q, k, v, g, b, w, initial_state):
+        out, final, c = sp_forward(ops, chain, (q, k, v, g, b, w), seg_raw, initial_state, exchange)
         chain.drain()
         ctx.ops, ctx.chain, ctx.c = ops, chain, c
         ctx.has_init = initial_state is not None
@@ -338,13 +419,13 @@ class _SPFunction(torch.autograd.Function):
             d_out = torch.zeros(B, Lq, Hv, V, device=c["seg"].device)
         (dq, dk, dv, dg, db, dw), d_in = sp_backward(ctx.ops, ctx.chain, c, d_out, d_final)
         ctx.chain.drain()
-        return None, None, None, dq, dk, dv, dg, db, dw, (d_in if ctx.has_init else None)
+        return None, None, None, None, dq, dk, dv, dg, db, dw, (d_in if ctx.has_init else None)
 
 
 def chunk_gdn2_sp(q, k, v, g, b, w, *, segment_ids: torch.Tensor, initial_state: Optional[torch.Tensor] = None,
                   group=None, chunk_size: int = 128, precision: str = "bf16", scale: Optional[float] = None,
                   qk_l2norm: bool = False, fuse_prologue: bool = False, recompute_states: bool = False,
-                  ops=None, chain=None):
+                  exchange: str = "gather", ops=None, chain=None):
     """chunk_gdn2 on this rank's contiguous shard of a packed sequence split over the ranks of ``group``.
 
     ``segment_ids`` (B, L_shard) are the GLOBAL document ids of the shard's tokens (any change of id is
@@ -352,9 +433,13 @@ def chunk_gdn2_sp(q, k, v, g, b, w, *, segment_ids: torch.Tensor, initial_state:
     ``(out, final_state)``; ``final_state`` is the state after this shard (the sequence's final state on
     the last rank) and is differentiable on every rank.  ``recompute_states`` keeps no prepass output or
     chunk state between forward and backward (``gdn2.py:1384-1386``).  Differentiable: backward runs the
-    reverse chain, so every rank must take part.
+    reverse chain, so every rank must take part.  ``exchange``: "gather" (one all-gather of the shards' affine
+    maps per direction, each rank composes its predecessors' maps itself) or "p2p" (the state handed from rank
+    to rank by send / recv, r hops before rank r can go on).
     """
+    if exchange not in ("gather", "p2p"):
+        raise ValueError(f"exchange must be 'gather' or 'p2p', got {exchange!r}")
     ops = ops or CudaOps(chunk_size=chunk_size, precision=precision, scale=scale, qk_l2norm=qk_l2norm,
                          fuse_prologue=fuse_prologue, recompute_states=recompute_states)
     chain = chain or Chain(group)
-    return _SPFunction.apply(ops, chain, segment_ids, q, k, v, g, b, w, initial_state)
+    return _SPFunction.apply(ops, chain, exchange, segment_ids, q, k, v, g, b, w, initial_state)

@@ -11,7 +11,7 @@ from oracle import delta_oracle as O
 pytestmark = pytest.mark.gpu
 
 
-def _run_sharded(n, ins, seg, init, do, dfs, **opts):
+def _run_sharded(n, ins, seg, init, do, dfs, exchange="gather", **opts):
     from deltanet_b200 import sp
     chains = sp.LocalChain.make(n)
     L = ins[0].shape[1]
@@ -25,7 +25,7 @@ def _run_sharded(n, ins, seg, init, do, dfs, **opts):
             # thread, where two emulated ranks would wait for each other forever.
             shard = [t[:, lo:hi].contiguous() for t in ins]
             ops = sp.CudaOps(**opts)
-            out, final, c = sp.sp_forward(ops, chains[r], shard, seg[:, lo:hi].contiguous(), init if r == 0 else None)
+            out, final, c = sp.sp_forward(ops, chains[r], shard, seg[:, lo:hi].contiguous(), init if r == 0 else None, exchange)
             grads, d_in = sp.sp_backward(ops, chains[r], c, do[:, lo:hi].contiguous(), dfs if r == n - 1 else None)
             results[r] = dict(out=out, final=final, grads=list(grads) + [d_in])
         except Exception as e:  # noqa: BLE001
@@ -60,7 +60,9 @@ def test_sharded_equals_unsharded(n, prec, C, K, V, tol, recompute):
     cu = lambda t: t.cuda()
     ins = [cu(t) for t in (q, k, v, g, b, w)]
     opts = dict(chunk_size=C, precision=prec, qk_l2norm=True)
-    res = _run_sharded(n, ins, cu(seg), cu(init), cu(do), cu(dfs), recompute_states=recompute, **opts)
+    # (the hop-by-hop exchange on the configurations that recompute, the gathered one elsewhere)
+    res = _run_sharded(n, ins, cu(seg), cu(init), cu(do), cu(dfs), exchange="p2p" if recompute else "gather",
+                       recompute_states=recompute, **opts)
 
     # the unsharded operator on the same device
     leaves = [t.clone().requires_grad_() for t in ins]

@@ -71,7 +71,7 @@ def _inputs():
     return (q, k, v, g, b, w), seg, init, do, dfs
 
 
-def _worker(rank, world, port, ret):
+def _worker(rank, world, port, ret, exchange):
     for p in (ROOT, PKG_DIR):
         if p not in sys.path:
             sys.path.insert(0, p)
@@ -84,7 +84,8 @@ def _worker(rank, world, port, ret):
     shard = [t[:, lo:hi].contiguous().requires_grad_() for t in ins]
     init_leaf = init.clone().requires_grad_()
     out, final = sp.chunk_gdn2_sp(*shard, segment_ids=seg[:, lo:hi].contiguous(),
-                                  initial_state=init_leaf if rank == 0 else None, ops=OracleOps(), chain=sp.Chain())
+                                  initial_state=init_leaf if rank == 0 else None, ops=OracleOps(), chain=sp.Chain(),
+                                  exchange=exchange)
     loss = (out * do[:, lo:hi]).sum()
     if rank == world - 1:
         loss = loss + (final * dfs).sum()
@@ -96,14 +97,14 @@ def _worker(rank, world, port, ret):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world", [2, 3])
-def test_sp_chain_matches_unsplit_oracle(world):
+@pytest.mark.parametrize("world,exchange", [(2, "p2p"), (3, "gather"), (3, "p2p")])
+def test_sp_chain_matches_unsplit_oracle(world, exchange):
     from oracle import delta_oracle as O
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
     ret = mp.Manager().dict()
-    mp.spawn(_worker, args=(world, port, ret), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, port, ret, exchange), nprocs=world, join=True)
     ins, seg, init, do, dfs = _inputs()
     leaves = [t.clone().requires_grad_() for t in ins]
     init_leaf = init.clone().requires_grad_()
