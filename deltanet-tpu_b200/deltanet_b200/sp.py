@@ -14,13 +14,15 @@ the whole state pass of its predecessor.  Two facts make the chain cheap instead
   forward   1. every rank: prepass, then ONE state pass from a zero state that writes outputs and
                chunk states for the whole shard (final after the first boundary, provisional
                before it) and yields Q and P;
-            2. chain: rank r receives S_in from r-1 and sends P S_in + Q to r+1 (zeroed where the
-               next shard starts a new document); that value is also the shard's final state;
+            2. exchange: one all-gather of every shard's (P, Q) and edge ids; rank r composes the
+               maps of shards 0..r-1 itself (zeroing the state where the next shard starts a new
+               document) and gets its S_in; P S_in + Q is the shard's final state.  (Or, with
+               exchange="p2p": rank r receives S_in from r-1 and sends P S_in + Q to r+1.);
             3. every rank: the state pass again from its true S_in, which stops at the first chunk
                that no longer depends on it.
   backward  the mirror image with the state cotangent: a reverse pass with zero incoming cotangent
-            writes dV / dH for the whole shard and d_init0, the chain carries
-            d_S_in = P^T d_final + d_init0 from rank r to r-1, a second reverse pass from the true
+            writes dV / dH for the whole shard and d_init0, the exchange (one all-gather, or hops
+            from rank r to r-1) yields d_S_in = P^T d_final + d_init0, a second reverse pass from the true
             d_final stops where dH no longer depends on it, and the chunk-parallel backward runs
             over the shard.
 
@@ -28,10 +30,9 @@ With ``recompute_states`` nothing but the inputs, P and S_in survives the forwar
 rebuilds the prepass outputs and the chunk states first (what ``gdn2.py:1545-1630`` does per call).
 
 The per-shard arithmetic is behind an ``ops`` object: ``CudaOps`` (the C-ABI kernels) on GPUs;
-tests substitute CPU ops to exercise the chain logic with the gloo backend.  Point-to-point
-transfers use ``torch.distributed`` (NCCL over NVLink on a B200 box); the received state always
-lands in a local buffer before any kernel reads it.  Sends are not waited for: the correction pass
-of a rank runs while its state travels on.
+tests substitute CPU ops to exercise the exchange logic with the gloo backend.  Transfers use
+``torch.distributed`` (NCCL over NVLink on a B200 box); what is received always lands in a local
+buffer before any kernel reads it.
 """
 from __future__ import annotations
 
