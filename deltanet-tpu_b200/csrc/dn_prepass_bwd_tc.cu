@@ -154,6 +154,22 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
     const int wC = CF::fixed ? (CF::scalar_bw ? 1 : g.V) : g.wC;
     const bool tm_cache = r.round_in;                    // k_hat, q_hat exactly bf16: they can be packed two per column
 
+    // staging rows of phase V (headline mode): v as bf16 and w as fp32, one row per token, padded pitches
+    constexpr int VP = 256 + 16, WP = 512 + 16;            // row pitches in bytes (padding: no bank conflicts)
+    uint8_t* const VB = smraw + 68 * 1024;
+    uint8_t* const WB = VB + 128 * VP;
+    auto v_rows_request = [&](int pass) {                  // all threads: one bulk copy per row and tensor
+      const int rows = g.L - t0 < C ? g.L - t0 : C;
+      const int hv = h * (VW / 128) + pass;
+      const size_t tok = (size_t)b * g.L + t0 + tid;
+      if (tid == 0) umma::mbar_expect_tx(&v_bar, (uint32_t)rows * (256 + 512));
+      __syncthreads();
+      if (tid < rows) {
+        umma::bulk_load(VB + tid * VP, reinterpret_cast<const __nv_bfloat16*>(a.v) + (tok * g.Hv + hv) * 128, 256, &v_bar);
+        umma::bulk_load(WB + tid * WP, reinterpret_cast<const float*>(a.w) + (tok * g.wH + g.w_head(hv)) * 128, 512, &v_bar);
+      }
+    };
+
     // ---- G. the matrix products (and dLambda_end from the carried state)
     {
       BwdTcIo io;
@@ -173,7 +189,11 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
       io.DQE = DQE; io.DKE = DKE; io.DX = DX; io.DM = DM; io.DA = DA;
       io.dlend_s = dlend_s; io.all_same = all_same;
       io.seg_s = seg_s; io.trunc = trunc;
-      bwd_gemms_tc<VW, NT>(cx, smraw, io, imgld);
+      // the rows of v and w of the first value head are requested as soon as the products are done: they
+      // travel while the last accumulator drains (phase V below waits for them)
+      bwd_gemms_tc<VW, NT>(cx, smraw, io, imgld, [&]() {
+        if (bulk_v) v_rows_request(0);
+      });
     }
 
     // ---- V. dv = dY * w_act, dw = dY * v (+ sigmoid adjoint; summed over a value head's columns
@@ -185,21 +205,13 @@ __global__ void __launch_bounds__(NT, 1) prepass_bwd_tc_kernel(PrepassBwdArgs a)
     //         through padded staging rows in shared memory: a 128-column pass (one value head) moves
     //         384 KB without a single load or store instruction of the CUDA cores touching global memory.
     if (bulk_v) {
-      constexpr int VP = 256 + 16, WP = 512 + 16;          // row pitches in bytes (padding: no bank conflicts)
-      uint8_t* VB = smraw + 68 * 1024;
-      uint8_t* WB = VB + 128 * VP;
       const int rows = g.L - t0 < C ? g.L - t0 : C;
       const uint4* Ximg = reinterpret_cast<const uint4*>(smraw);
 #pragma unroll 1
       for (int pass = 0; pass < VW / 128; ++pass) {
         const int hv = h * (VW / 128) + pass;                // V == 128: one value head per pass
         const size_t tok = (size_t)b * g.L + t0 + tid;
-        if (tid == 0) umma::mbar_expect_tx(&v_bar, (uint32_t)rows * (256 + 512));
-        __syncthreads();
-        if (tid < rows) {
-          umma::bulk_load(VB + tid * VP, reinterpret_cast<const __nv_bfloat16*>(a.v) + (tok * g.Hv + hv) * 128, 256, &v_bar);
-          umma::bulk_load(WB + tid * WP, reinterpret_cast<const float*>(a.w) + (tok * g.wH + g.w_head(hv)) * 128, 512, &v_bar);
-        }
+        if (pass > 0) v_rows_request(pass);                  // (pass 0 was requested before the last drain of phase G)
         if (!umma::mbar_wait(&v_bar, v_phase)) umma::report_timeout(a.err);
         v_phase ^= 1u;
 #pragma unroll

@@ -80,8 +80,12 @@ struct ImgLoader {
   }
 };
 
-template <int VW, int NT>
-__device__ __forceinline__ void bwd_gemms_tc(umma::Ctx& cx, uint8_t* img, const BwdTcIo& io, ImgLoader& ld) {
+// `after_products` is called by all threads once the last products have completed, i.e. when every operand
+// slot except X is free again, and before the last accumulator is drained: the caller starts the copies
+// of its next phase there, so that they travel during the drain.
+template <int VW, int NT, class AfterProducts>
+__device__ __forceinline__ void bwd_gemms_tc(umma::Ctx& cx, uint8_t* img, const BwdTcIo& io, ImgLoader& ld,
+                                             AfterProducts after_products) {
   constexpr int SLOT = 128 * VW * 2;
   uint4* X = reinterpret_cast<uint4*>(img);
   uint4* Y = reinterpret_cast<uint4*>(img + SLOT);
@@ -230,6 +234,7 @@ __device__ __forceinline__ void bwd_gemms_tc(umma::Ctx& cx, uint8_t* img, const 
   umma::issue<128, false, false>(cx, Y2, P, 128, 0, false);
   umma::issue<128, false, false>(cx, X, Z, VW, 0, true);
   umma::commit_wait(cx);
+  after_products();
   umma::drain<NT, 128>(cx, 0, [&](int row, int col, const float (&v)[16]) {
     float m[16];
 #pragma unroll
