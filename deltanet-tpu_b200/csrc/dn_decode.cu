@@ -304,6 +304,10 @@ __global__ void __launch_bounds__(NT, SB == 2 ? 2 : 1) decode_bulk_kernel(Decode
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
+  // everything above touched shared memory only; what follows reads what earlier kernels of the stream wrote
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  // the next launch of the stream may take the places of this grid's CTAs as they leave (all of them are resident)
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int first = blockIdx.x, stride = gridDim.x;
   if (tid == NT - 1)
     for (int i = 0; i < STAGES - 1; ++i) {
@@ -511,9 +515,19 @@ int launch_decode(const dn_decode_shape& s, const void* q, const void* k, const 
     const int slots = (sb16 ? 2 : 1) * sm_count();
     const int grid = tiles < slots ? tiles : slots;
     const size_t smem = (size_t)bulk::STAGES * (sb16 ? bulk::Stage<2>::BYTES : bulk::Stage<4>::BYTES);
+    // Programmatic dependent launch: the CTAs of this launch may become resident while the kernel before it
+    // in the stream is still finishing (a decode loop is a chain of short launches of this kernel); they set
+    // up their barriers and then wait, inside the kernel, for that kernel to have completed before they touch
+    // global memory.
     auto go = [&](auto kern) {
       cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      kern<<<grid, bulk::NT, smem, st>>>(a, tiles, device_error_ptr());
+      cudaLaunchConfig_t cfg{};
+      cfg.gridDim = dim3((unsigned)grid); cfg.blockDim = dim3(bulk::NT); cfg.dynamicSmemBytes = smem; cfg.stream = st;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[0].val.programmaticStreamSerializationAllowed = 1;
+      cfg.attrs = attr; cfg.numAttrs = 1;
+      cudaLaunchKernelEx(&cfg, kern, a, tiles, device_error_ptr());
     };
     if (sb16) { if (sc) go(bulk::decode_bulk_kernel<2, true>); else go(bulk::decode_bulk_kernel<2, false>); }
     else      { if (sc) go(bulk::decode_bulk_kernel<4, true>); else go(bulk::decode_bulk_kernel<4, false>); }
