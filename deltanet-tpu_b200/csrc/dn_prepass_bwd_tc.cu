@@ -8,20 +8,27 @@
 //   V. dv and dw from the bf16 image of dY that G leaves in shared memory; in the headline mode the
 //      rows of v, w, dv, dw move by bulk copies through padded staging rows.
 //   L. row normalisers and the cumulative log-decay of the chunk in shared memory.
-//   D. the 16x16 diagonal blocks of dA and dM, exact, one thread per (block, channel), from
-//      shared-memory caches of k_hat, q_hat, beta (64 rows at a time); this pass initialises dbeta',
-//      dq', dk' and parks k_hat | q_hat (two bf16 per column) and beta in tensor memory.
-//   H. adjoints of A and M through the same three-level factorisation as the forward.  In one level
-//      every row is either a ROW of the level's entries (lower block of its pair) or a COLUMN (upper
-//      block), so with dA_s / dM_s the entries the level owns, KR the image holding beta-images on
-//      lower rows and k-images on upper rows, and QK holding q-images / k-images,
-//        T1 = (dA_s + dA_s^T) KR,   T2 = (dM_s + dM_s^T) QK        (four MMAs, one drain)
-//        lower rows:  dbeta' += rowfac * T1,  dq' += rowfac * T2
-//        upper rows:  dk'    += colfac * (T1 + T2)
-//      with the same exp(Lam - Lam_ref) factors (all <= 1) as the forward.  KR and QK are built from
-//      the tensor-memory cache; a level's drain overlaps the next level's image build.
-//   E. combination into dLambda, d q_hat, d k_hat, d b (written), the l2norm adjoint and dq, dk; the
-//      operands of the second half wait in tensor memory.
+//   D/H. adjoints of A and M, i.e. dbeta', dq', dk', by one of three routes:
+//      (a) one scalar decay per (token, head): with f_ij = e^{lam_i - lam_j} applied entry-wise to dA and dM,
+//          two rounds of two products on the plain images of k_hat and q_hat;
+//      (b) channel-wise decay that stays within e^{+-32} of each document's midpoint over the chunk (tested
+//          per chunk on the device): the same two rounds on images of k_hat / f, q_hat f, beta k_hat f with
+//          f = e^{Lam - midpoint}; the results are scaled by f, f, 1 / f when phase E reads them;
+//          on (a) and (b) the three accumulators stay in tensor memory for phase E;
+//      (c) otherwise: D. the 16x16 diagonal blocks of dA and dM, exact, one thread per (block, channel), from
+//          shared-memory caches of k_hat, q_hat, beta (64 rows at a time), which initialises dbeta', dq', dk'
+//          in the scratch and parks k_hat | q_hat (two bf16 per column) and beta in tensor memory; then
+//          H. the three-level factorisation of the forward: in one level every row is either a ROW of the
+//          level's entries (lower block of its pair) or a COLUMN (upper block), so with dA_s / dM_s the
+//          entries the level owns, KR the image holding beta-images on lower rows and k-images on upper
+//          rows, and QK holding q-images / k-images,
+//            T1 = (dA_s + dA_s^T) KR,   T2 = (dM_s + dM_s^T) QK        (four MMAs, one drain)
+//            lower rows:  dbeta' += rowfac * T1,  dq' += rowfac * T2
+//            upper rows:  dk'    += colfac * (T1 + T2)
+//          with the same exp(Lam - Lam_ref) factors (all <= 1) as the forward; a level's drain overlaps the
+//          next level's image build.
+//   E. combination into dLambda, d q_hat, d k_hat, d b (written), the l2norm adjoint and dq, dk, in the
+//      thread mapping of a tensor-memory drain; the operands of the second half wait in tensor memory.
 //   R. dg by a within-document reverse cumulative sum plus the Lambda_end path; written with the
 //      gate adjoint.
 //
