@@ -3,8 +3,13 @@
 // (reference body: src/deltanet_tpu/gdn2.py:115-240), with the bf16 tiles W, U, M, qe, ke written
 // as tensor-core operand images ([col / 8][row][8], see Geo::img).
 //
-// A and M.  A_ij = sum_c beta_ic exp(Lam_ic - Lam_jc) k_jc cannot be one matrix product because
-// the decay couples i, j and the channel c.  It is built hierarchically: at level s in {16,32,64}
+// A and M.  A_ij = sum_c beta_ic exp(Lam_ic - Lam_jc) k_jc cannot in general be one matrix product
+// because the decay couples i, j and the channel c.  Two cases reduce to plain products and are taken
+// when they apply: one scalar decay per (token, head), where exp(lam_i - lam_j) is applied entry-wise
+// to the Gram products beta k k^T and q k^T while they drain; and channel-wise decay that stays
+// within e^{+-32} of each document's midpoint over the chunk (tested per chunk on the device),
+// where with f = exp(Lam - midpoint) the images k / f, q f, beta k f give A and M by one product
+// each.  Otherwise it is built hierarchically: at level s in {16,32,64}
 // the chunk is cut into pairs of adjacent s-row blocks, and for a pair with rows I (lower block),
 // columns J (upper block) and reference row r = first row of I
 //     A[I,J] = (beta_I * exp(Lam_I - Lam_r)) (k_J * exp(Lam_r - Lam_J))^T ,

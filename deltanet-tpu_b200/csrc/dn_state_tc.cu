@@ -5,9 +5,10 @@
 //   * the fp32 master copy of the slice lives in registers, one state row per thread
 //     (128 threads), and a bf16 copy in shared memory is the MMA operand -- the reference rounds
 //     the state to bf16 for these products as well (src/deltanet_tpu/gdn2.py:627-632);
-//   * the four 128x128 bf16 tiles of a chunk (W, qe, M, ke) are brought in with 16-byte
-//     cp.async copies one chunk ahead, each buffer refilled as soon as the MMA reading it
-//     has completed;
+//   * the four 128x128 bf16 tiles of a chunk (W, qe, M, ke) are operand images in global memory and
+//     arrive one chunk ahead by one bulk copy each (mbarrier completion), each buffer refilled as
+//     soon as the MMA reading it has completed (row-major tiles of the fp32-residual layout: 16-byte
+//     cp.async copies); passes that need no outputs fetch W and ke only;
 //   * every product is a 128 x VS x 128 tcgen05.mma with the accumulator in tensor memory,
 //     read back one row per thread.  A 128x128 tile image in shared memory serves both as the
 //     operand (K-major descriptor) and as its transpose (MN-major descriptor), so ke^T, M^T,
