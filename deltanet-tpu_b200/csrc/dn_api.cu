@@ -532,11 +532,11 @@ int dn_launch_count(const dn_shape* s, int backward, int recompute) {
   return n;
 }
 
-int dn_sp_apply(const float* P, const float* S_in, const float* Q, float* S_out, int32_t B, int32_t H,
-                int32_t G, int32_t K, int32_t V, int32_t transpose, void* stream) {
+int dn_sp_apply(const float* P, const float* S_in, const float* Q, float* S_out, const uint8_t* keep, int32_t B,
+                int32_t H, int32_t G, int32_t K, int32_t V, int32_t transpose, void* stream) {
   if (!P || !S_in || !S_out) return DN_ERR_NULL_POINTER;
   if (B < 1 || H < 1 || G < 1 || K < 1 || V < 1) return DN_ERR_BAD_SHAPE;
-  return launch_sp_apply(P, S_in, Q, S_out, B, H, G, K, V, transpose, (cudaStream_t)stream);
+  return launch_sp_apply(P, S_in, Q, S_out, keep, B, H, G, K, V, transpose, (cudaStream_t)stream);
 }
 
 int dn_decode_step(const dn_decode_shape* s, const void* q, const void* k, const void* v,

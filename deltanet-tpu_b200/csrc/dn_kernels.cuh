@@ -105,8 +105,8 @@ int launch_cu_seqlens_segments(const int32_t* cu, int n_cu, const int32_t* first
 int launch_group_sum(const float* in, void* out, int out_dt, size_t rows, int heads_out, int groups,
                      int cols, cudaStream_t st);
 // S_out[b, h*G+g] = op(P[b,h]) S_in[b, h*G+g] (+ Q); op = transpose when asked.  P (B,H,K,K), states (B,H*G,K,V).
-int launch_sp_apply(const float* P, const float* S_in, const float* Q, float* S_out, int B, int H, int G,
-                    int K, int V, int transpose, cudaStream_t st);
+int launch_sp_apply(const float* P, const float* S_in, const float* Q, float* S_out, const uint8_t* keep, int B, int H,
+                    int G, int K, int V, int transpose, cudaStream_t st);
 // Frobenius cap of n_states fp32 (K,V) states in place: S <- S * min(1, tau / sqrt(|S|^2 + 1e-6))
 int launch_cap_state(float* state, int64_t n_states, int KV, float tau, cudaStream_t st);
 int launch_decode(const dn_decode_shape& s, const void* q, const void* k, const void* v,

@@ -157,7 +157,8 @@ int launch_group_sum(const float* in, void* out, int out_dt, size_t rows, int he
 // One CTA per 64 x 64 tile of a (batch, value head)'s S_out = op(P) S_in + Q (K, V multiples of 64): the
 // kernel sits on the serial path between two ranks' transfers, so it is spread over many SMs.
 __global__ void __launch_bounds__(DN_THREADS) sp_apply_kernel(const float* P, const float* S_in, const float* Q,
-                                                              float* S_out, int H, int G, int K, int V, int transpose) {
+                                                              float* S_out, const uint8_t* keep, int H, int G, int K, int V,
+                                                              int transpose) {
   __shared__ __align__(16) float tile[GEMM_SMEM_FLOATS];
   const int tn = V / GT, tiles = (K / GT) * tn;
   const int tq = blockIdx.x % tiles, bhv = blockIdx.x / tiles;
@@ -168,9 +169,10 @@ __global__ void __launch_bounds__(DN_THREADS) sp_apply_kernel(const float* P, co
   const float* si = S_in + so + n0;
   const float* q = Q ? Q + so : nullptr;
   float* o = S_out + so;
+  const bool kept = !keep || keep[b] != 0;            // a dropped batch row ends as zeros
   auto store = [&](int i, int j, float acc) {
     const size_t e = (size_t)(m0 + i) * V + n0 + j;
-    o[e] = acc + (q ? q[e] : 0.f);
+    o[e] = kept ? acc + (q ? q[e] : 0.f) : 0.f;
   };
   if (transpose)
     cta_gemm<false, true>(GT, GT, K, [&](int i, int kk) { return p[kk * K + m0 + i]; }, [&](int kk, int j) { return si[kk * V + j]; }, store, tile);
@@ -178,10 +180,10 @@ __global__ void __launch_bounds__(DN_THREADS) sp_apply_kernel(const float* P, co
     cta_gemm<true, true>(GT, GT, K, [&](int i, int kk) { return p[(m0 + i) * K + kk]; }, [&](int kk, int j) { return si[kk * V + j]; }, store, tile);
 }
 
-int launch_sp_apply(const float* P, const float* S_in, const float* Q, float* S_out, int B, int H, int G,
-                    int K, int V, int transpose, cudaStream_t st) {
+int launch_sp_apply(const float* P, const float* S_in, const float* Q, float* S_out, const uint8_t* keep, int B, int H,
+                    int G, int K, int V, int transpose, cudaStream_t st) {
   if (K % GT || V % GT) return DN_ERR_BAD_SHAPE;
-  sp_apply_kernel<<<B * H * G * (K / GT) * (V / GT), DN_THREADS, 0, st>>>(P, S_in, Q, S_out, H, G, K, V, transpose);
+  sp_apply_kernel<<<B * H * G * (K / GT) * (V / GT), DN_THREADS, 0, st>>>(P, S_in, Q, S_out, keep, H, G, K, V, transpose);
   return launch_status();
 }
 

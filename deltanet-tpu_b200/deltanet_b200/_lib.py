@@ -71,7 +71,7 @@ _SIGNATURES = {
     "dn_sp_summary": (C.c_int, [C.POINTER(Shape), C.POINTER(Residuals)] + [_P] * 5),
     "dn_sp_correct_fwd": (C.c_int, [C.POINTER(Shape), C.POINTER(Residuals)] + [_P] * 4),
     "dn_sp_correct_bwd": (C.c_int, [C.POINTER(Shape), C.POINTER(Residuals)] + [_P] * 6),
-    "dn_sp_apply": (C.c_int, [_P] * 4 + [C.c_int32] * 6 + [_P]),
+    "dn_sp_apply": (C.c_int, [_P] * 5 + [C.c_int32] * 6 + [_P]),
     "dn_gdn_producer_scratch_bytes": (C.c_size_t, [C.c_int32] * 4),
     "dn_gdn_producer_fwd": (C.c_int, [_P] * 4 + [C.c_int32] * 8 + [_P] * 4),
     "dn_gdn_producer_bwd": (C.c_int, [_P] * 4 + [C.c_int32] * 8 + [_P] * 7 + [C.c_size_t, _P]),

@@ -229,14 +229,17 @@ class CudaOps:
                                       P.data_ptr(), _g._stream()), "dn_sp_summary")
         return P, Q
 
-    def apply(self, c, P, S_in, Q, transpose=False):
+    def apply(self, c, P, S_in, Q, transpose=False, keep=None):
+        """op(P) S_in + Q; ``keep`` (B,) bool: batch rows where it is False come out as zeros."""
         B, Lq, Hk, Hv, K, V = c["dims"]
         H = c["ex"].H
         S_in = S_in.contiguous()
         out = torch.empty_like(S_in)
+        if keep is not None:
+            keep = keep.to(torch.uint8).contiguous()
         L.check(L.lib().dn_sp_apply(P.data_ptr(), S_in.data_ptr(), None if Q is None else Q.data_ptr(),
-                                    out.data_ptr(), B, H, Hv // H, K, V, 1 if transpose else 0, _g._stream()),
-                "dn_sp_apply")
+                                    out.data_ptr(), None if keep is None else keep.data_ptr(), B, H, Hv // H, K, V,
+                                    1 if transpose else 0, _g._stream()), "dn_sp_apply")
         return out
 
     def finish(self, c, S_in, exact=False):
@@ -347,8 +350,7 @@ def _forward_gathered(ops, chain, c, P, Q, seg_raw, initial_state):
     else:
         S = got[0][1] * conts[1].view(B, 1, 1, 1).to(Q.dtype)                      # after shard 0; nothing of it where shard 1 starts a document
         for j in range(1, r):
-            S = ops.apply(c, got[j][0], S, got[j][1])                              # the state after shard j ...
-            S = S * conts[j + 1].view(B, 1, 1, 1).to(S.dtype)                      # ... masked the same way for shard j+1
+            S = ops.apply(c, got[j][0], S, got[j][1], keep=conts[j + 1])           # the state after shard j, masked the same way for shard j+1
         S_in = S
         final = ops.apply(c, P, S_in, Q)
     out = ops.finish(c, S_in, exact=(r == 0 and initial_state is None))
@@ -367,17 +369,19 @@ def _backward_gathered(ops, chain, c, d_out, d_final_state):
     got = chain.all_gather([e_mine.contiguous()])
     d_next = None                                                                  # d_in of the successor (None: zero)
     for j in range(n - 1, r, -1):
-        d = got[j][0] if d_next is None else ops.apply(c, c["P_all"][j], d_next, got[j][0], transpose=True)
-        d_next = d * c["conts"][j].view(B, 1, 1, 1).to(d.dtype)
+        if d_next is None:
+            d_next = got[j][0] * c["conts"][j].view(B, 1, 1, 1).to(got[j][0].dtype)
+        else:
+            d_next = ops.apply(c, c["P_all"][j], d_next, got[j][0], transpose=True, keep=c["conts"][j])
     own = d_final_state.float() if d_final_state is not None else None
     x = d_next if own is None else (own if d_next is None else d_next + own)       # cotangent of this shard's final state
-    if x is None:
+    if x is None:                                                                  # the last shard, no loss on its final state
         x = torch.zeros_like(d_init0)
         d_in = d_init0
+        if c["cont_in"] is not None:
+            d_in = d_in * c["cont_in"].view(B, 1, 1, 1).to(d_in.dtype)
     else:
-        d_in = ops.apply(c, c["P"], x.contiguous(), d_init0, transpose=True)
-    if c["cont_in"] is not None:
-        d_in = d_in * c["cont_in"].view(B, 1, 1, 1).to(d_in.dtype)
+        d_in = ops.apply(c, c["P"], x.contiguous(), d_init0, transpose=True, keep=c["cont_in"])
     grads = ops.bwd_finish(c, x, exact=(r == n - 1 and d_final_state is None))
     return grads, d_in
 

@@ -215,7 +215,8 @@ int dn_prepass_bwd(const dn_shape* s, const void* q, const void* k, const void* 
  * dn_sp_transition: P (B,H,K,K) f32 of a shard whose prepass residuals are `res` (W, ke, lam_end are
  *   read).  identity is a (B,H,K,K) f32 buffer holding the identity per head.
  * dn_sp_apply: S_out[b,hv] = P[b,hv/G] S_in[b,hv] + Q[b,hv] (Q may be NULL), or with P transposed
- *   (the adjoint, for the state cotangent).  States are (B, H*G, K, V) f32.
+ *   (the adjoint, for the state cotangent).  States are (B, H*G, K, V) f32.  keep (B bytes, may be NULL):
+ *   batch rows whose byte is 0 get S_out = 0 (the next shard starts a new document there).
  */
 int dn_sp_transition(const dn_shape* s, const dn_residuals* res, const int32_t* seg,
                      const float* identity, float* P, void* stream);
@@ -242,8 +243,8 @@ int dn_sp_correct_fwd(const dn_shape* s, const dn_residuals* res, const int32_t*
                       const float* S_in, void* out, void* stream);
 int dn_sp_correct_bwd(const dn_shape* s, const dn_residuals* res, const int32_t* seg,
                       const void* d_out, const float* d_final_state, float* dV, float* dH, void* stream);
-int dn_sp_apply(const float* P, const float* S_in, const float* Q, float* S_out, int32_t B, int32_t H,
-                int32_t G, int32_t K, int32_t V, int32_t transpose, void* stream);
+int dn_sp_apply(const float* P, const float* S_in, const float* Q, float* S_out, const uint8_t* keep, int32_t B,
+                int32_t H, int32_t G, int32_t K, int32_t V, int32_t transpose, void* stream);
 
 /*
  * Allocation-free forward prepass.  No counterpart in the reference.

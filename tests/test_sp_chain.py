@@ -40,9 +40,10 @@ class OracleOps:
             _, P = self._run(c, torch.eye(K).expand(B, Hv, K, K).contiguous(), v=zero_v, w=torch.ones(B, Lq, Hv, K))
         return P, Q
 
-    def apply(self, c, P, S_in, Q, transpose=False):
+    def apply(self, c, P, S_in, Q, transpose=False, keep=None):
         out = torch.einsum("bhji,bhjv->bhiv" if transpose else "bhij,bhjv->bhiv", P, S_in)
-        return out if Q is None else out + Q
+        out = out if Q is None else out + Q
+        return out if keep is None else out * keep.view(-1, 1, 1, 1).to(out.dtype)
 
     def finish(self, c, S_in, exact=False):
         c["S_in"] = S_in.detach().clone().requires_grad_()
