@@ -123,3 +123,49 @@ def test_sp_chain_matches_unsplit_oracle(world, exchange):
         got = torch.cat([ret[r]["grads"][i] for r in range(world)], 1)
         assert O.rel_l2(got, g_ref[i]) < 1e-4, i
     assert O.rel_l2(ret[0]["grads"][6], g_ref[6]) < 1e-4
+
+
+@pytest.mark.parametrize("exchange", ["gather", "p2p"])
+def test_four_local_ranks_without_initial_state_or_final_loss(exchange):
+    """Four shards as host threads (LocalChain), CPU ops from the oracle: one shard lies inside a single
+    document, one starts exactly at a document boundary, and neither an initial state nor a loss on the last
+    final state is given, so the corrections that are exact by construction are skipped."""
+    import threading
+    from oracle import delta_oracle as O
+    for p in (ROOT, PKG_DIR):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    from deltanet_b200 import sp
+    B, L, Hk, Hv, K, V, n = 1, 512, 1, 2, 64, 64, 4
+    q, k, v, g, b, w = O.make_inputs(78, B, L, Hk, Hv, K, V, qkv_scale=0.5)
+    # shard 0 = [0,128): boundary at 40; shard 1 = [128,256): inside document 1; shard 2 starts document 2 at 256
+    seg = torch.repeat_interleave(torch.tensor([0, 1, 2, 3], dtype=torch.int32), torch.tensor([40, 216, 200, 56]))[None]
+    do = torch.randn(B, L, Hv, V, generator=torch.Generator().manual_seed(8))
+    chains = sp.LocalChain.make(n)
+    results, errors = [None] * n, []
+
+    def work(r):
+        try:
+            lo, hi = r * L // n, (r + 1) * L // n
+            shard = [t[:, lo:hi].contiguous() for t in (q, k, v, g, b, w)]
+            ops = OracleOps()
+            out, final, c = sp.sp_forward(ops, chains[r], shard, seg[:, lo:hi].contiguous(), None, exchange)
+            grads, d_in = sp.sp_backward(ops, chains[r], c, do[:, lo:hi].contiguous(), None)
+            results[r] = dict(out=out, final=final, grads=list(grads))
+        except Exception as e:  # noqa: BLE001
+            errors.append(e)
+
+    threads = [threading.Thread(target=work, args=(r,)) for r in range(n)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join(timeout=600)
+    assert not errors, errors
+    leaves = [t.clone().requires_grad_() for t in (q, k, v, g, b, w)]
+    o_ref, f_ref = O.chunk_gdn2(*leaves, segment_ids=seg, output_final_state=True, chunk_size=64, precision="fp32",
+                                qk_l2norm=True)
+    g_ref = torch.autograd.grad((o_ref * do).sum(), leaves)
+    assert O.rel_l2(torch.cat([x["out"] for x in results], 1), o_ref.detach()) < 1e-5
+    assert O.rel_l2(results[-1]["final"], f_ref.detach()) < 1e-5
+    for i in range(6):
+        assert O.rel_l2(torch.cat([x["grads"][i] for x in results], 1), g_ref[i]) < 1e-4, i
