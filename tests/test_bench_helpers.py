@@ -41,3 +41,15 @@ def test_help_lists_the_contract_flags():
     assert out.returncode == 0
     for flag in ("--gpus", "--steps", "--warmup", "--impl"):
         assert flag in out.stdout
+
+
+def test_reference_arm_prints_the_contract_line():
+    """`--impl reference` needs no GPU: it times the CPU oracle on the whole workload and prints one JSON line."""
+    out = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--impl", "reference", "--steps", "1", "--warmup", "1"],
+                         capture_output=True, text=True, timeout=900)
+    assert out.returncode == 0, out.stderr[-2000:]
+    line = json.loads(out.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and line["unit"] == "tokens/s" and line["higher_is_better"] is True
+    assert line["metric"] == bench.METRIC and line["config"]["workload"] == bench.WORKLOAD
+    assert line["value"] > 0 and line["cpu_baseline"]["kind"] == "port" and line["cpu_baseline"]["cores"] >= 1
+    assert line["e2e"] == dict(value=line["value"], unit="tokens/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0)
