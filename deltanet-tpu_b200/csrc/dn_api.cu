@@ -487,6 +487,7 @@ int dn_sp_summary(const dn_shape* s, const dn_residuals* res, const int32_t* seg
   StateArgs a{};
   a.g = g; a.res = *res; a.seg = seg; a.init_state = nullptr;
   a.out = out; a.final_state = Q; a.states = res->states; a.P_out = P;
+  a.skip_provisional = (g.flags & DN_SP_SKIP_PROVISIONAL) != 0;
   return launch_state_fwd(a, (cudaStream_t)stream);
 }
 

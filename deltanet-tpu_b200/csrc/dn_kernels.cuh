@@ -43,8 +43,11 @@ struct StateArgs {
   // state it was started from (a document boundary cuts the dependence); outputs, chunk states, dV
   // and dH of the chunks before that point are (re)written, nothing else is, and neither the final
   // state nor d_init is produced.
+  // skip_provisional (forward, tensor-core path): outputs of the chunks that still depend on the state the
+  // launch started from are not computed; the caller runs an until_independent pass over them afterwards.
   float* P_out;
   bool until_independent;
+  bool skip_provisional;
 };
 
 struct PrepassBwdArgs {

@@ -154,18 +154,22 @@ __global__ void __launch_bounds__(128, 1) state_fwd_tc_kernel(StateArgs a) {
   // (a pass without outputs needs neither qe nor M: half the bytes a chunk step pulls through L2, which
   // is what bounds the step)
   const bool need_out_tiles = WITH_OUT && !trans;
-  auto fetch_QMK = [&](size_t it_) {
+  // With skip_provisional the outputs of the chunks that still depend on the state this launch started from
+  // are left to the pass that follows with the true state (it rewrites exactly those chunks): `indep` turns
+  // true after the first chunk that holds a document boundary or precedes one.  Uniform over the CTA.
+  bool indep = !a.skip_provisional;
+  auto fetch_QMK = [&](size_t it_, bool with_out) {
     if (img) {
       if (row == 0) {
-        umma::mbar_expect_tx(&tb[1], (need_out_tiles ? 3 : 1) * TILE_U4 * 16);
-        if (need_out_tiles) {
+        umma::mbar_expect_tx(&tb[1], (with_out ? 3 : 1) * TILE_U4 * 16);
+        if (with_out) {
           bulk_tile(sQE, QEg + it_ * C * K, &tb[1]);
           bulk_tile(sM, Mg + it_ * C * C, &tb[1]);
         }
         bulk_tile(sKE, KEg + it_ * C * K, &tb[1]);
       }
     } else {
-      if (need_out_tiles) {
+      if (with_out) {
         copy_tile_async(sQE, QEg + it_ * C * K, row, false);
         copy_tile_async(sM, Mg + it_ * C * C, row, false);
       }
@@ -174,7 +178,7 @@ __global__ void __launch_bounds__(128, 1) state_fwd_tc_kernel(StateArgs a) {
     umma::cp_async_commit();
   };
   fetch_W(item0 + cb);
-  fetch_QMK(item0 + cb);
+  fetch_QMK(item0 + cb, need_out_tiles && indep);
 
   float S[VS];
 #pragma unroll
@@ -256,16 +260,18 @@ __global__ void __launch_bounds__(128, 1) state_fwd_tc_kernel(StateArgs a) {
 
     if (img) tile_wait(1); else umma::cp_async_wait<1>();      // this chunk's qe, M, ke have landed
     umma::pre_issue_sync();
-    if (WITH_OUT && !trans) {
+    const bool outc = need_out_tiles && indep;                         // this chunk's outputs are wanted
+    indep = indep || !all_same || nis_new;                             // ... and the next chunk's
+    if (outc) {
       umma::issue<VS, false, true>(cx, sQE, sS, K, colO, false);       // O  = qe S
       umma::issue<VS, false, true>(cx, sM, sVn, C, colO, true);        //    + M V_new
     }
     umma::issue<VS, true, true>(cx, sKE, sVn, C, colS, false);         // ke^T V_new
     umma::commit_wait(cx);
-    if (!last) fetch_QMK(item + 1); else umma::cp_async_commit();
+    if (!last) fetch_QMK(item + 1, need_out_tiles && indep); else umma::cp_async_commit();
 
     float sn[VS];
-    if (WITH_OUT && !trans) {
+    if (outc) {
       float o[VS];
       read_acc_nowait<VS>(cx, colO, warp, o);
       read_acc_nowait<VS>(cx, colS, warp, sn);
@@ -289,7 +295,7 @@ __global__ void __launch_bounds__(128, 1) state_fwd_tc_kernel(StateArgs a) {
         }
       }
     }
-    if (!(WITH_OUT && !trans)) read_acc<VS>(cx, colS, warp, sn);
+    if (!outc) read_acc<VS>(cx, colS, warp, sn);
 #pragma unroll
     for (int j = 0; j < VS; ++j) S[j] = fmaf(dec, S[j], sn[j]);       // S <- decay * S + ke^T V_new
     umma::tc_fence_before();

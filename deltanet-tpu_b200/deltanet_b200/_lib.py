@@ -22,6 +22,7 @@ DN_STATE_FP32_MM = 1 << 4
 DN_INFERENCE = 1 << 5
 DN_TRUNC_DT_BF16 = 1 << 6
 DN_RESET_PER_HEAD = 1 << 7
+DN_SP_SKIP_PROVISIONAL = 1 << 8
 
 
 class Shape(C.Structure):

@@ -219,13 +219,19 @@ class CudaOps:
                 "dn_prepass_fwd")
         c.update(res=res, block=block, scratch=scratch)
 
-    def summary(self, c):
+    def summary(self, c, skip_provisional=False):
+        """``skip_provisional``: a correction pass (``finish`` without ``exact``) will follow, so the outputs of
+        the chunks that depend on the incoming state need not be computed here."""
         B, Lq, Hk, Hv, K, V = c["dims"]
         q, v = c["ins"][0], c["ins"][2]
         c["out"] = torch.empty(B, Lq, Hv, V, dtype=v.dtype, device=q.device)
         Q = torch.empty(B, Hv, K, V, device=q.device)
         P = torch.empty(B, c["ex"].H, K, K, device=q.device)
-        L.check(L.lib().dn_sp_summary(c["shape"], c["res"], c["seg"].data_ptr(), c["out"].data_ptr(), Q.data_ptr(),
+        shape = c["shape"]
+        if skip_provisional:
+            shape = L.Shape.from_buffer_copy(shape)
+            shape.flags |= L.DN_SP_SKIP_PROVISIONAL
+        L.check(L.lib().dn_sp_summary(shape, c["res"], c["seg"].data_ptr(), c["out"].data_ptr(), Q.data_ptr(),
                                       P.data_ptr(), _g._stream()), "dn_sp_summary")
         return P, Q
 
@@ -302,7 +308,8 @@ def sp_forward(ops, chain, tensors, seg_raw, initial_state, exchange="gather"):
     q, k, v, g, b, w = tensors
     B, Hv, K, V = q.shape[0], v.shape[2], q.shape[3], v.shape[3]
     c = ops.prepare(q, k, v, g, b, w, seg_raw)
-    P, Q = ops.summary(c)
+    # (only the first shard without an initial state keeps what the summary pass writes before its first boundary)
+    P, Q = ops.summary(c, skip_provisional=not (chain.rank == 0 and initial_state is None))
     if exchange == "gather":
         return _forward_gathered(ops, chain, c, P, Q, seg_raw, initial_state)
     edges = chain.gather_edges(shard_edges(seg_raw).to(q.device))

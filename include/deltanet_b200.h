@@ -56,7 +56,9 @@ enum {
   DN_STATE_FP32_MM  = 1u << 4, /* state_fp32_matmul (gdn2.py:625)                                   */
   DN_INFERENCE      = 1u << 5, /* forward only: no T / chunk-state residuals (gdn2.py:1257,1322)    */
   DN_TRUNC_DT_BF16  = 1u << 6, /* truncate_bwd_dT_bf16 (gdn2.py:327-330)                            */
-  DN_RESET_PER_HEAD = 1u << 7  /* decode: reset is (B,Hv), one flag per sequence and value head      */
+  DN_RESET_PER_HEAD = 1u << 7, /* decode: reset is (B,Hv), one flag per sequence and value head      */
+  DN_SP_SKIP_PROVISIONAL = 1u << 8 /* dn_sp_summary: leave the outputs of the chunks that depend on the
+                                      incoming state to dn_sp_correct_fwd, which rewrites exactly those  */
 };
 
 /* status codes */
@@ -227,7 +229,9 @@ int dn_sp_transition(const dn_shape* s, const dn_residuals* res, const int32_t* 
  * dn_sp_summary: ONE launch that runs the state pass from a zero state over the whole shard -- writing
  *   outputs (out may be NULL) and chunk-entry states (res->states may be NULL) as dn_state_fwd does, and
  *   Q (B,Hv,K,V) -- while K extra columns per (batch, exec head) start from the identity with U = 0 and
- *   end as P (B,H,K,K).  Everything it writes for chunks after the first boundary is final.
+ *   end as P (B,H,K,K).  Everything it writes for chunks after the first boundary is final.  With
+ *   DN_SP_SKIP_PROVISIONAL in the shape's flags (tensor-core path) it does not write the outputs of the
+ *   chunks before that point, which the caller must then obtain from dn_sp_correct_fwd.
  * dn_sp_correct_fwd: the forward chain again from the true incoming state S_in (B,Hv,K,V), stopping at
  *   the first chunk whose results no longer depend on it; rewrites out and the chunk-entry states of the
  *   chunks it walks.  The shard's final state is P S_in + Q (dn_sp_apply); this call does not produce it.

@@ -32,7 +32,7 @@ class OracleOps:
         B, Lq, Hk, K = q.shape
         return dict(leaves=leaves, seg=seg_raw, dims=(B, Lq, Hk, v.shape[2], K, v.shape[3]))
 
-    def summary(self, c):
+    def summary(self, c, skip_provisional=False):
         B, Lq, Hk, Hv, K, V = c["dims"]
         with torch.no_grad():
             _, Q = self._run(c, torch.zeros(B, Hv, K, V))
